@@ -1,0 +1,609 @@
+// C ABI of libbnkgpu.so (declared in include/bnk_gpu.h): contexts, device tables,
+// pinned packet rings with device mirrors, and the submit/wait pipeline that strings
+// host->device copies, the kernels and device->host copies on one CUDA stream per batch.
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <thread>
+
+#include "bnk_internal.cuh"
+
+namespace {
+
+thread_local std::string g_last_error; // for failures that have no context to hang on
+
+int fail(bnk_ctx *ctx, int code, const char *what, cudaError_t e = cudaSuccess) {
+    char buf[512];
+    if (e != cudaSuccess)
+        snprintf(buf, sizeof buf, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    else
+        snprintf(buf, sizeof buf, "%s", what);
+    if (ctx) {
+        std::lock_guard<std::mutex> g(ctx->mu);
+        ctx->last_error = buf;
+    }
+    g_last_error = buf;
+    return code;
+}
+
+#define CK(ctx, call)                                                  \
+    do {                                                               \
+        cudaError_t _e = (call);                                       \
+        if (_e != cudaSuccess) return fail((ctx), BNK_ECUDA, #call, _e); \
+    } while (0)
+
+bool is_pow2(uint64_t v) { return v && !(v & (v - 1)); }
+
+template <typename T>
+cudaError_t dev_alloc_zero(T **p, size_t count) {
+    cudaError_t e = cudaMalloc(p, count * sizeof(T));
+    if (e != cudaSuccess) return e;
+    return cudaMemset(*p, 0, count * sizeof(T));
+}
+
+// highest ring byte any of the first n packets can touch (input or output side)
+uint64_t ring_extent(const bnk_batch *b, uint32_t n, uint32_t slack) {
+    const uint32_t *off = b->host.off, *len = b->host.len;
+    uint64_t ext = 0;
+    for (uint32_t i = 0; i < n; i++) {
+        const uint64_t e = (uint64_t)off[i] + len[i] + slack;
+        if (e > ext) ext = e;
+    }
+    ext = (ext + 15) & ~15ull;
+    return ext > b->ring_bytes ? b->ring_bytes : ext;
+}
+
+int begin_submit(bnk_batch *b, uint32_t npkts) {
+    if (!b) return BNK_EINVAL;
+    if (npkts > b->max_pkts) return fail(b->ctx, BNK_EINVAL, "npkts exceeds the batch capacity");
+    if (b->in_flight) return fail(b->ctx, BNK_EBUSY, "batch has work in flight; call bnk_wait first");
+    CK(b->ctx, cudaSetDevice(b->ctx->device));
+    return BNK_SUCCESS;
+}
+
+int end_submit(bnk_batch *b) {
+    CK(b->ctx, cudaEventRecord(b->done, b->stream));
+    b->in_flight = true;
+    return BNK_SUCCESS;
+}
+
+AeadArgs aead_args(bnk_batch *b, uint32_t n, bool open, const uint32_t *order) {
+    bnk_ctx *ctx = b->ctx;
+    AeadArgs a{};
+    a.ring = b->dev.ring;
+    a.off = b->dev.off;
+    a.len = b->dev.len;
+    a.slot = b->dev.slot;
+    a.counter = b->dev.counter;
+    a.out_len = b->dev.out_len;
+    a.status = b->dev.status;
+    a.keys = open ? ctx->kt.recv_keys : ctx->kt.send_keys;
+    a.remote_index = ctx->kt.remote_index;
+    a.order = order;
+    a.n = n;
+    a.mtu = ctx->cfg.mtu;
+    a.max_slots = ctx->cfg.max_keypairs;
+    a.ring_bytes = b->ring_bytes;
+    return a;
+}
+
+} // namespace
+
+extern "C" {
+
+int bnk_abi_version(void) { return BNK_ABI_VERSION; }
+
+const char *bnk_strerror(int code) {
+    switch (code) {
+    case BNK_SUCCESS: return "success";
+    case BNK_EINVAL: return "invalid argument";
+    case BNK_ENOMEM: return "out of memory";
+    case BNK_ECUDA: return "CUDA error";
+    case BNK_ETIMEDOUT: return "timed out";
+    case BNK_EBUSY: return "batch busy";
+    case BNK_EFULL: return "table full";
+    default: return "unknown error";
+    }
+}
+
+int bnk_device_count(void) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) return fail(nullptr, BNK_ECUDA, "cudaGetDeviceCount", e);
+    return n;
+}
+
+const char *bnk_last_error_string(bnk_ctx *ctx) {
+    if (!ctx) return g_last_error.c_str();
+    std::lock_guard<std::mutex> g(ctx->mu);
+    g_last_error = ctx->last_error;
+    return g_last_error.c_str();
+}
+
+int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
+    if (!cfg || !out || cfg->struct_size != sizeof(bnk_cfg)) return fail(nullptr, BNK_EINVAL, "bad bnk_cfg");
+    if (cfg->max_keypairs == 0 || cfg->max_keypairs > (1u << 24)) return fail(nullptr, BNK_EINVAL, "max_keypairs out of range");
+    if (!is_pow2(cfg->replay_ring_blocks) || cfg->replay_ring_blocks < 2 || cfg->replay_ring_blocks > 1024)
+        return fail(nullptr, BNK_EINVAL, "replay_ring_blocks must be a power of two in 2..1024");
+    if (cfg->flow_capacity && (!is_pow2(cfg->flow_capacity) || cfg->flow_capacity < 16))
+        return fail(nullptr, BNK_EINVAL, "flow_capacity must be a power of two >= 16");
+    *out = nullptr;
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess) return fail(nullptr, BNK_ECUDA, "no usable CUDA device (there is no CPU fallback)", e);
+    if (cfg->device_id < 0 || cfg->device_id >= ndev) return fail(nullptr, BNK_EINVAL, "device_id out of range");
+    CK(nullptr, cudaSetDevice(cfg->device_id));
+    cudaDeviceProp prop;
+    CK(nullptr, cudaGetDeviceProperties(&prop, cfg->device_id));
+    if (prop.major != 10) return fail(nullptr, BNK_ECUDA, "device is not sm_100: this library carries sm_100a code only");
+
+    bnk_ctx *ctx = new (std::nothrow) bnk_ctx();
+    if (!ctx) return fail(nullptr, BNK_ENOMEM, "host allocation failed");
+    ctx->cfg = *cfg;
+    ctx->device = cfg->device_id;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->launches = 0;
+    ctx->kt = KeypairTables{};
+    ctx->ft = FilterTables{};
+    const size_t k = cfg->max_keypairs;
+    auto bail = [&](const char *what, cudaError_t err) {
+        int rc = fail(nullptr, BNK_ECUDA, what, err);
+        bnk_ctx_destroy(ctx);
+        return rc;
+    };
+    if ((e = cudaStreamCreateWithFlags(&ctx->admin_stream, cudaStreamNonBlocking)) != cudaSuccess) return bail("stream", e);
+    if ((e = cudaEventCreate(&ctx->timer_start)) != cudaSuccess) return bail("event", e);
+    if ((e = dev_alloc_zero(&ctx->kt.send_keys, k * 8)) != cudaSuccess) return bail("send_keys", e);
+    if ((e = dev_alloc_zero(&ctx->kt.recv_keys, k * 8)) != cudaSuccess) return bail("recv_keys", e);
+    if ((e = dev_alloc_zero(&ctx->kt.remote_index, k)) != cudaSuccess) return bail("remote_index", e);
+    if ((e = dev_alloc_zero(&ctx->kt.send_counter, k)) != cudaSuccess) return bail("send_counter", e);
+    if ((e = dev_alloc_zero(&ctx->kt.replay_last, k)) != cudaSuccess) return bail("replay_last", e);
+    if ((e = dev_alloc_zero(&ctx->kt.replay_ring, k * cfg->replay_ring_blocks)) != cudaSuccess) return bail("replay_ring", e);
+    if ((e = filter_tables_alloc(ctx)) != cudaSuccess) return bail("filter tables", e);
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return bail("sync", e);
+    *out = ctx;
+    return BNK_SUCCESS;
+}
+
+int bnk_ctx_destroy(bnk_ctx *ctx) {
+    if (!ctx) return BNK_EINVAL;
+    cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
+    cudaFree(ctx->kt.send_keys);
+    cudaFree(ctx->kt.recv_keys);
+    cudaFree(ctx->kt.remote_index);
+    cudaFree(ctx->kt.send_counter);
+    cudaFree(ctx->kt.replay_last);
+    cudaFree(ctx->kt.replay_ring);
+    filter_tables_free(ctx);
+    if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
+    if (ctx->admin_stream) cudaStreamDestroy(ctx->admin_stream);
+    delete ctx;
+    return BNK_SUCCESS;
+}
+
+int bnk_ctx_synchronize(bnk_ctx *ctx) {
+    if (!ctx) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, cudaDeviceSynchronize());
+    return BNK_SUCCESS;
+}
+
+/* ---- keypairs ---- */
+int bnk_keypair_set_many(bnk_ctx *ctx, uint32_t first_slot, uint32_t n, const uint8_t *send_keys,
+                         const uint8_t *recv_keys, const uint32_t *remote_index) {
+    if (!ctx || !send_keys || !recv_keys || !remote_index) return fail(ctx, BNK_EINVAL, "null argument");
+    if ((uint64_t)first_slot + n > ctx->cfg.max_keypairs) return fail(ctx, BNK_EINVAL, "keypair slot out of range");
+    if (n == 0) return BNK_SUCCESS;
+    CK(ctx, cudaSetDevice(ctx->device));
+    const uint32_t rb = ctx->cfg.replay_ring_blocks;
+    CK(ctx, cudaMemcpy(ctx->kt.send_keys + (size_t)first_slot * 8, send_keys, (size_t)n * 32, cudaMemcpyHostToDevice));
+    CK(ctx, cudaMemcpy(ctx->kt.recv_keys + (size_t)first_slot * 8, recv_keys, (size_t)n * 32, cudaMemcpyHostToDevice));
+    CK(ctx, cudaMemcpy(ctx->kt.remote_index + first_slot, remote_index, (size_t)n * 4, cudaMemcpyHostToDevice));
+    CK(ctx, cudaMemset(ctx->kt.send_counter + first_slot, 0, (size_t)n * 8));
+    CK(ctx, cudaMemset(ctx->kt.replay_last + first_slot, 0, (size_t)n * 8));
+    CK(ctx, cudaMemset(ctx->kt.replay_ring + (size_t)first_slot * rb, 0, (size_t)n * rb * 8));
+    return BNK_SUCCESS;
+}
+
+int bnk_keypair_set(bnk_ctx *ctx, uint32_t slot, const uint8_t send_key[32], const uint8_t recv_key[32],
+                    uint32_t remote_index) {
+    return bnk_keypair_set_many(ctx, slot, 1, send_key, recv_key, &remote_index);
+}
+
+int bnk_keypair_clear(bnk_ctx *ctx, uint32_t slot) {
+    static const uint8_t zeros[32] = {0};
+    return bnk_keypair_set(ctx, slot, zeros, zeros, 0);
+}
+
+int bnk_send_counter_get(bnk_ctx *ctx, uint32_t slot, uint64_t *counter) {
+    if (!ctx || !counter || slot >= ctx->cfg.max_keypairs) return fail(ctx, BNK_EINVAL, "bad slot");
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, cudaMemcpy(counter, ctx->kt.send_counter + slot, 8, cudaMemcpyDeviceToHost));
+    return BNK_SUCCESS;
+}
+
+int bnk_send_counter_set(bnk_ctx *ctx, uint32_t slot, uint64_t counter) {
+    if (!ctx || slot >= ctx->cfg.max_keypairs) return fail(ctx, BNK_EINVAL, "bad slot");
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, cudaMemcpy(ctx->kt.send_counter + slot, &counter, 8, cudaMemcpyHostToDevice));
+    return BNK_SUCCESS;
+}
+
+int bnk_replay_export(bnk_ctx *ctx, uint32_t slot, uint64_t *last, uint64_t *ring) {
+    if (!ctx || !last || !ring || slot >= ctx->cfg.max_keypairs) return fail(ctx, BNK_EINVAL, "bad slot");
+    CK(ctx, cudaSetDevice(ctx->device));
+    const uint32_t rb = ctx->cfg.replay_ring_blocks;
+    CK(ctx, cudaMemcpy(last, ctx->kt.replay_last + slot, 8, cudaMemcpyDeviceToHost));
+    CK(ctx, cudaMemcpy(ring, ctx->kt.replay_ring + (size_t)slot * rb, (size_t)rb * 8, cudaMemcpyDeviceToHost));
+    return BNK_SUCCESS;
+}
+
+int bnk_replay_import(bnk_ctx *ctx, uint32_t slot, uint64_t last, const uint64_t *ring) {
+    if (!ctx || !ring || slot >= ctx->cfg.max_keypairs) return fail(ctx, BNK_EINVAL, "bad slot");
+    CK(ctx, cudaSetDevice(ctx->device));
+    const uint32_t rb = ctx->cfg.replay_ring_blocks;
+    CK(ctx, cudaMemcpy(ctx->kt.replay_last + slot, &last, 8, cudaMemcpyHostToDevice));
+    CK(ctx, cudaMemcpy(ctx->kt.replay_ring + (size_t)slot * rb, ring, (size_t)rb * 8, cudaMemcpyHostToDevice));
+    return BNK_SUCCESS;
+}
+
+/* ---- ACL ---- */
+int bnk_acl_set(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n) {
+    if (!ctx || (n && !tuples)) return fail(ctx, BNK_EINVAL, "null tuples");
+    if (ctx->cfg.max_acl_tuples && n > ctx->cfg.max_acl_tuples) return fail(ctx, BNK_EFULL, "more tuples than max_acl_tuples");
+    CK(ctx, cudaSetDevice(ctx->device));
+    const int rc = filter_acl_upload(ctx, enforce, tuples, n);
+    if (rc != BNK_SUCCESS) return fail(ctx, rc, "rule table upload failed");
+    return BNK_SUCCESS;
+}
+
+int bnk_flows_clear(bnk_ctx *ctx) {
+    if (!ctx) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, cudaDeviceSynchronize());
+    CK(ctx, filter_flows_clear(ctx, ctx->admin_stream));
+    return BNK_SUCCESS;
+}
+
+int bnk_flows_count(bnk_ctx *ctx, uint64_t *live) {
+    if (!ctx || !live) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, cudaDeviceSynchronize());
+    unsigned long long v = 0;
+    CK(ctx, cudaMemcpy(&v, ctx->ft.flow_live, sizeof v, cudaMemcpyDeviceToHost));
+    *live = v;
+    return BNK_SUCCESS;
+}
+
+/* ---- batches ---- */
+int bnk_batch_destroy(bnk_batch *b) {
+    if (!b) return BNK_EINVAL;
+    cudaSetDevice(b->ctx->device);
+    if (b->stream) cudaStreamSynchronize(b->stream);
+    cudaFreeHost(b->host.ring);
+    cudaFreeHost(b->host.off);
+    cudaFreeHost(b->host.len);
+    cudaFreeHost(b->host.slot);
+    cudaFreeHost(b->host.counter);
+    cudaFreeHost(b->host.out_len);
+    cudaFreeHost(b->host.status);
+    cudaFreeHost(b->h_flow_error);
+    DeviceBatch &d = b->dev;
+    cudaFree(d.ring);
+    cudaFree(d.off);
+    cudaFree(d.len);
+    cudaFree(d.slot);
+    cudaFree(d.out_len);
+    cudaFree(d.counter);
+    cudaFree(d.status);
+    cudaFree(d.order);
+    cudaFree(d.order_tmp);
+    cudaFree(d.keys_tmp);
+    cudaFree(d.hist);
+    cudaFree(d.seg_head);
+    cudaFree(d.len_order);
+    cudaFree(d.counters32);
+    if (b->done) cudaEventDestroy(b->done);
+    if (b->k_begin) cudaEventDestroy(b->k_begin);
+    if (b->k_end) cudaEventDestroy(b->k_end);
+    if (b->t_end) cudaEventDestroy(b->t_end);
+    if (b->stream) cudaStreamDestroy(b->stream);
+    delete b;
+    return BNK_SUCCESS;
+}
+
+int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_batch **out) {
+    if (!ctx || !out || max_pkts == 0 || ring_bytes == 0) return fail(ctx, BNK_EINVAL, "bad batch size");
+    if (ring_bytes > 0xffffffffull || (ring_bytes & 15)) return fail(ctx, BNK_EINVAL, "ring_bytes must be a multiple of 16 below 4 GiB");
+    *out = nullptr;
+    CK(ctx, cudaSetDevice(ctx->device));
+    bnk_batch *b = new (std::nothrow) bnk_batch();
+    if (!b) return fail(ctx, BNK_ENOMEM, "host allocation failed");
+    memset(static_cast<void *>(b), 0, sizeof *b);
+    b->ctx = ctx;
+    b->max_pkts = max_pkts;
+    b->ring_bytes = ring_bytes;
+    const size_t n = max_pkts;
+    cudaError_t e = cudaSuccess;
+    auto H = [&](void **p, size_t bytes) {
+        if (e == cudaSuccess) e = cudaHostAlloc(p, bytes, cudaHostAllocDefault);
+        if (e == cudaSuccess) memset(*p, 0, bytes);
+    };
+    auto D = [&](void **p, size_t bytes) {
+        if (e == cudaSuccess) e = cudaMalloc(p, bytes);
+        if (e == cudaSuccess) e = cudaMemset(*p, 0, bytes);
+    };
+    H((void **)&b->host.ring, ring_bytes);
+    H((void **)&b->host.off, n * 4);
+    H((void **)&b->host.len, n * 4);
+    H((void **)&b->host.slot, n * 4);
+    H((void **)&b->host.counter, n * 8);
+    H((void **)&b->host.out_len, n * 4);
+    H((void **)&b->host.status, n);
+    H((void **)&b->h_flow_error, sizeof(int));
+    b->host.ring_bytes = ring_bytes;
+    b->host.max_pkts = max_pkts;
+    DeviceBatch &d = b->dev;
+    D((void **)&d.ring, ring_bytes);
+    D((void **)&d.off, n * 4);
+    D((void **)&d.len, n * 4);
+    D((void **)&d.slot, n * 4);
+    D((void **)&d.out_len, n * 4);
+    D((void **)&d.counter, n * 8);
+    D((void **)&d.status, n);
+    D((void **)&d.order, n * 4);
+    D((void **)&d.order_tmp, n * 4);
+    D((void **)&d.keys_tmp, 2 * n * 4);
+    D((void **)&d.hist, (size_t)2048 * group_sort_chunks(max_pkts) * 4);
+    D((void **)&d.seg_head, n * 4);
+    D((void **)&d.len_order, n * 4);
+    D((void **)&d.counters32, 2048 * 4);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->done, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreate(&b->k_begin);
+    if (e == cudaSuccess) e = cudaEventCreate(&b->k_end);
+    if (e == cudaSuccess) e = cudaEventCreate(&b->t_end);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        int rc = fail(ctx, e == cudaErrorMemoryAllocation ? BNK_ENOMEM : BNK_ECUDA, "batch allocation", e);
+        bnk_batch_destroy(b);
+        return rc;
+    }
+    *out = b;
+    return BNK_SUCCESS;
+}
+
+int bnk_batch_view_get(bnk_batch *b, bnk_batch_view *out) {
+    if (!b || !out) return BNK_EINVAL;
+    *out = b->host;
+    return BNK_SUCCESS;
+}
+
+int bnk_batch_upload(bnk_batch *b, uint32_t npkts) {
+    int rc = begin_submit(b, npkts);
+    if (rc) return rc;
+    bnk_ctx *ctx = b->ctx;
+    const size_t n = npkts;
+    const uint64_t ext = ring_extent(b, npkts, 64);
+    if (ext) CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, b->stream));
+    if (n) {
+        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, b->stream));
+        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, b->stream));
+        CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, b->stream));
+        CK(ctx, cudaMemcpyAsync(b->dev.counter, b->host.counter, n * 8, cudaMemcpyHostToDevice, b->stream));
+    }
+    return end_submit(b);
+}
+
+int bnk_batch_download(bnk_batch *b, uint32_t npkts) {
+    int rc = begin_submit(b, npkts);
+    if (rc) return rc;
+    bnk_ctx *ctx = b->ctx;
+    const size_t n = npkts;
+    const uint64_t ext = ring_extent(b, npkts, 64);
+    if (ext) CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, b->stream));
+    if (n) {
+        CK(ctx, cudaMemcpyAsync(b->host.counter, b->dev.counter, n * 8, cudaMemcpyDeviceToHost, b->stream));
+        CK(ctx, cudaMemcpyAsync(b->host.out_len, b->dev.out_len, n * 4, cudaMemcpyDeviceToHost, b->stream));
+        CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, b->stream));
+    }
+    return end_submit(b);
+}
+
+int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
+    int rc = begin_submit(b, npkts);
+    if (rc) return rc;
+    bnk_ctx *ctx = b->ctx;
+    cudaStream_t s = b->stream;
+    const size_t n = npkts;
+    // header room + payload + padding (< 16) + tag
+    const uint64_t ext = (flags & BNK_F_NO_H2D) && (flags & BNK_F_NO_D2H) ? 0 : ring_extent(b, npkts, 16 + 16 + 16);
+    if (!(flags & BNK_F_NO_H2D) && n) {
+        CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, s));
+        if (!(flags & BNK_F_ASSIGN_COUNTERS))
+            CK(ctx, cudaMemcpyAsync(b->dev.counter, b->host.counter, n * 8, cudaMemcpyHostToDevice, s));
+    }
+    CK(ctx, cudaEventRecord(b->k_begin, s));
+    if (flags & BNK_F_NOTE_OUTBOUND) {
+        CK(ctx, launch_filter_note(b, npkts, now_unix_ns, s));
+        CK(ctx, cudaMemcpyAsync(b->h_flow_error, ctx->ft.flow_error, sizeof(int), cudaMemcpyDeviceToHost, s));
+    }
+    if (flags & BNK_F_ASSIGN_COUNTERS) CK(ctx, launch_assign_counters(b, npkts, s));
+    const uint32_t *order = nullptr;
+    if (flags & BNK_F_SORT_BY_LENGTH) {
+        CK(ctx, launch_length_order(b, npkts, false, s));
+        order = b->dev.len_order;
+    }
+    CK(ctx, launch_seal(aead_args(b, npkts, false, order), s, &ctx->launches));
+    CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = true;
+    if (!(flags & BNK_F_NO_D2H) && n) {
+        CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
+        CK(ctx, cudaMemcpyAsync(b->host.counter, b->dev.counter, n * 8, cudaMemcpyDeviceToHost, s));
+        CK(ctx, cudaMemcpyAsync(b->host.out_len, b->dev.out_len, n * 4, cudaMemcpyDeviceToHost, s));
+        CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
+    }
+    return end_submit(b);
+}
+
+int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
+    int rc = begin_submit(b, npkts);
+    if (rc) return rc;
+    bnk_ctx *ctx = b->ctx;
+    cudaStream_t s = b->stream;
+    const size_t n = npkts;
+    const uint64_t ext = (flags & BNK_F_NO_H2D) && (flags & BNK_F_NO_D2H) ? 0 : ring_extent(b, npkts, 0);
+    if (!(flags & BNK_F_NO_H2D) && n) {
+        CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, s));
+    }
+    CK(ctx, cudaEventRecord(b->k_begin, s));
+    const uint32_t *order = nullptr;
+    if (flags & BNK_F_SORT_BY_LENGTH) {
+        CK(ctx, launch_length_order(b, npkts, true, s));
+        order = b->dev.len_order;
+    }
+    CK(ctx, launch_open(aead_args(b, npkts, true, order), s, &ctx->launches));
+    if (flags & BNK_F_REPLAY) CK(ctx, launch_replay(b, npkts, s));
+    if (flags & BNK_F_CHECK_INBOUND) CK(ctx, launch_filter_check(b, npkts, now_unix_ns, true, s));
+    CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = true;
+    if (!(flags & BNK_F_NO_D2H) && n) {
+        CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
+        CK(ctx, cudaMemcpyAsync(b->host.counter, b->dev.counter, n * 8, cudaMemcpyDeviceToHost, s));
+        CK(ctx, cudaMemcpyAsync(b->host.out_len, b->dev.out_len, n * 4, cudaMemcpyDeviceToHost, s));
+        CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
+    }
+    return end_submit(b);
+}
+
+int bnk_filter_note_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
+    int rc = begin_submit(b, npkts);
+    if (rc) return rc;
+    bnk_ctx *ctx = b->ctx;
+    cudaStream_t s = b->stream;
+    const size_t n = npkts;
+    if (!(flags & BNK_F_NO_H2D) && n) {
+        const uint64_t ext = ring_extent(b, npkts, 16);
+        CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+    }
+    CK(ctx, cudaEventRecord(b->k_begin, s));
+    CK(ctx, launch_filter_note(b, npkts, now_unix_ns, s));
+    CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = true;
+    CK(ctx, cudaMemcpyAsync(b->h_flow_error, ctx->ft.flow_error, sizeof(int), cudaMemcpyDeviceToHost, s));
+    return end_submit(b);
+}
+
+int bnk_filter_check_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
+    int rc = begin_submit(b, npkts);
+    if (rc) return rc;
+    bnk_ctx *ctx = b->ctx;
+    cudaStream_t s = b->stream;
+    const size_t n = npkts;
+    if (!(flags & BNK_F_NO_H2D) && n) {
+        const uint64_t ext = ring_extent(b, npkts, 16);
+        CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+    }
+    CK(ctx, cudaEventRecord(b->k_begin, s));
+    CK(ctx, launch_filter_check(b, npkts, now_unix_ns, false, s));
+    CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = true;
+    if (!(flags & BNK_F_NO_D2H) && n)
+        CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
+    return end_submit(b);
+}
+
+int bnk_wait(bnk_batch *b, uint64_t timeout_ns) {
+    if (!b) return BNK_EINVAL;
+    if (!b->in_flight) return BNK_SUCCESS;
+    bnk_ctx *ctx = b->ctx;
+    CK(ctx, cudaSetDevice(ctx->device));
+    if (timeout_ns == UINT64_MAX) {
+        CK(ctx, cudaEventSynchronize(b->done));
+    } else {
+        const auto deadline = std::chrono::steady_clock::now() + std::chrono::nanoseconds(timeout_ns);
+        for (;;) {
+            cudaError_t e = cudaEventQuery(b->done);
+            if (e == cudaSuccess) break;
+            if (e != cudaErrorNotReady) return fail(ctx, BNK_ECUDA, "cudaEventQuery", e);
+            if (std::chrono::steady_clock::now() >= deadline) return BNK_ETIMEDOUT;
+            std::this_thread::yield();
+        }
+    }
+    b->in_flight = false;
+    if (*b->h_flow_error) {
+        *b->h_flow_error = 0;
+        return fail(ctx, BNK_EFULL, "flow table full: some outbound flows were not recorded");
+    }
+    return BNK_SUCCESS;
+}
+
+/* ---- measurement ---- */
+int bnk_timer_start(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n) {
+    if (!ctx || !batches || n == 0) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, cudaEventRecord(ctx->timer_start, batches[0]->stream));
+    for (uint32_t i = 1; i < n; i++) CK(ctx, cudaStreamWaitEvent(batches[i]->stream, ctx->timer_start, 0));
+    return BNK_SUCCESS;
+}
+
+int bnk_timer_stop(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n, float *ms) {
+    if (!ctx || !batches || n == 0 || !ms) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    for (uint32_t i = 0; i < n; i++) CK(ctx, cudaEventRecord(batches[i]->t_end, batches[i]->stream));
+    float longest = 0.f;
+    for (uint32_t i = 0; i < n; i++) {
+        CK(ctx, cudaEventSynchronize(batches[i]->t_end));
+        float t = 0.f;
+        CK(ctx, cudaEventElapsedTime(&t, ctx->timer_start, batches[i]->t_end));
+        if (t > longest) longest = t;
+    }
+    *ms = longest;
+    return BNK_SUCCESS;
+}
+
+int bnk_batch_last_kernel_ms(bnk_batch *b, float *ms) {
+    if (!b || !ms) return BNK_EINVAL;
+    if (!b->kernel_timed) return fail(b->ctx, BNK_EINVAL, "no submit has been timed on this batch");
+    CK(b->ctx, cudaSetDevice(b->ctx->device));
+    CK(b->ctx, cudaEventSynchronize(b->k_end));
+    CK(b->ctx, cudaEventElapsedTime(ms, b->k_begin, b->k_end));
+    return BNK_SUCCESS;
+}
+
+int bnk_kernel_launch_count(bnk_ctx *ctx, uint64_t *count) {
+    if (!ctx || !count) return BNK_EINVAL;
+    *count = ctx->launches.load();
+    return BNK_SUCCESS;
+}
+
+int bnk_probe_int_throughput(bnk_ctx *ctx, int mix, double *tera_ops_per_s) {
+    if (!ctx || !tera_ops_per_s) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, probe_int_throughput(ctx, mix, tera_ops_per_s));
+    return BNK_SUCCESS;
+}
+
+int bnk_batch_fill_random(bnk_batch *b, uint64_t seed) {
+    if (!b) return BNK_EINVAL;
+    bnk_ctx *ctx = b->ctx;
+    if (b->in_flight) return fail(ctx, BNK_EBUSY, "batch has work in flight");
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, launch_fill_random(b->dev.ring, b->ring_bytes, seed, b->stream, &ctx->launches));
+    CK(ctx, cudaStreamSynchronize(b->stream));
+    return BNK_SUCCESS;
+}
+
+} // extern "C"

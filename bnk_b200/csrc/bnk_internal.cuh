@@ -1,0 +1,128 @@
+// Internal declarations shared by the translation units of libbnkgpu.so.
+// Nothing here is part of the C ABI (that is include/bnk_gpu.h).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <mutex>
+#include <string>
+
+#include "../../include/bnk_gpu.h"
+
+// ---------------------------------------------------------------------------
+// Device-resident tables of one context (one GPU).  All per-peer mutable state
+// lives here, indexed by keypair slot, so that peers shard across GPUs with no
+// exchange: keys, send counter, replay window.
+// ---------------------------------------------------------------------------
+struct KeypairTables {
+    uint32_t *send_keys;    // [max_keypairs][8] little-endian words
+    uint32_t *recv_keys;    // [max_keypairs][8]
+    uint32_t *remote_index; // [max_keypairs] receiver index written into sealed headers
+    uint64_t *send_counter; // [max_keypairs] next nonce to hand out
+    uint64_t *replay_last;  // [max_keypairs] highest counter accepted
+    uint64_t *replay_ring;  // [max_keypairs][ring_blocks] RFC 6479 bitmap ring
+};
+
+// Flattened, indexed ACL and the reply-flow table (filter_kernels.cu).
+struct FilterTables {
+    // rule index: open-addressing table keyed by (prefix_len, masked address)
+    uint64_t *rule_keys;   // [rule_slots] 0 = empty; else (1<<40 | len<<32 | masked addr)
+    uint2 *rule_span;      // [rule_slots] (first entry, entry count) into rule_entries
+    uint64_t *rule_entries; // packed (proto<<32 | first<<16 | last)
+    uint32_t rule_slots;   // power of two (0 when no tuples)
+    uint64_t len_mask;     // bit L set when some tuple has prefix length L (bits 0..32)
+    int enforce;
+    // flow table, one open-addressing region per protocol class (tcp, udp, icmp)
+    uint64_t *flow_keys;   // [3][flow_capacity] FLOW_EMPTY = all ones
+    long long *flow_exp;   // [3][flow_capacity] expiry in unix ns; FLOW_DEAD = deleted
+    uint32_t flow_capacity; // power of two
+    unsigned long long *flow_live;  // device counter: live entries (Go's len(f.flows))
+    long long *flow_special_exp;    // [3] entry for the one key that equals FLOW_EMPTY
+    int *flow_error;       // set to 1 when an insert found no free slot
+};
+
+struct bnk_ctx {
+    bnk_cfg cfg;
+    int device;
+    KeypairTables kt;
+    FilterTables ft;
+    cudaStream_t admin_stream;
+    cudaEvent_t timer_start;
+    int sm_count;
+    std::atomic<uint64_t> launches;
+    std::mutex mu;
+    std::string last_error;
+};
+
+struct DeviceBatch {
+    uint8_t *ring;
+    uint32_t *off, *len, *slot, *out_len;
+    uint64_t *counter;
+    uint8_t *status;
+    // scratch for grouping packets by keypair slot (group_kernels.cu)
+    uint32_t *order;      // [max_pkts] packet indices, stable by slot
+    uint32_t *order_tmp;  // [max_pkts]
+    uint32_t *keys_tmp;   // [2][max_pkts] radix keys ping-pong
+    uint32_t *hist;       // [256 * chunks]
+    uint32_t *seg_head;   // [max_pkts] 1 where a new slot segment starts in `order`
+    uint32_t *len_order;  // [max_pkts] packet indices ordered by length class
+    uint32_t *counters32; // small scratch (bins)
+};
+
+struct bnk_batch {
+    bnk_ctx *ctx;
+    uint32_t max_pkts;
+    uint64_t ring_bytes;
+    bnk_batch_view host; // pinned
+    DeviceBatch dev;
+    cudaStream_t stream;
+    cudaEvent_t done, k_begin, k_end, t_end;
+    bool in_flight;
+    bool kernel_timed;
+    int *h_flow_error; // pinned copy of the flow-table overflow flag, refreshed by filter work
+};
+
+// ---------------------------------------------------------------------------
+// Kernel launchers (each defined next to its kernels).  All are asynchronous on
+// `s` and return the cudaError_t of the launch.
+// ---------------------------------------------------------------------------
+struct AeadArgs {
+    uint8_t *ring;
+    const uint32_t *off;
+    const uint32_t *len;
+    const uint32_t *slot;
+    uint64_t *counter;
+    uint32_t *out_len;
+    uint8_t *status;
+    const uint32_t *keys;         // send keys (seal) or receive keys (open)
+    const uint32_t *remote_index; // seal only
+    const uint32_t *order;        // optional scheduling permutation, may be null
+    uint32_t n;
+    uint32_t mtu;
+    uint32_t max_slots;
+    uint64_t ring_bytes;
+};
+cudaError_t launch_seal(const AeadArgs &a, cudaStream_t s, std::atomic<uint64_t> *launches);
+cudaError_t launch_open(const AeadArgs &a, cudaStream_t s, std::atomic<uint64_t> *launches);
+
+// group_kernels.cu
+cudaError_t launch_group_by_slot(bnk_batch *b, uint32_t n, bool only_status_ok, cudaStream_t s);
+cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s);
+cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s);
+cudaError_t launch_length_order(bnk_batch *b, uint32_t n, bool open_side, cudaStream_t s);
+uint32_t group_sort_chunks(uint32_t max_pkts);
+
+// filter_kernels.cu
+cudaError_t launch_filter_note(bnk_batch *b, uint32_t n, long long now_ns, cudaStream_t s);
+cudaError_t launch_filter_check(bnk_batch *b, uint32_t n, long long now_ns, bool only_status_ok, cudaStream_t s);
+cudaError_t filter_tables_alloc(bnk_ctx *ctx);
+void filter_tables_free(bnk_ctx *ctx);
+int filter_acl_upload(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n);
+cudaError_t filter_flows_clear(bnk_ctx *ctx, cudaStream_t s);
+
+// probe_kernels.cu
+cudaError_t launch_fill_random(uint8_t *dst, uint64_t bytes, uint64_t seed, cudaStream_t s,
+                               std::atomic<uint64_t> *launches);
+cudaError_t probe_int_throughput(bnk_ctx *ctx, int mix, double *tops);

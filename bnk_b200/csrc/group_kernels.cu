@@ -1,0 +1,309 @@
+// Per-keypair ordering work for sm_100a: grouping a batch by keypair slot while
+// keeping arrival order (a stable least-significant-digit radix sort whose ranking
+// step uses warp match/ballot instead of per-element atomics), handing out send
+// counters, and walking the anti-replay window.
+//
+// Why a stable grouping: both the send counter (packets of one peer get
+// consecutive nonces in batch order) and the replay window (verdicts depend on
+// the arrival order of a peer's authenticated packets) are defined by a
+// sequential walk per peer.  Different peers are independent, so after grouping
+// one thread walks one peer's packets and all peers proceed in parallel.
+#include "bnk_internal.cuh"
+
+namespace {
+
+constexpr uint32_t kChunk = 2048;   // elements ranked by one warp
+constexpr uint32_t kMaxDigitBits = 11;
+constexpr uint32_t kMaxBins = 1u << kMaxDigitBits;
+
+struct SortKeySrc {
+    const uint32_t *slot;
+    const uint8_t *status;
+    uint32_t max_slots;
+    int only_status_ok; // 1: packets whose status is not OK/KEEPALIVE do not take part
+};
+
+// Key of packet i: its keypair slot, or max_slots ("takes no part", sorts last).
+__device__ __forceinline__ uint32_t slot_key(const SortKeySrc &k, uint32_t i) {
+    const uint32_t s = k.slot[i];
+    if (s >= k.max_slots) return k.max_slots;
+    if (k.only_status_ok) {
+        const uint8_t st = k.status[i];
+        if (st != BNK_PKT_OK && st != BNK_PKT_KEEPALIVE) return k.max_slots;
+    }
+    return s;
+}
+
+// --- pass step 1: per-chunk digit histogram -------------------------------------------
+// grid = chunks, block = 32.  hist is digit-major: hist[digit * chunks + chunk].
+__global__ void __launch_bounds__(32) radix_hist_kernel(SortKeySrc src, const uint32_t *keys_in, uint32_t n,
+                                                        uint32_t shift, uint32_t bins, uint32_t chunks,
+                                                        uint32_t *hist) {
+    __shared__ uint32_t cnt[kMaxBins];
+    const uint32_t lane = threadIdx.x, chunk = blockIdx.x;
+    for (uint32_t d = lane; d < bins; d += 32) cnt[d] = 0;
+    __syncwarp();
+    const uint32_t begin = chunk * kChunk;
+    const uint32_t end = min(n, begin + kChunk);
+    for (uint32_t i = begin + lane; i < end; i += 32) {
+        const uint32_t key = keys_in ? keys_in[i] : slot_key(src, i);
+        atomicAdd(&cnt[(key >> shift) & (bins - 1)], 1u);
+    }
+    __syncwarp();
+    for (uint32_t d = lane; d < bins; d += 32) hist[d * chunks + chunk] = cnt[d];
+}
+
+// --- pass step 2: exclusive scan of the histogram (single CTA) -------------------------
+// Tiles of 4096 values; each thread owns 4 consecutive ones, warps combine with shuffles
+// and a running carry links the tiles.
+__global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t *data, uint32_t n) {
+    __shared__ uint32_t warp_off[32];
+    __shared__ uint32_t carry_s;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) carry_s = 0;
+    __syncthreads();
+    for (uint32_t base = 0; base < n; base += 4096) {
+        const uint32_t i0 = base + tid * 4;
+        uint32_t v[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) v[k] = (i0 + k < n) ? data[i0 + k] : 0u;
+        const uint32_t mine = v[0] + v[1] + v[2] + v[3];
+        uint32_t incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= (uint32_t)o) incl += t;
+        }
+        if (lane == 31) warp_off[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            const uint32_t ws = warp_off[lane];
+            uint32_t wi = ws;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+                if (lane >= (uint32_t)o) wi += t;
+            }
+            warp_off[lane] = wi - ws;
+        }
+        __syncthreads();
+        uint32_t run = carry_s + warp_off[warp] + (incl - mine);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            if (i0 + k < n) data[i0 + k] = run;
+            run += v[k];
+        }
+        __syncthreads();
+        if (tid == 1023) carry_s = run; // carry + this tile's total
+        __syncthreads();
+    }
+}
+
+// --- pass step 3: stable scatter --------------------------------------------------------
+// grid = chunks, block = 32.  Each warp walks its chunk in order, 32 elements at a time;
+// lanes holding the same digit find each other with match_any and take consecutive
+// positions, so equal digits keep their input order.
+__global__ void __launch_bounds__(32) radix_scatter_kernel(SortKeySrc src, const uint32_t *keys_in,
+                                                           const uint32_t *vals_in, uint32_t n, uint32_t shift,
+                                                           uint32_t bins, uint32_t chunks, const uint32_t *hist,
+                                                           uint32_t *keys_out, uint32_t *vals_out) {
+    __shared__ uint32_t cur[kMaxBins];
+    const uint32_t lane = threadIdx.x, chunk = blockIdx.x;
+    for (uint32_t d = lane; d < bins; d += 32) cur[d] = hist[d * chunks + chunk];
+    __syncwarp();
+    const uint32_t begin = chunk * kChunk;
+    const uint32_t end = min(n, begin + kChunk);
+    const uint32_t lt = (1u << lane) - 1u;
+    for (uint32_t base = begin; base < end; base += 32) {
+        const uint32_t i = base + lane;
+        const bool have = i < end;
+        uint32_t key = 0, val = 0, digit = 0xffffffffu;
+        if (have) {
+            key = keys_in ? keys_in[i] : slot_key(src, i);
+            val = vals_in ? vals_in[i] : i;
+            digit = (key >> shift) & (bins - 1);
+        }
+        const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+        const uint32_t rank = __popc(peers & lt);
+        uint32_t pos = 0;
+        if (have) pos = cur[digit] + rank;
+        __syncwarp();
+        if (have && rank == 0) cur[digit] += __popc(peers);
+        __syncwarp();
+        if (have) {
+            keys_out[pos] = key;
+            vals_out[pos] = val;
+        }
+    }
+}
+
+// 1 where a run of equal keys starts
+__global__ void seg_head_kernel(const uint32_t *keys, uint32_t n, uint32_t *head) {
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    head[j] = (j == 0 || keys[j] != keys[j - 1]) ? 1u : 0u;
+}
+
+// --- send counters ----------------------------------------------------------------------
+// One thread per slot segment: packets of the slot get base, base+1, ... in batch order and
+// the slot's counter moves past them, saturating at Reject-After-Messages (packets at or
+// beyond it are refused by the seal kernel).
+__global__ void assign_counters_kernel(const uint32_t *keys, const uint32_t *order, const uint32_t *head,
+                                       uint32_t n, uint32_t max_slots, uint64_t *send_counter,
+                                       uint64_t *counter_out) {
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n || !head[j]) return;
+    const uint32_t slot = keys[j];
+    if (slot >= max_slots) return;
+    const uint64_t base = send_counter[slot];
+    uint32_t k = j;
+    for (; k < n && keys[k] == slot; k++) {
+        uint64_t c = base + (uint64_t)(k - j);
+        if (c < base || c > BNK_REJECT_AFTER_MESSAGES) c = BNK_REJECT_AFTER_MESSAGES;
+        counter_out[order[k]] = c;
+    }
+    uint64_t next = base + (uint64_t)(k - j);
+    if (next < base || next > BNK_REJECT_AFTER_MESSAGES) next = BNK_REJECT_AFTER_MESSAGES;
+    send_counter[slot] = next;
+}
+
+// --- anti-replay window, RFC 6479 -------------------------------------------------------
+// One thread per slot segment walks the slot's authenticated packets in arrival order.
+__global__ void replay_kernel(const uint32_t *keys, const uint32_t *order, const uint32_t *head, uint32_t n,
+                              uint32_t max_slots, uint32_t ring_blocks, uint64_t *replay_last,
+                              uint64_t *replay_ring, const uint64_t *counter, uint8_t *status) {
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n || !head[j]) return;
+    const uint32_t slot = keys[j];
+    if (slot >= max_slots) return;
+    uint64_t *ring = replay_ring + (size_t)slot * ring_blocks;
+    const uint64_t mask = ring_blocks - 1;
+    const uint64_t window = (uint64_t)(ring_blocks - 1) * 64u;
+    uint64_t last = replay_last[slot];
+    for (uint32_t k = j; k < n && keys[k] == slot; k++) {
+        const uint32_t pkt = order[k];
+        const uint64_t c = counter[pkt];
+        bool ok = c < BNK_REJECT_AFTER_MESSAGES;
+        if (ok) {
+            const uint64_t block = c >> 6;
+            if (c > last) {
+                const uint64_t top = last >> 6;
+                uint64_t steps = block - top;
+                if (steps > ring_blocks) steps = ring_blocks;
+                for (uint64_t s = 1; s <= steps; s++) ring[(top + s) & mask] = 0;
+                last = c;
+            } else if (last - c > window) {
+                ok = false;
+            }
+            if (ok) {
+                const uint64_t bit = 1ull << (c & 63u);
+                const uint64_t w = ring[block & mask];
+                if (w & bit) ok = false;
+                else ring[block & mask] = w | bit;
+            }
+        }
+        if (!ok) status[pkt] = BNK_PKT_REPLAY;
+    }
+    replay_last[slot] = last;
+}
+
+// --- scheduling order by length class (mixed packet sizes) ------------------------------
+// Packets with the same number of 64-byte cipher blocks end up next to each other so that
+// the lanes of a seal/open warp finish together.  Order inside a class does not matter.
+constexpr uint32_t kLenBins = 1026;
+__device__ __forceinline__ uint32_t len_bin(uint32_t len, bool open_side) {
+    uint32_t body = open_side ? (len >= 32u ? len - 32u : 0u) : len;
+    uint32_t blocks = (body + 63u) >> 6;
+    return blocks > kLenBins - 1 ? kLenBins - 1 : blocks;
+}
+__global__ void len_hist_kernel(const uint32_t *len, uint32_t n, int open_side, uint32_t *bins) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) atomicAdd(&bins[len_bin(len[i], open_side)], 1u);
+}
+__global__ void len_scatter_kernel(const uint32_t *len, uint32_t n, int open_side, uint32_t *bins,
+                                   uint32_t *order) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) order[atomicAdd(&bins[len_bin(len[i], open_side)], 1u)] = i;
+}
+
+struct SortPlan {
+    uint32_t passes, digit_bits;
+};
+SortPlan plan_for(uint32_t max_slots) {
+    uint32_t bits = 1;
+    while ((1ull << bits) <= (uint64_t)max_slots) bits++; // keys run 0..max_slots inclusive
+    SortPlan p;
+    p.passes = (bits + kMaxDigitBits - 1) / kMaxDigitBits;
+    p.digit_bits = (bits + p.passes - 1) / p.passes;
+    return p;
+}
+
+} // namespace
+
+uint32_t group_sort_chunks(uint32_t max_pkts) { return (max_pkts + kChunk - 1) / kChunk; }
+
+// Sorts packet indices 0..n-1 by keypair slot, stable.  Leaves the sorted keys in
+// dev.keys_tmp (second half), the packet indices in dev.order and run starts in dev.seg_head.
+cudaError_t launch_group_by_slot(bnk_batch *b, uint32_t n, bool only_status_ok, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    bnk_ctx *ctx = b->ctx;
+    DeviceBatch &d = b->dev;
+    const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
+    const uint32_t bins = 1u << plan.digit_bits;
+    const uint32_t chunks = (n + kChunk - 1) / kChunk;
+    SortKeySrc src{d.slot, d.status, ctx->cfg.max_keypairs, only_status_ok ? 1 : 0};
+    // ping-pong so that the last pass lands in (keys_tmp + max_pkts, order)
+    uint32_t *kbuf[2] = {d.keys_tmp + b->max_pkts, d.keys_tmp};
+    uint32_t *vbuf[2] = {d.order, d.order_tmp};
+    const uint32_t *kin = nullptr, *vin = nullptr;
+    for (uint32_t p = 0; p < plan.passes; p++) {
+        const uint32_t shift = p * plan.digit_bits;
+        const uint32_t o = (plan.passes - 1 - p) & 1u;
+        radix_hist_kernel<<<chunks, 32, 0, s>>>(src, kin, n, shift, bins, chunks, d.hist);
+        exclusive_scan_kernel<<<1, 1024, 0, s>>>(d.hist, bins * chunks);
+        radix_scatter_kernel<<<chunks, 32, 0, s>>>(src, kin, vin, n, shift, bins, chunks, d.hist, kbuf[o], vbuf[o]);
+        ctx->launches += 3;
+        kin = kbuf[o];
+        vin = vbuf[o];
+    }
+    seg_head_kernel<<<(n + 255) / 256, 256, 0, s>>>(kbuf[0], n, d.seg_head);
+    ctx->launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    cudaError_t e = launch_group_by_slot(b, n, false, s);
+    if (e != cudaSuccess) return e;
+    DeviceBatch &d = b->dev;
+    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, d.seg_head, n,
+                                                          b->ctx->cfg.max_keypairs, b->ctx->kt.send_counter,
+                                                          d.counter);
+    b->ctx->launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    cudaError_t e = launch_group_by_slot(b, n, true, s);
+    if (e != cudaSuccess) return e;
+    DeviceBatch &d = b->dev;
+    bnk_ctx *ctx = b->ctx;
+    replay_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, d.seg_head, n,
+                                                 ctx->cfg.max_keypairs, ctx->cfg.replay_ring_blocks,
+                                                 ctx->kt.replay_last, ctx->kt.replay_ring, d.counter, d.status);
+    ctx->launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_length_order(bnk_batch *b, uint32_t n, bool open_side, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    DeviceBatch &d = b->dev;
+    cudaError_t e = cudaMemsetAsync(d.counters32, 0, kLenBins * sizeof(uint32_t), s);
+    if (e != cudaSuccess) return e;
+    len_hist_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.len, n, open_side ? 1 : 0, d.counters32);
+    exclusive_scan_kernel<<<1, 1024, 0, s>>>(d.counters32, kLenBins);
+    len_scatter_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.len, n, open_side ? 1 : 0, d.counters32, d.len_order);
+    b->ctx->launches += 3;
+    return cudaGetLastError();
+}

@@ -1,0 +1,269 @@
+"""Host-side handles over the C ABI: one Context per GPU, Batches with pinned rings.
+
+This is plumbing for tests, the benchmark and the Python mirror of the reference's
+interfaces; all packet work happens in libbnkgpu.so's CUDA kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Iterable, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import (  # noqa: F401  (re-exported)
+    F_ASSIGN_COUNTERS,
+    F_CHECK_INBOUND,
+    F_NO_D2H,
+    F_NO_H2D,
+    F_NOTE_OUTBOUND,
+    F_REPLAY,
+    F_SORT_BY_LENGTH,
+    PKT_AUTH_FAIL,
+    PKT_BAD_DESC,
+    PKT_COUNTER_EXHAUSTED,
+    PKT_FILTER_DENY,
+    PKT_KEEPALIVE,
+    PKT_MALFORMED,
+    PKT_OK,
+    PKT_REPLAY,
+    WAIT_FOREVER,
+    BnkError,
+)
+
+ACL_TUPLE_DTYPE = np.dtype(_lib.AclTuple)
+
+
+def _np_view(ptr: int, dtype, count: int) -> np.ndarray:
+    nbytes = int(count) * np.dtype(dtype).itemsize
+    buf = (C.c_uint8 * nbytes).from_address(ptr)
+    return np.frombuffer(buf, dtype=dtype, count=count)
+
+
+def slot_size(mtu: int) -> int:
+    """Bytes one packet of up to `mtu` bytes needs in a ring: header room + padded payload + tag, 16-aligned."""
+    return (16 + ((mtu + 15) & ~15) + 16 + 15) & ~15
+
+
+class Context:
+    """One GPU: keypair table, replay windows, ACL + flow tables."""
+
+    def __init__(self, device_id: int = 0, max_keypairs: int = 1024, replay_ring_blocks: int = 128, mtu: int = 1420,
+                 flow_capacity: int = 1 << 16, max_acl_tuples: int = 0):
+        L = _lib.lib()
+        cfg = _lib.Cfg(C.sizeof(_lib.Cfg), device_id, max_keypairs, replay_ring_blocks, mtu, flow_capacity,
+                       max_acl_tuples, 0)
+        h = C.c_void_p()
+        _lib.check(L.bnk_ctx_create(C.byref(cfg), C.byref(h)))
+        self._h = h
+        self.cfg = cfg
+        self._batches: list[Batch] = []
+
+    # -- lifetime --
+    def close(self):
+        if getattr(self, "_h", None):
+            for b in list(self._batches):
+                b.close()
+            _lib.lib().bnk_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def _ck(self, code: int) -> int:
+        return _lib.check(code, self._h)
+
+    def synchronize(self):
+        self._ck(_lib.lib().bnk_ctx_synchronize(self._h))
+
+    # -- keypairs --
+    def set_keypair(self, slot: int, send_key: bytes, recv_key: bytes, remote_index: int):
+        self._ck(_lib.lib().bnk_keypair_set(self._h, slot, C.c_char_p(bytes(send_key)), C.c_char_p(bytes(recv_key)),
+                                            remote_index))
+
+    def set_keypairs(self, first_slot: int, send_keys: np.ndarray, recv_keys: np.ndarray, remote_index: np.ndarray):
+        send_keys = np.ascontiguousarray(send_keys, np.uint8)
+        recv_keys = np.ascontiguousarray(recv_keys, np.uint8)
+        remote_index = np.ascontiguousarray(remote_index, np.uint32)
+        n = len(remote_index)
+        assert send_keys.size == 32 * n and recv_keys.size == 32 * n
+        self._ck(_lib.lib().bnk_keypair_set_many(self._h, first_slot, n, send_keys.ctypes.data, recv_keys.ctypes.data,
+                                                 remote_index.ctypes.data))
+
+    def clear_keypair(self, slot: int):
+        self._ck(_lib.lib().bnk_keypair_clear(self._h, slot))
+
+    def send_counter(self, slot: int) -> int:
+        v = C.c_uint64()
+        self._ck(_lib.lib().bnk_send_counter_get(self._h, slot, C.byref(v)))
+        return v.value
+
+    def set_send_counter(self, slot: int, value: int):
+        self._ck(_lib.lib().bnk_send_counter_set(self._h, slot, value))
+
+    def replay_export(self, slot: int):
+        last = C.c_uint64()
+        ring = np.zeros(self.cfg.replay_ring_blocks, np.uint64)
+        self._ck(_lib.lib().bnk_replay_export(self._h, slot, C.byref(last), ring.ctypes.data))
+        return last.value, ring
+
+    def replay_import(self, slot: int, last: int, ring: np.ndarray):
+        ring = np.ascontiguousarray(ring, np.uint64)
+        assert len(ring) == self.cfg.replay_ring_blocks
+        self._ck(_lib.lib().bnk_replay_import(self._h, slot, last, ring.ctypes.data))
+
+    # -- ACL --
+    def acl_set(self, enforce: bool, tuples: np.ndarray | None = None):
+        if tuples is None or len(tuples) == 0:
+            self._ck(_lib.lib().bnk_acl_set(self._h, int(enforce), None, 0))
+            return
+        tuples = np.ascontiguousarray(tuples, ACL_TUPLE_DTYPE)
+        self._ck(_lib.lib().bnk_acl_set(self._h, int(enforce), tuples.ctypes.data, len(tuples)))
+
+    def flows_clear(self):
+        self._ck(_lib.lib().bnk_flows_clear(self._h))
+
+    def flows_count(self) -> int:
+        v = C.c_uint64()
+        self._ck(_lib.lib().bnk_flows_count(self._h, C.byref(v)))
+        return v.value
+
+    # -- batches / measurement --
+    def batch(self, max_pkts: int, ring_bytes: int) -> "Batch":
+        return Batch(self, max_pkts, ring_bytes)
+
+    def launch_count(self) -> int:
+        v = C.c_uint64()
+        self._ck(_lib.lib().bnk_kernel_launch_count(self._h, C.byref(v)))
+        return v.value
+
+    def probe_int_throughput(self, mix: int) -> float:
+        v = C.c_double()
+        self._ck(_lib.lib().bnk_probe_int_throughput(self._h, mix, C.byref(v)))
+        return v.value
+
+    def timer_start(self, batches: Sequence["Batch"]):
+        arr = (C.c_void_p * len(batches))(*[b._h for b in batches])
+        self._ck(_lib.lib().bnk_timer_start(self._h, arr, len(batches)))
+
+    def timer_stop(self, batches: Sequence["Batch"]) -> float:
+        arr = (C.c_void_p * len(batches))(*[b._h for b in batches])
+        ms = C.c_float()
+        self._ck(_lib.lib().bnk_timer_stop(self._h, arr, len(batches), C.byref(ms)))
+        return ms.value
+
+
+class Batch:
+    """Pinned host ring + descriptors (numpy views) with a device mirror and a CUDA stream."""
+
+    def __init__(self, ctx: Context, max_pkts: int, ring_bytes: int):
+        self.ctx = ctx
+        h = C.c_void_p()
+        ctx._ck(_lib.lib().bnk_batch_create(ctx._h, max_pkts, ring_bytes, C.byref(h)))
+        self._h = h
+        v = _lib.BatchView()
+        ctx._ck(_lib.lib().bnk_batch_view_get(h, C.byref(v)))
+        self.max_pkts = max_pkts
+        self.ring_bytes = ring_bytes
+        self.ring = _np_view(v.ring, np.uint8, ring_bytes)
+        self.off = _np_view(v.off, np.uint32, max_pkts)
+        self.len = _np_view(v.len, np.uint32, max_pkts)
+        self.slot = _np_view(v.slot, np.uint32, max_pkts)
+        self.counter = _np_view(v.counter, np.uint64, max_pkts)
+        self.out_len = _np_view(v.out_len, np.uint32, max_pkts)
+        self.status = _np_view(v.status, np.uint8, max_pkts)
+        ctx._batches.append(self)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            # the numpy views alias pinned memory that is about to be freed
+            for name in ("ring", "off", "len", "slot", "counter", "out_len", "status"):
+                setattr(self, name, None)
+            _lib.lib().bnk_batch_destroy(self._h)
+            self._h = None
+            if self in self.ctx._batches:
+                self.ctx._batches.remove(self)
+
+    def _ck(self, code: int) -> int:
+        return _lib.check(code, self.ctx._h)
+
+    # -- filling --
+    def put_packets(self, packets: Iterable[bytes], stride: int | None = None, headroom: int = 16) -> int:
+        """Lays packets out at fixed stride, payload at slot+headroom (headroom=0: whole messages). Returns n."""
+        packets = list(packets)
+        if stride is None:
+            longest = max((len(p) for p in packets), default=0)
+            stride = slot_size(longest)
+        for i, p in enumerate(packets):
+            o = i * stride
+            self.off[i] = o
+            self.len[i] = len(p)
+            self.ring[o + headroom:o + headroom + len(p)] = np.frombuffer(bytes(p), np.uint8)
+        return len(packets)
+
+    def message(self, i: int) -> bytes:
+        o = int(self.off[i])
+        return self.ring[o:o + int(self.out_len[i])].tobytes()
+
+    def payload(self, i: int, length: int | None = None) -> bytes:
+        o = int(self.off[i]) + 16
+        n = int(self.out_len[i]) if length is None else length
+        return self.ring[o:o + n].tobytes()
+
+    # -- work --
+    def seal(self, n: int, flags: int = 0, now_ns: int = 0, wait: bool = True):
+        self._ck(_lib.lib().bnk_seal_submit(self._h, n, flags, now_ns))
+        if wait:
+            self.wait()
+
+    def open(self, n: int, flags: int = 0, now_ns: int = 0, wait: bool = True):
+        self._ck(_lib.lib().bnk_open_submit(self._h, n, flags, now_ns))
+        if wait:
+            self.wait()
+
+    def filter_note(self, n: int, now_ns: int, flags: int = 0, wait: bool = True):
+        self._ck(_lib.lib().bnk_filter_note_submit(self._h, n, flags, now_ns))
+        if wait:
+            self.wait()
+
+    def filter_check(self, n: int, now_ns: int, flags: int = 0, wait: bool = True):
+        self._ck(_lib.lib().bnk_filter_check_submit(self._h, n, flags, now_ns))
+        if wait:
+            self.wait()
+
+    def upload(self, n: int, wait: bool = True):
+        self._ck(_lib.lib().bnk_batch_upload(self._h, n))
+        if wait:
+            self.wait()
+
+    def download(self, n: int, wait: bool = True):
+        self._ck(_lib.lib().bnk_batch_download(self._h, n))
+        if wait:
+            self.wait()
+
+    def wait(self, timeout_ns: int = WAIT_FOREVER):
+        self._ck(_lib.lib().bnk_wait(self._h, timeout_ns))
+
+    def try_wait(self, timeout_ns: int) -> bool:
+        rc = _lib.lib().bnk_wait(self._h, timeout_ns)
+        if rc == _lib.ETIMEDOUT:
+            return False
+        self._ck(rc)
+        return True
+
+    def last_kernel_ms(self) -> float:
+        ms = C.c_float()
+        self._ck(_lib.lib().bnk_batch_last_kernel_ms(self._h, C.byref(ms)))
+        return ms.value
+
+    def fill_random(self, seed: int):
+        self._ck(_lib.lib().bnk_batch_fill_random(self._h, seed))

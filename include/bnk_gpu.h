@@ -1,0 +1,189 @@
+/*
+ * bnk_gpu.h -- C ABI of libbnkgpu.so, the B200 (sm_100a) implementation of the
+ * bnk dataplane hot path: batched WireGuard transport-data seal/open
+ * (ChaCha20-Poly1305), per-keypair send counters, the anti-replay window and
+ * the ACL packet filter with reply-flow tracking.
+ *
+ * The reference (a Go program) has no FFI.  Each entry point below names the
+ * reference interface whose per-packet work it takes over; a cgo binding for
+ * them is shown in INTEGRATION.md.  Paths are relative to the reference tree;
+ * "wireguard-go" is golang.zx2c4.com/wireguard (go.mod:10) and "x/crypto" is
+ * golang.org/x/crypto (go.mod:7), both entered through device.NewDevice at
+ * internal/dataplane/engine.go:51.
+ *
+ * Conventions
+ *   - Every call returns an int: BNK_SUCCESS or a negative BNK_E* code.  No call
+ *     aborts the process.  bnk_last_error_string() describes the last failure.
+ *   - Per-packet outcomes are data (the status[] array), not errors.
+ *   - One bnk_ctx per GPU.  A bnk_batch owns one CUDA stream; calls on one batch
+ *     are single-producer, different batches may be driven from different
+ *     threads.  Table updates (keypairs, ACL) must not overlap submitted work.
+ *   - There is no CPU fallback: without a usable CUDA device every compute
+ *     entry point fails with BNK_ECUDA.
+ */
+#ifndef BNK_GPU_H
+#define BNK_GPU_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BNK_ABI_VERSION 1
+
+/* ---- return codes ---- */
+#define BNK_SUCCESS 0
+#define BNK_EINVAL (-1)    /* bad argument */
+#define BNK_ENOMEM (-2)    /* host or device allocation failed */
+#define BNK_ECUDA (-3)     /* CUDA runtime error, see bnk_last_error_string */
+#define BNK_ETIMEDOUT (-4) /* bnk_wait ran out of time; the batch is still in flight */
+#define BNK_EBUSY (-5)     /* batch already has work in flight */
+#define BNK_EFULL (-6)     /* flow table or rule table capacity exceeded */
+
+/* ---- per-packet status ---- */
+#define BNK_PKT_OK 0
+#define BNK_PKT_AUTH_FAIL 1         /* tag mismatch: plaintext zeroed, packet to be dropped */
+#define BNK_PKT_REPLAY 2            /* rejected by the anti-replay window */
+#define BNK_PKT_FILTER_DENY 3       /* ACL filter verdict: drop */
+#define BNK_PKT_MALFORMED 4         /* not a transport-data message (type != 4 or shorter than 32) */
+#define BNK_PKT_KEEPALIVE 5         /* authenticated zero-length payload */
+#define BNK_PKT_COUNTER_EXHAUSTED 6 /* send counter reached Reject-After-Messages */
+#define BNK_PKT_BAD_DESC 7          /* descriptor out of range (offset, length or keypair slot) */
+
+#define BNK_WG_HEADER 16u
+#define BNK_WG_TAG 16u
+#define BNK_REJECT_AFTER_MESSAGES 0xFFFFFFFFFFFFDFFFull /* 2^64 - 2^13 - 1 */
+
+/* ---- submit flags ---- */
+#define BNK_F_NO_H2D (1u << 0)          /* inputs are already in the batch's device mirror */
+#define BNK_F_NO_D2H (1u << 1)          /* leave results on the device */
+#define BNK_F_ASSIGN_COUNTERS (1u << 2) /* seal: take counters from the keypair's send counter */
+#define BNK_F_NOTE_OUTBOUND (1u << 3)   /* seal: feed plaintext headers to the flow table first */
+#define BNK_F_REPLAY (1u << 4)          /* open: run the anti-replay window on authenticated packets */
+#define BNK_F_CHECK_INBOUND (1u << 5)   /* open: run the ACL filter on accepted packets */
+#define BNK_F_SORT_BY_LENGTH (1u << 6)  /* schedule packets of similar length together (mixed sizes) */
+
+typedef struct bnk_ctx bnk_ctx;
+typedef struct bnk_batch bnk_batch;
+
+typedef struct bnk_cfg {
+    uint32_t struct_size;        /* sizeof(bnk_cfg), for ABI growth */
+    int32_t device_id;           /* CUDA device ordinal */
+    uint32_t max_keypairs;       /* keypair slots (one per peer direction pair) */
+    uint32_t replay_ring_blocks; /* 64-bit blocks per replay ring: power of two, 2..1024 (32 or 128 upstream) */
+    uint32_t mtu;                /* padding cap of the seal path; 0 = pad to 16 with no cap */
+    uint32_t flow_capacity;      /* flow-table slots, power of two; 0 = no flow table */
+    uint32_t max_acl_tuples;     /* capacity of the flattened rule table; 0 = no rule table */
+    uint32_t reserved;
+} bnk_cfg;
+
+/* One flattened ACL allowance: acl.CompiledRule (internal/acl/acl.go:33-42) expanded to
+ * the cross product of its Srcs and Ports.  addr is host-order IPv4 (a<<24|b<<16|c<<8|d). */
+typedef struct bnk_acl_tuple {
+    uint32_t addr;
+    uint8_t prefix_len; /* 0..32 */
+    uint8_t proto;      /* 6 tcp, 17 udp, 1 icmp */
+    uint16_t port_first;
+    uint16_t port_last; /* ignored for icmp */
+    uint16_t reserved;
+} bnk_acl_tuple;
+
+/* Pinned host memory of a batch.  Packet i occupies ring[off[i] ...]:
+ *   seal: 16 bytes of header room, then len[i] payload bytes, then room for padding + 16-byte tag;
+ *         on completion ring[off[i]] holds header|ciphertext|tag and out_len[i] its length.
+ *   open: the received message (len[i] bytes) at ring[off[i]]; on completion the plaintext is at
+ *         ring[off[i]+16], out_len[i] its length, counter[i] the counter parsed from the header.
+ * off[i] must be a multiple of 16 and the packet's span must lie inside the ring. */
+typedef struct bnk_batch_view {
+    uint8_t *ring;
+    uint32_t *off;
+    uint32_t *len;
+    uint32_t *slot;    /* keypair slot of the packet */
+    uint64_t *counter; /* seal without ASSIGN_COUNTERS: input; otherwise output */
+    uint32_t *out_len;
+    uint8_t *status;
+    uint64_t ring_bytes;
+    uint32_t max_pkts;
+    uint32_t reserved;
+} bnk_batch_view;
+
+/* ---- library / context ---- */
+int bnk_abi_version(void);
+const char *bnk_strerror(int code);
+/* Number of CUDA devices visible, or a negative code. */
+int bnk_device_count(void);
+/* Replaces the construction seam device.NewDevice(tun, bind, logger), internal/dataplane/engine.go:51. */
+int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out);
+int bnk_ctx_destroy(bnk_ctx *ctx);
+const char *bnk_last_error_string(bnk_ctx *ctx);
+/* Blocks until all work submitted on any batch of the context has finished. */
+int bnk_ctx_synchronize(bnk_ctx *ctx);
+
+/* ---- keypair table ----
+ * Replaces the keypair state wireguard-go builds from the UAPI text the reference sends with
+ * IpcSet (internal/dataplane/engine.go:292-299,334,341).  Setting a slot zeroes its send counter
+ * and replay window; clearing also wipes the keys. */
+int bnk_keypair_set(bnk_ctx *ctx, uint32_t slot, const uint8_t send_key[32], const uint8_t recv_key[32],
+                    uint32_t remote_index);
+int bnk_keypair_set_many(bnk_ctx *ctx, uint32_t first_slot, uint32_t n, const uint8_t *send_keys,
+                         const uint8_t *recv_keys, const uint32_t *remote_index);
+int bnk_keypair_clear(bnk_ctx *ctx, uint32_t slot);
+int bnk_send_counter_get(bnk_ctx *ctx, uint32_t slot, uint64_t *counter);
+int bnk_send_counter_set(bnk_ctx *ctx, uint32_t slot, uint64_t counter);
+/* Replay-window state, for tests and state hand-over: ring has replay_ring_blocks words. */
+int bnk_replay_export(bnk_ctx *ctx, uint32_t slot, uint64_t *last, uint64_t *ring);
+int bnk_replay_import(bnk_ctx *ctx, uint32_t slot, uint64_t last, const uint64_t *ring);
+
+/* ---- ACL filter tables ----
+ * bnk_acl_set replaces Filter.SetRules / Filter.SetAllowAll (internal/filter/filter.go:46-59):
+ * enforce=0 is allow-all mode, enforce=1 with n=0 is deny-all-but-flows.  The flow table is kept. */
+int bnk_acl_set(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n);
+int bnk_flows_clear(bnk_ctx *ctx);
+int bnk_flows_count(bnk_ctx *ctx, uint64_t *live);
+
+/* ---- batches ---- */
+int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_batch **out);
+int bnk_batch_destroy(bnk_batch *b);
+int bnk_batch_view_get(bnk_batch *b, bnk_batch_view *out);
+
+/* Replaces the per-packet work of wireguard-go's encryption worker (header, padding, x/crypto
+ * chacha20poly1305 Seal, nonce from the keypair's send counter) for one tun.Device.Read batch;
+ * with BNK_F_NOTE_OUTBOUND also filteredTUN.Read's NoteOutbound loop (internal/filter/filter.go:160-167). */
+int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns);
+/* Replaces wireguard-go's decryption worker (x/crypto Open), the sequential replay-window check, and
+ * with BNK_F_CHECK_INBOUND filteredTUN.Write's CheckInbound loop (internal/filter/filter.go:171-186)
+ * for one conn.ReceiveFunc batch. */
+int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns);
+/* Filter-only batches.  Packet i is the IP packet of len[i] bytes at ring[off[i]+16].
+ * Replaces Filter.NoteOutbound (filter.go:189-209) / Filter.CheckInbound (filter.go:121-147)
+ * called once per packet with one `now` per batch; status[i] is BNK_PKT_OK or BNK_PKT_FILTER_DENY. */
+int bnk_filter_note_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns);
+int bnk_filter_check_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns);
+/* Waits for the batch's submitted work.  timeout_ns = 0 polls once; UINT64_MAX waits without limit. */
+int bnk_wait(bnk_batch *b, uint64_t timeout_ns);
+/* Explicit transfers between the pinned ring/descriptors and the device mirror (asynchronous). */
+int bnk_batch_upload(bnk_batch *b, uint32_t npkts);
+int bnk_batch_download(bnk_batch *b, uint32_t npkts);
+
+/* ---- measurement helpers (CUDA events on the batches' own streams) ----
+ * bnk_timer_start records a start event on batches[0]'s stream and makes the other batches' streams
+ * wait for it; bnk_timer_stop records an end event on every batch, waits, and returns the longest
+ * start-to-end span in milliseconds. */
+int bnk_timer_start(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n);
+int bnk_timer_stop(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n, float *ms);
+/* Duration of the kernels of the batch's most recent submit (excluding copies), milliseconds. */
+int bnk_batch_last_kernel_ms(bnk_batch *b, float *ms);
+/* Number of kernels this library has launched on the context since creation. */
+int bnk_kernel_launch_count(bnk_ctx *ctx, uint64_t *count);
+/* Measures the 32-bit integer issue rate of the device (dependent chains of add/xor/funnel-shift on the
+ * ALU pipe, optionally mixed with multiply-adds on the FMA pipe); result in 10^12 operations/s. */
+int bnk_probe_int_throughput(bnk_ctx *ctx, int mix, double *tera_ops_per_s);
+/* Fills the device mirror of the batch's ring with SplitMix64 output (seeded, position-dependent). */
+int bnk_batch_fill_random(bnk_batch *b, uint64_t seed);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

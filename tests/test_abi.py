@@ -1,0 +1,48 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/bnk_gpu.h declares."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "bnk_gpu.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bnk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    from bnk_b200 import _lib
+
+    assert declared_symbols() == sorted(_lib.SYMBOLS)
+
+
+def test_library_exports_every_declared_symbol():
+    from bnk_b200 import _build, _lib
+
+    if _build.is_stale():
+        _build.build()
+    L = ctypes.CDLL(_lib.lib_path())
+    for name in declared_symbols():
+        assert hasattr(L, name), name
+    assert _lib.lib().bnk_abi_version() == 1
+    assert _lib.lib().bnk_strerror(-4) == b"timed out"
+
+
+def test_struct_layouts_match_header():
+    from bnk_b200 import _lib
+
+    assert ctypes.sizeof(_lib.Cfg) == 32
+    assert ctypes.sizeof(_lib.AclTuple) == 12
+    assert ctypes.sizeof(_lib.BatchView) == 72
+
+
+def test_no_cpu_fallback_in_product_path():
+    """Nothing under bnk_b200/ may import or link the CPU checker."""
+    pkg = os.path.join(ROOT, "bnk_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for fn in files:
+            if fn.endswith((".py", ".cu", ".cuh", ".cpp", ".hpp", ".h")):
+                src = open(os.path.join(dirpath, fn), errors="replace").read()
+                assert "oracle" not in src.lower(), os.path.join(dirpath, fn)

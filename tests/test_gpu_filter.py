@@ -1,0 +1,165 @@
+"""ACL filter parity on the GPU: the reference's own cases through the Python mirror of its
+interface, and configuration 3 against the CPU checker, verdict for verdict."""
+import numpy as np
+import pytest
+
+from tests import reference_cases as RC
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx(gpu_lib):
+    from bnk_b200 import Context
+
+    c = Context(max_keypairs=4, flow_capacity=1 << 14)
+    yield c
+    c.close()
+
+
+@pytest.fixture()
+def make(ctx):
+    from bnk_b200.filter import Filter
+
+    made = []
+
+    def _make():
+        ctx.flows_clear()
+        f = Filter(ctx, batch_pkts=8)
+        made.append(f)
+        return f
+
+    yield _make
+    for f in made:
+        f._batch.close()
+
+
+@pytest.mark.parametrize("case", RC.ALL_CASES, ids=lambda c: c.__name__)
+def test_reference_cases(make, case):
+    case(make)
+
+
+def test_wrap_tun_cases(make):
+    from bnk_b200.filter import wrap_tun
+
+    RC.tun_case_drops_denied_inbound_writes(make, wrap_tun)
+    RC.tun_case_read_records_outbound_flows(make, wrap_tun)
+
+
+def _load_headers(b, hdr, lens):
+    from bnk_b200 import gen
+
+    n = len(lens)
+    stride = gen.HDR_STRIDE
+    view = b.ring[:n * stride].reshape(n, stride)
+    view[:, 16:16 + hdr.shape[1]] = hdr
+    b.off[:n] = (np.arange(n, dtype=np.uint64) * stride).astype(np.uint32)
+    b.len[:n] = lens
+    return n
+
+
+def _run_config3(oracle, n_rules, n_nodes, n_out, n_in, seed=None, flow_capacity=1 << 20, step=1):
+    from bnk_b200 import Context, gen
+    from bnk_b200.device import PKT_OK
+    from bnk_b200.filter import flatten_rule_arrays
+
+    w = gen.config3(n_rules, n_nodes, n_out, n_in, seed=seed)
+    # CPU checker
+    f = oracle.Filter()
+    f.set_rules_arrays(w.rules.astype(oracle.RULE_DTYPE), w.srcs.astype(oracle.PREFIX_DTYPE),
+                       w.ports.astype(oracle.PORT_DTYPE))
+    f.note_batch(np.ascontiguousarray(w.outbound), 28, w.outbound_len, w.t0_ns)
+    # Verdicts inside one batch do not depend on each other (one clock value, refreshes all write the same
+    # expiry), so the scalar checker may look at every `step`-th packet only and still be exact for those.
+    want = f.check_batch(np.ascontiguousarray(w.inbound[::step]), 28, np.ascontiguousarray(w.inbound_len[::step]),
+                         w.t0_ns + RC.SEC)
+    want_late = f.check_batch(np.ascontiguousarray(w.late), 28, w.late_len, w.t0_ns + 10 * RC.MIN)
+    want_again = f.check_batch(np.ascontiguousarray(w.late), 28, w.late_len, w.t0_ns + 2 * RC.SEC)
+    want_flows = f.flow_count
+    # GPU
+    c = Context(max_keypairs=4, flow_capacity=flow_capacity)
+    try:
+        c.acl_set(True, flatten_rule_arrays(w.rules, w.srcs, w.ports))
+        cap = max(n_out, n_in)
+        b = c.batch(cap, cap * gen.HDR_STRIDE)
+        n = _load_headers(b, w.outbound, w.outbound_len)
+        b.filter_note(n, w.t0_ns)
+        n = _load_headers(b, w.inbound, w.inbound_len)
+        b.filter_check(n, w.t0_ns + RC.SEC)
+        got_all = (np.array(b.status[:n]) == PKT_OK).astype(np.uint8)
+        got = got_all[::step]
+        n = _load_headers(b, w.late, w.late_len)
+        b.filter_check(n, w.t0_ns + 10 * RC.MIN)
+        got_late = (np.array(b.status[:n]) == PKT_OK).astype(np.uint8)
+        b.filter_check(n, w.t0_ns + 2 * RC.SEC)
+        got_again = (np.array(b.status[:n]) == PKT_OK).astype(np.uint8)
+        got_flows = c.flows_count()
+    finally:
+        c.close()
+    assert np.array_equal(got, want), f"{np.flatnonzero(got != want)[:10]} differ"
+    assert np.array_equal(got_late, want_late)
+    assert np.array_equal(got_again, want_again)
+    assert got_flows == want_flows
+    return w, got_all, want_late
+
+
+def test_config3_small(oracle):
+    w, want, late = _run_config3(oracle, 500, 2000, 6000, 20000, seed=77, flow_capacity=1 << 14)
+    assert 0.25 < want.mean() < 0.9      # both verdicts well represented
+    assert late.sum() < len(late)        # replies whose flow ran out are refused
+
+
+def test_config3_full_size(oracle):
+    """10,000 rules, 300,000 noted flows, 1,000,000 inbound headers: every verdict equal."""
+    w, got, late = _run_config3(oracle, 10_000, 50_000, 300_000, 1_000_000, step=16)
+    assert len(got) == 1_000_000 and got.sum() > 300_000
+    # size-independent properties over all 1,000,000 verdicts: malformed headers never pass ...
+    bad = (w.inbound_len < 28) | (w.inbound[:, 0] != 0x45) | ~np.isin(w.inbound[:, 9], (1, 6, 17))
+    assert bad.sum() > 40_000 and got[bad].sum() == 0
+    # ... and every exact mirror of a noted flow passes while its TTL runs
+    reply = np.zeros(len(got), bool)
+    key_out = {bytes(h[9:10]) + bytes(h[16:20]) + bytes(h[22:24]) + bytes(h[20:22]) for h in w.outbound[::7]}
+    for i in range(0, len(got), 97):
+        h = w.inbound[i]
+        if not bad[i] and bytes(h[9:10]) + bytes(h[12:16]) + bytes(h[20:24]) in key_out:
+            reply[i] = True
+    assert reply.sum() > 100 and got[reply].all()
+
+
+def test_flow_sweep_and_count(ctx):
+    """filter.go:202-208 through the batch path: counts and the >4096 sweep follow the reference."""
+    from bnk_b200.filter import Filter
+
+    ctx.flows_clear()
+    f = Filter(ctx, batch_pkts=5000)
+    f.set_rules([])
+    f.note_outbound_batch([RC.udp(RC.SELF, RC.PEER, 1 + i, 7) for i in range(4096)], RC.T0)
+    assert ctx.flows_count() == 4096
+    f.note_outbound(RC.udp(RC.SELF, RC.PEER, 5000, 7), RC.T0 + 10 * RC.SEC)
+    assert ctx.flows_count() == 4097
+    f.note_outbound(RC.udp(RC.SELF, RC.PEER, 5001, 7), RC.T0 + 31 * RC.SEC)
+    assert ctx.flows_count() == 2
+    assert not f.check_inbound(RC.udp(RC.PEER, RC.SELF, 7, 1), RC.T0 + 5 * RC.SEC)
+    # duplicates inside one batch count once; the all-ones key has its own slot
+    ctx.flows_clear()
+    f.note_outbound_batch([RC.udp(RC.SELF, RC.PEER, 9, 9)] * 100 + [RC.udp(RC.SELF, 0xFFFFFFFF, 65535, 65535)] * 3, RC.T0)
+    assert ctx.flows_count() == 2
+    assert f.check_inbound(RC.udp(0xFFFFFFFF, RC.SELF, 65535, 65535), RC.T0 + RC.SEC)
+    assert not f.check_inbound(RC.tcp(0xFFFFFFFF, RC.SELF, 65535, 65535), RC.T0 + RC.SEC)
+    f._batch.close()
+
+
+def test_flow_table_full_is_reported(gpu_lib):
+    from bnk_b200 import Context
+    from bnk_b200.device import BnkError
+    from bnk_b200.filter import Filter
+
+    c = Context(max_keypairs=4, flow_capacity=16)
+    try:
+        f = Filter(c, batch_pkts=64)
+        f.set_rules([])
+        with pytest.raises(BnkError) as e:
+            f.note_outbound_batch([RC.udp(RC.SELF, RC.PEER, 1 + i, 7) for i in range(40)], RC.T0)
+        assert e.value.code == -6
+    finally:
+        c.close()

@@ -1,0 +1,141 @@
+"""Configuration 2 end to end on the GPU: open + replay (+ filter) of an IMIX arrival stream with
+reordering, duplicates and damaged tags; statuses and plaintext equal to the CPU checker's."""
+import numpy as np
+import pytest
+
+from tests import helpers as H
+from tests import reference_cases as RC
+
+pytestmark = pytest.mark.gpu
+
+
+def _arrival_stream(oracle, w):
+    b = w.base
+    sealed = [oracle.wg_seal(b.keys[int(b.peer[i])].tobytes(), int(b.remote_index[int(b.peer[i])]), int(b.counter[i]),
+                             b.payloads[i], 1420) for i in range(len(b.payloads))]
+    msgs = [bytearray(sealed[i]) for i in w.arrival]
+    for p, k in zip(w.flip_pos, w.flip_byte):
+        msgs[int(p)][len(msgs[int(p)]) - 16 + int(k)] ^= 0x01
+    slots = b.peer[w.arrival].astype(np.uint32)
+    return [bytes(m) for m in msgs], slots
+
+
+@pytest.mark.parametrize("blocks,sort", [(32, False), (128, True)])
+def test_config2_open_replay(gpu_lib, oracle, blocks, sort):
+    from bnk_b200 import Context, gen
+    from bnk_b200.device import F_REPLAY, F_SORT_BY_LENGTH
+
+    w = gen.config2()
+    msgs, slots = _arrival_stream(oracle, w)
+    n = len(msgs)
+    assert n == 4096
+    lengths = np.array([len(m) for m in msgs], np.uint32)
+    off = H.layout_packed(lengths, slack=16)
+    c = Context(max_keypairs=w.n_peers, replay_ring_blocks=blocks, mtu=1420, flow_capacity=0)
+    try:
+        c.set_keypairs(0, w.base.keys, w.base.keys, w.base.remote_index)
+        b = c.batch(n, H.ring_bytes_for(off, lengths))
+        H.fill_payloads(b.ring, off, msgs, headroom=0)
+        b.off[:n], b.len[:n], b.slot[:n] = off, lengths, slots
+        w_ring, st, ctr, w_len = H.oracle_open(oracle, w.base.keys, b.ring, off, lengths, slots)
+        want, _ = H.oracle_replay(oracle, blocks, slots, ctr, st)
+        b.open(n, F_REPLAY | (F_SORT_BY_LENGTH if sort else 0))
+        got = np.array(b.status[:n])
+        assert np.array_equal(got, want)
+        assert np.array_equal(b.counter[:n], ctr)
+        assert np.array_equal(b.out_len[:n], w_len)
+        assert H.spans_equal(np.array(b.ring), w_ring, off, lengths - 32, start=16) == []
+        n_dup = n - len(w.base.payloads)
+        assert (want == oracle.AUTH_FAIL).sum() >= len(set(w.flip_pos.tolist())) > 0
+        assert (want == oracle.REPLAY).sum() >= n_dup - len(w.flip_pos) > 0
+        b.close()
+    finally:
+        c.close()
+
+
+def test_open_replay_filter_chain(gpu_lib, oracle):
+    """Open -> replay -> CheckInbound in one submit: only authenticated, fresh, permitted packets stay OK."""
+    from bnk_b200 import Context, gen
+    from bnk_b200.device import F_CHECK_INBOUND, F_REPLAY
+    from bnk_b200.filter import CompiledRule, PortRange, flatten_rules
+
+    w = gen.config2(n_arrivals=1024, n_peers=32)
+    msgs, slots = _arrival_stream(oracle, w)
+    n = len(msgs)
+    lengths = np.array([len(m) for m in msgs], np.uint32)
+    off = H.layout_packed(lengths, slack=16)
+    # peers 0..15 may reach udp/51820; everyone else only as a reply (none here)
+    rules = [CompiledRule(srcs=["100.64.1.0/28"], proto="udp", ports=[PortRange(51820, 51820)])]
+    c = Context(max_keypairs=32, replay_ring_blocks=128, mtu=1420, flow_capacity=1 << 10)
+    try:
+        c.set_keypairs(0, w.base.keys, w.base.keys, w.base.remote_index)
+        c.acl_set(True, flatten_rules(rules))
+        b = c.batch(n, H.ring_bytes_for(off, lengths))
+        H.fill_payloads(b.ring, off, msgs, headroom=0)
+        b.off[:n], b.len[:n], b.slot[:n] = off, lengths, slots
+        w_ring, st, ctr, w_len = H.oracle_open(oracle, w.base.keys, b.ring, off, lengths, slots)
+        want, _ = H.oracle_replay(oracle, 128, slots, ctr, st)
+        f = oracle.Filter()
+        f.set_rules([([(gen.ip4(100, 64, 1, 0), 28)], "udp", [(51820, 51820)])])
+        for i in range(n):
+            if want[i] == oracle.OK:
+                o = int(off[i]) + 16
+                if not f.check_inbound(w_ring[o:o + int(w_len[i])].tobytes(), RC.T0):
+                    want[i] = oracle.FILTER_DENY
+        b.open(n, F_REPLAY | F_CHECK_INBOUND, now_ns=RC.T0)
+        assert np.array_equal(np.array(b.status[:n]), want)
+        assert (want == oracle.FILTER_DENY).sum() > 100 and (want == oracle.OK).sum() > 100
+        b.close()
+    finally:
+        c.close()
+
+
+def test_seal_with_note_outbound_then_reply_passes(gpu_lib, oracle):
+    """Seal with NOTE_OUTBOUND records the flows of the plaintext packets before they are encrypted."""
+    from bnk_b200 import Context
+    from bnk_b200.device import F_NOTE_OUTBOUND
+    from bnk_b200.filter import Filter
+
+    c = Context(max_keypairs=2, mtu=1420, flow_capacity=1 << 10)
+    try:
+        key = np.arange(64, dtype=np.uint8).reshape(2, 32)
+        c.set_keypairs(0, key, key, np.array([7, 8], np.uint32))
+        f = Filter(c, batch_pkts=8)
+        f.set_rules([])
+        out = [RC.udp(RC.SELF, RC.PEER, 40000, 9999), RC.tcp(RC.SELF, RC.OTHER, 40001, 443)]
+        b = c.batch(4, 4 * 128)
+        n = b.put_packets(out, stride=128)
+        b.slot[:n] = [0, 1]
+        b.counter[:n] = [10, 11]
+        b.seal(n, F_NOTE_OUTBOUND, now_ns=RC.T0)
+        assert b.message(0) == oracle.wg_seal(key[0].tobytes(), 7, 10, out[0], 1420)
+        assert c.flows_count() == 2
+        assert f.check_inbound(RC.udp(RC.PEER, RC.SELF, 9999, 40000), RC.T0 + RC.SEC)
+        assert f.check_inbound(RC.tcp(RC.OTHER, RC.SELF, 443, 40001, False), RC.T0 + RC.SEC)
+        assert not f.check_inbound(RC.tcp(RC.OTHER, RC.SELF, 443, 40002, False), RC.T0 + RC.SEC)
+        b.close()
+    finally:
+        c.close()
+
+
+def test_wait_timeout_and_busy(gpu_lib):
+    """bnk_wait with a deadline returns BNK_ETIMEDOUT-or-done without blocking; a second submit before
+    the wait is refused with BNK_EBUSY."""
+    from bnk_b200 import Context, _lib
+
+    c = Context(max_keypairs=1, mtu=1420, flow_capacity=0)
+    try:
+        b = c.batch(1 << 14, (1 << 14) * 1472)
+        n = 1 << 14
+        b.off[:n] = (np.arange(n, dtype=np.uint64) * 1472).astype(np.uint32)
+        b.len[:n] = 1420
+        b.seal(n, wait=False)
+        rc = _lib.lib().bnk_seal_submit(b._h, n, 0, 0)
+        assert rc == _lib.EBUSY
+        done = b.try_wait(0)
+        assert done in (True, False)
+        assert b.try_wait(5_000_000_000)
+        assert (b.status[:n] == 0).all()
+        b.close()
+    finally:
+        c.close()

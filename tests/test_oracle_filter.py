@@ -1,0 +1,61 @@
+"""Pins the CPU checker's filter against every case of the reference's own filter / ACL tests."""
+import numpy as np
+import pytest
+
+from bnk_b200.filter import _prefix
+from tests import reference_cases as RC
+
+
+class OracleFilterAdapter:
+    """Gives the CPU checker the reference's interface (rules as CompiledRule objects)."""
+
+    def __init__(self, O):
+        self.O = O
+        self.f = O.Filter()
+
+    def set_rules(self, rules):
+        conv = []
+        for r in rules:
+            srcs = []
+            for s in r.srcs:
+                p = _prefix(s)
+                srcs.append(p if p is not None else (0, -1))
+            conv.append((srcs, r.proto, [(p.first, p.last) for p in r.ports]))
+        self.f.set_rules(conv)
+
+    def set_allow_all(self):
+        self.f.set_allow_all()
+
+    def check_inbound(self, pkt, now):
+        return self.f.check_inbound(pkt, now)
+
+    def note_outbound(self, pkt, now):
+        self.f.note_outbound(pkt, now)
+
+
+@pytest.mark.parametrize("case", RC.ALL_CASES, ids=lambda c: c.__name__)
+def test_reference_cases(oracle, case):
+    case(lambda: OracleFilterAdapter(oracle))
+
+
+def test_sweep_above_4096_flows(oracle):
+    """filter.go:202-208: once more than 4096 flows exist, a NoteOutbound sweeps the expired ones."""
+    f = oracle.Filter()
+    f.set_rules([])
+    for i in range(4096):
+        f.note_outbound(RC.udp(RC.SELF, RC.PEER, 1 + i, 7), RC.T0)
+    assert f.flow_count == 4096
+    f.note_outbound(RC.udp(RC.SELF, RC.PEER, 5000, 7), RC.T0 + 10 * RC.SEC)  # 4097 live, nothing expired yet
+    assert f.flow_count == 4097
+    f.note_outbound(RC.udp(RC.SELF, RC.PEER, 5001, 7), RC.T0 + 31 * RC.SEC)  # the first 4096 have expired
+    assert f.flow_count == 2
+    assert not f.check_inbound(RC.udp(RC.PEER, RC.SELF, 7, 1), RC.T0 + 5 * RC.SEC)  # swept, even at an earlier clock
+
+
+def test_parse_fields(oracle):
+    out = (np.zeros(6, np.uint32))
+    pkt = RC.tcp(RC.PEER, RC.SELF, 0x1234, 0x5678)
+    import ctypes
+
+    assert oracle.lib().bnko_filter_parse(pkt, len(pkt), out.ctypes.data_as(ctypes.c_void_p)) == 1
+    assert list(out) == [6, RC.PEER, RC.SELF, 0x1234, 0x5678, 0]
