@@ -1,0 +1,467 @@
+#!/usr/bin/env python
+"""Benchmark of the bnk dataplane hot path on B200.
+
+One "step" = one pass of the hot path over one batch of synthetic packets: the per-keypair
+send counters are handed out and 1,048,576 packets of 1420 B (65,536 peers, 16 packets each)
+are sealed, then the sealed messages are opened and run through the anti-replay window.
+`value` is payload bits sealed plus payload bits opened per second with everything resident in
+HBM; `e2e` is the same work through the C ABI with pinned host rings, host->device and
+device->host copies inside the timed region.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+With N > 1 it is launched by torchrun, one rank per GPU; ranks own disjoint peers (peer index
+mod N) and never exchange packet data, so the only collectives are the barrier around the
+timed region and the max over ranks of the measured time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_PACKETS = 1 << 20
+N_PEERS = 1 << 16
+SIZE = 1420
+HBM_BYTES_PER_PACKET = 2 * SIZE + 32          # seal: read 1420 + write 1452; open: the mirror
+# 32-bit integer operations per 1420-byte packet: (23 + 1) ChaCha20 blocks x 992 + 90 Poly1305 blocks x 40
+INT_OPS_PER_PACKET = 24 * 992 + 90 * 40
+E2E_BATCHES = 8
+# dram__bytes_read.sum + dram__bytes_write.sum per packet of the seal kernel, from the ncu capture summarised in
+# profiles/ (captured on 131,072 packets; traffic grows in proportion to the packet count); None until measured
+NCU_DRAM_BYTES_PER_PACKET = None
+
+
+# ----------------------------------------------------------------------------------------------
+# plumbing
+# ----------------------------------------------------------------------------------------------
+def env_world():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+class Dist:
+    """Barrier and max-over-ranks; a no-op for one rank (torch is only imported for N > 1)."""
+
+    def __init__(self, rank, world, local_rank):
+        self.rank, self.world = rank, world
+        self.torch = None
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+
+            torch.cuda.set_device(local_rank)
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            self.torch, self.dist = torch, dist
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max(self, v: float) -> float:
+        if self.world == 1:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_true(self, ok: bool) -> bool:
+        return self.max(0.0 if ok else 1.0) == 0.0
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, windows):
+        """windows: [(t_begin, t_end)] wall-clock spans of the timed regions."""
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.lines:
+            if not any(a - 0.05 <= t <= b + 0.15 for a, b in windows):
+                continue
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 7:
+                continue
+            try:
+                sm.append(float(p[0]))
+                smax.append(float(p[1]))
+                power.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, p[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    except Exception:
+        return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+# ----------------------------------------------------------------------------------------------
+# the CPU arm: OpenSSL ChaCha20-Poly1305 on every host core, same packets, same framing
+# ----------------------------------------------------------------------------------------------
+def cpu_sample(n: int, peers: int, seed: int):
+    from bnk_b200 import gen
+    from bnk_b200.device import slot_size
+
+    stride = slot_size(SIZE)
+    ring = gen.splitmix_fill(seed, n * stride)
+    i = np.arange(n, dtype=np.uint64)
+    off = (i * stride).astype(np.uint32)
+    length = np.full(n, SIZE, np.uint32)
+    slot = (i % peers).astype(np.uint32)
+    counter = i // np.uint64(peers)
+    keys = gen.SplitMix64(seed + 1).bytes(peers * 32)
+    ridx = np.arange(peers, dtype=np.uint32)
+    return ring, off, length, slot, counter, keys, ridx
+
+
+def cpu_seal_open(threads: int, n: int, passes: int):
+    """-> (Gbit/s over seal+open, seconds).  Output is checked against the input round trip."""
+    from oracle import oracle as O
+
+    ring, off, length, slot, counter, keys, ridx = cpu_sample(n, min(N_PEERS, n // 16), 0xB2000004)
+    first = ring[16:16 + SIZE].copy()
+    total = 0.0
+    for _ in range(passes):
+        s1, st, out_len = O.cpu_aead_batch(False, threads, keys, ridx, SIZE, ring, off, length, slot, counter)
+        ctr = np.zeros(n, np.uint64)
+        s2, st2, _ = O.cpu_aead_batch(True, threads, keys, ridx, SIZE, ring, off, out_len, slot, ctr)
+        assert (st == 0).all() and (st2 == 0).all() and np.array_equal(ctr, counter)
+        assert np.array_equal(ring[16:16 + SIZE], first)
+        total += s1 + s2
+    bits = 2.0 * n * SIZE * 8 * passes
+    return bits / total / 1e9, total
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = host_threads()
+    # a bounded sample of the same workload: 16 packets per peer, 1420 B, sized for ~1-2 s per step
+    n = 1 << 18
+    for _ in range(args.warmup):
+        cpu_seal_open(threads, 1 << 14, 1)
+    t0 = time.time()
+    vals = [cpu_seal_open(threads, n, 1) for _ in range(args.steps)]
+    secs = sum(v[1] for v in vals)
+    gbps = 2.0 * n * SIZE * 8 * args.steps / secs / 1e9
+    sample = f"{n} packets x {SIZE} B sealed then opened per step (a quarter of the GPU arm's batch)"
+    line = {
+        "impl": "reference", "metric": "aead_seal_open_gbps_1420B", "value": gbps, "unit": "Gbit/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": gbps, "unit": "Gbit/s", "cores": threads, "kind": "port", "sample": sample,
+                         "note": "OpenSSL EVP_chacha20_poly1305 (AVX2/AVX-512 assembly) standing in for x/crypto's "
+                                 "assembly: the Go reference path cannot be built here (no Go toolchain or module cache)"},
+        "e2e": {"value": gbps, "unit": "Gbit/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.time() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {
+        "workload": "bulk seal+open at scale (BASELINE configs[3]): 1,048,576 packets x 1420 B over 65,536 peers per GPU, "
+                    "16 sequential counters per peer, MTU 1420, replay ring 128 blocks",
+        "packets_per_gpu": N_PACKETS, "peers_per_gpu": N_PEERS, "payload_bytes": SIZE,
+        "sharding": f"peer index mod {n_gpus}, no inter-GPU traffic",
+        "bits_counted": "payload bits sealed + payload bits opened",
+        "l2": "inputs (1.5 GB per pass) are larger than L2, no flush needed",
+    }
+
+
+# ----------------------------------------------------------------------------------------------
+# the GPU arm
+# ----------------------------------------------------------------------------------------------
+def setup_batch(ctx, n, stride, peers, first_peer=0):
+    b = ctx.batch(n, n * stride)
+    i = np.arange(n, dtype=np.uint64)
+    b.off[:] = (i * np.uint64(stride)).astype(np.uint32)
+    b.len[:] = SIZE
+    b.slot[:] = (first_peer + (i % np.uint64(peers))).astype(np.uint32)
+    b.counter[:] = 0
+    return b
+
+
+def run_ours(args, rank, world, local_rank):
+    from bnk_b200 import Context, gen
+    from bnk_b200.device import (F_ASSIGN_COUNTERS, F_NO_D2H, F_NO_H2D, F_REPLAY, F_SORT_BY_LENGTH, F_USE_OUT_LEN,
+                                 slot_size)
+
+    dist = Dist(rank, world, local_rank)
+    K, W = args.steps, args.warmup
+    n, peers = args.packets, min(N_PEERS, max(1, args.packets // 16))
+    plan = gen.config4(n, peers, SIZE, rank, world)
+    stride = plan.stride
+    ctx = Context(device_id=local_rank, max_keypairs=2 * peers, replay_ring_blocks=128, mtu=SIZE, flow_capacity=0)
+    keys = gen.bulk_keys(plan)
+    # slots [0, peers) serve the device-resident run, [peers, 2*peers) the host-ring run
+    ctx.set_keypairs(0, np.concatenate([keys, keys]), np.concatenate([keys, keys]),
+                     np.arange(2 * peers, dtype=np.uint32))
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    windows = []
+
+    # ---- device-resident: value + roofline ----
+    dev = setup_batch(ctx, n, stride, peers)
+    dev.upload(n)
+    dev.fill_random(plan.payload_seed)
+    SEAL = F_NO_H2D | F_NO_D2H | F_ASSIGN_COUNTERS
+    OPEN = F_NO_H2D | F_NO_D2H | F_REPLAY | F_USE_OUT_LEN
+
+    def step_dev():
+        dev.seal(n, SEAL, wait=False)
+        dev.open(n, OPEN, wait=False)
+
+    for _ in range(W):
+        step_dev()
+    ctx.synchronize()
+    dist.barrier()
+    launches0 = ctx.launch_count()
+    t_begin = time.time()
+    ctx.timer_start([dev])
+    for _ in range(K):
+        step_dev()
+    ms_local = ctx.timer_stop([dev])
+    ctx.synchronize()
+    dist.barrier()
+    windows.append((t_begin, time.time()))
+    launches = ctx.launch_count() - launches0
+    ms = dist.max(ms_local)
+    dev.wait()
+    dev.download(n)
+    verified = bool((dev.status[:n] == 0).all() and (dev.out_len[:n] == SIZE).all()
+                    and int(dev.counter[:n].max()) == 16 * (W + K) - 1 if n >= 16 * peers else True)
+    bits_per_step = 2.0 * n * SIZE * 8
+    value = world * bits_per_step * K / (ms * 1e-3) / 1e9
+
+    # per-launch duration of the dominant kernels (CUDA events around the seal / open kernel alone)
+    seal_ms, open_ms = [], []
+    t_begin = time.time()
+    for _ in range(max(K, 3)):
+        dev.seal(n, SEAL, wait=False)
+        seal_ms.append(dev.last_aead_ms())
+        dev.open(n, OPEN, wait=False)
+        open_ms.append(dev.last_aead_ms())
+    dev.wait()
+    windows.append((t_begin, time.time()))
+    seal_avg, open_avg = statistics.mean(seal_ms), statistics.mean(open_ms)
+    aead_avg = 0.5 * (seal_avg + open_avg)
+    peak, peak_src = measured_hbm_peak()
+    achieved = n * HBM_BYTES_PER_PACKET / (aead_avg * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+        "traffic": None if NCU_DRAM_BYTES_PER_PACKET is None else NCU_DRAM_BYTES_PER_PACKET * n,
+        "kernel": "aead_kernel<seal> / aead_kernel<open> (one launch each per step, 2872 algorithmic bytes per packet)",
+        "peak_source": peak_src, "seal_ms": seal_avg, "open_ms": open_avg,
+        "note": "the path is bound by the 32-bit integer pipes, not by HBM: see `alu`",
+    }
+    alu = None
+    if rank == 0 and not args.no_probe:
+        probes = {name: ctx.probe_int_throughput(mix) for mix, name in
+                  enumerate(["add_xor", "chacha_rounds", "imad", "add_xor_plus_imad"])}
+        int_peak = max(probes.values())
+        ops = n * INT_OPS_PER_PACKET / (aead_avg * 1e-3) / 1e12
+        alu = {"bound": "int32 issue", "achieved": ops, "peak": int_peak, "unit": "Tops/s", "frac": ops / int_peak,
+               "ops_per_packet": INT_OPS_PER_PACKET, "probes_tops": probes,
+               "peak_source": "measured live by bnk_probe_int_throughput (best of the instruction mixes)"}
+    dev.close()
+
+    # ---- IMIX, device-resident ----
+    imix = None
+    if not args.no_imix:
+        g = gen.SplitMix64(gen.seed_for(2) + 7919 * rank)
+        sizes = gen.imix_sizes(g, n)
+        slots_sz = ((sizes.astype(np.uint64) + np.uint64(48 + 15)) // np.uint64(16)) * np.uint64(16)
+        offs = np.concatenate([[0], np.cumsum(slots_sz)[:-1]]).astype(np.uint64)
+        ib = ctx.batch(n, int(offs[-1] + slots_sz[-1]))
+        ib.off[:] = offs.astype(np.uint32)
+        ib.len[:] = sizes
+        ib.slot[:] = (np.arange(n, dtype=np.uint64) % np.uint64(peers)).astype(np.uint32)
+        ib.upload(n)
+        ib.fill_random(plan.payload_seed + 5)
+
+        def step_imix():
+            ib.seal(n, SEAL | F_SORT_BY_LENGTH, wait=False)
+            ib.open(n, OPEN | F_SORT_BY_LENGTH, wait=False)
+
+        for _ in range(W):
+            step_imix()
+        ctx.synchronize()
+        dist.barrier()
+        t_begin = time.time()
+        ctx.timer_start([ib])
+        for _ in range(K):
+            step_imix()
+        ims = dist.max(ctx.timer_stop([ib]))
+        dist.barrier()
+        windows.append((t_begin, time.time()))
+        ib.wait()
+        ib.download(n)
+        imix_ok = bool((ib.status[:n] == 0).all())
+        imix = {"mpps": world * 2.0 * n * K / (ims * 1e-3) / 1e6, "unit": "Mpps",
+                "packets_counted": "packets sealed + packets opened", "sizes": "64/576/1420 B at 7:4:1",
+                "gbps": world * 2.0 * float(sizes.sum()) * 8 * K / (ims * 1e-3) / 1e9, "verified": imix_ok,
+                "ms_per_step": ims / K}
+        ib.close()
+
+    # ---- end to end: pinned host rings, H2D and D2H inside the timed region ----
+    nb = E2E_BATCHES
+    per = n // nb
+    batches = [setup_batch(ctx, per, stride, peers, first_peer=peers) for _ in range(nb)]
+    ppb = max(1, peers // nb)  # batches in flight together own disjoint peers: nonce and replay order is per peer
+    for j, b in enumerate(batches):
+        b.slot[:] = (peers + j * ppb + (np.arange(per, dtype=np.uint64) % np.uint64(ppb))).astype(np.uint32)
+        b.upload(per)
+        b.fill_random(plan.payload_seed + 11 + j)
+        b.download(per)  # the pinned host ring now holds the synthetic plaintext
+
+    def step_e2e():
+        for b in batches:
+            b.seal(per, F_ASSIGN_COUNTERS, wait=False)
+        for b in batches:
+            b.wait()
+            b.len[:per] = b.out_len[:per]
+            b.open(per, F_REPLAY, wait=False)
+        for b in batches:
+            b.wait()
+            b.len[:per] = SIZE
+
+    for _ in range(W):
+        step_e2e()
+    ctx.synchronize()
+    dist.barrier()
+    t_begin = time.time()
+    ctx.timer_start(batches)
+    for _ in range(K):
+        step_e2e()
+    e2e_ms = dist.max(ctx.timer_stop(batches))
+    dist.barrier()
+    windows.append((t_begin, time.time()))
+    e2e_ok = all(bool((b.status[:per] == 0).all() and (b.out_len[:per] == SIZE).all()) for b in batches)
+    ring_span = per * stride
+    h2d = nb * ((ring_span + 3 * 4 * per) + (ring_span + 3 * 4 * per))
+    d2h = nb * 2 * (ring_span + (8 + 4 + 1) * per)
+    e2e_value = world * bits_per_step * K / (e2e_ms * 1e-3) / 1e9
+    for b in batches:
+        b.close()
+
+    sampler.stop()
+    clocks = sampler.summary(windows)
+    ok = dist.all_true(verified and e2e_ok and (imix is None or imix["verified"]))
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = host_threads()
+        sample_n = 1 << 18
+        passes = 2
+        gbps, secs = cpu_seal_open(threads, sample_n, passes)
+        cpu = {"value": gbps, "unit": "Gbit/s", "cores": threads, "kind": "port",
+               "sample": f"{sample_n} packets x {SIZE} B sealed then opened, {passes} passes ({secs:.2f} s)",
+               "note": "OpenSSL EVP_chacha20_poly1305 stand-in for x/crypto's assembly (no Go toolchain on this box)"}
+
+    if rank == 0:
+        line = {
+            "metric": "aead_seal_open_gbps_1420B", "value": value, "unit": "Gbit/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u32", "data": "synthetic", "config": workload_config(world),
+            "mpps": world * 2.0 * n * K / (ms * 1e-3) / 1e6,
+            "e2e": {"value": e2e_value, "unit": "Gbit/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / K, "batches_in_flight": nb,
+                    "mpps": world * 2.0 * n * K / (e2e_ms * 1e-3) / 1e6},
+            "gpu_launches": int(launches), "roofline": roofline, "alu": alu, "imix": imix, "cpu_baseline": cpu,
+            "clocks": clocks, "verified": ok,
+        }
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    dist.close()
+    if not ok:
+        sys.exit(3)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--packets", type=int, default=N_PACKETS, help="packets per GPU (smaller only for profiling)")
+    ap.add_argument("--no-imix", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-probe", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and args.packets == N_PACKETS else args.warmup
+    rank, world, local_rank = env_world()
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -21,6 +21,7 @@ F_NOTE_OUTBOUND = 1 << 3
 F_REPLAY = 1 << 4
 F_CHECK_INBOUND = 1 << 5
 F_SORT_BY_LENGTH = 1 << 6
+F_USE_OUT_LEN = 1 << 7
 
 WG_HEADER = 16
 WG_TAG = 16
@@ -100,6 +101,7 @@ SYMBOLS = {
     "bnk_timer_start": (_i, [_vp, C.POINTER(_vp), _u32]),
     "bnk_timer_stop": (_i, [_vp, C.POINTER(_vp), _u32, C.POINTER(C.c_float)]),
     "bnk_batch_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),
+    "bnk_batch_last_aead_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "bnk_kernel_launch_count": (_i, [_vp, C.POINTER(_u64)]),
     "bnk_probe_int_throughput": (_i, [_vp, _i, C.POINTER(C.c_double)]),
     "bnk_batch_fill_random": (_i, [_vp, _u64]),

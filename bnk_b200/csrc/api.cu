@@ -54,10 +54,10 @@ uint64_t ring_extent(const bnk_batch *b, uint32_t n, uint32_t slack) {
     return ext > b->ring_bytes ? b->ring_bytes : ext;
 }
 
-int begin_submit(bnk_batch *b, uint32_t npkts) {
+int begin_submit(bnk_batch *b, uint32_t npkts, bool touches_host = true) {
     if (!b) return BNK_EINVAL;
     if (npkts > b->max_pkts) return fail(b->ctx, BNK_EINVAL, "npkts exceeds the batch capacity");
-    if (b->in_flight) return fail(b->ctx, BNK_EBUSY, "batch has work in flight; call bnk_wait first");
+    if (b->in_flight && touches_host) return fail(b->ctx, BNK_EBUSY, "batch has work in flight; call bnk_wait first");
     CK(b->ctx, cudaSetDevice(b->ctx->device));
     return BNK_SUCCESS;
 }
@@ -308,6 +308,8 @@ int bnk_batch_destroy(bnk_batch *b) {
     if (b->done) cudaEventDestroy(b->done);
     if (b->k_begin) cudaEventDestroy(b->k_begin);
     if (b->k_end) cudaEventDestroy(b->k_end);
+    if (b->a_begin) cudaEventDestroy(b->a_begin);
+    if (b->a_end) cudaEventDestroy(b->a_end);
     if (b->t_end) cudaEventDestroy(b->t_end);
     if (b->stream) cudaStreamDestroy(b->stream);
     delete b;
@@ -365,6 +367,8 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     if (e == cudaSuccess) e = cudaEventCreate(&b->k_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&b->k_end);
     if (e == cudaSuccess) e = cudaEventCreate(&b->t_end);
+    if (e == cudaSuccess) e = cudaEventCreate(&b->a_begin);
+    if (e == cudaSuccess) e = cudaEventCreate(&b->a_end);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
         int rc = fail(ctx, e == cudaErrorMemoryAllocation ? BNK_ENOMEM : BNK_ECUDA, "batch allocation", e);
@@ -413,13 +417,14 @@ int bnk_batch_download(bnk_batch *b, uint32_t npkts) {
 }
 
 int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
-    int rc = begin_submit(b, npkts);
+    const bool device_only = (flags & BNK_F_NO_H2D) && (flags & BNK_F_NO_D2H);
+    int rc = begin_submit(b, npkts, !device_only);
     if (rc) return rc;
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
     const size_t n = npkts;
     // header room + payload + padding (< 16) + tag
-    const uint64_t ext = (flags & BNK_F_NO_H2D) && (flags & BNK_F_NO_D2H) ? 0 : ring_extent(b, npkts, 16 + 16 + 16);
+    const uint64_t ext = device_only ? 0 : ring_extent(b, npkts, 16 + 16 + 16);
     if (!(flags & BNK_F_NO_H2D) && n) {
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
         CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
@@ -436,12 +441,15 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     if (flags & BNK_F_ASSIGN_COUNTERS) CK(ctx, launch_assign_counters(b, npkts, s));
     const uint32_t *order = nullptr;
     if (flags & BNK_F_SORT_BY_LENGTH) {
-        CK(ctx, launch_length_order(b, npkts, false, s));
+        CK(ctx, launch_length_order(b, npkts, b->dev.len, false, s));
         order = b->dev.len_order;
     }
+    CK(ctx, cudaEventRecord(b->a_begin, s));
     CK(ctx, launch_seal(aead_args(b, npkts, false, order), s, &ctx->launches));
+    CK(ctx, cudaEventRecord(b->a_end, s));
     CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = true;
+    b->aead_timed = true;
     if (!(flags & BNK_F_NO_D2H) && n) {
         CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
         CK(ctx, cudaMemcpyAsync(b->host.counter, b->dev.counter, n * 8, cudaMemcpyDeviceToHost, s));
@@ -452,12 +460,13 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
 }
 
 int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
-    int rc = begin_submit(b, npkts);
+    const bool device_only = (flags & BNK_F_NO_H2D) && (flags & BNK_F_NO_D2H);
+    int rc = begin_submit(b, npkts, !device_only);
     if (rc) return rc;
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
     const size_t n = npkts;
-    const uint64_t ext = (flags & BNK_F_NO_H2D) && (flags & BNK_F_NO_D2H) ? 0 : ring_extent(b, npkts, 0);
+    const uint64_t ext = device_only ? 0 : ring_extent(b, npkts, (flags & BNK_F_USE_OUT_LEN) ? 48 : 0);
     if (!(flags & BNK_F_NO_H2D) && n) {
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
         CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
@@ -466,11 +475,17 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     }
     CK(ctx, cudaEventRecord(b->k_begin, s));
     const uint32_t *order = nullptr;
+    AeadArgs oa = aead_args(b, npkts, true, nullptr);
+    if (flags & BNK_F_USE_OUT_LEN) oa.len = b->dev.out_len;
     if (flags & BNK_F_SORT_BY_LENGTH) {
-        CK(ctx, launch_length_order(b, npkts, true, s));
+        CK(ctx, launch_length_order(b, npkts, oa.len, true, s));
         order = b->dev.len_order;
     }
-    CK(ctx, launch_open(aead_args(b, npkts, true, order), s, &ctx->launches));
+    oa.order = order;
+    CK(ctx, cudaEventRecord(b->a_begin, s));
+    CK(ctx, launch_open(oa, s, &ctx->launches));
+    CK(ctx, cudaEventRecord(b->a_end, s));
+    b->aead_timed = true;
     if (flags & BNK_F_REPLAY) CK(ctx, launch_replay(b, npkts, s));
     if (flags & BNK_F_CHECK_INBOUND) CK(ctx, launch_filter_check(b, npkts, now_unix_ns, true, s));
     CK(ctx, cudaEventRecord(b->k_end, s));
@@ -580,6 +595,15 @@ int bnk_batch_last_kernel_ms(bnk_batch *b, float *ms) {
     CK(b->ctx, cudaSetDevice(b->ctx->device));
     CK(b->ctx, cudaEventSynchronize(b->k_end));
     CK(b->ctx, cudaEventElapsedTime(ms, b->k_begin, b->k_end));
+    return BNK_SUCCESS;
+}
+
+int bnk_batch_last_aead_ms(bnk_batch *b, float *ms) {
+    if (!b || !ms) return BNK_EINVAL;
+    if (!b->aead_timed) return fail(b->ctx, BNK_EINVAL, "no seal/open has been submitted on this batch");
+    CK(b->ctx, cudaSetDevice(b->ctx->device));
+    CK(b->ctx, cudaEventSynchronize(b->a_end));
+    CK(b->ctx, cudaEventElapsedTime(ms, b->a_begin, b->a_end));
     return BNK_SUCCESS;
 }
 

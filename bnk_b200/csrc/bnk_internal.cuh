@@ -78,9 +78,10 @@ struct bnk_batch {
     bnk_batch_view host; // pinned
     DeviceBatch dev;
     cudaStream_t stream;
-    cudaEvent_t done, k_begin, k_end, t_end;
+    cudaEvent_t done, k_begin, k_end, t_end, a_begin, a_end;
     bool in_flight;
     bool kernel_timed;
+    bool aead_timed;
     int *h_flow_error; // pinned copy of the flow-table overflow flag, refreshed by filter work
 };
 
@@ -111,7 +112,7 @@ cudaError_t launch_open(const AeadArgs &a, cudaStream_t s, std::atomic<uint64_t>
 cudaError_t launch_group_by_slot(bnk_batch *b, uint32_t n, bool only_status_ok, cudaStream_t s);
 cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s);
 cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s);
-cudaError_t launch_length_order(bnk_batch *b, uint32_t n, bool open_side, cudaStream_t s);
+cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, bool open_side, cudaStream_t s);
 uint32_t group_sort_chunks(uint32_t max_pkts);
 
 // filter_kernels.cu

@@ -296,14 +296,14 @@ cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-cudaError_t launch_length_order(bnk_batch *b, uint32_t n, bool open_side, cudaStream_t s) {
+cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, bool open_side, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     DeviceBatch &d = b->dev;
     cudaError_t e = cudaMemsetAsync(d.counters32, 0, kLenBins * sizeof(uint32_t), s);
     if (e != cudaSuccess) return e;
-    len_hist_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.len, n, open_side ? 1 : 0, d.counters32);
+    len_hist_kernel<<<(n + 255) / 256, 256, 0, s>>>(len, n, open_side ? 1 : 0, d.counters32);
     exclusive_scan_kernel<<<1, 1024, 0, s>>>(d.counters32, kLenBins);
-    len_scatter_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.len, n, open_side ? 1 : 0, d.counters32, d.len_order);
+    len_scatter_kernel<<<(n + 255) / 256, 256, 0, s>>>(len, n, open_side ? 1 : 0, d.counters32, d.len_order);
     b->ctx->launches += 3;
     return cudaGetLastError();
 }

@@ -19,6 +19,7 @@ from ._lib import (  # noqa: F401  (re-exported)
     F_NOTE_OUTBOUND,
     F_REPLAY,
     F_SORT_BY_LENGTH,
+    F_USE_OUT_LEN,
     PKT_AUTH_FAIL,
     PKT_BAD_DESC,
     PKT_COUNTER_EXHAUSTED,
@@ -263,6 +264,11 @@ class Batch:
     def last_kernel_ms(self) -> float:
         ms = C.c_float()
         self._ck(_lib.lib().bnk_batch_last_kernel_ms(self._h, C.byref(ms)))
+        return ms.value
+
+    def last_aead_ms(self) -> float:
+        ms = C.c_float()
+        self._ck(_lib.lib().bnk_batch_last_aead_ms(self._h, C.byref(ms)))
         return ms.value
 
     def fill_random(self, seed: int):

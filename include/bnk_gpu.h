@@ -18,6 +18,15 @@
  *   - One bnk_ctx per GPU.  A bnk_batch owns one CUDA stream; calls on one batch
  *     are single-producer, different batches may be driven from different
  *     threads.  Table updates (keypairs, ACL) must not overlap submitted work.
+ *   - A submit that copies to or from the pinned ring needs the previous submit
+ *     of that batch to have been waited for (BNK_EBUSY otherwise).  Submits with
+ *     both BNK_F_NO_H2D and BNK_F_NO_D2H only queue kernels on the batch's stream
+ *     and may be issued back to back.
+ *   - Send counters and replay windows are per keypair and ordered: batches that
+ *     are in flight at the same time must not carry packets of the same keypair
+ *     slot when BNK_F_ASSIGN_COUNTERS or BNK_F_REPLAY is used (give each peer's
+ *     traffic to one batch at a time, as wireguard-go gives it to one sequential
+ *     worker per peer).
  *   - There is no CPU fallback: without a usable CUDA device every compute
  *     entry point fails with BNK_ECUDA.
  */
@@ -64,6 +73,7 @@ extern "C" {
 #define BNK_F_REPLAY (1u << 4)          /* open: run the anti-replay window on authenticated packets */
 #define BNK_F_CHECK_INBOUND (1u << 5)   /* open: run the ACL filter on accepted packets */
 #define BNK_F_SORT_BY_LENGTH (1u << 6)  /* schedule packets of similar length together (mixed sizes) */
+#define BNK_F_USE_OUT_LEN (1u << 7)     /* open: message lengths are the out_len[] a seal left on the device */
 
 typedef struct bnk_ctx bnk_ctx;
 typedef struct bnk_batch bnk_batch;
@@ -175,6 +185,8 @@ int bnk_timer_start(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n);
 int bnk_timer_stop(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n, float *ms);
 /* Duration of the kernels of the batch's most recent submit (excluding copies), milliseconds. */
 int bnk_batch_last_kernel_ms(bnk_batch *b, float *ms);
+/* Duration of the seal or open kernel alone in the batch's most recent seal/open submit, milliseconds. */
+int bnk_batch_last_aead_ms(bnk_batch *b, float *ms);
 /* Number of kernels this library has launched on the context since creation. */
 int bnk_kernel_launch_count(bnk_ctx *ctx, uint64_t *count);
 /* Measures the 32-bit integer issue rate of the device (dependent chains of add/xor/funnel-shift on the

@@ -47,7 +47,7 @@ def test_config2_open_replay(gpu_lib, oracle, blocks, sort):
         assert H.spans_equal(np.array(b.ring), w_ring, off, lengths - 32, start=16) == []
         n_dup = n - len(w.base.payloads)
         assert (want == oracle.AUTH_FAIL).sum() >= len(set(w.flip_pos.tolist())) > 0
-        assert (want == oracle.REPLAY).sum() >= n_dup - len(w.flip_pos) > 0
+        assert 0 < (want == oracle.REPLAY).sum() <= n_dup
         b.close()
     finally:
         c.close()
