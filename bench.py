@@ -53,27 +53,31 @@ def env_world():
 class Dist:
     """Barrier and max-over-ranks; a no-op for one rank (torch is only imported for N > 1)."""
 
-    def __init__(self, rank, world, local_rank):
-        self.rank, self.world = rank, world
+    def __init__(self, rank, world, local_rank, backend="nccl"):
+        self.rank, self.world, self.backend = rank, world, backend
         self.torch = None
         if world > 1:
             import torch
             import torch.distributed as dist
 
-            torch.cuda.set_device(local_rank)
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            if backend == "nccl":
+                torch.cuda.set_device(local_rank)
+                dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            else:  # gloo: the CPU tests of this plumbing
+                dist.init_process_group(backend, rank=rank, world_size=world)
             self.torch, self.dist = torch, dist
 
     def barrier(self):
         if self.world > 1:
             self.dist.barrier()
-            self.torch.cuda.synchronize()
+            if self.backend == "nccl":
+                self.torch.cuda.synchronize()
 
     def max(self, v: float) -> float:
         if self.world == 1:
             return v
-        t = self.torch.tensor([v], dtype=self.torch.float64, device="cuda")
+        t = self.torch.tensor([v], dtype=self.torch.float64, device="cuda" if self.backend == "nccl" else "cpu")
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 

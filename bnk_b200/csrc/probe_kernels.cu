@@ -11,6 +11,10 @@ constexpr int kProbeIters = 4096;
 // mix 1: ChaCha20 quarter rounds on 16 registers (add, xor, byte-permute, funnel shift)
 // mix 2: 32-bit multiply-add chains (FMA pipe only)
 // mix 3: add/xor chains interleaved 1:1 with multiply-add chains (both pipes)
+// mix 4: funnel-shift rotations by a run-time amount
+// mix 5: byte permutes with a run-time selector
+// mix 6: 32x32+64 -> 64-bit multiply-adds (the Poly1305 product form)
+// mix 7: three-input adds and three-input logic ops
 template <int MIX>
 __global__ void __launch_bounds__(256) int_probe_kernel(uint32_t *sink, uint32_t seed, uint32_t mul) {
     uint32_t x[16];
@@ -58,7 +62,7 @@ __global__ void __launch_bounds__(256) int_probe_kernel(uint32_t *sink, uint32_t
                 for (int i = 0; i < 8; i++) x[i] = x[i] * mul + y;
             }
         }
-    } else {
+    } else if (MIX == 3) {
 #pragma unroll 1
         for (int it = 0; it < kProbeIters; it++) {
 #pragma unroll
@@ -72,6 +76,52 @@ __global__ void __launch_bounds__(256) int_probe_kernel(uint32_t *sink, uint32_t
                 }
             }
         }
+    } else if (MIX == 4) {
+        const uint32_t sh = mul + 4; // 7 at run time: the compiler cannot fold consecutive rotations
+#pragma unroll 1
+        for (int it = 0; it < kProbeIters; it++) {
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) x[i] = __funnelshift_l(x[i], x[i], sh);
+            }
+        }
+    } else if (MIX == 5) {
+        const uint32_t sel = 0x2100u + mul; // 0x2103 at run time
+#pragma unroll 1
+        for (int it = 0; it < kProbeIters; it++) {
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) x[i] = __byte_perm(x[i], y, sel);
+            }
+        }
+    } else if (MIX == 6) {
+        uint64_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) w[i] = ((uint64_t)x[i] << 32) | x[8 + i];
+#pragma unroll 1
+        for (int it = 0; it < kProbeIters; it++) {
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) w[i] = (uint64_t)(uint32_t)w[i] * mul + w[i];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[i] = (uint32_t)w[i] ^ (uint32_t)(w[i] >> 32);
+    } else {
+#pragma unroll 1
+        for (int it = 0; it < kProbeIters; it++) {
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    x[i] = x[i] + x[(i + 1) & 7] + y;
+                    x[i] = x[i] ^ x[(i + 3) & 7] ^ z;
+                }
+            }
+        }
     }
     uint32_t acc = 0;
 #pragma unroll
@@ -80,7 +130,7 @@ __global__ void __launch_bounds__(256) int_probe_kernel(uint32_t *sink, uint32_t
 }
 
 constexpr double ops_per_iter(int mix) {
-    return mix == 0 ? 64.0 : mix == 1 ? 96.0 : mix == 2 ? 64.0 : 128.0;
+    return mix == 1 ? 96.0 : mix == 3 ? 128.0 : 64.0;
 }
 
 // SplitMix64: the k-th output (k = 0, 1, ...) of the stream seeded with `seed`
@@ -108,7 +158,7 @@ cudaError_t launch_fill_random(uint8_t *dst, uint64_t bytes, uint64_t seed, cuda
 }
 
 cudaError_t probe_int_throughput(bnk_ctx *ctx, int mix, double *tops) {
-    if (mix < 0 || mix > 3) return cudaErrorInvalidValue;
+    if (mix < 0 || mix > 7) return cudaErrorInvalidValue;
     const int ctas = ctx->sm_count * 8, threads = 256;
     uint32_t *sink = nullptr;
     cudaError_t e = cudaMalloc(&sink, (size_t)ctas * threads * sizeof(uint32_t));
@@ -124,7 +174,11 @@ cudaError_t probe_int_throughput(bnk_ctx *ctx, int mix, double *tops) {
         case 0: int_probe_kernel<0><<<ctas, threads, 0, s>>>(sink, 17u + rep, 3u); break;
         case 1: int_probe_kernel<1><<<ctas, threads, 0, s>>>(sink, 17u + rep, 3u); break;
         case 2: int_probe_kernel<2><<<ctas, threads, 0, s>>>(sink, 17u + rep, 3u); break;
-        default: int_probe_kernel<3><<<ctas, threads, 0, s>>>(sink, 17u + rep, 3u); break;
+        case 3: int_probe_kernel<3><<<ctas, threads, 0, s>>>(sink, 17u + rep, 3u); break;
+        case 4: int_probe_kernel<4><<<ctas, threads, 0, s>>>(sink, 17u + rep, 3u); break;
+        case 5: int_probe_kernel<5><<<ctas, threads, 0, s>>>(sink, 17u + rep, 3u); break;
+        case 6: int_probe_kernel<6><<<ctas, threads, 0, s>>>(sink, 17u + rep, 3u); break;
+        default: int_probe_kernel<7><<<ctas, threads, 0, s>>>(sink, 17u + rep, 3u); break;
         }
         cudaEventRecord(t1, s);
         ctx->launches += 1;
