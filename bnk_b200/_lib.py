@@ -27,6 +27,7 @@ WG_HEADER = 16
 WG_TAG = 16
 REJECT_AFTER_MESSAGES = 0xFFFFFFFFFFFFDFFF
 WAIT_FOREVER = 0xFFFFFFFFFFFFFFFF
+NOALLOC_MAX_PKTS = 16384
 
 
 class Cfg(C.Structure):
@@ -98,6 +99,7 @@ SYMBOLS = {
     "bnk_wait": (_i, [_vp, _u64]),
     "bnk_batch_upload": (_i, [_vp, _u32]),
     "bnk_batch_download": (_i, [_vp, _u32]),
+    "bnk_assign_counters_noalloc": (_i, [_vp, _vp, _vp, _u32, _vp]),
     "bnk_timer_start": (_i, [_vp, C.POINTER(_vp), _u32]),
     "bnk_timer_stop": (_i, [_vp, C.POINTER(_vp), _u32, C.POINTER(C.c_float)]),
     "bnk_batch_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),

@@ -307,3 +307,103 @@ cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, b
     b->ctx->launches += 3;
     return cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------
+// Send-counter hand-out for callers that must not allocate.
+//
+// The packet loop of a forwarder cannot afford cudaMalloc/cudaFree: both serialise the
+// whole device, so one allocation stalls every other batch in flight, and a caller that
+// keeps packets in device buffers of its own (for instance buffers a NIC writes into
+// directly) has no bnk_batch whose creation would have set the grouping scratch aside.
+// For those callers the same grouping kernels run here on a fixed scratch area that is
+// part of the library image: kNoAllocMaxPkts packets at most, 384 KiB held by every GPU
+// that loads the library until the process exits.
+//
+// The area is shared by every call and keeps whatever the previous call left in it.  All
+// regions are written before they are read within one call (the histogram kernel stores
+// every bin of every chunk it later scans, the scatter and segment kernels store every
+// element below npkts), so nothing needs clearing; calls that overlap on the GPU race on
+// the area and must be ordered by the caller (same stream, or an event between them).
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr uint32_t kNoAllocMaxPkts = BNK_NOALLOC_MAX_PKTS;
+constexpr uint32_t kNoAllocChunks = (kNoAllocMaxPkts + kChunk - 1) / kChunk;
+constexpr size_t kNoAllocWords = (size_t)5 * kNoAllocMaxPkts + (size_t)kMaxBins * kNoAllocChunks;
+
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocWords];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mu;
+uint32_t *g_noalloc_ptr[kNoAllocMaxDevices] = {};
+
+// Device address of the scratch area on the current device.  In host code the array's name
+// is only a handle, so the address is asked for once per device and remembered.
+cudaError_t noalloc_scratch(int device, uint32_t **out) {
+    std::lock_guard<std::mutex> g(g_noalloc_mu);
+    if (!g_noalloc_ptr[device]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        g_noalloc_ptr[device] = static_cast<uint32_t *>(p);
+    }
+    *out = g_noalloc_ptr[device];
+    return cudaSuccess;
+}
+
+int noalloc_fail(bnk_ctx *ctx, int code, const char *what, cudaError_t e = cudaSuccess) {
+    std::lock_guard<std::mutex> g(ctx->mu);
+    ctx->last_error = what;
+    if (e != cudaSuccess) {
+        ctx->last_error += ": ";
+        ctx->last_error += cudaGetErrorString(e);
+    }
+    return code;
+}
+
+} // namespace
+
+extern "C" int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uint32_t *dev_slot, uint32_t npkts,
+                                           uint64_t *dev_counter) {
+    if (!ctx) return BNK_EINVAL;
+    if (!dev_slot || !dev_counter) return noalloc_fail(ctx, BNK_EINVAL, "bnk_assign_counters_noalloc: null buffer");
+    if (npkts > kNoAllocMaxPkts)
+        return noalloc_fail(ctx, BNK_EINVAL,
+                            "bnk_assign_counters_noalloc: npkts exceeds BNK_NOALLOC_MAX_PKTS (16384); split the batch "
+                            "or use bnk_seal_submit with BNK_F_ASSIGN_COUNTERS");
+    if (ctx->device < 0 || ctx->device >= kNoAllocMaxDevices)
+        return noalloc_fail(ctx, BNK_EINVAL, "bnk_assign_counters_noalloc: device ordinal above 63");
+    if (npkts == 0) return BNK_SUCCESS;
+    cudaError_t e = cudaSetDevice(ctx->device);
+    if (e != cudaSuccess) return noalloc_fail(ctx, BNK_ECUDA, "cudaSetDevice", e);
+    uint32_t *base = nullptr;
+    if ((e = noalloc_scratch(ctx->device, &base)) != cudaSuccess)
+        return noalloc_fail(ctx, BNK_ECUDA, "cudaGetSymbolAddress(scratch)", e);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    const uint32_t n = npkts, cap = kNoAllocMaxPkts;
+    uint32_t *keys_a = base, *keys_b = base + cap, *vals_a = base + 2 * cap, *order = base + 3 * cap;
+    uint32_t *head = base + 4 * cap, *hist = base + 5 * cap;
+    const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
+    const uint32_t bins = 1u << plan.digit_bits;
+    const uint32_t chunks = (n + kChunk - 1) / kChunk;
+    SortKeySrc src{dev_slot, nullptr, ctx->cfg.max_keypairs, 0};
+    uint32_t *kbuf[2] = {keys_b, keys_a};
+    uint32_t *vbuf[2] = {order, vals_a};
+    const uint32_t *kin = nullptr, *vin = nullptr;
+    for (uint32_t p = 0; p < plan.passes; p++) {
+        const uint32_t shift = p * plan.digit_bits;
+        const uint32_t o = (plan.passes - 1 - p) & 1u;
+        radix_hist_kernel<<<chunks, 32, 0, s>>>(src, kin, n, shift, bins, chunks, hist);
+        exclusive_scan_kernel<<<1, 1024, 0, s>>>(hist, bins * chunks);
+        radix_scatter_kernel<<<chunks, 32, 0, s>>>(src, kin, vin, n, shift, bins, chunks, hist, kbuf[o], vbuf[o]);
+        kin = kbuf[o];
+        vin = vbuf[o];
+    }
+    seg_head_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, n, head);
+    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, order, head, n, ctx->cfg.max_keypairs,
+                                                          ctx->kt.send_counter, dev_counter);
+    ctx->launches += 3 * plan.passes + 2;
+    if ((e = cudaGetLastError()) != cudaSuccess) return noalloc_fail(ctx, BNK_ECUDA, "kernel launch", e);
+    return BNK_SUCCESS;
+}

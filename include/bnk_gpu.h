@@ -177,6 +177,31 @@ int bnk_wait(bnk_batch *b, uint64_t timeout_ns);
 int bnk_batch_upload(bnk_batch *b, uint32_t npkts);
 int bnk_batch_download(bnk_batch *b, uint32_t npkts);
 
+/* ---- for callers that must not allocate ----
+ * No counterpart in the reference.  A packet loop cannot call cudaMalloc or cudaFree (either one
+ * stalls every stream of the device), and a caller that keeps packets in device buffers of its own,
+ * such as buffers a NIC writes into directly, has no bnk_batch to lend it grouping scratch.  This
+ * entry point does the send-counter stage of bnk_seal_submit(BNK_F_ASSIGN_COUNTERS) on the caller's
+ * buffers and allocates nothing: its scratch is a fixed 384 KiB area inside the library image,
+ * present on every GPU that loads the library, which limits a call to BNK_NOALLOC_MAX_PKTS packets
+ * (more is refused with BNK_EINVAL).
+ *   dev_slot[i]    (device memory, in)  keypair slot of packet i
+ *   dev_counter[i] (device memory, out) the nonce handed to packet i: packets of one slot get
+ *                  consecutive values in batch order and the slot's send counter moves past them,
+ *                  saturating at BNK_REJECT_AFTER_MESSAGES; packets whose slot is not below
+ *                  max_keypairs are left untouched
+ *   stream         a cudaStream_t of ctx's device, or NULL for the default stream; the work is
+ *                  queued on it and the call returns without waiting.
+ * The first call on each device looks up the address of the scratch area (the device must be usable
+ * at that moment); make that first call before any stream capture begins.  The scratch is shared by
+ * all calls and keeps the previous call's contents; each call overwrites what it reads, so nothing
+ * has to be cleared, but two calls whose work overlaps on the GPU would corrupt each other: order
+ * them on one stream or with an event.  The same holds against batches in flight that hand out
+ * counters for the same keypair slots. */
+#define BNK_NOALLOC_MAX_PKTS 16384u
+int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uint32_t *dev_slot, uint32_t npkts,
+                                uint64_t *dev_counter);
+
 /* ---- measurement helpers (CUDA events on the batches' own streams) ----
  * bnk_timer_start records a start event on batches[0]'s stream and makes the other batches' streams
  * wait for it; bnk_timer_stop records an end event on every batch, waits, and returns the longest
