@@ -120,7 +120,8 @@ class BnkError(RuntimeError):
 
 
 def lib_path() -> str:
-    return _build.LIB_PATH
+    """Path of the shared library; BNK_B200_LIB points at another build of the same ABI."""
+    return os.environ.get("BNK_B200_LIB") or _build.LIB_PATH
 
 
 def lib() -> C.CDLL:

@@ -302,7 +302,6 @@ int bnk_batch_destroy(bnk_batch *b) {
     cudaFree(d.order_tmp);
     cudaFree(d.keys_tmp);
     cudaFree(d.hist);
-    cudaFree(d.seg_head);
     cudaFree(d.len_order);
     cudaFree(d.counters32);
     if (b->done) cudaEventDestroy(b->done);
@@ -358,8 +357,7 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     D((void **)&d.order, n * 4);
     D((void **)&d.order_tmp, n * 4);
     D((void **)&d.keys_tmp, 2 * n * 4);
-    D((void **)&d.hist, (size_t)2048 * group_sort_chunks(max_pkts) * 4);
-    D((void **)&d.seg_head, n * 4);
+    D((void **)&d.hist, (size_t)512 * group_sort_chunks(max_pkts) * 4);
     D((void **)&d.len_order, n * 4);
     D((void **)&d.counters32, 2048 * 4);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking);
@@ -445,7 +443,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         order = b->dev.len_order;
     }
     CK(ctx, cudaEventRecord(b->a_begin, s));
-    CK(ctx, launch_seal(aead_args(b, npkts, false, order), s, &ctx->launches));
+    CK(ctx, launch_seal(aead_args(b, npkts, false, order), s, ctx));
     CK(ctx, cudaEventRecord(b->a_end, s));
     CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = true;
@@ -483,7 +481,7 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     }
     oa.order = order;
     CK(ctx, cudaEventRecord(b->a_begin, s));
-    CK(ctx, launch_open(oa, s, &ctx->launches));
+    CK(ctx, launch_open(oa, s, ctx));
     CK(ctx, cudaEventRecord(b->a_end, s));
     b->aead_timed = true;
     if (flags & BNK_F_REPLAY) CK(ctx, launch_replay(b, npkts, s));

@@ -65,8 +65,7 @@ struct DeviceBatch {
     uint32_t *order;      // [max_pkts] packet indices, stable by slot
     uint32_t *order_tmp;  // [max_pkts]
     uint32_t *keys_tmp;   // [2][max_pkts] radix keys ping-pong
-    uint32_t *hist;       // [256 * chunks]
-    uint32_t *seg_head;   // [max_pkts] 1 where a new slot segment starts in `order`
+    uint32_t *hist;       // [512 * chunks] digit-major histograms
     uint32_t *len_order;  // [max_pkts] packet indices ordered by length class
     uint32_t *counters32; // small scratch (bins)
 };
@@ -105,8 +104,8 @@ struct AeadArgs {
     uint32_t max_slots;
     uint64_t ring_bytes;
 };
-cudaError_t launch_seal(const AeadArgs &a, cudaStream_t s, std::atomic<uint64_t> *launches);
-cudaError_t launch_open(const AeadArgs &a, cudaStream_t s, std::atomic<uint64_t> *launches);
+cudaError_t launch_seal(const AeadArgs &a, cudaStream_t s, bnk_ctx *ctx);
+cudaError_t launch_open(const AeadArgs &a, cudaStream_t s, bnk_ctx *ctx);
 
 // group_kernels.cu
 cudaError_t launch_group_by_slot(bnk_batch *b, uint32_t n, bool only_status_ok, cudaStream_t s);

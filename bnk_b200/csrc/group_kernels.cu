@@ -12,8 +12,12 @@
 
 namespace {
 
-constexpr uint32_t kChunk = 2048;   // elements ranked by one warp
-constexpr uint32_t kMaxDigitBits = 11;
+constexpr uint32_t kSortThreads = 256;                  // 8 warps per CTA
+constexpr uint32_t kSortWarps = kSortThreads / 32;
+constexpr uint32_t kTilesPerWarp = 32;                  // a lane keeps 32 keys in registers
+constexpr uint32_t kWarpSpan = 32 * kTilesPerWarp;      // 1024 consecutive elements per warp
+constexpr uint32_t kChunk = kSortWarps * kWarpSpan;     // 8192 elements per CTA
+constexpr uint32_t kMaxDigitBits = 9;
 constexpr uint32_t kMaxBins = 1u << kMaxDigitBits;
 
 struct SortKeySrc {
@@ -34,23 +38,32 @@ __device__ __forceinline__ uint32_t slot_key(const SortKeySrc &k, uint32_t i) {
     return s;
 }
 
+// one shared-memory add per distinct digit in the warp instead of one per lane
+__device__ __forceinline__ void warp_hist_add(uint32_t *cnt, uint32_t digit, bool have) {
+    const uint32_t peers = __match_any_sync(0xffffffffu, have ? digit : 0xffffffffu);
+    if (have && (__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&cnt[digit], __popc(peers));
+}
+
 // --- pass step 1: per-chunk digit histogram -------------------------------------------
-// grid = chunks, block = 32.  hist is digit-major: hist[digit * chunks + chunk].
-__global__ void __launch_bounds__(32) radix_hist_kernel(SortKeySrc src, const uint32_t *keys_in, uint32_t n,
-                                                        uint32_t shift, uint32_t bins, uint32_t chunks,
-                                                        uint32_t *hist) {
+// grid = chunks, block = 256.  hist is digit-major: hist[digit * chunks + chunk].
+__global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(SortKeySrc src, const uint32_t *keys_in,
+                                                                  uint32_t n, uint32_t shift, uint32_t bins,
+                                                                  uint32_t chunks, uint32_t *hist) {
     __shared__ uint32_t cnt[kMaxBins];
-    const uint32_t lane = threadIdx.x, chunk = blockIdx.x;
-    for (uint32_t d = lane; d < bins; d += 32) cnt[d] = 0;
-    __syncwarp();
+    const uint32_t tid = threadIdx.x, chunk = blockIdx.x;
+    for (uint32_t d = tid; d < bins; d += kSortThreads) cnt[d] = 0;
+    __syncthreads();
     const uint32_t begin = chunk * kChunk;
     const uint32_t end = min(n, begin + kChunk);
-    for (uint32_t i = begin + lane; i < end; i += 32) {
-        const uint32_t key = keys_in ? keys_in[i] : slot_key(src, i);
-        atomicAdd(&cnt[(key >> shift) & (bins - 1)], 1u);
+    for (uint32_t base = begin; base < end; base += kSortThreads) { // uniform trip count per warp
+        const uint32_t i = base + tid;
+        const bool have = i < end;
+        uint32_t digit = 0;
+        if (have) digit = ((keys_in ? keys_in[i] : slot_key(src, i)) >> shift) & (bins - 1);
+        warp_hist_add(cnt, digit, have);
     }
-    __syncwarp();
-    for (uint32_t d = lane; d < bins; d += 32) hist[d * chunks + chunk] = cnt[d];
+    __syncthreads();
+    for (uint32_t d = tid; d < bins; d += kSortThreads) hist[d * chunks + chunk] = cnt[d];
 }
 
 // --- pass step 2: exclusive scan of the histogram (single CTA) -------------------------
@@ -100,48 +113,61 @@ __global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t *data, ui
 }
 
 // --- pass step 3: stable scatter --------------------------------------------------------
-// grid = chunks, block = 32.  Each warp walks its chunk in order, 32 elements at a time;
-// lanes holding the same digit find each other with match_any and take consecutive
-// positions, so equal digits keep their input order.
-__global__ void __launch_bounds__(32) radix_scatter_kernel(SortKeySrc src, const uint32_t *keys_in,
-                                                           const uint32_t *vals_in, uint32_t n, uint32_t shift,
-                                                           uint32_t bins, uint32_t chunks, const uint32_t *hist,
-                                                           uint32_t *keys_out, uint32_t *vals_out) {
-    __shared__ uint32_t cur[kMaxBins];
-    const uint32_t lane = threadIdx.x, chunk = blockIdx.x;
-    for (uint32_t d = lane; d < bins; d += 32) cur[d] = hist[d * chunks + chunk];
-    __syncwarp();
-    const uint32_t begin = chunk * kChunk;
-    const uint32_t end = min(n, begin + kChunk);
-    const uint32_t lt = (1u << lane) - 1u;
-    for (uint32_t base = begin; base < end; base += 32) {
-        const uint32_t i = base + lane;
+// grid = chunks, block = 256.  Warp w owns the 1024 consecutive elements [w*1024, (w+1)*1024) of
+// the chunk and keeps their keys in registers.  (A) every warp counts its digits, (B) the counts
+// become start positions: global start of the digit for this chunk, plus the counts of the warps
+// before, (C) every warp walks its elements in order, 32 at a time; lanes holding the same digit
+// find each other with match_any and take consecutive positions, so equal digits keep their
+// input order.  No per-element atomics on global memory.
+__global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(SortKeySrc src, const uint32_t *keys_in,
+                                                                     const uint32_t *vals_in, uint32_t n,
+                                                                     uint32_t shift, uint32_t bins, uint32_t chunks,
+                                                                     const uint32_t *hist, uint32_t *keys_out,
+                                                                     uint32_t *vals_out) {
+    __shared__ uint32_t cur[kSortWarps][kMaxBins];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, chunk = blockIdx.x;
+    for (uint32_t d = tid; d < kSortWarps * kMaxBins; d += kSortThreads) (&cur[0][0])[d] = 0;
+    __syncthreads();
+    const uint32_t begin = chunk * kChunk + warp * kWarpSpan;
+    const uint32_t end = min(n, chunk * kChunk + kChunk);
+    uint32_t key[kTilesPerWarp];
+#pragma unroll
+    for (uint32_t t = 0; t < kTilesPerWarp; t++) {
+        const uint32_t i = begin + t * 32 + lane;
         const bool have = i < end;
-        uint32_t key = 0, val = 0, digit = 0xffffffffu;
-        if (have) {
-            key = keys_in ? keys_in[i] : slot_key(src, i);
-            val = vals_in ? vals_in[i] : i;
-            digit = (key >> shift) & (bins - 1);
+        key[t] = have ? (keys_in ? keys_in[i] : slot_key(src, i)) : 0xffffffffu;
+        warp_hist_add(cur[warp], (key[t] >> shift) & (bins - 1), have);
+    }
+    __syncthreads();
+    for (uint32_t d = tid; d < bins; d += kSortThreads) {
+        uint32_t run = hist[d * chunks + chunk];
+#pragma unroll
+        for (uint32_t w = 0; w < kSortWarps; w++) {
+            const uint32_t c = cur[w][d];
+            cur[w][d] = run;
+            run += c;
         }
+    }
+    __syncthreads();
+    const uint32_t lt = (1u << lane) - 1u;
+    uint32_t *mine = cur[warp];
+#pragma unroll
+    for (uint32_t t = 0; t < kTilesPerWarp; t++) {
+        const uint32_t i = begin + t * 32 + lane;
+        const bool have = i < end;
+        const uint32_t digit = have ? ((key[t] >> shift) & (bins - 1)) : 0xffffffffu;
         const uint32_t peers = __match_any_sync(0xffffffffu, digit);
         const uint32_t rank = __popc(peers & lt);
         uint32_t pos = 0;
-        if (have) pos = cur[digit] + rank;
+        if (have) pos = mine[digit] + rank;
         __syncwarp();
-        if (have && rank == 0) cur[digit] += __popc(peers);
+        if (have && rank == 0) mine[digit] += __popc(peers);
         __syncwarp();
         if (have) {
-            keys_out[pos] = key;
-            vals_out[pos] = val;
+            keys_out[pos] = key[t];
+            vals_out[pos] = vals_in ? vals_in[i] : i;
         }
     }
-}
-
-// 1 where a run of equal keys starts
-__global__ void seg_head_kernel(const uint32_t *keys, uint32_t n, uint32_t *head) {
-    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n) return;
-    head[j] = (j == 0 || keys[j] != keys[j - 1]) ? 1u : 0u;
 }
 
 // --- send counters ----------------------------------------------------------------------
@@ -152,8 +178,9 @@ __global__ void assign_counters_kernel(const uint32_t *keys, const uint32_t *ord
                                        uint32_t n, uint32_t max_slots, uint64_t *send_counter,
                                        uint64_t *counter_out) {
     const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n || !head[j]) return;
+    if (j >= n) return;
     const uint32_t slot = keys[j];
+    if (head ? !head[j] : (j != 0 && keys[j - 1] == slot)) return; // only the first packet of a run walks it
     if (slot >= max_slots) return;
     const uint64_t base = send_counter[slot];
     uint32_t k = j;
@@ -173,8 +200,9 @@ __global__ void replay_kernel(const uint32_t *keys, const uint32_t *order, const
                               uint32_t max_slots, uint32_t ring_blocks, uint64_t *replay_last,
                               uint64_t *replay_ring, const uint64_t *counter, uint8_t *status) {
     const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n || !head[j]) return;
+    if (j >= n) return;
     const uint32_t slot = keys[j];
+    if (head ? !head[j] : (j != 0 && keys[j - 1] == slot)) return;
     if (slot >= max_slots) return;
     uint64_t *ring = replay_ring + (size_t)slot * ring_blocks;
     const uint64_t mask = ring_blocks - 1;
@@ -216,14 +244,28 @@ __device__ __forceinline__ uint32_t len_bin(uint32_t len, bool open_side) {
     uint32_t blocks = (body + 63u) >> 6;
     return blocks > kLenBins - 1 ? kLenBins - 1 : blocks;
 }
-__global__ void len_hist_kernel(const uint32_t *len, uint32_t n, int open_side, uint32_t *bins) {
+// Real traffic has a handful of sizes, so all lanes of a warp tend to hit the same few bins: lanes
+// with equal bins elect a leader that does one atomic for the group.
+__global__ void __launch_bounds__(256) len_hist_kernel(const uint32_t *len, uint32_t n, int open_side,
+                                                       uint32_t *bins) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) atomicAdd(&bins[len_bin(len[i], open_side)], 1u);
+    const bool have = i < n;
+    const uint32_t bin = have ? len_bin(len[i], open_side) : 0xffffffffu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+    if (have && (__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&bins[bin], __popc(peers));
 }
-__global__ void len_scatter_kernel(const uint32_t *len, uint32_t n, int open_side, uint32_t *bins,
-                                   uint32_t *order) {
+__global__ void __launch_bounds__(256) len_scatter_kernel(const uint32_t *len, uint32_t n, int open_side,
+                                                          uint32_t *bins, uint32_t *order) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) order[atomicAdd(&bins[len_bin(len[i], open_side)], 1u)] = i;
+    const uint32_t lane = threadIdx.x & 31;
+    const bool have = i < n;
+    const uint32_t bin = have ? len_bin(len[i], open_side) : 0xffffffffu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+    const int leader = __ffs(peers) - 1;
+    uint32_t base = 0;
+    if (have && leader == (int)lane) base = atomicAdd(&bins[bin], __popc(peers));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (have) order[base + __popc(peers & ((1u << lane) - 1u))] = i;
 }
 
 struct SortPlan {
@@ -243,7 +285,7 @@ SortPlan plan_for(uint32_t max_slots) {
 uint32_t group_sort_chunks(uint32_t max_pkts) { return (max_pkts + kChunk - 1) / kChunk; }
 
 // Sorts packet indices 0..n-1 by keypair slot, stable.  Leaves the sorted keys in
-// dev.keys_tmp (second half), the packet indices in dev.order and run starts in dev.seg_head.
+// dev.keys_tmp (second half) and the packet indices in dev.order.
 cudaError_t launch_group_by_slot(bnk_batch *b, uint32_t n, bool only_status_ok, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     bnk_ctx *ctx = b->ctx;
@@ -259,15 +301,14 @@ cudaError_t launch_group_by_slot(bnk_batch *b, uint32_t n, bool only_status_ok, 
     for (uint32_t p = 0; p < plan.passes; p++) {
         const uint32_t shift = p * plan.digit_bits;
         const uint32_t o = (plan.passes - 1 - p) & 1u;
-        radix_hist_kernel<<<chunks, 32, 0, s>>>(src, kin, n, shift, bins, chunks, d.hist);
+        radix_hist_kernel<<<chunks, kSortThreads, 0, s>>>(src, kin, n, shift, bins, chunks, d.hist);
         exclusive_scan_kernel<<<1, 1024, 0, s>>>(d.hist, bins * chunks);
-        radix_scatter_kernel<<<chunks, 32, 0, s>>>(src, kin, vin, n, shift, bins, chunks, d.hist, kbuf[o], vbuf[o]);
+        radix_scatter_kernel<<<chunks, kSortThreads, 0, s>>>(src, kin, vin, n, shift, bins, chunks, d.hist, kbuf[o],
+                                                            vbuf[o]);
         ctx->launches += 3;
         kin = kbuf[o];
         vin = vbuf[o];
     }
-    seg_head_kernel<<<(n + 255) / 256, 256, 0, s>>>(kbuf[0], n, d.seg_head);
-    ctx->launches += 1;
     return cudaGetLastError();
 }
 
@@ -276,7 +317,7 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
     cudaError_t e = launch_group_by_slot(b, n, false, s);
     if (e != cudaSuccess) return e;
     DeviceBatch &d = b->dev;
-    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, d.seg_head, n,
+    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, nullptr, n,
                                                           b->ctx->cfg.max_keypairs, b->ctx->kt.send_counter,
                                                           d.counter);
     b->ctx->launches += 1;
@@ -289,7 +330,7 @@ cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     DeviceBatch &d = b->dev;
     bnk_ctx *ctx = b->ctx;
-    replay_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, d.seg_head, n,
+    replay_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, nullptr, n,
                                                  ctx->cfg.max_keypairs, ctx->cfg.replay_ring_blocks,
                                                  ctx->kt.replay_last, ctx->kt.replay_ring, d.counter, d.status);
     ctx->launches += 1;
@@ -321,15 +362,16 @@ cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, b
 //
 // The area is shared by every call and keeps whatever the previous call left in it.  All
 // regions are written before they are read within one call (the histogram kernel stores
-// every bin of every chunk it later scans, the scatter and segment kernels store every
-// element below npkts), so nothing needs clearing; calls that overlap on the GPU race on
+// every bin of every chunk it later scans, the scatter kernel stores every element below
+// npkts), so nothing needs clearing; calls that overlap on the GPU race on
 // the area and must be ordered by the caller (same stream, or an event between them).
 // ---------------------------------------------------------------------------------------
 namespace {
 
 constexpr uint32_t kNoAllocMaxPkts = BNK_NOALLOC_MAX_PKTS;
 constexpr uint32_t kNoAllocChunks = (kNoAllocMaxPkts + kChunk - 1) / kChunk;
-constexpr size_t kNoAllocWords = (size_t)5 * kNoAllocMaxPkts + (size_t)kMaxBins * kNoAllocChunks;
+constexpr size_t kNoAllocWords = (size_t)5 * kNoAllocMaxPkts + 16384; // 384 KiB; the histogram needs kMaxBins * kNoAllocChunks words
+static_assert((size_t)kMaxBins * kNoAllocChunks <= 16384, "histogram region too small");
 
 static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocWords];
 
@@ -383,7 +425,7 @@ extern "C" int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uin
 
     const uint32_t n = npkts, cap = kNoAllocMaxPkts;
     uint32_t *keys_a = base, *keys_b = base + cap, *vals_a = base + 2 * cap, *order = base + 3 * cap;
-    uint32_t *head = base + 4 * cap, *hist = base + 5 * cap;
+    uint32_t *hist = base + 5 * cap; // [4*cap, 5*cap) is spare
     const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
     const uint32_t bins = 1u << plan.digit_bits;
     const uint32_t chunks = (n + kChunk - 1) / kChunk;
@@ -394,16 +436,15 @@ extern "C" int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uin
     for (uint32_t p = 0; p < plan.passes; p++) {
         const uint32_t shift = p * plan.digit_bits;
         const uint32_t o = (plan.passes - 1 - p) & 1u;
-        radix_hist_kernel<<<chunks, 32, 0, s>>>(src, kin, n, shift, bins, chunks, hist);
+        radix_hist_kernel<<<chunks, kSortThreads, 0, s>>>(src, kin, n, shift, bins, chunks, hist);
         exclusive_scan_kernel<<<1, 1024, 0, s>>>(hist, bins * chunks);
-        radix_scatter_kernel<<<chunks, 32, 0, s>>>(src, kin, vin, n, shift, bins, chunks, hist, kbuf[o], vbuf[o]);
+        radix_scatter_kernel<<<chunks, kSortThreads, 0, s>>>(src, kin, vin, n, shift, bins, chunks, hist, kbuf[o], vbuf[o]);
         kin = kbuf[o];
         vin = vbuf[o];
     }
-    seg_head_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, n, head);
-    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, order, head, n, ctx->cfg.max_keypairs,
+    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, order, nullptr, n, ctx->cfg.max_keypairs,
                                                           ctx->kt.send_counter, dev_counter);
-    ctx->launches += 3 * plan.passes + 2;
+    ctx->launches += 3 * plan.passes + 1;
     if ((e = cudaGetLastError()) != cudaSuccess) return noalloc_fail(ctx, BNK_ECUDA, "kernel launch", e);
     return BNK_SUCCESS;
 }
