@@ -432,7 +432,7 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = host_threads()
         sample_n = 1 << 18
-        passes = 2
+        passes = 6
         gbps, secs = cpu_seal_open(threads, sample_n, passes)
         cpu = {"value": gbps, "unit": "Gbit/s", "cores": threads, "kind": "port",
                "sample": f"{sample_n} packets x {SIZE} B sealed then opened, {passes} passes ({secs:.2f} s)",

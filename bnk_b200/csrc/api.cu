@@ -310,6 +310,9 @@ int bnk_batch_destroy(bnk_batch *b) {
     if (b->a_begin) cudaEventDestroy(b->a_begin);
     if (b->a_end) cudaEventDestroy(b->a_end);
     if (b->t_end) cudaEventDestroy(b->t_end);
+    if (b->ev_fork) cudaEventDestroy(b->ev_fork);
+    if (b->ev_join) cudaEventDestroy(b->ev_join);
+    if (b->aux_stream) cudaStreamDestroy(b->aux_stream);
     if (b->stream) cudaStreamDestroy(b->stream);
     delete b;
     return BNK_SUCCESS;
@@ -361,6 +364,9 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     D((void **)&d.len_order, n * 4);
     D((void **)&d.counters32, 2048 * 4);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->aux_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_join, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->done, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreate(&b->k_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&b->k_end);
@@ -480,11 +486,21 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         order = b->dev.len_order;
     }
     oa.order = order;
+    if (flags & BNK_F_REPLAY) {
+        // grouping by keypair needs only the descriptors: it runs on the side stream beside the open kernel
+        CK(ctx, cudaEventRecord(b->ev_fork, s));
+        CK(ctx, cudaStreamWaitEvent(b->aux_stream, b->ev_fork, 0));
+        CK(ctx, launch_group_by_slot(b, npkts, false, b->aux_stream));
+        CK(ctx, cudaEventRecord(b->ev_join, b->aux_stream));
+    }
     CK(ctx, cudaEventRecord(b->a_begin, s));
     CK(ctx, launch_open(oa, s, ctx));
     CK(ctx, cudaEventRecord(b->a_end, s));
     b->aead_timed = true;
-    if (flags & BNK_F_REPLAY) CK(ctx, launch_replay(b, npkts, s));
+    if (flags & BNK_F_REPLAY) {
+        CK(ctx, cudaStreamWaitEvent(s, b->ev_join, 0));
+        CK(ctx, launch_replay(b, npkts, s));
+    }
     if (flags & BNK_F_CHECK_INBOUND) CK(ctx, launch_filter_check(b, npkts, now_unix_ns, true, s));
     CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = true;

@@ -77,6 +77,8 @@ struct bnk_batch {
     bnk_batch_view host; // pinned
     DeviceBatch dev;
     cudaStream_t stream;
+    cudaStream_t aux_stream;   // grouping work that can run beside the open kernel
+    cudaEvent_t ev_fork, ev_join;
     cudaEvent_t done, k_begin, k_end, t_end, a_begin, a_end;
     bool in_flight;
     bool kernel_timed;

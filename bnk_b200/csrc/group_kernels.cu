@@ -195,7 +195,8 @@ __global__ void assign_counters_kernel(const uint32_t *keys, const uint32_t *ord
 }
 
 // --- anti-replay window, RFC 6479 -------------------------------------------------------
-// One thread per slot segment walks the slot's authenticated packets in arrival order.
+// One thread per slot segment walks the slot's packets in arrival order; only packets the open
+// kernel authenticated (status OK or KEEPALIVE) reach the window, the others are stepped over.
 __global__ void replay_kernel(const uint32_t *keys, const uint32_t *order, const uint32_t *head, uint32_t n,
                               uint32_t max_slots, uint32_t ring_blocks, uint64_t *replay_last,
                               uint64_t *replay_ring, const uint64_t *counter, uint8_t *status) {
@@ -210,6 +211,8 @@ __global__ void replay_kernel(const uint32_t *keys, const uint32_t *order, const
     uint64_t last = replay_last[slot];
     for (uint32_t k = j; k < n && keys[k] == slot; k++) {
         const uint32_t pkt = order[k];
+        const uint8_t st = status[pkt];
+        if (st != BNK_PKT_OK && st != BNK_PKT_KEEPALIVE) continue;
         const uint64_t c = counter[pkt];
         bool ok = c < BNK_REJECT_AFTER_MESSAGES;
         if (ok) {
@@ -324,10 +327,9 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+// Expects launch_group_by_slot(b, n, false, ...) to have completed before this point of stream s.
 cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    cudaError_t e = launch_group_by_slot(b, n, true, s);
-    if (e != cudaSuccess) return e;
     DeviceBatch &d = b->dev;
     bnk_ctx *ctx = b->ctx;
     replay_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, nullptr, n,
