@@ -22,13 +22,17 @@ NVCC_FLAGS = [
 ]
 
 
+HOST = os.path.join(PKG_DIR, "host")
+
+
 def sources() -> list[str]:
-    return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    """CUDA kernels + C ABI, and the C++ host mirror of the reference's interfaces."""
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu"))) + sorted(glob.glob(os.path.join(HOST, "*.cpp")))
 
 
 def _deps() -> list[str]:
     inc = os.path.join(os.path.dirname(PKG_DIR), "include", "bnk_gpu.h")
-    return sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [inc]
+    return sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(HOST, "*.hpp")) + [inc]
 
 
 def is_stale() -> bool:
@@ -59,6 +63,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         print(res.stderr)
     return LIB_PATH
+
+
+def build_host_test(force: bool = False) -> str:
+    """Compiles tests/cpp/host_test.cpp (the reference's Go tests restated in C++) against libbnkgpu.so."""
+    root = os.path.dirname(PKG_DIR)
+    src = os.path.join(root, "tests", "cpp", "host_test.cpp")
+    exe = os.path.join(root, "tests", "cpp", "host_test")
+    build()
+    deps = [src, LIB_PATH, os.path.join(HOST, "bnk_host.hpp")]
+    if not force and os.path.exists(exe) and all(os.path.getmtime(d) <= os.path.getmtime(exe) for d in deps):
+        return exe
+    cxx = shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-Wall", "-o", exe, src, "-L" + PKG_DIR, "-lbnkgpu",
+           "-Wl,-rpath," + PKG_DIR, "-Wl,-rpath,$ORIGIN/../../bnk_b200"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    return exe
 
 
 if __name__ == "__main__":

@@ -13,6 +13,7 @@ from . import _build
 SUCCESS, EINVAL, ENOMEM, ECUDA, ETIMEDOUT, EBUSY, EFULL = 0, -1, -2, -3, -4, -5, -6
 
 PKT_OK, PKT_AUTH_FAIL, PKT_REPLAY, PKT_FILTER_DENY, PKT_MALFORMED, PKT_KEEPALIVE, PKT_COUNTER_EXHAUSTED, PKT_BAD_DESC = range(8)
+PKT_NO_KEYPAIR, PKT_BAD_INNER = 8, 9
 
 F_NO_H2D = 1 << 0
 F_NO_D2H = 1 << 1
@@ -22,6 +23,8 @@ F_REPLAY = 1 << 4
 F_CHECK_INBOUND = 1 << 5
 F_SORT_BY_LENGTH = 1 << 6
 F_USE_OUT_LEN = 1 << 7
+F_DEMUX_INDEX = 1 << 8
+F_INNER_CHECK = 1 << 9
 
 WG_HEADER = 16
 WG_TAG = 16
@@ -84,6 +87,9 @@ SYMBOLS = {
     "bnk_keypair_clear": (_i, [_vp, _u32]),
     "bnk_send_counter_get": (_i, [_vp, _u32, C.POINTER(_u64)]),
     "bnk_send_counter_set": (_i, [_vp, _u32, _u64]),
+    "bnk_index_set": (_i, [_vp, _u32, _u32]),
+    "bnk_index_clear": (_i, [_vp, _u32]),
+    "bnk_keypair_set_allowed_ip": (_i, [_vp, _u32, _u32]),
     "bnk_replay_export": (_i, [_vp, _u32, C.POINTER(_u64), _vp]),
     "bnk_replay_import": (_i, [_vp, _u32, _u64, _vp]),
     "bnk_acl_set": (_i, [_vp, _i, _vp, _sz]),

@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const Aead
         slot = a.slot[pkt];
         live = true;
         if ((off & 15u) || slot >= a.max_slots) {
-            st = BNK_PKT_BAD_DESC;
+            st = (OPEN && slot == kSlotNoKeypair) ? BNK_PKT_NO_KEYPAIR : BNK_PKT_BAD_DESC;
             live = false;
         } else if (!OPEN) {
             body = wg_padded_len(len, a.mtu);

@@ -160,6 +160,13 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     if ((e = dev_alloc_zero(&ctx->kt.send_counter, k)) != cudaSuccess) return bail("send_counter", e);
     if ((e = dev_alloc_zero(&ctx->kt.replay_last, k)) != cudaSuccess) return bail("replay_last", e);
     if ((e = dev_alloc_zero(&ctx->kt.replay_ring, k * cfg->replay_ring_blocks)) != cudaSuccess) return bail("replay_ring", e);
+    if ((e = dev_alloc_zero(&ctx->kt.allowed_ip, k)) != cudaSuccess) return bail("allowed_ip", e);
+    uint32_t islots = 16;
+    while (islots < 2 * k) islots <<= 1;
+    ctx->kt.index_slots = islots;
+    ctx->index_keys_host.assign(islots, 0);
+    if ((e = dev_alloc_zero(&ctx->kt.index_keys, (size_t)islots)) != cudaSuccess) return bail("index_keys", e);
+    if ((e = dev_alloc_zero(&ctx->kt.index_vals, (size_t)islots)) != cudaSuccess) return bail("index_vals", e);
     if ((e = filter_tables_alloc(ctx)) != cudaSuccess) return bail("filter tables", e);
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return bail("sync", e);
     *out = ctx;
@@ -176,6 +183,9 @@ int bnk_ctx_destroy(bnk_ctx *ctx) {
     cudaFree(ctx->kt.send_counter);
     cudaFree(ctx->kt.replay_last);
     cudaFree(ctx->kt.replay_ring);
+    cudaFree(ctx->kt.allowed_ip);
+    cudaFree(ctx->kt.index_keys);
+    cudaFree(ctx->kt.index_vals);
     filter_tables_free(ctx);
     if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
     if (ctx->admin_stream) cudaStreamDestroy(ctx->admin_stream);
@@ -204,6 +214,7 @@ int bnk_keypair_set_many(bnk_ctx *ctx, uint32_t first_slot, uint32_t n, const ui
     CK(ctx, cudaMemset(ctx->kt.send_counter + first_slot, 0, (size_t)n * 8));
     CK(ctx, cudaMemset(ctx->kt.replay_last + first_slot, 0, (size_t)n * 8));
     CK(ctx, cudaMemset(ctx->kt.replay_ring + (size_t)first_slot * rb, 0, (size_t)n * rb * 8));
+    CK(ctx, cudaMemset(ctx->kt.allowed_ip + first_slot, 0, (size_t)n * 4));
     return BNK_SUCCESS;
 }
 
@@ -229,6 +240,60 @@ int bnk_send_counter_set(bnk_ctx *ctx, uint32_t slot, uint64_t counter) {
     CK(ctx, cudaSetDevice(ctx->device));
     CK(ctx, cudaMemcpy(ctx->kt.send_counter + slot, &counter, 8, cudaMemcpyHostToDevice));
     return BNK_SUCCESS;
+}
+
+int bnk_keypair_set_allowed_ip(bnk_ctx *ctx, uint32_t slot, uint32_t ipv4) {
+    if (!ctx || slot >= ctx->cfg.max_keypairs) return fail(ctx, BNK_EINVAL, "bad slot");
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, cudaMemcpy(ctx->kt.allowed_ip + slot, &ipv4, 4, cudaMemcpyHostToDevice));
+    return BNK_SUCCESS;
+}
+
+// The index table is edited in a host shadow and the touched entry is copied over: updates happen once per
+// handshake, lookups once per packet.
+static int index_update(bnk_ctx *ctx, uint32_t local_index, bool insert, uint32_t slot) {
+    const uint64_t key = (1ull << 32) | local_index, dead = 2ull << 32;
+    std::vector<uint64_t> &keys = ctx->index_keys_host;
+    const uint32_t mask = ctx->kt.index_slots - 1;
+    uint32_t h = index_hash(local_index) & mask;
+    int64_t spare = -1, at = -1;
+    for (uint32_t probe = 0; probe <= mask; probe++) {
+        if (keys[h] == key) {
+            at = h;
+            break;
+        }
+        if (keys[h] == dead && spare < 0) spare = h;
+        if (keys[h] == 0) {
+            if (spare < 0) spare = h;
+            break;
+        }
+        h = (h + 1) & mask;
+    }
+    if (!insert) {
+        if (at < 0) return BNK_SUCCESS;
+        keys[at] = dead;
+        CK(ctx, cudaMemcpy(ctx->kt.index_keys + at, &dead, 8, cudaMemcpyHostToDevice));
+        return BNK_SUCCESS;
+    }
+    if (at < 0) at = spare;
+    if (at < 0) return fail(ctx, BNK_EFULL, "receiver index table full");
+    // value first, then the key that makes the entry visible
+    CK(ctx, cudaMemcpy(ctx->kt.index_vals + at, &slot, 4, cudaMemcpyHostToDevice));
+    keys[at] = key;
+    CK(ctx, cudaMemcpy(ctx->kt.index_keys + at, &key, 8, cudaMemcpyHostToDevice));
+    return BNK_SUCCESS;
+}
+
+int bnk_index_set(bnk_ctx *ctx, uint32_t local_index, uint32_t slot) {
+    if (!ctx || slot >= ctx->cfg.max_keypairs) return fail(ctx, BNK_EINVAL, "bad slot");
+    CK(ctx, cudaSetDevice(ctx->device));
+    return index_update(ctx, local_index, true, slot);
+}
+
+int bnk_index_clear(bnk_ctx *ctx, uint32_t local_index) {
+    if (!ctx) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    return index_update(ctx, local_index, false, 0);
 }
 
 int bnk_replay_export(bnk_ctx *ctx, uint32_t slot, uint64_t *last, uint64_t *ring) {
@@ -475,12 +540,14 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
         CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
         CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, s));
+        if (!(flags & BNK_F_DEMUX_INDEX))
+            CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, s));
     }
     CK(ctx, cudaEventRecord(b->k_begin, s));
     const uint32_t *order = nullptr;
     AeadArgs oa = aead_args(b, npkts, true, nullptr);
     if (flags & BNK_F_USE_OUT_LEN) oa.len = b->dev.out_len;
+    if (flags & BNK_F_DEMUX_INDEX) CK(ctx, launch_demux_index(b, npkts, oa.len, s));
     if (flags & BNK_F_SORT_BY_LENGTH) {
         CK(ctx, launch_length_order(b, npkts, oa.len, true, s));
         order = b->dev.len_order;
@@ -501,10 +568,13 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         CK(ctx, cudaStreamWaitEvent(s, b->ev_join, 0));
         CK(ctx, launch_replay(b, npkts, s));
     }
+    if (flags & BNK_F_INNER_CHECK) CK(ctx, launch_inner_check(b, npkts, s));
     if (flags & BNK_F_CHECK_INBOUND) CK(ctx, launch_filter_check(b, npkts, now_unix_ns, true, s));
     CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = true;
     if (!(flags & BNK_F_NO_D2H) && n) {
+        if (flags & BNK_F_DEMUX_INDEX)
+            CK(ctx, cudaMemcpyAsync(b->host.slot, b->dev.slot, n * 4, cudaMemcpyDeviceToHost, s));
         CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
         CK(ctx, cudaMemcpyAsync(b->host.counter, b->dev.counter, n * 8, cudaMemcpyDeviceToHost, s));
         CK(ctx, cudaMemcpyAsync(b->host.out_len, b->dev.out_len, n * 4, cudaMemcpyDeviceToHost, s));

@@ -8,6 +8,7 @@
 #include <atomic>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/bnk_gpu.h"
 
@@ -23,6 +24,11 @@ struct KeypairTables {
     uint64_t *send_counter; // [max_keypairs] next nonce to hand out
     uint64_t *replay_last;  // [max_keypairs] highest counter accepted
     uint64_t *replay_ring;  // [max_keypairs][ring_blocks] RFC 6479 bitmap ring
+    uint32_t *allowed_ip;   // [max_keypairs] the peer's tunnel address, host order (0 = none)
+    // receiver index -> slot: open addressing, key = 1<<32 | index (0 = empty, 2<<32 = deleted)
+    uint64_t *index_keys;   // [index_slots]
+    uint32_t *index_vals;   // [index_slots]
+    uint32_t index_slots;   // power of two
 };
 
 // Flattened, indexed ACL and the reply-flow table (filter_kernels.cu).
@@ -54,6 +60,7 @@ struct bnk_ctx {
     std::atomic<uint64_t> launches;
     std::mutex mu;
     std::string last_error;
+    std::vector<uint64_t> index_keys_host; // host shadow of kt.index_keys (updates are rare: one per handshake)
 };
 
 struct DeviceBatch {
@@ -123,6 +130,17 @@ cudaError_t filter_tables_alloc(bnk_ctx *ctx);
 void filter_tables_free(bnk_ctx *ctx);
 int filter_acl_upload(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n);
 cudaError_t filter_flows_clear(bnk_ctx *ctx, cudaStream_t s);
+
+// inner_kernels.cu
+constexpr uint32_t kSlotNoKeypair = 0xfffffffeu; // demux found no keypair for the receiver index
+cudaError_t launch_demux_index(bnk_batch *b, uint32_t n, const uint32_t *len, cudaStream_t s);
+cudaError_t launch_inner_check(bnk_batch *b, uint32_t n, cudaStream_t s);
+__host__ __device__ inline uint32_t index_hash(uint32_t index) {
+    uint32_t z = index * 0x9e3779b1u;
+    z ^= z >> 15;
+    z *= 0x85ebca6bu;
+    return z ^ (z >> 13);
+}
 
 // probe_kernels.cu
 cudaError_t launch_fill_random(uint8_t *dst, uint64_t bytes, uint64_t seed, cudaStream_t s,

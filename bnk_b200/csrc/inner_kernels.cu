@@ -1,0 +1,76 @@
+// Receive-side bookkeeping around the open kernel, one thread per packet:
+//  - demux: receiver index in the transport header -> keypair slot (the lookup wireguard-go's receive
+//    routine does in its index table before it hands a message to a decryption worker);
+//  - inner check: what its sequential receiver does with an authenticated, fresh plaintext before the
+//    TUN write: IPv4 only here (the reference gives peers one IPv4 /32 each, internal/dataplane/engine.go:294),
+//    20 <= total-length field <= decrypted length, cut to the total length, source address must be the
+//    sending peer's allowed address.
+#include "bnk_internal.cuh"
+
+namespace {
+
+__global__ void demux_index_kernel(KeypairTables kt, const uint8_t *ring, const uint32_t *off, const uint32_t *len,
+                                   uint32_t *slot, uint32_t n, uint64_t ring_bytes) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t o = off[i], l = len[i];
+    if ((o & 15u) || (uint64_t)o + l > ring_bytes || l < BNK_WG_HEADER + BNK_WG_TAG) {
+        slot[i] = 0; // the open kernel reports BAD_DESC / MALFORMED for these on its own
+        return;
+    }
+    const uint32_t index = *reinterpret_cast<const uint32_t *>(ring + o + 4);
+    const uint64_t key = (1ull << 32) | index;
+    uint32_t found = kSlotNoKeypair;
+    if (kt.index_slots) {
+        uint32_t h = index_hash(index) & (kt.index_slots - 1);
+        for (uint32_t probe = 0; probe < kt.index_slots; probe++) {
+            const uint64_t k = kt.index_keys[h];
+            if (k == 0) break;
+            if (k == key) {
+                found = kt.index_vals[h];
+                break;
+            }
+            h = (h + 1) & (kt.index_slots - 1);
+        }
+    }
+    slot[i] = found;
+}
+
+__global__ void inner_check_kernel(KeypairTables kt, const uint8_t *ring, const uint32_t *off, const uint32_t *slot,
+                                   uint32_t *out_len, uint8_t *status, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n || status[i] != BNK_PKT_OK) return;
+    const uint8_t *p = ring + off[i] + BNK_WG_HEADER; // 16-byte aligned
+    const uint32_t l = out_len[i];
+    bool ok = false;
+    if (l >= 20) {
+        const uint4 w = *reinterpret_cast<const uint4 *>(p);
+        if (((w.x & 0xffu) >> 4) == 4u) {
+            const uint32_t total = ((w.x >> 8) & 0xff00u) | (w.x >> 24); // bytes 2,3 big-endian
+            const uint32_t src = __byte_perm(w.w, 0, 0x0123);
+            if (total >= 20 && total <= l && src == kt.allowed_ip[slot[i]] && src != 0) {
+                out_len[i] = total;
+                ok = true;
+            }
+        }
+    }
+    if (!ok) status[i] = BNK_PKT_BAD_INNER;
+}
+
+} // namespace
+
+cudaError_t launch_demux_index(bnk_batch *b, uint32_t n, const uint32_t *len, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    demux_index_kernel<<<(n + 255) / 256, 256, 0, s>>>(b->ctx->kt, b->dev.ring, b->dev.off, len, b->dev.slot, n,
+                                                      b->ring_bytes);
+    ++b->ctx->launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_inner_check(bnk_batch *b, uint32_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    inner_check_kernel<<<(n + 255) / 256, 256, 0, s>>>(b->ctx->kt, b->dev.ring, b->dev.off, b->dev.slot, b->dev.out_len,
+                                                      b->dev.status, n);
+    ++b->ctx->launches;
+    return cudaGetLastError();
+}

@@ -14,6 +14,8 @@ from . import _lib
 from ._lib import (  # noqa: F401  (re-exported)
     F_ASSIGN_COUNTERS,
     F_CHECK_INBOUND,
+    F_DEMUX_INDEX,
+    F_INNER_CHECK,
     F_NO_D2H,
     F_NO_H2D,
     F_NOTE_OUTBOUND,
@@ -22,6 +24,8 @@ from ._lib import (  # noqa: F401  (re-exported)
     F_USE_OUT_LEN,
     PKT_AUTH_FAIL,
     PKT_BAD_DESC,
+    PKT_BAD_INNER,
+    PKT_NO_KEYPAIR,
     PKT_COUNTER_EXHAUSTED,
     PKT_FILTER_DENY,
     PKT_KEEPALIVE,
@@ -110,6 +114,15 @@ class Context:
 
     def set_send_counter(self, slot: int, value: int):
         self._ck(_lib.lib().bnk_send_counter_set(self._h, slot, value))
+
+    def index_set(self, local_index: int, slot: int):
+        self._ck(_lib.lib().bnk_index_set(self._h, local_index, slot))
+
+    def index_clear(self, local_index: int):
+        self._ck(_lib.lib().bnk_index_clear(self._h, local_index))
+
+    def set_allowed_ip(self, slot: int, ipv4: int):
+        self._ck(_lib.lib().bnk_keypair_set_allowed_ip(self._h, slot, ipv4))
 
     def replay_export(self, slot: int):
         last = C.c_uint64()

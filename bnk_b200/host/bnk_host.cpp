@@ -1,0 +1,323 @@
+// Host side above the C ABI (see bnk_host.hpp).  Byte shuffling only: every verdict, ciphertext byte and
+// counter comes back from libbnkgpu's kernels.
+#include "bnk_host.hpp"
+
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+
+namespace bnk {
+
+TimeNs Now() {
+    return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::system_clock::now().time_since_epoch()).count();
+}
+
+// ---- acl ----
+namespace {
+
+// netip.ParsePrefix restricted to what can contain an IPv4 address; anything else "never contains"
+bool parse_prefix(const std::string &s, uint32_t &addr, int &bits) {
+    const size_t slash = s.find('/');
+    if (slash == std::string::npos) return false;
+    unsigned a[4];
+    char extra;
+    if (sscanf(s.substr(0, slash).c_str(), "%u.%u.%u.%u%c", &a[0], &a[1], &a[2], &a[3], &extra) != 4) return false;
+    for (unsigned v : a)
+        if (v > 255) return false;
+    int b = -1;
+    if (sscanf(s.c_str() + slash + 1, "%d%c", &b, &extra) != 1 || b < 0 || b > 32) return false;
+    addr = (a[0] << 24) | (a[1] << 16) | (a[2] << 8) | a[3];
+    bits = b;
+    return true;
+}
+
+} // namespace
+
+std::vector<bnk_acl_tuple> FlattenRules(const std::vector<CompiledRule> &rules) {
+    std::vector<bnk_acl_tuple> out;
+    for (const CompiledRule &r : rules) {
+        uint8_t proto = r.Proto == "tcp" ? 6 : r.Proto == "udp" ? 17 : r.Proto == "icmp" ? 1 : 0;
+        if (!proto) continue; // can never equal a parsed packet's protocol name (acl.go:150)
+        for (const std::string &s : r.Srcs) {
+            uint32_t addr;
+            int bits;
+            if (!parse_prefix(s, addr, bits)) continue;
+            if (proto == 1) {
+                out.push_back(bnk_acl_tuple{addr, (uint8_t)bits, proto, 0, 0, 0}); // icmp ignores ports (acl.go:163)
+            } else {
+                for (const PortRange &p : r.Ports)
+                    if (p.First <= p.Last) out.push_back(bnk_acl_tuple{addr, (uint8_t)bits, proto, p.First, p.Last, 0});
+            }
+        }
+    }
+    return out;
+}
+
+// ---- Context / Batch ----
+Context::Context(int device, uint32_t max_keypairs, uint32_t mtu, uint32_t flow_capacity, uint32_t replay_ring_blocks)
+    : mtu_(mtu) {
+    bnk_cfg cfg{};
+    cfg.struct_size = sizeof cfg;
+    cfg.device_id = device;
+    cfg.max_keypairs = max_keypairs;
+    cfg.replay_ring_blocks = replay_ring_blocks;
+    cfg.mtu = mtu;
+    cfg.flow_capacity = flow_capacity;
+    const int rc = bnk_ctx_create(&cfg, &ctx_);
+    if (rc != BNK_SUCCESS) throw Error(rc, std::string("bnk_ctx_create: ") + bnk_last_error_string(nullptr));
+}
+
+Context::~Context() {
+    if (ctx_) bnk_ctx_destroy(ctx_);
+}
+
+void Context::Check(int rc) const {
+    if (rc < 0) throw Error(rc, std::string(bnk_strerror(rc)) + ": " + bnk_last_error_string(ctx_));
+}
+
+Batch::Batch(Context &ctx, uint32_t max_pkts, uint32_t slot_bytes) : ctx_(ctx), slot_((slot_bytes + 15u) & ~15u) {
+    ctx_.Check(bnk_batch_create(ctx_.raw(), max_pkts, (uint64_t)max_pkts * slot_, &b_));
+    ctx_.Check(bnk_batch_view_get(b_, &v_));
+}
+
+Batch::~Batch() {
+    if (b_) bnk_batch_destroy(b_);
+}
+
+void Batch::Put(uint32_t i, const uint8_t *data, size_t len, uint32_t headroom, uint32_t keypair_slot) {
+    if (i >= v_.max_pkts || headroom + len + 32 > slot_) throw Error(BNK_EINVAL, "packet does not fit its slot");
+    v_.off[i] = i * slot_;
+    v_.len[i] = (uint32_t)len;
+    v_.slot[i] = keypair_slot;
+    if (len) memcpy(slot(i) + headroom, data, len);
+}
+
+void Batch::Wait(uint64_t timeout_ns) { ctx_.Check(bnk_wait(b_, timeout_ns)); }
+
+// ---- Filter ----
+Filter::Filter(Context &ctx, uint32_t batch_pkts, uint32_t max_packet)
+    : ctx_(ctx), batch_(ctx, batch_pkts, 16 + max_packet + 32) {
+    ctx_.Check(bnk_acl_set(ctx_.raw(), 0, nullptr, 0)); // allow-all until rules are pushed (filter.go:41-43)
+}
+
+std::unique_ptr<Filter> Filter::New(Context &ctx, uint32_t batch_pkts, uint32_t max_packet) {
+    return std::unique_ptr<Filter>(new Filter(ctx, batch_pkts, max_packet));
+}
+
+void Filter::SetRules(const std::vector<CompiledRule> &rules) {
+    const std::vector<bnk_acl_tuple> t = FlattenRules(rules);
+    ctx_.Check(bnk_acl_set(ctx_.raw(), 1, t.empty() ? nullptr : t.data(), t.size()));
+}
+
+void Filter::SetAllowAll() { ctx_.Check(bnk_acl_set(ctx_.raw(), 0, nullptr, 0)); }
+
+uint32_t Filter::Load(const std::vector<Span> &pkts, size_t first) {
+    const uint32_t n = (uint32_t)std::min<size_t>(batch_.capacity(), pkts.size() - first);
+    for (uint32_t i = 0; i < n; i++) batch_.Put(i, pkts[first + i].data, pkts[first + i].len, 16);
+    return n;
+}
+
+std::vector<uint8_t> Filter::CheckInboundBatch(const std::vector<Span> &pkts, TimeNs now) {
+    std::vector<uint8_t> verdict(pkts.size(), 0);
+    for (size_t first = 0; first < pkts.size(); first += batch_.capacity()) {
+        const uint32_t n = Load(pkts, first);
+        ctx_.Check(bnk_filter_check_submit(batch_.raw(), n, 0, now));
+        batch_.Wait();
+        for (uint32_t i = 0; i < n; i++) verdict[first + i] = batch_.view().status[i] == BNK_PKT_OK;
+    }
+    return verdict;
+}
+
+void Filter::NoteOutboundBatch(const std::vector<Span> &pkts, TimeNs now) {
+    for (size_t first = 0; first < pkts.size(); first += batch_.capacity()) {
+        const uint32_t n = Load(pkts, first);
+        ctx_.Check(bnk_filter_note_submit(batch_.raw(), n, 0, now));
+        batch_.Wait();
+    }
+}
+
+bool Filter::CheckInbound(const uint8_t *pkt, size_t len, TimeNs now) {
+    return CheckInboundBatch({Span{pkt, len}}, now)[0] != 0;
+}
+
+void Filter::NoteOutbound(const uint8_t *pkt, size_t len, TimeNs now) { NoteOutboundBatch({Span{pkt, len}}, now); }
+
+uint64_t Filter::FlowCount() const {
+    uint64_t live = 0;
+    ctx_.Check(bnk_flows_count(ctx_.raw(), &live));
+    return live;
+}
+
+// ---- WrapTUN ----
+namespace {
+
+class FilteredTUN final : public TunDevice { // filteredTUN, filter.go:155-186
+  public:
+    FilteredTUN(TunDevice *inner, Filter *f, std::function<TimeNs()> clock)
+        : inner_(inner), f_(f), clock_(std::move(clock)) {}
+
+    int Read(std::vector<Packet> &bufs, std::vector<int> &sizes, int offset) override {
+        const int n = inner_->Read(bufs, sizes, offset);
+        const TimeNs now = clock_(); // one clock sample per batch (filter.go:162)
+        std::vector<Filter::Span> spans;
+        for (int i = 0; i < n; i++) spans.push_back({bufs[i].data() + offset, (size_t)sizes[i]});
+        f_->NoteOutboundBatch(spans, now);
+        return n;
+    }
+
+    // Drops denied packets in place but still reports them written (filter.go:169-186).
+    int Write(std::vector<Packet> &bufs, int offset) override {
+        const TimeNs now = clock_();
+        std::vector<Filter::Span> spans;
+        for (const Packet &b : bufs)
+            spans.push_back({b.data() + std::min<size_t>(offset, b.size()), b.size() > (size_t)offset ? b.size() - offset : 0});
+        const std::vector<uint8_t> ok = f_->CheckInboundBatch(spans, now);
+        std::vector<Packet> kept;
+        for (size_t i = 0; i < bufs.size(); i++)
+            if (ok[i]) kept.push_back(bufs[i]);
+        if (kept.empty()) return (int)bufs.size();
+        inner_->Write(kept, offset); // an inner failure propagates as the exception it throws
+        return (int)bufs.size();
+    }
+
+    int MTU() override { return inner_->MTU(); }
+    std::string Name() override { return inner_->Name(); }
+    int BatchSize() override { return inner_->BatchSize(); }
+    void Close() override { inner_->Close(); }
+
+  private:
+    TunDevice *inner_;
+    Filter *f_;
+    std::function<TimeNs()> clock_;
+};
+
+} // namespace
+
+std::unique_ptr<TunDevice> WrapTUN(TunDevice *inner, Filter *f, std::function<TimeNs()> clock) {
+    return std::unique_ptr<TunDevice>(new FilteredTUN(inner, f, std::move(clock)));
+}
+
+// ---- Device ----
+Device::Device(Context &ctx, TunDevice *tun, Bind *bind, uint32_t batch_pkts)
+    : ctx_(ctx), tun_(tun), bind_(bind), batch_(ctx, batch_pkts, 16 + ((ctx.mtu() ? ctx.mtu() : 1500) + 15) / 16 * 16 + 32) {}
+
+void Device::SetPeer(uint32_t slot, const uint8_t send_key[32], const uint8_t recv_key[32], uint32_t remote_index,
+                     uint32_t local_index, uint32_t allowed_ip) {
+    RemovePeer(slot);
+    ctx_.Check(bnk_keypair_set(ctx_.raw(), slot, send_key, recv_key, remote_index));
+    ctx_.Check(bnk_keypair_set_allowed_ip(ctx_.raw(), slot, allowed_ip));
+    ctx_.Check(bnk_index_set(ctx_.raw(), local_index, slot));
+    route_[allowed_ip] = slot;
+    by_index_[slot] = local_index;
+    src_of_[slot] = allowed_ip;
+}
+
+void Device::RemovePeer(uint32_t slot) {
+    auto it = by_index_.find(slot);
+    if (it == by_index_.end()) return;
+    ctx_.Check(bnk_index_clear(ctx_.raw(), it->second));
+    ctx_.Check(bnk_keypair_clear(ctx_.raw(), slot));
+    route_.erase(src_of_[slot]);
+    src_of_.erase(slot);
+    by_index_.erase(it);
+}
+
+void Device::AttachFilter(Filter *f, std::function<TimeNs()> clock) {
+    filter_ = f;
+    clock_ = std::move(clock);
+}
+
+int Device::PumpOutbound() {
+    const int cap = std::min<int>(batch_.capacity(), std::max(1, tun_->BatchSize()));
+    const size_t room = (size_t)kOffset + (ctx_.mtu() ? ctx_.mtu() : 1500) + 32;
+    std::vector<Packet> bufs(cap, Packet(room));
+    std::vector<int> sizes(cap, 0);
+    const int n = tun_->Read(bufs, sizes, kOffset);
+    uint32_t m = 0;
+    std::vector<uint32_t> peer_of;
+    for (int i = 0; i < n; i++) {
+        const uint8_t *p = bufs[i].data() + kOffset;
+        // outbound routing: destination address -> peer (allowed-IPs, one /32 per peer)
+        if (sizes[i] < 20 || (p[0] >> 4) != 4) {
+            stats_.no_route++;
+            continue;
+        }
+        const uint32_t dst = ((uint32_t)p[16] << 24) | ((uint32_t)p[17] << 16) | ((uint32_t)p[18] << 8) | p[19];
+        auto it = route_.find(dst);
+        if (it == route_.end()) {
+            stats_.no_route++;
+            continue;
+        }
+        batch_.Put(m++, p, (size_t)sizes[i], kOffset, it->second);
+        peer_of.push_back(it->second);
+    }
+    if (m == 0) return 0;
+    uint32_t flags = BNK_F_ASSIGN_COUNTERS;
+    if (filter_) flags |= BNK_F_NOTE_OUTBOUND;
+    ctx_.Check(bnk_seal_submit(batch_.raw(), m, flags, clock_()));
+    batch_.Wait();
+    // per-peer sends, batch order kept inside each peer (bind.go:296, called once per peer by the device)
+    int sent = 0;
+    std::vector<uint8_t> done(m, 0);
+    for (uint32_t i = 0; i < m; i++) {
+        if (done[i]) continue;
+        std::vector<Packet> out;
+        for (uint32_t j = i; j < m; j++) {
+            if (done[j] || peer_of[j] != peer_of[i]) continue;
+            done[j] = 1;
+            if (batch_.view().status[j] != BNK_PKT_OK) continue; // counter exhausted: dropped, a rekey is due
+            const uint8_t *msg = batch_.slot(j);
+            out.emplace_back(msg, msg + batch_.view().out_len[j]);
+            stats_.sealed++;
+        }
+        if (!out.empty()) {
+            bind_->Send(out, Endpoint{peer_of[i]});
+            sent += (int)out.size();
+        }
+    }
+    return sent;
+}
+
+int Device::PumpInbound() {
+    const int cap = std::min<int>(batch_.capacity(), std::max(1, bind_->BatchSize()));
+    std::vector<Packet> packets(cap, Packet(batch_.slot_bytes()));
+    std::vector<int> sizes(cap, 0);
+    std::vector<Endpoint> eps(cap);
+    const int n = bind_->Receive(packets, sizes, eps);
+    if (n <= 0) return 0;
+    uint32_t m = 0;
+    for (int i = 0; i < n; i++) {
+        if ((size_t)sizes[i] + 32 > batch_.slot_bytes()) {
+            stats_.malformed++;
+            continue;
+        }
+        batch_.Put(m++, packets[i].data(), (size_t)sizes[i], 0, 0);
+    }
+    if (m == 0) return 0;
+    uint32_t flags = BNK_F_DEMUX_INDEX | BNK_F_REPLAY | BNK_F_INNER_CHECK;
+    if (filter_) flags |= BNK_F_CHECK_INBOUND;
+    ctx_.Check(bnk_open_submit(batch_.raw(), m, flags, clock_()));
+    batch_.Wait();
+    std::vector<Packet> up;
+    for (uint32_t j = 0; j < m; j++) {
+        switch (batch_.view().status[j]) {
+        case BNK_PKT_OK: {
+            Packet b((size_t)kOffset + batch_.view().out_len[j]);
+            memcpy(b.data() + kOffset, batch_.slot(j) + 16, batch_.view().out_len[j]);
+            up.push_back(std::move(b));
+            stats_.opened++;
+            break;
+        }
+        case BNK_PKT_KEEPALIVE: stats_.keepalive++; break;
+        case BNK_PKT_AUTH_FAIL: stats_.auth_fail++; break;
+        case BNK_PKT_REPLAY: stats_.replay++; break;
+        case BNK_PKT_FILTER_DENY: stats_.filter_deny++; break;
+        case BNK_PKT_BAD_INNER: stats_.bad_source++; break;
+        default: stats_.malformed++; break;
+        }
+    }
+    if (!up.empty()) tun_->Write(up, kOffset);
+    return (int)up.size();
+}
+
+} // namespace bnk

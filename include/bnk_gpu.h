@@ -60,6 +60,9 @@ extern "C" {
 #define BNK_PKT_KEEPALIVE 5         /* authenticated zero-length payload */
 #define BNK_PKT_COUNTER_EXHAUSTED 6 /* send counter reached Reject-After-Messages */
 #define BNK_PKT_BAD_DESC 7          /* descriptor out of range (offset, length or keypair slot) */
+#define BNK_PKT_NO_KEYPAIR 8        /* BNK_F_DEMUX_INDEX: the receiver index in the header maps to no keypair */
+#define BNK_PKT_BAD_INNER 9         /* BNK_F_INNER_CHECK: decrypted packet is not IPv4, lies about its length,
+                                       or does not come from the peer's allowed address */
 
 #define BNK_WG_HEADER 16u
 #define BNK_WG_TAG 16u
@@ -74,6 +77,8 @@ extern "C" {
 #define BNK_F_CHECK_INBOUND (1u << 5)   /* open: run the ACL filter on accepted packets */
 #define BNK_F_SORT_BY_LENGTH (1u << 6)  /* schedule packets of similar length together (mixed sizes) */
 #define BNK_F_USE_OUT_LEN (1u << 7)     /* open: message lengths are the out_len[] a seal left on the device */
+#define BNK_F_DEMUX_INDEX (1u << 8)     /* open: slot[] is an output, looked up from each header's receiver index */
+#define BNK_F_INNER_CHECK (1u << 9)     /* open: cut the plaintext to its IPv4 total length and check its source */
 
 typedef struct bnk_ctx bnk_ctx;
 typedef struct bnk_batch bnk_batch;
@@ -142,6 +147,16 @@ int bnk_keypair_set_many(bnk_ctx *ctx, uint32_t first_slot, uint32_t n, const ui
 int bnk_keypair_clear(bnk_ctx *ctx, uint32_t slot);
 int bnk_send_counter_get(bnk_ctx *ctx, uint32_t slot, uint64_t *counter);
 int bnk_send_counter_set(bnk_ctx *ctx, uint32_t slot, uint64_t counter);
+/* Receive-side demultiplexing, the type/index lookup wireguard-go's receive routine does before it
+ * queues a message for decryption: local receiver index -> keypair slot.  With BNK_F_DEMUX_INDEX the open
+ * path fills slot[] from the header (bytes 4..7); an unknown index yields BNK_PKT_NO_KEYPAIR. */
+int bnk_index_set(bnk_ctx *ctx, uint32_t local_index, uint32_t slot);
+int bnk_index_clear(bnk_ctx *ctx, uint32_t local_index);
+/* The peer's tunnel address (the reference gives every peer exactly one /32, internal/dataplane/engine.go:294).
+ * With BNK_F_INNER_CHECK the open path does what wireguard-go's sequential receiver does after the replay
+ * check: the plaintext must be IPv4 with 20 <= total length <= decrypted length (out_len becomes the total
+ * length) and its source address must be this one; otherwise BNK_PKT_BAD_INNER.  ipv4 is host order. */
+int bnk_keypair_set_allowed_ip(bnk_ctx *ctx, uint32_t slot, uint32_t ipv4);
 /* Replay-window state, for tests and state hand-over: ring has replay_ring_blocks words. */
 int bnk_replay_export(bnk_ctx *ctx, uint32_t slot, uint64_t *last, uint64_t *ring);
 int bnk_replay_import(bnk_ctx *ctx, uint32_t slot, uint64_t last, const uint64_t *ring);

@@ -295,6 +295,16 @@ int bnko_wg_open(const uint8_t key[32], const uint8_t *msg, size_t msg_len, uint
     return len == 0 ? BNKO_KEEPALIVE : BNKO_OK;
 }
 
+int bnko_inner_check(const uint8_t *pt, size_t len, uint32_t allowed_ip, size_t *new_len) {
+    if (len < 20 || (pt[0] >> 4) != 4) return 0;
+    size_t total = ((size_t)pt[2] << 8) | pt[3];
+    if (total > len || total < 20) return 0;
+    uint32_t src = ((uint32_t)pt[12] << 24) | ((uint32_t)pt[13] << 16) | ((uint32_t)pt[14] << 8) | pt[15];
+    if (allowed_ip == 0 || src != allowed_ip) return 0;
+    if (new_len) *new_len = total;
+    return 1;
+}
+
 /* Batch forms.  Packet i occupies ring[off[i] ...]: 16 bytes of header room, then
  * the payload.  Seal works in place (payload -> header|ciphertext|tag at off[i]);
  * open reads the message at off[i] and leaves the plaintext at off[i]+16. */

@@ -71,6 +71,12 @@ size_t bnko_wg_seal(const uint8_t key[32], uint32_t receiver_index, uint64_t cou
 int bnko_wg_open(const uint8_t key[32], const uint8_t *msg, size_t msg_len, uint8_t *out_pt, size_t *pt_len,
                  uint64_t *counter, uint32_t *receiver_index);
 
+/* What the upstream sequential receiver does with an authenticated, fresh plaintext before the TUN write
+ * (restated from its documented behaviour): IPv4 only, 20 <= total-length field <= len, the packet is cut to the
+ * total length, and its source address must be the sending peer's allowed address (the reference gives each peer
+ * one /32, internal/dataplane/engine.go:294).  Returns 1 and the new length, or 0 = drop. */
+int bnko_inner_check(const uint8_t *pt, size_t len, uint32_t allowed_ip, size_t *new_len);
+
 /* batch forms over a packet ring (same descriptor layout as the GPU library) */
 void bnko_wg_seal_batch(const uint8_t *keys /* n_keys*32 */, const uint32_t *remote_index /* n_keys */,
                         size_t mtu, uint8_t *ring, const uint32_t *off, const uint32_t *len,

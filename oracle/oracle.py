@@ -15,6 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
 OK, AUTH_FAIL, REPLAY, FILTER_DENY, MALFORMED, KEEPALIVE, COUNTER_EXHAUSTED, BAD_DESC = range(8)
+NO_KEYPAIR, BAD_INNER = 8, 9
 REJECT_AFTER_MESSAGES = 0xFFFFFFFFFFFFDFFF
 
 
@@ -79,6 +80,8 @@ def lib() -> C.CDLL:
     L.bnko_wg_seal.restype = sz
     L.bnko_wg_open.argtypes = [vp, vp, sz, vp, C.POINTER(sz), u64p, u32p]
     L.bnko_wg_open.restype = C.c_int
+    L.bnko_inner_check.argtypes = [vp, sz, C.c_uint32, C.POINTER(sz)]
+    L.bnko_inner_check.restype = C.c_int
     L.bnko_wg_seal_batch.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, vp, vp, sz]
     L.bnko_wg_seal_batch.restype = None
     L.bnko_wg_open_batch.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz]
@@ -175,6 +178,13 @@ def wg_open(key: bytes, msg: bytes):
     rx = C.c_uint32(0)
     st = lib().bnko_wg_open(_buf(key), _buf(msg), len(msg), out, C.byref(pl), C.byref(ctr), C.byref(rx))
     return st, out.raw[: pl.value], ctr.value, rx.value
+
+
+def inner_check(pt: bytes, allowed_ip: int):
+    """-> new length, or None when the packet is to be dropped."""
+    nl = C.c_size_t(0)
+    ok = lib().bnko_inner_check(_buf(pt), len(pt), allowed_ip, C.byref(nl))
+    return nl.value if ok else None
 
 
 def wg_seal_batch(keys, remote_index, mtu, ring, off, length, slot, counter):

@@ -1,0 +1,321 @@
+// The reference's Go tests for the hot path, restated against the C++ host mirror (bnk_b200/host/bnk_host.hpp):
+//   internal/filter/filter_test.go:56-170, internal/filter/tun_test.go:43-94, internal/acl/acl_test.go:83-114,
+// plus the functional round trip the reference's device tests make (internal/dataplane/device_test.go:85-91):
+// two devices joined by an in-memory bind, packets written into one TUN come out of the other.
+// Needs a B200: every verdict and every ciphertext byte is produced by libbnkgpu.so.
+#include <cstdio>
+#include <cstring>
+#include <deque>
+#include <string>
+
+#include "../../bnk_b200/host/bnk_host.hpp"
+
+using namespace bnk;
+
+static int g_failed = 0, g_checks = 0;
+static const char *g_test = "";
+#define CHECK(cond, msg)                                                      \
+    do {                                                                      \
+        g_checks++;                                                           \
+        if (!(cond)) {                                                        \
+            g_failed++;                                                       \
+            printf("FAIL %s: %s (%s:%d)\n", g_test, msg, __FILE__, __LINE__); \
+        }                                                                     \
+    } while (0)
+
+// ---- packet builders, filter_test.go:13-54 ----
+static uint32_t ip(int a, int b, int c, int d) { return ((uint32_t)a << 24) | (b << 16) | (c << 8) | d; }
+static void put16(Packet &p, size_t at, uint16_t v) { p[at] = v >> 8; p[at + 1] = v & 0xff; }
+static void put32(Packet &p, size_t at, uint32_t v) { put16(p, at, v >> 16); put16(p, at + 2, v & 0xffff); }
+static Packet ipv4(uint8_t proto, uint32_t src, uint32_t dst, const Packet &payload) {
+    Packet pkt(20 + payload.size());
+    pkt[0] = 0x45;
+    put16(pkt, 2, (uint16_t)pkt.size());
+    pkt[8] = 64;
+    pkt[9] = proto;
+    put32(pkt, 12, src);
+    put32(pkt, 16, dst);
+    std::copy(payload.begin(), payload.end(), pkt.begin() + 20);
+    return pkt;
+}
+static Packet tcp(uint32_t src, uint32_t dst, uint16_t sport, uint16_t dport, bool syn) {
+    Packet h(20);
+    put16(h, 0, sport);
+    put16(h, 2, dport);
+    h[12] = 5 << 4;
+    h[13] = syn ? 0x02 : 0x10;
+    return ipv4(6, src, dst, h);
+}
+static Packet udp(uint32_t src, uint32_t dst, uint16_t sport, uint16_t dport) {
+    Packet h(8);
+    put16(h, 0, sport);
+    put16(h, 2, dport);
+    put16(h, 4, 8);
+    return ipv4(17, src, dst, h);
+}
+static Packet icmpEcho(uint32_t src, uint32_t dst, bool reply) {
+    Packet h(8);
+    h[0] = reply ? 0 : 8;
+    return ipv4(1, src, dst, h);
+}
+
+static const uint32_t peer = ip(100, 64, 0, 9), other = ip(100, 64, 0, 7), self = ip(100, 64, 0, 1);
+static const TimeNs SEC = 1000000000ll, MIN = 60 * SEC, t0 = 1700000000ll * SEC; // filter_test.go:57-60
+
+static std::unique_ptr<Filter> sshOnlyFilter(Context &ctx) { // filter_test.go:63-71
+    bnk_flows_clear(ctx.raw());
+    auto f = Filter::New(ctx);
+    f->SetRules({CompiledRule{{"100.64.0.9/32"}, "tcp", {PortRange{22, 22}}}});
+    return f;
+}
+static std::unique_ptr<Filter> fresh(Context &ctx) {
+    bnk_flows_clear(ctx.raw());
+    return Filter::New(ctx);
+}
+
+static void TestAllowAllModePassesEverything(Context &ctx) {
+    auto f = fresh(ctx);
+    CHECK(f->CheckInbound(tcp(peer, self, 5555, 23, true), t0), "allow-all dropped a packet");
+}
+static void TestRuleAllowsMatchingInbound(Context &ctx) {
+    auto f = sshOnlyFilter(ctx);
+    CHECK(f->CheckInbound(tcp(peer, self, 5555, 22, true), t0), "rule-allowed tcp/22 dropped");
+}
+static void TestDefaultDenyDropsNonMatching(Context &ctx) {
+    auto f = sshOnlyFilter(ctx);
+    CHECK(!f->CheckInbound(tcp(peer, self, 5555, 23, true), t0), "tcp/23 passed despite ssh-only policy");
+    CHECK(!f->CheckInbound(tcp(other, self, 5555, 22, true), t0), "tcp/22 from disallowed source passed");
+    CHECK(!f->CheckInbound(udp(peer, self, 53, 22), t0), "udp passed a tcp-only rule");
+}
+static void TestReturnTrafficAllowedViaFlowTable(Context &ctx) {
+    auto f = sshOnlyFilter(ctx);
+    f->NoteOutbound(udp(self, peer, 40000, 9999), t0);
+    CHECK(f->CheckInbound(udp(peer, self, 9999, 40000), t0 + 2 * SEC), "UDP reply to our own outbound flow was dropped");
+    CHECK(!f->CheckInbound(udp(peer, self, 9999, 40000), t0 + 5 * MIN), "UDP reply passed long after the flow expired");
+    CHECK(!f->CheckInbound(udp(peer, self, 9998, 40000), t0 + SEC), "UDP from a different source port matched the flow");
+}
+static void TestTCPReturnFlowAllowed(Context &ctx) {
+    auto f = sshOnlyFilter(ctx);
+    f->NoteOutbound(tcp(self, peer, 40000, 8080, true), t0);
+    CHECK(f->CheckInbound(tcp(peer, self, 8080, 40000, false), t0 + SEC), "TCP reply to our outbound connection was dropped");
+    CHECK(!f->CheckInbound(tcp(peer, self, 8081, 40000, false), t0 + SEC), "TCP from wrong port matched the flow");
+}
+static void TestICMPEchoReplyViaFlow(Context &ctx) {
+    auto f = sshOnlyFilter(ctx);
+    f->NoteOutbound(icmpEcho(self, peer, false), t0);
+    CHECK(f->CheckInbound(icmpEcho(peer, self, true), t0 + SEC), "ICMP echo reply to our ping was dropped");
+    CHECK(!f->CheckInbound(icmpEcho(other, self, true), t0 + SEC), "ICMP reply from a host we never pinged passed");
+}
+static void TestICMPRuleAllowsInboundPing(Context &ctx) {
+    auto f = fresh(ctx);
+    f->SetRules({CompiledRule{{"100.64.0.9/32"}, "icmp", {}}});
+    CHECK(f->CheckInbound(icmpEcho(peer, self, false), t0), "icmp rule did not allow inbound ping");
+}
+static void TestMalformedAndNonIPv4Dropped(Context &ctx) {
+    auto f = sshOnlyFilter(ctx);
+    CHECK(!f->CheckInbound(Packet{0x60, 0x00, 0x00}, t0), "IPv6/short packet passed while enforcing");
+    CHECK(!f->CheckInbound(nullptr, 0, t0), "nil packet passed");
+    Packet truncated = tcp(peer, self, 1, 22, true);
+    truncated.resize(22);
+    CHECK(!f->CheckInbound(truncated, t0), "truncated transport header passed");
+}
+static void TestSetAllowAllDisablesEnforcement(Context &ctx) {
+    auto f = sshOnlyFilter(ctx);
+    f->SetAllowAll();
+    CHECK(f->CheckInbound(tcp(other, self, 5555, 23, true), t0), "allow-all after rules still dropped");
+}
+static void TestCompiledRuleMatch(Context &ctx) { // acl_test.go:83-107 through the filter
+    auto f = fresh(ctx);
+    f->SetRules({CompiledRule{{"100.64.0.1/32"}, "tcp", {PortRange{22, 22}, PortRange{8000, 9000}}}});
+    const uint32_t a = ip(100, 64, 0, 1), b = ip(100, 64, 0, 9);
+    CHECK(f->CheckInbound(tcp(a, self, 1, 22, true), t0), "tcp/22");
+    CHECK(f->CheckInbound(tcp(a, self, 1, 8500, true), t0), "tcp/8500");
+    CHECK(!f->CheckInbound(tcp(a, self, 1, 23, true), t0), "tcp/23");
+    CHECK(!f->CheckInbound(udp(a, self, 1, 22), t0), "udp/22");
+    CHECK(!f->CheckInbound(tcp(b, self, 1, 22, true), t0), "other source");
+}
+static void TestICMPRuleIgnoresPorts(Context &ctx) { // acl_test.go:109-114
+    auto f = fresh(ctx);
+    f->SetRules({CompiledRule{{"100.64.0.0/10"}, "icmp", {}}});
+    CHECK(f->CheckInbound(icmpEcho(ip(100, 64, 0, 1), self, false), t0), "icmp rule did not match");
+    CHECK(!f->CheckInbound(icmpEcho(ip(100, 128, 0, 1), self, false), t0), "address outside the /10 matched");
+}
+
+// ---- fakeTUN, tun_test.go:13-41 ----
+struct FakeTUN : TunDevice {
+    std::vector<Packet> written;
+    std::deque<Packet> pending;
+    int Read(std::vector<Packet> &bufs, std::vector<int> &sizes, int offset) override {
+        int n = 0;
+        while (n < (int)bufs.size() && !pending.empty()) {
+            const Packet &pkt = pending.front();
+            if (bufs[n].size() < offset + pkt.size()) bufs[n].resize(offset + pkt.size());
+            std::copy(pkt.begin(), pkt.end(), bufs[n].begin() + offset);
+            sizes[n] = (int)pkt.size();
+            pending.pop_front();
+            n++;
+        }
+        return n;
+    }
+    int Write(std::vector<Packet> &bufs, int offset) override {
+        for (const Packet &b : bufs) written.emplace_back(b.begin() + offset, b.end());
+        return (int)bufs.size();
+    }
+    int MTU() override { return 1280; }
+    std::string Name() override { return "fake0"; }
+    int BatchSize() override { return 4; }
+};
+static Packet pad(const Packet &p, int offset) {
+    Packet out(offset);
+    out.insert(out.end(), p.begin(), p.end());
+    return out;
+}
+static void TestWrapTUNDropsDeniedInboundWrites(Context &ctx) { // tun_test.go:43-66
+    FakeTUN inner;
+    auto f = sshOnlyFilter(ctx);
+    auto wrapped = WrapTUN(&inner, f.get(), [] { return t0; });
+    const Packet allowed = tcp(peer, self, 5555, 22, true), denied = tcp(peer, self, 5555, 23, true);
+    std::vector<Packet> bufs{pad(allowed, 16), pad(denied, 16)};
+    const int n = wrapped->Write(bufs, 16);
+    CHECK(n == 2, "Write must report 2: denied packets are silently dropped");
+    CHECK(inner.written.size() == 1, "inner TUN must get only the allowed packet");
+    CHECK(!inner.written.empty() && inner.written[0] == allowed, "the surviving packet is not the allowed one");
+    std::vector<Packet> all_denied{pad(denied, 16)};
+    CHECK(wrapped->Write(all_denied, 16) == 1 && inner.written.size() == 1, "all-denied batch still reports its length");
+}
+static void TestWrapTUNReadRecordsOutboundFlows(Context &ctx) { // tun_test.go:68-94
+    FakeTUN inner;
+    auto f = fresh(ctx);
+    f->SetRules({}); // deny-all policy: only flows admit traffic
+    auto wrapped = WrapTUN(&inner, f.get(), [] { return t0; });
+    inner.pending.push_back(udp(self, peer, 40000, 9999));
+    std::vector<Packet> bufs{Packet(2048)};
+    std::vector<int> sizes(1);
+    CHECK(wrapped->Read(bufs, sizes, 16) == 1, "read one packet");
+    const Packet reply = udp(peer, self, 9999, 40000), unrelated = udp(peer, self, 9999, 40001);
+    std::vector<Packet> in{pad(reply, 16), pad(unrelated, 16)};
+    wrapped->Write(in, 16);
+    CHECK(inner.written.size() == 1 && inner.written[0] == reply, "inner must get just the reply");
+}
+
+// ---- two devices over an in-memory bind ----
+struct WireBind : Bind {
+    std::deque<Packet> *tx = nullptr, *rx = nullptr;
+    void Send(std::vector<Packet> &bufs, const Endpoint &) override {
+        for (Packet &b : bufs) tx->push_back(b);
+    }
+    int Receive(std::vector<Packet> &packets, std::vector<int> &sizes, std::vector<Endpoint> &) override {
+        int n = 0;
+        while (n < (int)packets.size() && !rx->empty()) {
+            packets[n].assign(rx->front().begin(), rx->front().end());
+            sizes[n] = (int)rx->front().size();
+            rx->pop_front();
+            n++;
+        }
+        return n;
+    }
+    int BatchSize() override { return 128; }
+};
+
+static void TestTwoDevicesRoundTrip(Context &) {
+    // two nodes, each with its own tables (keypairs, rules, flows), here on the same GPU
+    Context ctxA(0, 16, 1420, 1u << 12), ctxB(0, 16, 1420, 1u << 12);
+    std::deque<Packet> a2b, b2a;
+    WireBind bindA, bindB;
+    bindA.tx = &a2b; bindA.rx = &b2a;
+    bindB.tx = &b2a; bindB.rx = &a2b;
+    FakeTUN tunA, tunB;
+    Device A(ctxA, &tunA, &bindA), B(ctxB, &tunB, &bindB);
+    uint8_t kAB[32], kBA[32];
+    for (int i = 0; i < 32; i++) { kAB[i] = (uint8_t)(i * 7 + 1); kBA[i] = (uint8_t)(200 - i); }
+    const uint32_t ipA = ip(100, 64, 0, 1), ipB = ip(100, 64, 0, 2);
+    A.SetPeer(0, kAB, kBA, /*remote_index=*/0xB0B0B0B0u, /*local_index=*/0xA0A0A0A0u, ipB);
+    B.SetPeer(1, kBA, kAB, /*remote_index=*/0xA0A0A0A0u, /*local_index=*/0xB0B0B0B0u, ipA);
+    auto fB = Filter::New(ctxB);
+    fB->SetRules({CompiledRule{{"100.64.0.1/32"}, "tcp", {PortRange{7777, 7777}}}}); // acl_integration_test.go:20-80
+    B.AttachFilter(fB.get(), [] { return t0; });
+
+    std::vector<Packet> sent;
+    for (int i = 0; i < 4; i++) sent.push_back(tcp(ipA, ipB, 40000 + i, 7777, true));
+    sent.push_back(tcp(ipA, ipB, 40010, 8888, true));       // blocked port
+    sent.push_back(tcp(ip(100, 64, 0, 3), ipB, 1, 7777, true)); // spoofed source: not A's allowed address
+    sent.push_back(udp(ipA, ip(100, 64, 0, 99), 1, 2));      // no peer owns that address: never leaves A
+    for (const Packet &p : sent) tunA.pending.push_back(p);
+    int out = 0, rounds = 0;
+    while (!tunA.pending.empty() && rounds++ < 8) out += A.PumpOutbound();
+    CHECK(out == 6, "six packets have a route");
+    CHECK(A.counters().no_route == 1, "one packet has no route");
+    CHECK(a2b.size() == 6, "six datagrams on the wire");
+    const std::deque<Packet> wire = a2b; // keep the ciphertext for the replay below
+    bool headers_ok = true;
+    uint64_t ctr = 0;
+    for (const Packet &m : wire) {
+        headers_ok = headers_ok && m.size() == 16 + 48 + 16 && m[0] == 4 && m[1] == 0 && m[4] == 0xB0;
+        uint64_t c = 0;
+        memcpy(&c, m.data() + 8, 8);
+        headers_ok = headers_ok && c == ctr++;
+    }
+    CHECK(headers_ok, "transport headers: type 4, receiver index of B, counters 0..5 in send order");
+    int in = 0;
+    while (!a2b.empty()) in += B.PumpInbound();
+    CHECK(in == 4 && tunB.written.size() == 4, "four packets reach B's TUN");
+    bool same = tunB.written.size() == 4;
+    for (int i = 0; same && i < 4; i++) same = tunB.written[i] == sent[i];
+    CHECK(same, "plaintext arrives byte for byte, in order");
+    CHECK(B.counters().filter_deny == 1, "tcp/8888 is blocked by B's filter");
+    CHECK(B.counters().bad_source == 1, "spoofed inner source is dropped");
+    // replay the same ciphertext: every datagram is refused by the window
+    a2b = wire;
+    while (!a2b.empty()) B.PumpInbound();
+    CHECK(B.counters().replay == 6 && tunB.written.size() == 4, "replayed datagrams are dropped");
+    // a flipped bit fails authentication; a datagram for an unknown receiver index is ignored
+    Packet bad = wire.front();
+    bad[20] ^= 1;
+    Packet stranger = wire.front();
+    stranger[5] ^= 0x55;
+    a2b.push_back(bad);
+    a2b.push_back(stranger);
+    B.PumpInbound();
+    CHECK(B.counters().auth_fail == 1 && B.counters().malformed == 1, "forged and stranger datagrams are dropped");
+    // B answers on the flow A opened: A has no rule for it, only the reply-flow entry (A's filter sees its own sends)
+    auto fA = Filter::New(ctxA);
+    fA->SetRules({});
+    A.AttachFilter(fA.get(), [] { return t0 + SEC; });
+    tunA.pending.push_back(tcp(ipA, ipB, 41000, 7777, true));
+    A.PumpOutbound();
+    while (!a2b.empty()) B.PumpInbound();
+    tunB.pending.push_back(tcp(ipB, ipA, 7777, 41000, false)); // reply
+    tunB.pending.push_back(tcp(ipB, ipA, 7777, 41001, false)); // not a reply to anything
+    B.PumpOutbound();
+    while (!b2a.empty()) A.PumpInbound();
+    CHECK(tunA.written.size() == 1 && tunA.written[0] == tcp(ipB, ipA, 7777, 41000, false), "only the reply reaches A's TUN");
+}
+
+int main() {
+    try {
+        Context ctx(0, /*max_keypairs=*/16, /*mtu=*/1420, /*flow_capacity=*/1u << 12);
+#define RUN(t)      \
+    g_test = #t;    \
+    t(ctx);         \
+    printf("ran %s\n", #t);
+        RUN(TestAllowAllModePassesEverything)
+        RUN(TestRuleAllowsMatchingInbound)
+        RUN(TestDefaultDenyDropsNonMatching)
+        RUN(TestReturnTrafficAllowedViaFlowTable)
+        RUN(TestTCPReturnFlowAllowed)
+        RUN(TestICMPEchoReplyViaFlow)
+        RUN(TestICMPRuleAllowsInboundPing)
+        RUN(TestMalformedAndNonIPv4Dropped)
+        RUN(TestSetAllowAllDisablesEnforcement)
+        RUN(TestCompiledRuleMatch)
+        RUN(TestICMPRuleIgnoresPorts)
+        RUN(TestWrapTUNDropsDeniedInboundWrites)
+        RUN(TestWrapTUNReadRecordsOutboundFlows)
+        RUN(TestTwoDevicesRoundTrip)
+    } catch (const Error &e) {
+        printf("FAIL %s: exception %d %s\n", g_test, e.code, e.what());
+        return 2;
+    }
+    printf("%d checks, %d failed\n", g_checks, g_failed);
+    return g_failed ? 1 : 0;
+}

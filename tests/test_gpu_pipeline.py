@@ -139,3 +139,91 @@ def test_wait_timeout_and_busy(gpu_lib):
         b.close()
     finally:
         c.close()
+
+
+def test_demux_by_receiver_index_and_inner_check(gpu_lib, oracle):
+    """Open with the keypair looked up from the header's receiver index, then the post-decrypt checks:
+    IPv4 total-length truncation and source-address check, against the CPU checker."""
+    from bnk_b200 import Context, gen
+    from bnk_b200.device import (F_DEMUX_INDEX, F_INNER_CHECK, F_REPLAY, PKT_BAD_INNER, PKT_KEEPALIVE, PKT_MALFORMED,
+                                 PKT_NO_KEYPAIR, PKT_OK)
+
+    rng = np.random.default_rng(21)
+    n_peers = 50
+    keys = rng.integers(0, 256, (n_peers, 32), dtype=np.uint8)
+    local_index = rng.choice(2**32, n_peers, replace=False).astype(np.uint64)
+    local_index[0] = 0                     # index 0 is a legal index
+    peer_ip = gen.ip4(100, 64, 1, 0) + np.arange(n_peers)
+    c = Context(max_keypairs=64, mtu=1420, flow_capacity=0)
+    try:
+        c.set_keypairs(0, keys, keys, np.zeros(n_peers, np.uint32))
+        for s in range(n_peers):
+            c.index_set(int(local_index[s]), s)
+            c.set_allowed_ip(s, int(peer_ip[s]))
+        c.index_set(0xDEAD0001, 7)
+        c.index_clear(0xDEAD0001)          # removed again: must not resolve
+        c.set_allowed_ip(49, 0)            # a peer without an allowed address can deliver nothing
+        msgs, want_slot, want = [], [], []
+        for i in range(600):
+            s = int(rng.integers(0, n_peers))
+            kind = i % 10
+            size = int(rng.choice([28, 64, 576, 1420]))
+            src = int(peer_ip[s])
+            total = size
+            version, ihl = 4, 5
+            if kind == 1:
+                src = int(peer_ip[(s + 1) % n_peers])      # spoofed source
+            elif kind == 2:
+                total = size + 1                            # claims more than was sent
+            elif kind == 3:
+                total = max(20, size - int(rng.integers(1, 9)))  # shorter than the padded payload: cut
+            elif kind == 4:
+                total = 19                                  # below an IPv4 header
+            elif kind == 5:
+                version = 6
+            hdr = bytes(gen.ipv4_header(17, src, gen.ip4(100, 64, 0, 1), total, ihl, version))
+            pt = hdr + rng.integers(0, 256, size - 20, dtype=np.uint8).tobytes()
+            idx = int(local_index[s])
+            if kind == 6:
+                idx = 0xDEAD0001 if i % 20 == 6 else int(rng.integers(1, 2**32))  # unknown receiver index
+            if kind == 7:
+                pt = b""                                    # keepalive
+            m = oracle.wg_seal(keys[s].tobytes(), idx, 1000 + i, pt, 1420)
+            if kind == 8:
+                m = m[:24]                                  # truncated datagram
+            msgs.append(m)
+            known = {int(v): k for k, v in enumerate(local_index)}
+            slot = known.get(idx)
+            if kind == 8:
+                want.append(PKT_MALFORMED)
+            elif slot is None:
+                want.append(PKT_NO_KEYPAIR)
+            elif not pt:
+                want.append(PKT_KEEPALIVE)
+            else:
+                padded = pt + bytes(oracle.wg_padded_len(len(pt), 1420) - len(pt))
+                nl = oracle.inner_check(padded, 0 if slot == 49 else int(peer_ip[slot]))
+                want.append((PKT_OK, nl) if nl is not None else PKT_BAD_INNER)
+            want_slot.append(slot)
+        n = len(msgs)
+        lengths = np.array([len(m) for m in msgs], np.uint32)
+        off = H.layout_packed(lengths, slack=16)
+        b = c.batch(n, H.ring_bytes_for(off, lengths))
+        H.fill_payloads(b.ring, off, msgs, headroom=0)
+        b.off[:n], b.len[:n] = off, lengths
+        b.slot[:n] = 0xFFFFFFFF
+        b.open(n, F_DEMUX_INDEX | F_REPLAY | F_INNER_CHECK)
+        seen = set()
+        for i in range(n):
+            w = want[i]
+            if isinstance(w, tuple):
+                assert b.status[i] == PKT_OK and b.out_len[i] == w[1], i
+            else:
+                assert b.status[i] == w, (i, b.status[i], w)
+            if want_slot[i] is not None and w != PKT_MALFORMED:
+                assert b.slot[i] == want_slot[i]
+            seen.add(int(b.status[i]))
+        assert seen == {PKT_OK, PKT_BAD_INNER, PKT_NO_KEYPAIR, PKT_KEEPALIVE, PKT_MALFORMED}
+        b.close()
+    finally:
+        c.close()

@@ -96,3 +96,20 @@ def test_transport_framing_and_padding(oracle):
     assert oracle.wg_open(key, m[:31])[0] == oracle.MALFORMED
     assert oracle.wg_seal(key, 1, oracle.REJECT_AFTER_MESSAGES, b"x", 1420) == b""
     assert len(oracle.wg_seal(key, 1, oracle.REJECT_AFTER_MESSAGES - 1, b"x", 1420)) == 48
+
+
+def test_inner_check_rules(oracle):
+    from bnk_b200 import gen
+
+    ip = gen.ip4(100, 64, 0, 9)
+    pkt = bytes(gen.ipv4_header(6, ip, gen.ip4(100, 64, 0, 1), 40)) + bytes(20) + bytes(8)  # 8 bytes of padding behind it
+    assert oracle.inner_check(pkt, ip) == 40                      # cut to the total-length field
+    assert oracle.inner_check(pkt[:40], ip) == 40
+    assert oracle.inner_check(pkt[:39], ip) is None               # claims more than there is
+    assert oracle.inner_check(pkt, ip + 1) is None                # not this peer's address
+    assert oracle.inner_check(pkt, 0) is None                     # peer without an allowed address
+    assert oracle.inner_check(bytes([0x60]) + pkt[1:], ip) is None  # IPv6 nibble: the reference hands out IPv4 only
+    short = bytearray(pkt)
+    short[2:4] = (19).to_bytes(2, "big")
+    assert oracle.inner_check(bytes(short), ip) is None           # shorter than an IPv4 header
+    assert oracle.inner_check(pkt[:19], ip) is None
