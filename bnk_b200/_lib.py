@@ -57,6 +57,21 @@ class AclTuple(C.Structure):
     ]
 
 
+class GsoSuper(C.Structure):
+    _fields_ = [
+        ("src_off", C.c_uint32),
+        ("src_len", C.c_uint32),
+        ("first_pkt", C.c_uint32),
+        ("n_pkts", C.c_uint32),
+        ("hdr_len", C.c_uint16),
+        ("gso_size", C.c_uint16),
+        ("csum_start", C.c_uint16),
+        ("csum_offset", C.c_uint16),
+        ("proto", C.c_uint8),
+        ("reserved", C.c_uint8 * 3),
+    ]
+
+
 class BatchView(C.Structure):
     _fields_ = [
         ("ring", C.c_void_p),
@@ -102,6 +117,7 @@ SYMBOLS = {
     "bnk_open_submit": (_i, [_vp, _u32, _u32, _i64]),
     "bnk_filter_note_submit": (_i, [_vp, _u32, _u32, _i64]),
     "bnk_filter_check_submit": (_i, [_vp, _u32, _u32, _i64]),
+    "bnk_gso_split_submit": (_i, [_vp, _vp, _u32, _u32, _u32]),
     "bnk_wait": (_i, [_vp, _u64]),
     "bnk_batch_upload": (_i, [_vp, _u32]),
     "bnk_batch_download": (_i, [_vp, _u32]),

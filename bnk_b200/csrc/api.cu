@@ -355,6 +355,7 @@ int bnk_batch_destroy(bnk_batch *b) {
     cudaFreeHost(b->host.out_len);
     cudaFreeHost(b->host.status);
     cudaFreeHost(b->h_flow_error);
+    cudaFreeHost(b->h_gso);
     DeviceBatch &d = b->dev;
     cudaFree(d.ring);
     cudaFree(d.off);
@@ -369,6 +370,7 @@ int bnk_batch_destroy(bnk_batch *b) {
     cudaFree(d.hist);
     cudaFree(d.len_order);
     cudaFree(d.counters32);
+    cudaFree(d.gso);
     if (b->done) cudaEventDestroy(b->done);
     if (b->k_begin) cudaEventDestroy(b->k_begin);
     if (b->k_end) cudaEventDestroy(b->k_end);
@@ -412,6 +414,7 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     H((void **)&b->host.out_len, n * 4);
     H((void **)&b->host.status, n);
     H((void **)&b->h_flow_error, sizeof(int));
+    H((void **)&b->h_gso, n * sizeof(bnk_gso_super));
     b->host.ring_bytes = ring_bytes;
     b->host.max_pkts = max_pkts;
     DeviceBatch &d = b->dev;
@@ -428,6 +431,7 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     D((void **)&d.hist, (size_t)512 * group_sort_chunks(max_pkts) * 4);
     D((void **)&d.len_order, n * 4);
     D((void **)&d.counters32, 2048 * 4);
+    D((void **)&d.gso, n * sizeof(bnk_gso_super));
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->aux_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_fork, cudaEventDisableTiming);
@@ -621,6 +625,42 @@ int bnk_filter_check_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_
     b->kernel_timed = true;
     if (!(flags & BNK_F_NO_D2H) && n)
         CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
+    return end_submit(b);
+}
+
+int bnk_gso_split_submit(bnk_batch *b, const bnk_gso_super *supers, uint32_t n_super, uint32_t n_pkts,
+                         uint32_t flags) {
+    int rc = begin_submit(b, n_pkts, true); // the descriptor staging area is host memory in any case
+    if (rc) return rc;
+    bnk_ctx *ctx = b->ctx;
+    cudaStream_t s = b->stream;
+    if (n_super > b->max_pkts || (n_super && !supers)) return fail(ctx, BNK_EINVAL, "bad super-packet list");
+    const size_t n = n_pkts;
+    if (!(flags & BNK_F_NO_H2D)) {
+        // the ring span holds the segments' slots and the super-packets
+        uint64_t ext = ring_extent(b, n_pkts, 16 + 16 + 16);
+        for (uint32_t j = 0; j < n_super; j++) {
+            const uint64_t e = (uint64_t)supers[j].src_off + supers[j].src_len;
+            if (e > b->ring_bytes) return fail(ctx, BNK_EINVAL, "super-packet lies outside the ring");
+            if (e > ext) ext = e;
+        }
+        ext = (ext + 15) & ~15ull;
+        if (ext > b->ring_bytes) ext = b->ring_bytes;
+        if (ext) CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
+        if (n) {
+            CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
+            CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+            CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, s));
+        }
+    }
+    if (n_super) {
+        memcpy(b->h_gso, supers, (size_t)n_super * sizeof(bnk_gso_super));
+        CK(ctx, cudaMemcpyAsync(b->dev.gso, b->h_gso, (size_t)n_super * sizeof(bnk_gso_super), cudaMemcpyHostToDevice, s));
+    }
+    CK(ctx, cudaEventRecord(b->k_begin, s));
+    CK(ctx, launch_gso_split(b, n_super, n_pkts, s));
+    CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = true;
     return end_submit(b);
 }
 

@@ -75,6 +75,7 @@ struct DeviceBatch {
     uint32_t *hist;       // [512 * chunks] digit-major histograms
     uint32_t *len_order;  // [max_pkts] packet indices ordered by length class
     uint32_t *counters32; // small scratch (bins)
+    bnk_gso_super *gso;   // [max_pkts] super-packet descriptors of a GSO split
 };
 
 struct bnk_batch {
@@ -90,6 +91,7 @@ struct bnk_batch {
     bool in_flight;
     bool kernel_timed;
     bool aead_timed;
+    bnk_gso_super *h_gso; // pinned staging for the super-packet descriptors
     int *h_flow_error; // pinned copy of the flow-table overflow flag, refreshed by filter work
 };
 
@@ -141,6 +143,9 @@ __host__ __device__ inline uint32_t index_hash(uint32_t index) {
     z *= 0x85ebca6bu;
     return z ^ (z >> 13);
 }
+
+// gso_kernels.cu
+cudaError_t launch_gso_split(bnk_batch *b, uint32_t n_super, uint32_t n_pkts, cudaStream_t s);
 
 // probe_kernels.cu
 cudaError_t launch_fill_random(uint8_t *dst, uint64_t bytes, uint64_t seed, cudaStream_t s,

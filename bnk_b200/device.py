@@ -37,6 +37,7 @@ from ._lib import (  # noqa: F401  (re-exported)
 )
 
 ACL_TUPLE_DTYPE = np.dtype(_lib.AclTuple)
+GSO_SUPER_DTYPE = np.dtype(_lib.GsoSuper)
 
 
 def _np_view(ptr: int, dtype, count: int) -> np.ndarray:
@@ -251,6 +252,13 @@ class Batch:
 
     def filter_check(self, n: int, now_ns: int, flags: int = 0, wait: bool = True):
         self._ck(_lib.lib().bnk_filter_check_submit(self._h, n, flags, now_ns))
+        if wait:
+            self.wait()
+
+    def gso_split(self, supers: np.ndarray, n_pkts: int, flags: int = 0, wait: bool = True):
+        """supers: array of GSO_SUPER_DTYPE; segment descriptors (off, len, slot) must already be filled."""
+        supers = np.ascontiguousarray(supers, GSO_SUPER_DTYPE)
+        self._ck(_lib.lib().bnk_gso_split_submit(self._h, supers.ctypes.data, len(supers), n_pkts, flags))
         if wait:
             self.wait()
 

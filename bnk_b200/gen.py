@@ -363,3 +363,54 @@ def bulk_keys(plan: BulkSealPlan) -> np.ndarray:
 def shard_of_peer(peer_index: int, world: int) -> int:
     """Which GPU owns a peer: all mutable per-peer state lives on exactly one device."""
     return peer_index % world
+
+
+# ---------------------------------------------------------------------------------------
+# configuration 5: GSO super-packets, Zipf peer popularity
+# ---------------------------------------------------------------------------------------
+@dataclass
+class GsoWorkload:
+    supers: list                 # byte strings: IPv4 + TCP header (40 B) + n_seg * mss payload bytes
+    peer: np.ndarray             # [n_super] destination peer of each super-packet
+    peer_ip: np.ndarray          # [n_peers] tunnel address of each peer
+    self_ip: int
+    keys: np.ndarray             # [n_peers, 32]
+    mss: int
+    hdr_len: int = 40
+    csum_start: int = 20
+    csum_offset: int = 16
+
+
+def zipf_ranks(g: SplitMix64, n: int, n_items: int, s: float = 1.1) -> np.ndarray:
+    """n draws from Zipf(s) over ranks 0..n_items-1 by inverse CDF on a 53-bit uniform."""
+    w = 1.0 / np.power(np.arange(1, n_items + 1, dtype=np.float64), s)
+    cdf = np.cumsum(w) / w.sum()
+    u = (g.u64(n) >> np.uint64(11)).astype(np.float64) / float(1 << 53)
+    return np.minimum(np.searchsorted(cdf, u, side="left"), n_items - 1).astype(np.uint32)
+
+
+def config5(n_super: int = 64, n_peers: int = 10_000, n_seg: int = 47, mss: int = 1380, seed: int | None = None) -> GsoWorkload:
+    """Draw order: n_peers*32 key bytes; n_super Zipf(1.1) peer draws; per super-packet: source port,
+    destination port, sequence number, IP id (one u64 each), then n_seg*mss payload bytes.  Peer p has tunnel
+    address 100.64.0.0 + 256 + p."""
+    g = SplitMix64(seed_for(5) if seed is None else seed)
+    keys = g.bytes(n_peers * 32).reshape(n_peers, 32)
+    peer = zipf_ranks(g, n_super, n_peers)
+    self_ip = ip4(100, 64, 0, 1)
+    peer_ip = (ip4(100, 64, 0, 0) + 256 + np.arange(n_peers)).astype(np.uint64)
+    supers = []
+    for j in range(n_super):
+        sport = 1024 + g.one_below(60000)
+        dport = 1 + g.one_below(65535)
+        seq = g.one_below(1 << 32)
+        ipid = g.one_below(1 << 16)
+        payload = g.bytes(n_seg * mss).tobytes()
+        ip = bytearray(ipv4_header(6, self_ip, int(peer_ip[peer[j]]), 40 + len(payload)))
+        ip[4], ip[5] = ipid >> 8, ipid & 0xFF
+        tcp = bytearray(20)
+        tcp[0:4] = bytes(l4_ports(sport, dport))
+        tcp[4:8] = seq.to_bytes(4, "big")
+        tcp[12] = 5 << 4
+        tcp[13] = 0x18  # PSH | ACK
+        supers.append(bytes(ip) + bytes(tcp) + payload)
+    return GsoWorkload(supers=supers, peer=peer, peer_ip=peer_ip, self_ip=self_ip, keys=keys, mss=mss)

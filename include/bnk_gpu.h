@@ -192,6 +192,34 @@ int bnk_wait(bnk_batch *b, uint64_t timeout_ns);
 int bnk_batch_upload(bnk_batch *b, uint32_t npkts);
 int bnk_batch_download(bnk_batch *b, uint32_t npkts);
 
+/* ---- segmentation offload (GSO) ----
+ * Replaces the split wireguard-go's Linux TUN code performs on a super-packet read with a virtio-net
+ * header (TCP or UDP over IPv4) before the packets reach the encryption workers: every segment gets
+ * the IP and transport headers, its IPv4 total length, identification (first id + segment number) and
+ * header checksum, its TCP sequence number (first + segment number * gso_size) with FIN/PSH kept only
+ * on the last segment, or its UDP length, and a freshly computed transport checksum.
+ * Super-packet j is ring[src_off .. src_off+src_len); its segments are packets first_pkt .. first_pkt +
+ * n_pkts - 1 of the batch, whose off[], len[] (= hdr_len + segment payload) and slot[] the caller has
+ * filled; each segment is written at ring[off+16], ready for bnk_seal_submit(... BNK_F_NO_H2D ...).
+ * The submit copies ring, descriptors and `supers` to the device unless BNK_F_NO_H2D is given, and
+ * copies nothing back.  A segment whose descriptor does not match the split (wrong len, out of range,
+ * unsupported header layout) has its device-side slot[] set to an invalid keypair, so the seal that
+ * follows reports BNK_PKT_BAD_DESC for it. */
+typedef struct bnk_gso_super {
+    uint32_t src_off;     /* 4-byte aligned */
+    uint32_t src_len;
+    uint32_t first_pkt;
+    uint32_t n_pkts;
+    uint16_t hdr_len;     /* IP + transport header bytes (virtio hdr_len) */
+    uint16_t gso_size;    /* payload bytes per segment */
+    uint16_t csum_start;  /* IP header bytes (virtio csum_start) */
+    uint16_t csum_offset; /* 16 for TCP, 6 for UDP */
+    uint8_t proto;        /* 6 tcp, 17 udp */
+    uint8_t reserved[3];
+} bnk_gso_super;
+int bnk_gso_split_submit(bnk_batch *b, const bnk_gso_super *supers, uint32_t n_super, uint32_t n_pkts,
+                         uint32_t flags);
+
 /* ---- for callers that must not allocate ----
  * No counterpart in the reference.  A packet loop cannot call cudaMalloc or cudaFree (either one
  * stalls every stream of the device), and a caller that keeps packets in device buffers of its own,

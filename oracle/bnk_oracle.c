@@ -305,6 +305,74 @@ int bnko_inner_check(const uint8_t *pt, size_t len, uint32_t allowed_ip, size_t 
     return 1;
 }
 
+/* one's-complement sum of big-endian 16-bit words (RFC 1071), odd tail padded with a zero byte; NOT inverted */
+static uint32_t csum_add(const uint8_t *p, size_t len, uint32_t acc) {
+    uint64_t s = acc;
+    size_t i = 0;
+    for (; i + 1 < len; i += 2) s += ((uint32_t)p[i] << 8) | p[i + 1];
+    if (i < len) s += (uint32_t)p[i] << 8;
+    while (s >> 16) s = (s & 0xffff) + (s >> 16);
+    return (uint32_t)s;
+}
+
+uint16_t bnko_inet_checksum(const uint8_t *p, size_t len, uint32_t initial) {
+    return (uint16_t)~csum_add(p, len, initial);
+}
+
+int bnko_gso_split(const uint8_t *in, size_t in_len, unsigned hdr_len, unsigned gso_size, unsigned csum_start,
+                   unsigned csum_offset, unsigned proto, uint8_t *out, size_t out_stride, uint32_t *sizes,
+                   size_t max_segs) {
+    if ((proto != 6 && proto != 17) || csum_start < 20 || hdr_len <= csum_start || gso_size == 0 || in_len <= hdr_len ||
+        csum_offset + 2 > hdr_len - csum_start || (in[0] >> 4) != 4)
+        return -1;
+    const unsigned th = hdr_len - csum_start;
+    const uint32_t first_seq = proto == 6 ? (((uint32_t)in[csum_start + 4] << 24) | ((uint32_t)in[csum_start + 5] << 16) |
+                                             ((uint32_t)in[csum_start + 6] << 8) | in[csum_start + 7])
+                                          : 0;
+    const unsigned first_id = ((unsigned)in[4] << 8) | in[5];
+    size_t at = hdr_len, i = 0;
+    for (; at < in_len; i++, at += gso_size) {
+        if (i == max_segs) return -1;
+        size_t seg = in_len - at < gso_size ? in_len - at : gso_size;
+        size_t total = hdr_len + seg;
+        uint8_t *o = out + i * out_stride;
+        sizes[i] = (uint32_t)total;
+        memcpy(o, in, hdr_len);
+        unsigned id = (first_id + (unsigned)i) & 0xffff;
+        o[4] = (uint8_t)(id >> 8);
+        o[5] = (uint8_t)id;
+        o[2] = (uint8_t)(total >> 8);
+        o[3] = (uint8_t)total;
+        o[10] = o[11] = 0;
+        uint16_t ipc = bnko_inet_checksum(o, csum_start, 0);
+        o[10] = (uint8_t)(ipc >> 8);
+        o[11] = (uint8_t)ipc;
+        uint8_t *t = o + csum_start;
+        if (proto == 6) {
+            uint32_t seq = first_seq + (uint32_t)(i * gso_size);
+            t[4] = (uint8_t)(seq >> 24);
+            t[5] = (uint8_t)(seq >> 16);
+            t[6] = (uint8_t)(seq >> 8);
+            t[7] = (uint8_t)seq;
+            if (at + seg != in_len) t[13] &= (uint8_t)~0x09; /* FIN | PSH only on the last segment */
+        } else {
+            unsigned ulen = th + (unsigned)seg;
+            t[4] = (uint8_t)(ulen >> 8);
+            t[5] = (uint8_t)ulen;
+        }
+        t[csum_offset] = t[csum_offset + 1] = 0;
+        memcpy(o + hdr_len, in + at, seg);
+        /* pseudo header: src, dst, zero+proto, transport length */
+        uint32_t acc = csum_add(o + 12, 8, 0);
+        acc += proto;
+        acc += (uint32_t)(th + seg);
+        uint16_t tc = bnko_inet_checksum(t, th + seg, acc);
+        t[csum_offset] = (uint8_t)(tc >> 8);
+        t[csum_offset + 1] = (uint8_t)tc;
+    }
+    return (int)i;
+}
+
 /* Batch forms.  Packet i occupies ring[off[i] ...]: 16 bytes of header room, then
  * the payload.  Seal works in place (payload -> header|ciphertext|tag at off[i]);
  * open reads the message at off[i] and leaves the plaintext at off[i]+16. */

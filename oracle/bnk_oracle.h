@@ -77,6 +77,18 @@ int bnko_wg_open(const uint8_t key[32], const uint8_t *msg, size_t msg_len, uint
  * one /32, internal/dataplane/engine.go:294).  Returns 1 and the new length, or 0 = drop. */
 int bnko_inner_check(const uint8_t *pt, size_t len, uint32_t allowed_ip, size_t *new_len);
 
+/* Segmentation of an IPv4 TCP/UDP super-packet the way the upstream Linux TUN offload code splits a read that
+ * carries a virtio-net header (restated from its documented behaviour; the module is not in the reference tree):
+ * per segment the headers are copied, IPv4 id += segment number, total length and header checksum are rewritten,
+ * TCP sequence += segment number * gso_size with FIN/PSH only on the last segment, UDP length is rewritten, and
+ * the transport checksum is recomputed.  Segment i is written at out + i*out_stride, its length to sizes[i].
+ * Returns the number of segments, or -1 when the headers are inconsistent or max_segs is too small. */
+int bnko_gso_split(const uint8_t *in, size_t in_len, unsigned hdr_len, unsigned gso_size, unsigned csum_start,
+                   unsigned csum_offset, unsigned proto, uint8_t *out, size_t out_stride, uint32_t *sizes,
+                   size_t max_segs);
+/* RFC 1071 checksum helpers, for tests */
+uint16_t bnko_inet_checksum(const uint8_t *p, size_t len, uint32_t initial);
+
 /* batch forms over a packet ring (same descriptor layout as the GPU library) */
 void bnko_wg_seal_batch(const uint8_t *keys /* n_keys*32 */, const uint32_t *remote_index /* n_keys */,
                         size_t mtu, uint8_t *ring, const uint32_t *off, const uint32_t *len,

@@ -82,6 +82,10 @@ def lib() -> C.CDLL:
     L.bnko_wg_open.restype = C.c_int
     L.bnko_inner_check.argtypes = [vp, sz, C.c_uint32, C.POINTER(sz)]
     L.bnko_inner_check.restype = C.c_int
+    L.bnko_gso_split.argtypes = [vp, sz, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint, vp, sz, vp, sz]
+    L.bnko_gso_split.restype = C.c_int
+    L.bnko_inet_checksum.argtypes = [vp, sz, C.c_uint32]
+    L.bnko_inet_checksum.restype = C.c_uint16
     L.bnko_wg_seal_batch.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, vp, vp, sz]
     L.bnko_wg_seal_batch.restype = None
     L.bnko_wg_open_batch.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz]
@@ -185,6 +189,23 @@ def inner_check(pt: bytes, allowed_ip: int):
     nl = C.c_size_t(0)
     ok = lib().bnko_inner_check(_buf(pt), len(pt), allowed_ip, C.byref(nl))
     return nl.value if ok else None
+
+
+def gso_split(pkt: bytes, hdr_len: int, gso_size: int, csum_start: int, csum_offset: int, proto: int):
+    """-> list of segments (bytes), or None when the split is refused."""
+    max_segs = max(1, (len(pkt) - hdr_len + gso_size - 1) // max(gso_size, 1)) + 1
+    stride = hdr_len + gso_size + 8
+    out = np.zeros(max_segs * stride, np.uint8)
+    sizes = np.zeros(max_segs, np.uint32)
+    n = lib().bnko_gso_split(_buf(pkt), len(pkt), hdr_len, gso_size, csum_start, csum_offset, proto, _ptr(out), stride,
+                             _ptr(sizes), max_segs)
+    if n < 0:
+        return None
+    return [out[i * stride:i * stride + int(sizes[i])].tobytes() for i in range(n)]
+
+
+def inet_checksum(data: bytes, initial: int = 0) -> int:
+    return lib().bnko_inet_checksum(_buf(data), len(data), initial)
 
 
 def wg_seal_batch(keys, remote_index, mtu, ring, off, length, slot, counter):
