@@ -2,29 +2,33 @@
 //
 // Work mapping: one thread owns one packet from the first ChaCha20 block to the
 // Poly1305 tag, so every lane of a warp does useful 32-bit integer work on every
-// instruction (the path is bound by the integer pipes, not by HBM: ~19 integer
-// operations per payload byte against ~2 bytes of traffic per payload byte).
-// A warp therefore holds 32 packets.  Their payloads sit a slot stride apart in
-// the ring, so the warp moves them through shared memory: in every 64-byte step
-// the 32 lanes fetch 32 x 64 B as four 512-byte wavefronts of 16-byte cp.async
-// copies (4 lanes cover one packet's 64 B, i.e. whole 32-byte sectors), double
-// buffered so the next step's bytes are in flight while this step's 80 quarter
-// rounds run; results go back through the same buffer with 128-bit stores.
+// instruction.  The path is bound by instruction issue on the integer pipes, not
+// by HBM: ~19 integer operations per payload byte against ~2 bytes of traffic
+// per payload byte, and the rotations of ChaCha20 issue at half rate on sm_100.
+//
+// Data movement is therefore kept to the fewest instructions: per 64-byte step a
+// lane issues four 16-byte loads of its own packet ahead of the step's 80 quarter
+// rounds (the rounds hide the latency; the two loads that share a 32-byte sector
+// meet in L1) and four 16-byte stores after them (L2 merges the half sectors
+// before they reach HBM).  No shared memory, no barriers, no cross-lane traffic:
+// staging the 32 packets of a warp through shared memory so that global accesses
+// are 512-byte wavefronts was measured and is 6 % slower, because its address
+// arithmetic, shuffles and barriers cost issue slots that the rounds need.
 //
 // Arithmetic: ChaCha20 is RFC 8439 section 2.3 on 16 registers (rotations by 16
 // and 8 are byte permutes, by 12 and 7 funnel shifts).  Poly1305 keeps h in five
-// 32-bit limbs (radix 2^32) and multiplies with 32x32->64 multiply-adds, which
-// issue on the FMA pipe and so overlap the ALU-pipe ChaCha work of other warps.
-// The MAC input is ciphertext | zero pad to 16 | le64(0) | le64(ct_len), RFC 8439
-// section 2.8 with empty AAD; nonce = 32 zero bits | le64(counter) and the header
-// is le32(4) | le32(receiver index) | le64(counter) (WireGuard whitepaper 5.4.6).
+// 32-bit limbs (radix 2^32) and multiplies with 32x32->64 multiply-adds on the
+// FMA pipe.  The MAC input is ciphertext | zero pad to 16 | le64(0) | le64(ct_len),
+// RFC 8439 section 2.8 with empty AAD; nonce = 32 zero bits | le64(counter) and the
+// header is le32(4) | le32(receiver index) | le64(counter) (WireGuard whitepaper 5.4.6).
 #include "bnk_internal.cuh"
 
 namespace {
 
-// Occupancy target for the register allocator: 5 CTAs of 128 threads per SM (96 registers).
+// Occupancy target for the register allocator: 4 CTAs of 128 threads per SM (up to 128 registers, no
+// spills).  Measured within 2 % of each other: 3..6 CTAs of 128 threads, 3 CTAs of 256, 10 CTAs of 64.
 #ifndef BNK_MIN_CTAS
-#define BNK_MIN_CTAS 5
+#define BNK_MIN_CTAS 4
 #endif
 #ifndef BNK_WARPS_PER_CTA
 #define BNK_WARPS_PER_CTA 4
@@ -209,34 +213,12 @@ __device__ __forceinline__ uint32_t wg_padded_len(uint32_t len, uint32_t mtu) {
     return len + (padded - last);
 }
 
-__device__ __forceinline__ void cp_async16(void *smem, const void *gmem, bool real) {
-    uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-    int bytes = real ? 16 : 0; // 0 source bytes = fill the 16 destination bytes with zeros
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-// position (in 16-byte units) of chunk c of row p in a warp's 32 x 64 B staging
-// tile; the XOR keeps both the row-wise (owner) and the 4-lanes-per-row
-// (cooperative) access patterns free of bank conflicts
-__device__ __forceinline__ int tile_pos(int row, int chunk) { return row * 4 + (chunk ^ ((row >> 1) & 3)); }
-
 // ---------------------------------------------------------------------------
 // The kernel.  OPEN=false: seal in place.  OPEN=true: authenticate + decrypt in place.
 // ---------------------------------------------------------------------------
 template <bool OPEN>
 __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const AeadArgs a) {
-    __shared__ uint4 tiles[kWarpsPerCta][2][128];
-
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    uint4 *tile0 = tiles[warp][0];
-    uint4 *tile1 = tiles[warp][1];
-    const uint32_t idx = (blockIdx.x * kWarpsPerCta + warp) * 32u + lane;
+    const uint32_t idx = blockIdx.x * kThreads + threadIdx.x;
     const bool have = idx < a.n;
     const uint32_t pkt = have ? (a.order ? a.order[idx] : idx) : 0u;
 
@@ -295,8 +277,7 @@ __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const Aead
         }
     }
     const uint32_t nblk = (body + 63u) >> 6;
-    const uint32_t wmax = __reduce_max_sync(0xffffffffu, nblk);
-    const uint32_t data_off = off + BNK_WG_HEADER;
+    uint8_t *const data = a.ring + (size_t)off + BNK_WG_HEADER; // 16-byte aligned
 
     uint32_t key[8];
     Poly poly;
@@ -316,95 +297,56 @@ __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const Aead
         poly_init(poly, 0, 0, 0, 0);
     }
 
-    // fetch step b of all 32 packets of the warp into a tile
-    auto fetch = [&](uint32_t b, uint4 *tile) {
+    for (uint32_t b = 0; b < nblk; b++) {
+        const uint32_t base = b * 64u;
+        uint32_t d[16];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const int row = q * 8 + (lane >> 2);
-            const int chunk = lane & 3;
-            const uint32_t r_in = __shfl_sync(0xffffffffu, in_len, row);
-            const uint32_t r_off = __shfl_sync(0xffffffffu, data_off, row);
-            const uint32_t pos = b * 64u + chunk * 16u;
-            const bool real = pos < r_in;
-            const uint8_t *src = a.ring + (real ? (size_t)r_off + pos : (size_t)0);
-            cp_async16(&tile[tile_pos(row, chunk)], src, real);
+        for (int c = 0; c < 4; c++) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            // a chunk that starts inside the input is read whole: the bytes past in_len lie in the packet's own
+            // padding / tag room and are masked below
+            if (base + 16u * c < in_len) v = *reinterpret_cast<const uint4 *>(data + base + 16u * c);
+            d[4 * c + 0] = v.x; d[4 * c + 1] = v.y; d[4 * c + 2] = v.z; d[4 * c + 3] = v.w;
         }
-        cp_async_commit();
-    };
-
-    if (wmax) fetch(0, tile0);
-    for (uint32_t b = 0; b < wmax; b++) {
-        uint4 *tile = (b & 1) ? tile1 : tile0;
-        if (b + 1 < wmax) {
-            fetch(b + 1, (b & 1) ? tile0 : tile1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncwarp();
-
-        if (b < nblk) {
-            uint32_t x[16];
-            chacha20_block(x, key, b + 1u, n_lo, n_hi);
-            uint32_t d[16];
+        uint32_t x[16];
+        chacha20_block(x, key, b + 1u, n_lo, n_hi);
+        if (base + 64u <= in_len) {
+            // whole block of real bytes
 #pragma unroll
             for (int c = 0; c < 4; c++) {
-                const uint4 v = tile[tile_pos(lane, c)];
-                d[4 * c + 0] = v.x; d[4 * c + 1] = v.y; d[4 * c + 2] = v.z; d[4 * c + 3] = v.w;
+                const uint32_t o0 = d[4 * c + 0] ^ x[4 * c + 0], o1 = d[4 * c + 1] ^ x[4 * c + 1];
+                const uint32_t o2 = d[4 * c + 2] ^ x[4 * c + 2], o3 = d[4 * c + 3] ^ x[4 * c + 3];
+                if (OPEN) poly_block(poly, d[4 * c + 0], d[4 * c + 1], d[4 * c + 2], d[4 * c + 3]);
+                else poly_block(poly, o0, o1, o2, o3);
+                *reinterpret_cast<uint4 *>(data + base + 16u * c) = make_uint4(o0, o1, o2, o3);
             }
-            const uint32_t base = b * 64u;
-            if (base + 64u <= in_len) {
-                // whole block of real bytes
+        } else {
+            // ragged end: bytes past in_len are zero padding (seal) and bytes past body do not exist
+            const int in_left = (int)in_len - (int)base;
+            const int body_left = (int)body - (int)base;
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    uint32_t o0 = d[4 * c + 0] ^ x[4 * c + 0], o1 = d[4 * c + 1] ^ x[4 * c + 1];
-                    uint32_t o2 = d[4 * c + 2] ^ x[4 * c + 2], o3 = d[4 * c + 3] ^ x[4 * c + 3];
-                    if (OPEN) poly_block(poly, d[4 * c + 0], d[4 * c + 1], d[4 * c + 2], d[4 * c + 3]);
-                    else poly_block(poly, o0, o1, o2, o3);
-                    tile[tile_pos(lane, c)] = make_uint4(o0, o1, o2, o3);
+            for (int c = 0; c < 4; c++) {
+                uint32_t o[4], m[4];
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const int k = 16 * c + 4 * w;
+                    const uint32_t in_w = keep_bytes(d[4 * c + w], in_left - k);
+                    o[w] = keep_bytes(in_w ^ x[4 * c + w], body_left - k);
+                    m[w] = OPEN ? in_w : o[w];
                 }
-            } else {
-                // ragged end: bytes past in_len are zero padding (seal) and bytes past body do not exist
-                const int in_left = (int)in_len - (int)base;
-                const int body_left = (int)body - (int)base;
+                if (16 * c < body_left) poly_block(poly, m[0], m[1], m[2], m[3]);
+                if (16 * c + 16 <= body_left) {
+                    *reinterpret_cast<uint4 *>(data + base + 16u * c) = make_uint4(o[0], o[1], o[2], o[3]);
+                } else if (16 * c < body_left) {
+                    // last, partial chunk: byte stores
+                    uint8_t *dst = data + base + 16u * c;
+                    const int tail = body_left - 16 * c;
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    uint32_t o[4], m[4];
-#pragma unroll
-                    for (int w = 0; w < 4; w++) {
-                        const int k = 16 * c + 4 * w;
-                        const uint32_t in_w = keep_bytes(d[4 * c + w], in_left - k);
-                        o[w] = keep_bytes(in_w ^ x[4 * c + w], body_left - k);
-                        m[w] = OPEN ? in_w : o[w];
-                    }
-                    if (16 * c < body_left) poly_block(poly, m[0], m[1], m[2], m[3]);
-                    tile[tile_pos(lane, c)] = make_uint4(o[0], o[1], o[2], o[3]);
+                    for (int k = 0; k < 15; k++)
+                        if (k < tail) dst[k] = (uint8_t)(o[k >> 2] >> (8 * (k & 3)));
                 }
             }
         }
-        __syncwarp();
-
-        // write back the whole 16-byte chunks of this step, 4 lanes per packet
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const int row = q * 8 + (lane >> 2);
-            const int chunk = lane & 3;
-            const uint32_t r_body = __shfl_sync(0xffffffffu, body, row);
-            const uint32_t r_off = __shfl_sync(0xffffffffu, data_off, row);
-            const uint32_t pos = b * 64u + chunk * 16u;
-            if (pos + 16u <= r_body)
-                *reinterpret_cast<uint4 *>(a.ring + (size_t)r_off + pos) = tile[tile_pos(row, chunk)];
-        }
-        // the owner writes the last, partial chunk byte by byte
-        if (b + 1 == nblk && (body & 15u)) {
-            const uint32_t tail = body & 15u;
-            const uint32_t pos = body - tail;
-            const int chunk = (int)((pos >> 4) & 3u);
-            const uint8_t *src = reinterpret_cast<const uint8_t *>(&tile[tile_pos(lane, chunk)]);
-            uint8_t *dst = a.ring + (size_t)data_off + pos;
-            for (uint32_t k = 0; k < tail; k++) dst[k] = src[k];
-        }
-        __syncwarp();
     }
 
     if (!live) return;
@@ -414,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const Aead
     poly_block(poly, 0u, 0u, body, 0u);
     uint32_t tag[4];
     poly_finish(poly, pad, tag);
-    uint8_t *tagp = a.ring + (size_t)data_off + body;
+    uint8_t *tagp = data + body;
 
     if (!OPEN) {
         *reinterpret_cast<uint4 *>(a.ring + off) = make_uint4(4u, a.remote_index[slot], n_lo, n_hi);
@@ -445,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const Aead
             a.out_len[pkt] = body;
         } else {
             // forged or damaged: no plaintext may leave, wipe what the fused pass wrote
-            uint8_t *dst = a.ring + (size_t)data_off;
+            uint8_t *dst = data;
             uint32_t k = 0;
             for (; k + 16u <= body; k += 16u) *reinterpret_cast<uint4 *>(dst + k) = make_uint4(0, 0, 0, 0);
             for (; k < body; k++) dst[k] = 0;

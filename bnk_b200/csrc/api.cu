@@ -428,7 +428,7 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     D((void **)&d.order, n * 4);
     D((void **)&d.order_tmp, n * 4);
     D((void **)&d.keys_tmp, 2 * n * 4);
-    D((void **)&d.hist, (size_t)512 * group_sort_chunks(max_pkts) * 4);
+    D((void **)&d.hist, (size_t)512 * group_sort_chunks(max_pkts) * 4); // histogram columns + one row of totals
     D((void **)&d.len_order, n * 4);
     D((void **)&d.counters32, 2048 * 4);
     D((void **)&d.gso, n * sizeof(bnk_gso_super));

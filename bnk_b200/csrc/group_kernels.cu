@@ -12,13 +12,12 @@
 
 namespace {
 
-constexpr uint32_t kSortThreads = 256;                  // 8 warps per CTA
+constexpr uint32_t kSortThreads = 256; // 8 warps per CTA
 constexpr uint32_t kSortWarps = kSortThreads / 32;
-constexpr uint32_t kTilesPerWarp = 32;                  // a lane keeps 32 keys in registers
-constexpr uint32_t kWarpSpan = 32 * kTilesPerWarp;      // 1024 consecutive elements per warp
-constexpr uint32_t kChunk = kSortWarps * kWarpSpan;     // 8192 elements per CTA
+constexpr uint32_t kMaxTiles = 32;     // a lane keeps up to 32 keys in registers
 constexpr uint32_t kMaxDigitBits = 9;
 constexpr uint32_t kMaxBins = 1u << kMaxDigitBits;
+constexpr uint32_t kBatchMaxChunks = 320; // ~2 CTAs per SM: enough to fill the GPU, few enough to scan quickly
 
 struct SortKeySrc {
     const uint32_t *slot;
@@ -44,8 +43,12 @@ __device__ __forceinline__ void warp_hist_add(uint32_t *cnt, uint32_t digit, boo
     if (have && (__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&cnt[digit], __popc(peers));
 }
 
+// A CTA owns a chunk of 256 * TILES consecutive elements; warp w owns the 32 * TILES consecutive
+// elements [w * 32 * TILES, (w + 1) * 32 * TILES) of it.
+
 // --- pass step 1: per-chunk digit histogram -------------------------------------------
 // grid = chunks, block = 256.  hist is digit-major: hist[digit * chunks + chunk].
+template <uint32_t TILES>
 __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(SortKeySrc src, const uint32_t *keys_in,
                                                                   uint32_t n, uint32_t shift, uint32_t bins,
                                                                   uint32_t chunks, uint32_t *hist) {
@@ -53,10 +56,11 @@ __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(SortKeySrc src
     const uint32_t tid = threadIdx.x, chunk = blockIdx.x;
     for (uint32_t d = tid; d < bins; d += kSortThreads) cnt[d] = 0;
     __syncthreads();
-    const uint32_t begin = chunk * kChunk;
-    const uint32_t end = min(n, begin + kChunk);
-    for (uint32_t base = begin; base < end; base += kSortThreads) { // uniform trip count per warp
-        const uint32_t i = base + tid;
+    const uint32_t begin = chunk * (kSortThreads * TILES);
+    const uint32_t end = min(n, begin + kSortThreads * TILES);
+#pragma unroll
+    for (uint32_t t = 0; t < TILES; t++) {
+        const uint32_t i = begin + t * kSortThreads + tid;
         const bool have = i < end;
         uint32_t digit = 0;
         if (have) digit = ((keys_in ? keys_in[i] : slot_key(src, i)) >> shift) & (bins - 1);
@@ -66,9 +70,32 @@ __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(SortKeySrc src
     for (uint32_t d = tid; d < bins; d += kSortThreads) hist[d * chunks + chunk] = cnt[d];
 }
 
-// --- pass step 2: exclusive scan of the histogram (single CTA) -------------------------
-// Tiles of 4096 values; each thread owns 4 consecutive ones, warps combine with shuffles
-// and a running carry links the tiles.
+// --- pass step 2: per digit, exclusive prefix over the chunks -------------------------
+// One warp per digit row (coalesced: the row is contiguous).  Row totals go to totals[digit]; the
+// scatter kernel turns them into digit bases on its own.
+__global__ void __launch_bounds__(kSortThreads) radix_rowscan_kernel(uint32_t *hist, uint32_t bins, uint32_t chunks,
+                                                                     uint32_t *totals) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t d = (blockIdx.x * kSortThreads + threadIdx.x) >> 5;
+    if (d >= bins) return;
+    uint32_t *row = hist + (size_t)d * chunks;
+    uint32_t carry = 0;
+    for (uint32_t base = 0; base < chunks; base += 32) {
+        const uint32_t c = base + lane;
+        const uint32_t v = c < chunks ? row[c] : 0u;
+        uint32_t incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= (uint32_t)o) incl += t;
+        }
+        if (c < chunks) row[c] = carry + incl - v;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) totals[d] = carry;
+}
+
+// --- exclusive scan of a small array by one CTA (length-class bins) ---------------------
 __global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t *data, uint32_t n) {
     __shared__ uint32_t warp_off[32];
     __shared__ uint32_t carry_s;
@@ -113,34 +140,55 @@ __global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t *data, ui
 }
 
 // --- pass step 3: stable scatter --------------------------------------------------------
-// grid = chunks, block = 256.  Warp w owns the 1024 consecutive elements [w*1024, (w+1)*1024) of
-// the chunk and keeps their keys in registers.  (A) every warp counts its digits, (B) the counts
-// become start positions: global start of the digit for this chunk, plus the counts of the warps
-// before, (C) every warp walks its elements in order, 32 at a time; lanes holding the same digit
-// find each other with match_any and take consecutive positions, so equal digits keep their
-// input order.  No per-element atomics on global memory.
+// grid = chunks, block = 256.  (A) every warp counts the digits of its elements (kept in registers),
+// (B) the counts become start positions: base of the digit (exclusive prefix of the row totals, done
+// here per CTA) + the digit's elements in earlier chunks + the counts of the warps before,
+// (C) every warp walks its elements in order, 32 at a time; lanes holding the same digit find each
+// other with match_any and take consecutive positions, so equal digits keep their input order.
+// No per-element atomics on global memory.
+template <uint32_t TILES>
 __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(SortKeySrc src, const uint32_t *keys_in,
                                                                      const uint32_t *vals_in, uint32_t n,
                                                                      uint32_t shift, uint32_t bins, uint32_t chunks,
-                                                                     const uint32_t *hist, uint32_t *keys_out,
-                                                                     uint32_t *vals_out) {
+                                                                     const uint32_t *hist, const uint32_t *totals,
+                                                                     uint32_t *keys_out, uint32_t *vals_out) {
     __shared__ uint32_t cur[kSortWarps][kMaxBins];
+    __shared__ uint32_t base_of[kMaxBins];
+    __shared__ uint32_t warp_sum[kSortWarps];
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, chunk = blockIdx.x;
     for (uint32_t d = tid; d < kSortWarps * kMaxBins; d += kSortThreads) (&cur[0][0])[d] = 0;
     __syncthreads();
-    const uint32_t begin = chunk * kChunk + warp * kWarpSpan;
-    const uint32_t end = min(n, chunk * kChunk + kChunk);
-    uint32_t key[kTilesPerWarp];
+    const uint32_t begin = chunk * (kSortThreads * TILES) + warp * (32 * TILES);
+    const uint32_t end = min(n, (chunk + 1) * (kSortThreads * TILES));
+    uint32_t key[TILES];
 #pragma unroll
-    for (uint32_t t = 0; t < kTilesPerWarp; t++) {
+    for (uint32_t t = 0; t < TILES; t++) {
         const uint32_t i = begin + t * 32 + lane;
         const bool have = i < end;
         key[t] = have ? (keys_in ? keys_in[i] : slot_key(src, i)) : 0xffffffffu;
         warp_hist_add(cur[warp], (key[t] >> shift) & (bins - 1), have);
     }
+    // digit bases: exclusive prefix over totals[0..bins), two digits per thread (bins <= 512)
+    {
+        const uint32_t d0 = 2 * tid, d1 = 2 * tid + 1;
+        const uint32_t v0 = d0 < bins ? totals[d0] : 0u, v1 = d1 < bins ? totals[d1] : 0u;
+        uint32_t incl = v0 + v1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= (uint32_t)o) incl += t;
+        }
+        if (lane == 31) warp_sum[warp] = incl;
+        __syncthreads();
+        uint32_t before = 0;
+        for (uint32_t w = 0; w < warp; w++) before += warp_sum[w];
+        const uint32_t excl = before + incl - (v0 + v1);
+        if (d0 < bins) base_of[d0] = excl;
+        if (d1 < bins) base_of[d1] = excl + v0;
+    }
     __syncthreads();
     for (uint32_t d = tid; d < bins; d += kSortThreads) {
-        uint32_t run = hist[d * chunks + chunk];
+        uint32_t run = base_of[d] + hist[d * chunks + chunk];
 #pragma unroll
         for (uint32_t w = 0; w < kSortWarps; w++) {
             const uint32_t c = cur[w][d];
@@ -152,7 +200,7 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(SortKeySrc 
     const uint32_t lt = (1u << lane) - 1u;
     uint32_t *mine = cur[warp];
 #pragma unroll
-    for (uint32_t t = 0; t < kTilesPerWarp; t++) {
+    for (uint32_t t = 0; t < TILES; t++) {
         const uint32_t i = begin + t * 32 + lane;
         const bool have = i < end;
         const uint32_t digit = have ? ((key[t] >> shift) & (bins - 1)) : 0xffffffffu;
@@ -283,9 +331,65 @@ SortPlan plan_for(uint32_t max_slots) {
     return p;
 }
 
+// elements per lane: the smallest power of two that keeps the chunk count at or below max_chunks
+uint32_t tiles_for(uint32_t n, uint32_t max_chunks) {
+    uint32_t tiles = 1;
+    while (tiles < kMaxTiles && (n + kSortThreads * tiles - 1) / (kSortThreads * tiles) > max_chunks) tiles <<= 1;
+    return tiles;
+}
+uint32_t chunks_for(uint32_t n, uint32_t tiles) { return (n + kSortThreads * tiles - 1) / (kSortThreads * tiles); }
+
+struct SortBuffers {
+    uint32_t *keys_a, *keys_b; // the sorted keys end up in keys_b
+    uint32_t *vals_a, *order;  // the sorted packet indices end up in order
+    uint32_t *hist;            // [bins * chunks]
+    uint32_t *totals;          // [bins]
+};
+
+template <uint32_t TILES>
+void sort_pass(const SortKeySrc &src, const uint32_t *kin, const uint32_t *vin, uint32_t n, uint32_t shift,
+               uint32_t bins, uint32_t chunks, const SortBuffers &sb, uint32_t *kout, uint32_t *vout, cudaStream_t s) {
+    radix_hist_kernel<TILES><<<chunks, kSortThreads, 0, s>>>(src, kin, n, shift, bins, chunks, sb.hist);
+    radix_rowscan_kernel<<<(bins * 32 + kSortThreads - 1) / kSortThreads, kSortThreads, 0, s>>>(sb.hist, bins, chunks,
+                                                                                               sb.totals);
+    radix_scatter_kernel<TILES><<<chunks, kSortThreads, 0, s>>>(src, kin, vin, n, shift, bins, chunks, sb.hist, sb.totals,
+                                                               kout, vout);
+}
+
+// Stable sort of packet indices 0..n-1 by key.  Returns the number of kernel launches.
+uint32_t group_sort(const SortKeySrc &src, uint32_t n, uint32_t max_chunks, const SortBuffers &sb, cudaStream_t s) {
+    const SortPlan plan = plan_for(src.max_slots);
+    const uint32_t bins = 1u << plan.digit_bits;
+    const uint32_t tiles = tiles_for(n, max_chunks);
+    const uint32_t chunks = chunks_for(n, tiles);
+    // ping-pong so that the last pass lands in (keys_b, order)
+    uint32_t *kbuf[2] = {sb.keys_b, sb.keys_a};
+    uint32_t *vbuf[2] = {sb.order, sb.vals_a};
+    const uint32_t *kin = nullptr, *vin = nullptr;
+    for (uint32_t p = 0; p < plan.passes; p++) {
+        const uint32_t shift = p * plan.digit_bits;
+        const uint32_t o = (plan.passes - 1 - p) & 1u;
+        switch (tiles) {
+        case 1: sort_pass<1>(src, kin, vin, n, shift, bins, chunks, sb, kbuf[o], vbuf[o], s); break;
+        case 2: sort_pass<2>(src, kin, vin, n, shift, bins, chunks, sb, kbuf[o], vbuf[o], s); break;
+        case 4: sort_pass<4>(src, kin, vin, n, shift, bins, chunks, sb, kbuf[o], vbuf[o], s); break;
+        case 8: sort_pass<8>(src, kin, vin, n, shift, bins, chunks, sb, kbuf[o], vbuf[o], s); break;
+        case 16: sort_pass<16>(src, kin, vin, n, shift, bins, chunks, sb, kbuf[o], vbuf[o], s); break;
+        default: sort_pass<32>(src, kin, vin, n, shift, bins, chunks, sb, kbuf[o], vbuf[o], s); break;
+        }
+        kin = kbuf[o];
+        vin = vbuf[o];
+    }
+    return 3 * plan.passes;
+}
+
 } // namespace
 
-uint32_t group_sort_chunks(uint32_t max_pkts) { return (max_pkts + kChunk - 1) / kChunk; }
+// words of histogram scratch a batch of max_pkts packets needs
+uint32_t group_sort_chunks(uint32_t max_pkts) {
+    const uint32_t worst = chunks_for(max_pkts, kMaxTiles);
+    return (worst > kBatchMaxChunks ? worst : kBatchMaxChunks) + 1; // + one row of digit totals
+}
 
 // Sorts packet indices 0..n-1 by keypair slot, stable.  Leaves the sorted keys in
 // dev.keys_tmp (second half) and the packet indices in dev.order.
@@ -293,25 +397,9 @@ cudaError_t launch_group_by_slot(bnk_batch *b, uint32_t n, bool only_status_ok, 
     if (n == 0) return cudaSuccess;
     bnk_ctx *ctx = b->ctx;
     DeviceBatch &d = b->dev;
-    const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
-    const uint32_t bins = 1u << plan.digit_bits;
-    const uint32_t chunks = (n + kChunk - 1) / kChunk;
     SortKeySrc src{d.slot, d.status, ctx->cfg.max_keypairs, only_status_ok ? 1 : 0};
-    // ping-pong so that the last pass lands in (keys_tmp + max_pkts, order)
-    uint32_t *kbuf[2] = {d.keys_tmp + b->max_pkts, d.keys_tmp};
-    uint32_t *vbuf[2] = {d.order, d.order_tmp};
-    const uint32_t *kin = nullptr, *vin = nullptr;
-    for (uint32_t p = 0; p < plan.passes; p++) {
-        const uint32_t shift = p * plan.digit_bits;
-        const uint32_t o = (plan.passes - 1 - p) & 1u;
-        radix_hist_kernel<<<chunks, kSortThreads, 0, s>>>(src, kin, n, shift, bins, chunks, d.hist);
-        exclusive_scan_kernel<<<1, 1024, 0, s>>>(d.hist, bins * chunks);
-        radix_scatter_kernel<<<chunks, kSortThreads, 0, s>>>(src, kin, vin, n, shift, bins, chunks, d.hist, kbuf[o],
-                                                            vbuf[o]);
-        ctx->launches += 3;
-        kin = kbuf[o];
-        vin = vbuf[o];
-    }
+    SortBuffers sb{d.keys_tmp, d.keys_tmp + b->max_pkts, d.order_tmp, d.order, d.hist + kMaxBins, d.hist};
+    ctx->launches += group_sort(src, n, kBatchMaxChunks, sb, s);
     return cudaGetLastError();
 }
 
@@ -371,9 +459,9 @@ cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, b
 namespace {
 
 constexpr uint32_t kNoAllocMaxPkts = BNK_NOALLOC_MAX_PKTS;
-constexpr uint32_t kNoAllocChunks = (kNoAllocMaxPkts + kChunk - 1) / kChunk;
-constexpr size_t kNoAllocWords = (size_t)5 * kNoAllocMaxPkts + 16384; // 384 KiB; the histogram needs kMaxBins * kNoAllocChunks words
-static_assert((size_t)kMaxBins * kNoAllocChunks <= 16384, "histogram region too small");
+constexpr uint32_t kNoAllocMaxChunks = 31; // (31 chunk columns + 1 row of totals) * 512 bins = the 16384-word histogram region
+constexpr size_t kNoAllocWords = (size_t)5 * kNoAllocMaxPkts + 16384; // 384 KiB
+static_assert((size_t)kMaxBins * (kNoAllocMaxChunks + 1) <= 16384, "histogram region too small");
 
 static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocWords];
 
@@ -428,25 +516,12 @@ extern "C" int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uin
     const uint32_t n = npkts, cap = kNoAllocMaxPkts;
     uint32_t *keys_a = base, *keys_b = base + cap, *vals_a = base + 2 * cap, *order = base + 3 * cap;
     uint32_t *hist = base + 5 * cap; // [4*cap, 5*cap) is spare
-    const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
-    const uint32_t bins = 1u << plan.digit_bits;
-    const uint32_t chunks = (n + kChunk - 1) / kChunk;
     SortKeySrc src{dev_slot, nullptr, ctx->cfg.max_keypairs, 0};
-    uint32_t *kbuf[2] = {keys_b, keys_a};
-    uint32_t *vbuf[2] = {order, vals_a};
-    const uint32_t *kin = nullptr, *vin = nullptr;
-    for (uint32_t p = 0; p < plan.passes; p++) {
-        const uint32_t shift = p * plan.digit_bits;
-        const uint32_t o = (plan.passes - 1 - p) & 1u;
-        radix_hist_kernel<<<chunks, kSortThreads, 0, s>>>(src, kin, n, shift, bins, chunks, hist);
-        exclusive_scan_kernel<<<1, 1024, 0, s>>>(hist, bins * chunks);
-        radix_scatter_kernel<<<chunks, kSortThreads, 0, s>>>(src, kin, vin, n, shift, bins, chunks, hist, kbuf[o], vbuf[o]);
-        kin = kbuf[o];
-        vin = vbuf[o];
-    }
+    SortBuffers sb{keys_a, keys_b, vals_a, order, hist + kMaxBins, hist};
+    const uint32_t sort_launches = group_sort(src, n, kNoAllocMaxChunks, sb, s);
     assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, order, nullptr, n, ctx->cfg.max_keypairs,
                                                           ctx->kt.send_counter, dev_counter);
-    ctx->launches += 3 * plan.passes + 1;
+    ctx->launches += sort_launches + 1;
     if ((e = cudaGetLastError()) != cudaSuccess) return noalloc_fail(ctx, BNK_ECUDA, "kernel launch", e);
     return BNK_SUCCESS;
 }
