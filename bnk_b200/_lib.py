@@ -84,8 +84,12 @@ class BatchView(C.Structure):
         ("ring_bytes", C.c_uint64),
         ("max_pkts", C.c_uint32),
         ("reserved", C.c_uint32),
+        ("src_addr", C.c_void_p),
     ]
 
+
+SRC_ADDR_STRIDE = 20
+CLASS_WIREGUARD, CLASS_DISCO, CLASS_STUN, CLASS_STRANGER = 0, 10, 11, 12
 
 # every symbol include/bnk_gpu.h declares: name -> (restype, argtypes)
 _vp, _i, _u32, _u64, _i64, _sz = C.c_void_p, C.c_int, C.c_uint32, C.c_uint64, C.c_int64, C.c_size_t
@@ -117,6 +121,9 @@ SYMBOLS = {
     "bnk_open_submit": (_i, [_vp, _u32, _u32, _i64]),
     "bnk_filter_note_submit": (_i, [_vp, _u32, _u32, _i64]),
     "bnk_filter_check_submit": (_i, [_vp, _u32, _u32, _i64]),
+    "bnk_addr_set": (_i, [_vp, _vp, C.c_uint16, _u32]),
+    "bnk_addr_clear": (_i, [_vp, _vp, C.c_uint16]),
+    "bnk_classify_submit": (_i, [_vp, _u32, _u32]),
     "bnk_gso_split_submit": (_i, [_vp, _vp, _u32, _u32, _u32]),
     "bnk_wait": (_i, [_vp, _u64]),
     "bnk_batch_upload": (_i, [_vp, _u32]),

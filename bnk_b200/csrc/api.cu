@@ -167,6 +167,9 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     ctx->index_keys_host.assign(islots, 0);
     if ((e = dev_alloc_zero(&ctx->kt.index_keys, (size_t)islots)) != cudaSuccess) return bail("index_keys", e);
     if ((e = dev_alloc_zero(&ctx->kt.index_vals, (size_t)islots)) != cudaSuccess) return bail("index_vals", e);
+    ctx->kt.addr_slots = islots;
+    ctx->addr_host.assign(islots, KeypairTables::AddrEntry{});
+    if ((e = dev_alloc_zero(&ctx->kt.addr_tab, (size_t)islots)) != cudaSuccess) return bail("addr_tab", e);
     if ((e = filter_tables_alloc(ctx)) != cudaSuccess) return bail("filter tables", e);
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return bail("sync", e);
     *out = ctx;
@@ -186,6 +189,7 @@ int bnk_ctx_destroy(bnk_ctx *ctx) {
     cudaFree(ctx->kt.allowed_ip);
     cudaFree(ctx->kt.index_keys);
     cudaFree(ctx->kt.index_vals);
+    cudaFree(ctx->kt.addr_tab);
     filter_tables_free(ctx);
     if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
     if (ctx->admin_stream) cudaStreamDestroy(ctx->admin_stream);
@@ -296,6 +300,54 @@ int bnk_index_clear(bnk_ctx *ctx, uint32_t local_index) {
     return index_update(ctx, local_index, false, 0);
 }
 
+// byAddr: same host-shadow scheme as the receiver-index table
+static int addr_update(bnk_ctx *ctx, const uint8_t addr[16], uint16_t port, bool insert, uint32_t peer) {
+    uint64_t hi, lo;
+    memcpy(&hi, addr, 8);
+    memcpy(&lo, addr + 8, 8);
+    const uint32_t live = (uint32_t)port | (1u << 16), dead = 2u << 16;
+    std::vector<KeypairTables::AddrEntry> &tab = ctx->addr_host;
+    const uint32_t mask = ctx->kt.addr_slots - 1;
+    uint32_t h = addr_hash(hi, lo, port) & mask;
+    int64_t spare = -1, at = -1;
+    for (uint32_t probe = 0; probe <= mask; probe++) {
+        const KeypairTables::AddrEntry &e = tab[h];
+        if (e.port == live && e.hi == hi && e.lo == lo) {
+            at = h;
+            break;
+        }
+        if (e.port == dead && spare < 0) spare = h;
+        if (e.port == 0) {
+            if (spare < 0) spare = h;
+            break;
+        }
+        h = (h + 1) & mask;
+    }
+    if (!insert) {
+        if (at < 0) return BNK_SUCCESS;
+        tab[at].port = dead;
+    } else {
+        if (at < 0) at = spare;
+        if (at < 0) return fail(ctx, BNK_EFULL, "source address table full");
+        tab[at] = KeypairTables::AddrEntry{hi, lo, live, peer, 0};
+    }
+    CK(ctx, cudaDeviceSynchronize()); // entries are 32 bytes: never rewrite one under a running kernel
+    CK(ctx, cudaMemcpy(ctx->kt.addr_tab + at, &tab[at], sizeof tab[at], cudaMemcpyHostToDevice));
+    return BNK_SUCCESS;
+}
+
+int bnk_addr_set(bnk_ctx *ctx, const uint8_t addr[16], uint16_t port, uint32_t peer_id) {
+    if (!ctx || !addr) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    return addr_update(ctx, addr, port, true, peer_id);
+}
+
+int bnk_addr_clear(bnk_ctx *ctx, const uint8_t addr[16], uint16_t port) {
+    if (!ctx || !addr) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    return addr_update(ctx, addr, port, false, 0);
+}
+
 int bnk_replay_export(bnk_ctx *ctx, uint32_t slot, uint64_t *last, uint64_t *ring) {
     if (!ctx || !last || !ring || slot >= ctx->cfg.max_keypairs) return fail(ctx, BNK_EINVAL, "bad slot");
     CK(ctx, cudaSetDevice(ctx->device));
@@ -354,6 +406,7 @@ int bnk_batch_destroy(bnk_batch *b) {
     cudaFreeHost(b->host.counter);
     cudaFreeHost(b->host.out_len);
     cudaFreeHost(b->host.status);
+    cudaFreeHost(b->host.src_addr);
     cudaFreeHost(b->h_flow_error);
     cudaFreeHost(b->h_gso);
     DeviceBatch &d = b->dev;
@@ -364,6 +417,7 @@ int bnk_batch_destroy(bnk_batch *b) {
     cudaFree(d.out_len);
     cudaFree(d.counter);
     cudaFree(d.status);
+    cudaFree(d.src_addr);
     cudaFree(d.order);
     cudaFree(d.order_tmp);
     cudaFree(d.keys_tmp);
@@ -413,6 +467,7 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     H((void **)&b->host.counter, n * 8);
     H((void **)&b->host.out_len, n * 4);
     H((void **)&b->host.status, n);
+    H((void **)&b->host.src_addr, n * BNK_SRC_ADDR_STRIDE);
     H((void **)&b->h_flow_error, sizeof(int));
     H((void **)&b->h_gso, n * sizeof(bnk_gso_super));
     b->host.ring_bytes = ring_bytes;
@@ -425,6 +480,7 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     D((void **)&d.out_len, n * 4);
     D((void **)&d.counter, n * 8);
     D((void **)&d.status, n);
+    D((void **)&d.src_addr, n * BNK_SRC_ADDR_STRIDE);
     D((void **)&d.order, n * 4);
     D((void **)&d.order_tmp, n * 4);
     D((void **)&d.keys_tmp, 2 * n * 4);
@@ -625,6 +681,30 @@ int bnk_filter_check_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_
     b->kernel_timed = true;
     if (!(flags & BNK_F_NO_D2H) && n)
         CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
+    return end_submit(b);
+}
+
+int bnk_classify_submit(bnk_batch *b, uint32_t npkts, uint32_t flags) {
+    int rc = begin_submit(b, npkts);
+    if (rc) return rc;
+    bnk_ctx *ctx = b->ctx;
+    cudaStream_t s = b->stream;
+    const size_t n = npkts;
+    if (!(flags & BNK_F_NO_H2D) && n) {
+        const uint64_t ext = ring_extent(b, npkts, 0);
+        if (ext) CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+        CK(ctx, cudaMemcpyAsync(b->dev.src_addr, b->host.src_addr, n * BNK_SRC_ADDR_STRIDE, cudaMemcpyHostToDevice, s));
+    }
+    CK(ctx, cudaEventRecord(b->k_begin, s));
+    CK(ctx, launch_classify(b, npkts, s));
+    CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = true;
+    if (!(flags & BNK_F_NO_D2H) && n) {
+        CK(ctx, cudaMemcpyAsync(b->host.slot, b->dev.slot, n * 4, cudaMemcpyDeviceToHost, s));
+        CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
+    }
     return end_submit(b);
 }
 

@@ -29,6 +29,15 @@ struct KeypairTables {
     uint64_t *index_keys;   // [index_slots]
     uint32_t *index_vals;   // [index_slots]
     uint32_t index_slots;   // power of two
+    // source address -> peer id (Bind.byAddr): open addressing over 32-byte entries
+    struct AddrEntry {
+        uint64_t hi, lo;   // the 16 address bytes as two little-endian words
+        uint32_t port;     // port | 1<<16 when live, 2<<16 when deleted, 0 when empty
+        uint32_t peer;
+        uint64_t pad;
+    };
+    AddrEntry *addr_tab;    // [addr_slots]
+    uint32_t addr_slots;    // power of two
 };
 
 // Flattened, indexed ACL and the reply-flow table (filter_kernels.cu).
@@ -60,6 +69,7 @@ struct bnk_ctx {
     std::atomic<uint64_t> launches;
     std::mutex mu;
     std::string last_error;
+    std::vector<KeypairTables::AddrEntry> addr_host; // host shadow of kt.addr_tab
     std::vector<uint64_t> index_keys_host; // host shadow of kt.index_keys (updates are rare: one per handshake)
 };
 
@@ -68,6 +78,7 @@ struct DeviceBatch {
     uint32_t *off, *len, *slot, *out_len;
     uint64_t *counter;
     uint8_t *status;
+    uint8_t *src_addr;    // [max_pkts][BNK_SRC_ADDR_STRIDE]
     // scratch for grouping packets by keypair slot (group_kernels.cu)
     uint32_t *order;      // [max_pkts] packet indices, stable by slot
     uint32_t *order_tmp;  // [max_pkts]
@@ -137,6 +148,13 @@ cudaError_t filter_flows_clear(bnk_ctx *ctx, cudaStream_t s);
 constexpr uint32_t kSlotNoKeypair = 0xfffffffeu; // demux found no keypair for the receiver index
 cudaError_t launch_demux_index(bnk_batch *b, uint32_t n, const uint32_t *len, cudaStream_t s);
 cudaError_t launch_inner_check(bnk_batch *b, uint32_t n, cudaStream_t s);
+cudaError_t launch_classify(bnk_batch *b, uint32_t n, cudaStream_t s);
+__host__ __device__ inline uint32_t addr_hash(uint64_t hi, uint64_t lo, uint32_t port) {
+    uint64_t z = hi * 0x9e3779b97f4a7c15ull ^ (lo + 0xbf58476d1ce4e5b9ull) * 0x94d049bb133111ebull ^ ((uint64_t)port << 40);
+    z ^= z >> 29;
+    z *= 0xbf58476d1ce4e5b9ull;
+    return (uint32_t)(z >> 32);
+}
 __host__ __device__ inline uint32_t index_hash(uint32_t index) {
     uint32_t z = index * 0x9e3779b1u;
     z ^= z >> 15;

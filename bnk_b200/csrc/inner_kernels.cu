@@ -57,7 +57,70 @@ __global__ void inner_check_kernel(KeypairTables kt, const uint8_t *ring, const 
     if (!ok) status[i] = BNK_PKT_BAD_INNER;
 }
 
+// Bind.classify, internal/magicsock/bind.go:207-228
+__global__ void classify_kernel(KeypairTables kt, const uint8_t *ring, const uint32_t *off, const uint32_t *len,
+                                const uint8_t *src_addr, uint32_t *slot, uint8_t *status, uint32_t n,
+                                uint64_t ring_bytes) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t o = off[i], l = len[i];
+    if ((o & 15u) || (uint64_t)o + l > ring_bytes) {
+        status[i] = BNK_PKT_BAD_DESC;
+        return;
+    }
+    const uint8_t *p = ring + o;
+    uint4 w = make_uint4(0, 0, 0, 0);
+    if (l >= 16) {
+        w = *reinterpret_cast<const uint4 *>(p);
+    } else { // short datagram: whole words as far as they go, the rest zero
+        const uint32_t *p32 = reinterpret_cast<const uint32_t *>(p);
+        if (l >= 4) w.x = p32[0];
+        if (l >= 8) w.y = p32[1];
+        if (l >= 12) w.z = p32[2];
+        else if (l >= 10) w.z = (uint32_t)p[8] | ((uint32_t)p[9] << 8);
+    }
+    // disco.IsDisco: "bnk\0disco\0", 10 bytes
+    if (l >= 10 && w.x == 0x006b6e62u /* b n k \0 */ && w.y == 0x63736964u /* d i s c */ &&
+        (w.z & 0xffffu) == 0x006fu /* o \0 */) {
+        status[i] = BNK_CLASS_DISCO;
+        return;
+    }
+    // isSTUN: RFC 5389 shape
+    if (l >= 20 && ((w.x & 0xffu) >> 6) == 0 && w.y == 0x42a41221u) {
+        status[i] = BNK_CLASS_STUN;
+        return;
+    }
+    // byAddr[normalize(src)]
+    const uint8_t *sa = src_addr + (size_t)i * BNK_SRC_ADDR_STRIDE;
+    const uint32_t *s32 = reinterpret_cast<const uint32_t *>(sa); // stride 20 keeps 4-byte alignment
+    const uint64_t hi = (uint64_t)s32[0] | ((uint64_t)s32[1] << 32), lo = (uint64_t)s32[2] | ((uint64_t)s32[3] << 32);
+    const uint32_t port = ((uint32_t)sa[16] << 8) | sa[17];
+    uint8_t cls = BNK_CLASS_STRANGER;
+    if (kt.addr_slots) {
+        uint32_t h = addr_hash(hi, lo, port) & (kt.addr_slots - 1);
+        for (uint32_t probe = 0; probe < kt.addr_slots; probe++) {
+            const KeypairTables::AddrEntry e = kt.addr_tab[h];
+            if (e.port == 0) break;
+            if (e.port == (port | (1u << 16)) && e.hi == hi && e.lo == lo) {
+                slot[i] = e.peer;
+                cls = BNK_CLASS_WIREGUARD;
+                break;
+            }
+            h = (h + 1) & (kt.addr_slots - 1);
+        }
+    }
+    status[i] = cls;
+}
+
 } // namespace
+
+cudaError_t launch_classify(bnk_batch *b, uint32_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    classify_kernel<<<(n + 255) / 256, 256, 0, s>>>(b->ctx->kt, b->dev.ring, b->dev.off, b->dev.len, b->dev.src_addr,
+                                                   b->dev.slot, b->dev.status, n, b->ring_bytes);
+    ++b->ctx->launches;
+    return cudaGetLastError();
+}
 
 cudaError_t launch_demux_index(bnk_batch *b, uint32_t n, const uint32_t *len, cudaStream_t s) {
     if (n == 0) return cudaSuccess;

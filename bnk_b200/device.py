@@ -125,6 +125,13 @@ class Context:
     def set_allowed_ip(self, slot: int, ipv4: int):
         self._ck(_lib.lib().bnk_keypair_set_allowed_ip(self._h, slot, ipv4))
 
+    def addr_set(self, addr16: bytes, port: int, peer_id: int):
+        """byAddr[addr:port] = peer_id; addr16 is 16 bytes, IPv4 as ::ffff:a.b.c.d."""
+        self._ck(_lib.lib().bnk_addr_set(self._h, C.c_char_p(bytes(addr16)), port, peer_id))
+
+    def addr_clear(self, addr16: bytes, port: int):
+        self._ck(_lib.lib().bnk_addr_clear(self._h, C.c_char_p(bytes(addr16)), port))
+
     def replay_export(self, slot: int):
         last = C.c_uint64()
         ring = np.zeros(self.cfg.replay_ring_blocks, np.uint64)
@@ -196,12 +203,13 @@ class Batch:
         self.counter = _np_view(v.counter, np.uint64, max_pkts)
         self.out_len = _np_view(v.out_len, np.uint32, max_pkts)
         self.status = _np_view(v.status, np.uint8, max_pkts)
+        self.src_addr = _np_view(v.src_addr, np.uint8, max_pkts * _lib.SRC_ADDR_STRIDE).reshape(max_pkts, _lib.SRC_ADDR_STRIDE)
         ctx._batches.append(self)
 
     def close(self):
         if getattr(self, "_h", None):
             # the numpy views alias pinned memory that is about to be freed
-            for name in ("ring", "off", "len", "slot", "counter", "out_len", "status"):
+            for name in ("ring", "off", "len", "slot", "counter", "out_len", "status", "src_addr"):
                 setattr(self, name, None)
             _lib.lib().bnk_batch_destroy(self._h)
             self._h = None
@@ -259,6 +267,11 @@ class Batch:
         """supers: array of GSO_SUPER_DTYPE; segment descriptors (off, len, slot) must already be filled."""
         supers = np.ascontiguousarray(supers, GSO_SUPER_DTYPE)
         self._ck(_lib.lib().bnk_gso_split_submit(self._h, supers.ctypes.data, len(supers), n_pkts, flags))
+        if wait:
+            self.wait()
+
+    def classify(self, n: int, flags: int = 0, wait: bool = True):
+        self._ck(_lib.lib().bnk_classify_submit(self._h, n, flags))
         if wait:
             self.wait()
 

@@ -122,7 +122,10 @@ typedef struct bnk_batch_view {
     uint64_t ring_bytes;
     uint32_t max_pkts;
     uint32_t reserved;
+    uint8_t *src_addr; /* [max_pkts][BNK_SRC_ADDR_STRIDE], bnk_classify_submit only: the datagram's source,
+                          16 address bytes (IPv4 as ::ffff:a.b.c.d) then the port, big-endian */
 } bnk_batch_view;
+#define BNK_SRC_ADDR_STRIDE 20u
 
 /* ---- library / context ---- */
 int bnk_abi_version(void);
@@ -191,6 +194,21 @@ int bnk_wait(bnk_batch *b, uint64_t timeout_ns);
 /* Explicit transfers between the pinned ring/descriptors and the device mirror (asynchronous). */
 int bnk_batch_upload(bnk_batch *b, uint32_t npkts);
 int bnk_batch_download(bnk_batch *b, uint32_t npkts);
+
+/* ---- receive classification ----
+ * Replaces Bind.classify (internal/magicsock/bind.go:207-228) for one ReadBatch: disco.IsDisco
+ * (internal/disco/disco.go:20,177-179: the datagram starts with "bnk\0disco\0"), then isSTUN
+ * (bind.go:250-253: at least 20 bytes, top two bits zero, magic cookie 21 12 A4 42 at bytes 4..7), then
+ * the byAddr lookup of the normalised source address (bind.go:263-274).  status[i] becomes one of the
+ * classes below; for BNK_CLASS_WIREGUARD slot[i] is the peer id registered for the source address.
+ * Addresses are 16 bytes, IPv4 in its ::ffff:a.b.c.d form (what normalize()'s Unmap makes equal). */
+#define BNK_CLASS_WIREGUARD 0
+#define BNK_CLASS_DISCO 10
+#define BNK_CLASS_STUN 11
+#define BNK_CLASS_STRANGER 12 /* unknown source: dropped by the reference */
+int bnk_addr_set(bnk_ctx *ctx, const uint8_t addr[16], uint16_t port, uint32_t peer_id);
+int bnk_addr_clear(bnk_ctx *ctx, const uint8_t addr[16], uint16_t port);
+int bnk_classify_submit(bnk_batch *b, uint32_t npkts, uint32_t flags);
 
 /* ---- segmentation offload (GSO) ----
  * Replaces the split wireguard-go's Linux TUN code performs on a super-packet read with a virtio-net

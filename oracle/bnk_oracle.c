@@ -305,6 +305,13 @@ int bnko_inner_check(const uint8_t *pt, size_t len, uint32_t allowed_ip, size_t 
     return 1;
 }
 
+int bnko_classify_shape(const uint8_t *pkt, size_t len) {
+    static const uint8_t magic[10] = {'b', 'n', 'k', 0, 'd', 'i', 's', 'c', 'o', 0}; /* disco.go:20 */
+    if (len >= sizeof magic && memcmp(pkt, magic, sizeof magic) == 0) return 10;
+    if (len >= 20 && (pkt[0] >> 6) == 0 && pkt[4] == 0x21 && pkt[5] == 0x12 && pkt[6] == 0xA4 && pkt[7] == 0x42) return 11;
+    return 0;
+}
+
 /* one's-complement sum of big-endian 16-bit words (RFC 1071), odd tail padded with a zero byte; NOT inverted */
 static uint32_t csum_add(const uint8_t *p, size_t len, uint32_t acc) {
     uint64_t s = acc;

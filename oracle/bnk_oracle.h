@@ -89,6 +89,10 @@ int bnko_gso_split(const uint8_t *in, size_t in_len, unsigned hdr_len, unsigned 
 /* RFC 1071 checksum helpers, for tests */
 uint16_t bnko_inet_checksum(const uint8_t *p, size_t len, uint32_t initial);
 
+/* Shape tests of Bind.classify (internal/magicsock/bind.go:207-228): 10 = disco.IsDisco
+ * (internal/disco/disco.go:20,177-179), 11 = isSTUN (bind.go:250-253), 0 = neither (goes to the byAddr lookup). */
+int bnko_classify_shape(const uint8_t *pkt, size_t len);
+
 /* batch forms over a packet ring (same descriptor layout as the GPU library) */
 void bnko_wg_seal_batch(const uint8_t *keys /* n_keys*32 */, const uint32_t *remote_index /* n_keys */,
                         size_t mtu, uint8_t *ring, const uint32_t *off, const uint32_t *len,

@@ -82,6 +82,8 @@ def lib() -> C.CDLL:
     L.bnko_wg_open.restype = C.c_int
     L.bnko_inner_check.argtypes = [vp, sz, C.c_uint32, C.POINTER(sz)]
     L.bnko_inner_check.restype = C.c_int
+    L.bnko_classify_shape.argtypes = [vp, sz]
+    L.bnko_classify_shape.restype = C.c_int
     L.bnko_gso_split.argtypes = [vp, sz, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint, vp, sz, vp, sz]
     L.bnko_gso_split.restype = C.c_int
     L.bnko_inet_checksum.argtypes = [vp, sz, C.c_uint32]
@@ -189,6 +191,10 @@ def inner_check(pt: bytes, allowed_ip: int):
     nl = C.c_size_t(0)
     ok = lib().bnko_inner_check(_buf(pt), len(pt), allowed_ip, C.byref(nl))
     return nl.value if ok else None
+
+
+def classify_shape(pkt: bytes) -> int:
+    return lib().bnko_classify_shape(_buf(pkt), len(pkt))
 
 
 def gso_split(pkt: bytes, hdr_len: int, gso_size: int, csum_start: int, csum_offset: int, proto: int):

@@ -35,7 +35,7 @@ def test_struct_layouts_match_header():
 
     assert ctypes.sizeof(_lib.Cfg) == 32
     assert ctypes.sizeof(_lib.AclTuple) == 12
-    assert ctypes.sizeof(_lib.BatchView) == 72
+    assert ctypes.sizeof(_lib.BatchView) == 80
 
 
 def test_no_cpu_fallback_in_product_path():

@@ -227,3 +227,58 @@ def test_demux_by_receiver_index_and_inner_check(gpu_lib, oracle):
         b.close()
     finally:
         c.close()
+
+
+def test_receive_classification(gpu_lib, oracle):
+    """Bind.classify on the GPU: disco and STUN peel off first, then the source address decides."""
+    import ipaddress
+
+    from bnk_b200 import Context, _lib
+
+    rng = np.random.default_rng(33)
+
+    def a16(text):
+        ip = ipaddress.ip_address(text)
+        return (ipaddress.IPv6Address("::ffff:" + text) if ip.version == 4 else ip).packed
+
+    known = [("203.0.113.5", 51820, 3), ("203.0.113.5", 51821, 4), ("2001:db8::7", 4000, 9), ("198.51.100.200", 1, 0)]
+    magic = b"bnk\x00disco\x00"
+    stun = bytes([0x01, 0x01, 0x00, 0x00, 0x21, 0x12, 0xA4, 0x42]) + bytes(12)
+    wg = b"\x04\x00\x00\x00" + bytes(60)
+    cases = []  # (datagram, source text, port)
+    for pkt in [magic + bytes(80), magic, magic[:9] + b"\x01" + bytes(20), magic[:9], stun, stun[:19], bytes([0x41]) + stun[1:],
+                stun[:4] + b"\x21\x12\xA4\x43" + bytes(12), wg, b"", b"\x04"]:
+        for src in [("203.0.113.5", 51820), ("203.0.113.5", 51822), ("2001:db8::7", 4000), ("2001:db8::8", 4000),
+                    ("198.51.100.200", 1), ("10.1.1.1", 9)]:
+            cases.append((pkt, src[0], src[1]))
+    n = len(cases)
+    with Context(max_keypairs=16, flow_capacity=0) as c:
+        for text, port, peer in known:
+            c.addr_set(a16(text), port, peer)
+        c.addr_set(a16("10.1.1.1"), 9, 5)
+        c.addr_clear(a16("10.1.1.1"), 9)  # a path that was demoted again
+        lengths = np.array([len(p) for p, _, _ in cases], np.uint32)
+        off = H.layout_packed(lengths, slack=16)
+        b = c.batch(n, H.ring_bytes_for(off, lengths))
+        H.fill_payloads(b.ring, off, [p for p, _, _ in cases], headroom=0)
+        b.off[:n], b.len[:n] = off, lengths
+        b.slot[:n] = 0xFFFFFFFF
+        for i, (_, text, port) in enumerate(cases):
+            b.src_addr[i, :16] = np.frombuffer(a16(text), np.uint8)
+            b.src_addr[i, 16], b.src_addr[i, 17] = port >> 8, port & 0xFF
+        b.classify(n)
+        table = {(a16(t), p): peer for t, p, peer in known}
+        seen = set()
+        for i, (pkt, text, port) in enumerate(cases):
+            shape = oracle.classify_shape(pkt)
+            if shape:
+                want = shape
+            else:
+                peer = table.get((a16(text), port))
+                want = _lib.CLASS_WIREGUARD if peer is not None else _lib.CLASS_STRANGER
+                if peer is not None:
+                    assert b.slot[i] == peer
+            assert b.status[i] == want, (i, pkt[:12], text, port)
+            seen.add(int(b.status[i]))
+        assert seen == {_lib.CLASS_WIREGUARD, _lib.CLASS_DISCO, _lib.CLASS_STUN, _lib.CLASS_STRANGER}
+        b.close()
