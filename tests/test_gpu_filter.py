@@ -164,3 +164,27 @@ def test_flow_table_full_is_reported(gpu_lib):
         assert e.value.code == -6
     finally:
         c.close()
+
+
+def test_policy_to_verdicts_end_to_end(make):
+    """Policy document -> Compile -> netmap -> ApplyNetmap -> GPU verdicts, the route of the reference's
+    internal/dataplane/acl_integration_test.go:20-80 (tcp/7777 allowed, tcp/8888 blocked, replies pass)."""
+    from bnk_b200 import acl
+
+    nodes = [acl.NodeInfo("a", "100.64.0.1"), acl.NodeInfo("b", "100.64.0.2"), acl.NodeInfo("c", "100.64.0.3")]
+    policy = acl.Policy(rules=[acl.Rule(["a"], ["b"], ["tcp/7777"])])
+    compiled = acl.compile_policy(policy, nodes)
+    a, b, c = RC.ip("100.64.0.1"), RC.ip("100.64.0.2"), RC.ip("100.64.0.3")
+    f = make()
+    acl.apply_netmap_filter(f, {"filter_enabled": True, "filter": acl.rules_to_netmap(compiled.get("b", []))})
+    assert f.check_inbound(RC.tcp(a, b, 40000, 7777), RC.T0)
+    assert not f.check_inbound(RC.tcp(a, b, 40000, 8888), RC.T0)
+    assert not f.check_inbound(RC.tcp(c, b, 40000, 7777), RC.T0)
+    # node a has no inbound rule at all under this policy: deny all but replies to what it opened
+    acl.apply_netmap_filter(f, {"filter_enabled": True, "filter": acl.rules_to_netmap(compiled.get("a", []))})
+    assert not f.check_inbound(RC.tcp(b, a, 7777, 40000, False), RC.T0)
+    f.note_outbound(RC.tcp(a, b, 40000, 7777), RC.T0)
+    assert f.check_inbound(RC.tcp(b, a, 7777, 40000, False), RC.T0 + RC.SEC)
+    # the policy is withdrawn: allow all (flows are kept, rules are gone)
+    acl.apply_netmap_filter(f, {"filter_enabled": False})
+    assert f.check_inbound(RC.tcp(c, a, 1, 2), RC.T0)
