@@ -214,68 +214,83 @@ __device__ __forceinline__ uint32_t wg_padded_len(uint32_t len, uint32_t mtu) {
 }
 
 // ---------------------------------------------------------------------------
-// The kernel.  OPEN=false: seal in place.  OPEN=true: authenticate + decrypt in place.
+// Descriptor of one packet, validated.  `writer` says whether this thread records the
+// outcome of a refused packet (one thread per packet does).
+// ---------------------------------------------------------------------------
+struct Desc {
+    uint32_t off, body /* bytes under the cipher */, in_len /* bytes to fetch */, n_lo, n_hi, slot;
+    bool live;
+};
+
+template <bool OPEN>
+__device__ __forceinline__ Desc load_desc(const AeadArgs &a, uint32_t pkt, bool have, bool writer) {
+    Desc d{0, 0, 0, 0, 0, 0, false};
+    if (!have) return d;
+    uint8_t st = BNK_PKT_OK;
+    d.off = a.off[pkt];
+    const uint32_t len = a.len[pkt];
+    d.slot = a.slot[pkt];
+    d.live = true;
+    if ((d.off & 15u) || d.slot >= a.max_slots) {
+        st = (OPEN && d.slot == kSlotNoKeypair) ? BNK_PKT_NO_KEYPAIR : BNK_PKT_BAD_DESC;
+        d.live = false;
+    } else if (!OPEN) {
+        d.body = wg_padded_len(len, a.mtu);
+        d.in_len = len;
+        const uint64_t ctr = a.counter[pkt];
+        d.n_lo = (uint32_t)ctr;
+        d.n_hi = (uint32_t)(ctr >> 32);
+        if ((uint64_t)d.off + BNK_WG_HEADER + d.body + BNK_WG_TAG > a.ring_bytes || d.body < len) {
+            st = BNK_PKT_BAD_DESC;
+            d.live = false;
+        } else if (ctr >= BNK_REJECT_AFTER_MESSAGES) {
+            st = BNK_PKT_COUNTER_EXHAUSTED;
+            d.live = false;
+        }
+    } else {
+        if ((uint64_t)d.off + len > a.ring_bytes) {
+            st = BNK_PKT_BAD_DESC;
+            d.live = false;
+        } else if (len < BNK_WG_HEADER + BNK_WG_TAG) {
+            st = BNK_PKT_MALFORMED;
+            d.live = false;
+        } else {
+            const uint4 hdr = *reinterpret_cast<const uint4 *>(a.ring + d.off);
+            d.n_lo = hdr.z;
+            d.n_hi = hdr.w;
+            if (writer) a.counter[pkt] = ((uint64_t)hdr.w << 32) | hdr.z;
+            if (hdr.x != 4u) {
+                st = BNK_PKT_MALFORMED;
+                d.live = false;
+            } else {
+                d.body = len - (BNK_WG_HEADER + BNK_WG_TAG);
+                d.in_len = d.body;
+            }
+        }
+    }
+    if (!d.live) {
+        if (writer) {
+            a.status[pkt] = st;
+            a.out_len[pkt] = 0;
+        }
+        d.body = 0;
+        d.in_len = 0;
+    }
+    return d;
+}
+
+// ---------------------------------------------------------------------------
+// Kernel 1, thread per packet.  OPEN=false: seal in place.  OPEN=true: authenticate + decrypt in place.
+// The throughput kernel: used when the batch is large enough to fill the GPU with one packet per thread.
 // ---------------------------------------------------------------------------
 template <bool OPEN>
 __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const AeadArgs a) {
     const uint32_t idx = blockIdx.x * kThreads + threadIdx.x;
     const bool have = idx < a.n;
     const uint32_t pkt = have ? (a.order ? a.order[idx] : idx) : 0u;
-
-    // ---- descriptor ----
-    uint32_t off = 0, body = 0 /* bytes under the cipher */, in_len = 0 /* bytes to fetch */;
-    uint32_t n_lo = 0, n_hi = 0, slot = 0;
-    uint8_t st = BNK_PKT_OK;
-    bool live = false;
-    if (have) {
-        off = a.off[pkt];
-        const uint32_t len = a.len[pkt];
-        slot = a.slot[pkt];
-        live = true;
-        if ((off & 15u) || slot >= a.max_slots) {
-            st = (OPEN && slot == kSlotNoKeypair) ? BNK_PKT_NO_KEYPAIR : BNK_PKT_BAD_DESC;
-            live = false;
-        } else if (!OPEN) {
-            body = wg_padded_len(len, a.mtu);
-            in_len = len;
-            const uint64_t ctr = a.counter[pkt];
-            n_lo = (uint32_t)ctr;
-            n_hi = (uint32_t)(ctr >> 32);
-            if ((uint64_t)off + BNK_WG_HEADER + body + BNK_WG_TAG > a.ring_bytes || body < len) {
-                st = BNK_PKT_BAD_DESC;
-                live = false;
-            } else if (ctr >= BNK_REJECT_AFTER_MESSAGES) {
-                st = BNK_PKT_COUNTER_EXHAUSTED;
-                live = false;
-            }
-        } else {
-            if ((uint64_t)off + len > a.ring_bytes) {
-                st = BNK_PKT_BAD_DESC;
-                live = false;
-            } else if (len < BNK_WG_HEADER + BNK_WG_TAG) {
-                st = BNK_PKT_MALFORMED;
-                live = false;
-            } else {
-                const uint4 hdr = *reinterpret_cast<const uint4 *>(a.ring + off);
-                n_lo = hdr.z;
-                n_hi = hdr.w;
-                a.counter[pkt] = ((uint64_t)hdr.w << 32) | hdr.z;
-                if (hdr.x != 4u) {
-                    st = BNK_PKT_MALFORMED;
-                    live = false;
-                } else {
-                    body = len - (BNK_WG_HEADER + BNK_WG_TAG);
-                    in_len = body;
-                }
-            }
-        }
-        if (!live) {
-            a.status[pkt] = st;
-            a.out_len[pkt] = 0;
-            body = 0;
-            in_len = 0;
-        }
-    }
+    const Desc dsc = load_desc<OPEN>(a, pkt, have, true);
+    const uint32_t off = dsc.off, body = dsc.body, in_len = dsc.in_len, n_lo = dsc.n_lo, n_hi = dsc.n_hi, slot = dsc.slot;
+    const bool live = dsc.live;
     const uint32_t nblk = (body + 63u) >> 6;
     uint8_t *const data = a.ring + (size_t)off + BNK_WG_HEADER; // 16-byte aligned
 
@@ -397,13 +412,282 @@ __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const Aead
     }
 }
 
-// One warp per 32 packets, one CTA per 128.  The hardware hands CTAs to SMs as slots free up, which
-// measured faster here than persistent warps with an even static share of the packets.
+// ---------------------------------------------------------------------------
+// Poly1305 in radix 2^26 with both factors arbitrary: the warp-per-packet kernel multiplies by powers
+// of r, which are not clamped, so the 5/4 trick of the radix-2^32 code above does not apply.
+// Limbs of a product are below 2^26 (limb 1 may carry a few extra units); sums of two such values are
+// valid left factors.
+// ---------------------------------------------------------------------------
+struct P26 {
+    uint32_t v[5];
+};
+constexpr uint32_t kM26 = 0x3ffffffu;
+
+__device__ __forceinline__ P26 p26_zero() { return P26{{0, 0, 0, 0, 0}}; }
+__device__ __forceinline__ P26 p26_words(uint32_t t0, uint32_t t1, uint32_t t2, uint32_t t3, uint32_t hibit) {
+    P26 m;
+    m.v[0] = t0 & kM26;
+    m.v[1] = ((t0 >> 26) | (t1 << 6)) & kM26;
+    m.v[2] = ((t1 >> 20) | (t2 << 12)) & kM26;
+    m.v[3] = ((t2 >> 14) | (t3 << 18)) & kM26;
+    m.v[4] = (t3 >> 8) | (hibit << 24);
+    return m;
+}
+__device__ __forceinline__ P26 p26_add(const P26 &x, const P26 &y) {
+    P26 o;
+#pragma unroll
+    for (int i = 0; i < 5; i++) o.v[i] = x.v[i] + y.v[i];
+    return o;
+}
+__device__ __forceinline__ P26 p26_mul(const P26 &x, const P26 &y) {
+    const uint32_t s1 = y.v[1] * 5u, s2 = y.v[2] * 5u, s3 = y.v[3] * 5u, s4 = y.v[4] * 5u; // 2^130 = 5 (mod p)
+    uint64_t d0 = (uint64_t)x.v[0] * y.v[0] + (uint64_t)x.v[1] * s4 + (uint64_t)x.v[2] * s3 + (uint64_t)x.v[3] * s2 +
+                  (uint64_t)x.v[4] * s1;
+    uint64_t d1 = (uint64_t)x.v[0] * y.v[1] + (uint64_t)x.v[1] * y.v[0] + (uint64_t)x.v[2] * s4 + (uint64_t)x.v[3] * s3 +
+                  (uint64_t)x.v[4] * s2;
+    uint64_t d2 = (uint64_t)x.v[0] * y.v[2] + (uint64_t)x.v[1] * y.v[1] + (uint64_t)x.v[2] * y.v[0] + (uint64_t)x.v[3] * s4 +
+                  (uint64_t)x.v[4] * s3;
+    uint64_t d3 = (uint64_t)x.v[0] * y.v[3] + (uint64_t)x.v[1] * y.v[2] + (uint64_t)x.v[2] * y.v[1] + (uint64_t)x.v[3] * y.v[0] +
+                  (uint64_t)x.v[4] * s4;
+    uint64_t d4 = (uint64_t)x.v[0] * y.v[4] + (uint64_t)x.v[1] * y.v[3] + (uint64_t)x.v[2] * y.v[2] + (uint64_t)x.v[3] * y.v[1] +
+                  (uint64_t)x.v[4] * y.v[0];
+    P26 o;
+    d1 += d0 >> 26;
+    d2 += d1 >> 26;
+    d3 += d2 >> 26;
+    d4 += d3 >> 26;
+    const uint64_t t = (d0 & kM26) + (d4 >> 26) * 5u;
+    o.v[0] = (uint32_t)t & kM26;
+    o.v[1] = ((uint32_t)d1 & kM26) + (uint32_t)(t >> 26);
+    o.v[2] = (uint32_t)d2 & kM26;
+    o.v[3] = (uint32_t)d3 & kM26;
+    o.v[4] = (uint32_t)d4 & kM26;
+    return o;
+}
+__device__ __forceinline__ P26 p26_shfl(const P26 &x, int src) {
+    P26 o;
+#pragma unroll
+    for (int i = 0; i < 5; i++) o.v[i] = __shfl_sync(0xffffffffu, x.v[i], src);
+    return o;
+}
+__device__ __forceinline__ P26 p26_shfl_up(const P26 &x, int delta) {
+    P26 o;
+#pragma unroll
+    for (int i = 0; i < 5; i++) o.v[i] = __shfl_up_sync(0xffffffffu, x.v[i], delta);
+    return o;
+}
+// tag = ((h mod p) + pad) mod 2^128
+__device__ __forceinline__ void p26_finish(const P26 &x, const uint32_t (&pad)[4], uint32_t (&tag)[4]) {
+    uint32_t h0 = x.v[0], h1 = x.v[1], h2 = x.v[2], h3 = x.v[3], h4 = x.v[4], c;
+    c = h1 >> 26; h1 &= kM26; h2 += c;
+    c = h2 >> 26; h2 &= kM26; h3 += c;
+    c = h3 >> 26; h3 &= kM26; h4 += c;
+    c = h4 >> 26; h4 &= kM26; h0 += c * 5u;
+    c = h0 >> 26; h0 &= kM26; h1 += c;
+    // g = h + 5 - 2^130; g is non-negative exactly when h >= p
+    uint32_t g0 = h0 + 5u; c = g0 >> 26; g0 &= kM26;
+    uint32_t g1 = h1 + c;  c = g1 >> 26; g1 &= kM26;
+    uint32_t g2 = h2 + c;  c = g2 >> 26; g2 &= kM26;
+    uint32_t g3 = h3 + c;  c = g3 >> 26; g3 &= kM26;
+    const uint32_t g4 = h4 + c - (1u << 26);
+    if (!(g4 >> 31)) {
+        h0 = g0; h1 = g1; h2 = g2; h3 = g3; h4 = g4;
+    }
+    const uint32_t w0 = h0 | (h1 << 26), w1 = (h1 >> 6) | (h2 << 20), w2 = (h2 >> 12) | (h3 << 14),
+                   w3 = (h3 >> 18) | (h4 << 8);
+    asm("add.cc.u32 %0, %4, %8;\n\t"
+        "addc.cc.u32 %1, %5, %9;\n\t"
+        "addc.cc.u32 %2, %6, %10;\n\t"
+        "addc.u32 %3, %7, %11;"
+        : "=r"(tag[0]), "=r"(tag[1]), "=r"(tag[2]), "=r"(tag[3])
+        : "r"(w0), "r"(w1), "r"(w2), "r"(w3), "r"(pad[0]), "r"(pad[1]), "r"(pad[2]), "r"(pad[3]));
+}
+
+// ---------------------------------------------------------------------------
+// Kernel 2, warp per packet: the latency kernel for batches too small to fill the GPU with one
+// packet per thread (a 128-packet batch takes ~24 sequential cipher blocks per thread there).
+// Lane j of a round takes one 64-byte chunk: its ChaCha20 block and the Poly1305 Horner steps over
+// its four 16-byte blocks starting from zero, Q_j = sum_s b_s r^(5-s).  The chunks of a round, up
+// to 30, sit right-aligned in lanes 31-F..30; lane 30-F carries the running state in; a binary
+// tree over the warp (five shuffle + multiply steps with r^4, r^8, ... r^64) folds them to
+//   state' = state * r^(4F) + sum_j Q_j * r^(4(F-1-j))
+// on lane 30.  Lane 31 then continues sequentially over what is left of the packet (up to three whole
+// blocks and a ragged one) and the length block, and makes the tag.  Block 0 of the keystream (the
+// one-time Poly1305 key) is computed by the carry lane of the first round in the same pass as the data
+// blocks.  Accesses are coalesced by construction: consecutive lanes hold consecutive 64 bytes.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kWppFull = 30;
+
+template <bool OPEN>
+__global__ void __launch_bounds__(128) aead_wpp_kernel(const AeadArgs a) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (idx >= a.n) return; // a whole warp at a time
+    const uint32_t pkt = a.order ? a.order[idx] : idx;
+    const Desc dsc = load_desc<OPEN>(a, pkt, true, lane == 0);
+    if (!dsc.live) return;
+    const uint32_t body = dsc.body, in_len = dsc.in_len;
+    uint8_t *const data = a.ring + (size_t)dsc.off + BNK_WG_HEADER;
+
+    uint32_t key[8];
+    {
+        const uint4 *kp = reinterpret_cast<const uint4 *>(a.keys + (size_t)dsc.slot * 8);
+        const uint4 ka = kp[0], kb = kp[1];
+        key[0] = ka.x; key[1] = ka.y; key[2] = ka.z; key[3] = ka.w;
+        key[4] = kb.x; key[5] = kb.y; key[6] = kb.z; key[7] = kb.w;
+    }
+    const uint32_t full_total = body >> 6, tail_bytes = body & 63u;
+    P26 r = p26_zero(), state = p26_zero();
+    uint32_t pad[4] = {0, 0, 0, 0};
+    uint32_t ct[16]; // the lane's ciphertext words of the current round (lane 31: the ragged tail)
+#pragma unroll
+    for (int i = 0; i < 16; i++) ct[i] = 0;
+
+    uint32_t done = 0;
+    bool first = true, last_round;
+    do {
+        const uint32_t remaining = full_total - done;
+        last_round = remaining <= kWppFull;
+        const uint32_t F = last_round ? remaining : kWppFull;
+        const bool is_chunk = lane + F >= 31u && lane <= 30u;
+        const bool is_carry = lane + F == 30u;
+        const bool is_tail = last_round && lane == 31u && tail_bytes != 0;
+        const bool works = is_chunk || is_tail;
+        const uint32_t chunk = is_tail ? full_total : done + (lane + F - 31u);
+        const uint32_t base = chunk * 64u;
+
+        uint32_t d[16];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (works && base + 16u * c < in_len) v = *reinterpret_cast<const uint4 *>(data + base + 16u * c);
+            d[4 * c + 0] = v.x; d[4 * c + 1] = v.y; d[4 * c + 2] = v.z; d[4 * c + 3] = v.w;
+        }
+        uint32_t x[16];
+        chacha20_block(x, key, works ? chunk + 1u : 0u, dsc.n_lo, dsc.n_hi); // idle lanes and the carry lane: block 0
+        if (first) {
+            const int src = 30 - (int)F; // the carry lane holds block 0
+            const uint32_t k0 = __shfl_sync(0xffffffffu, x[0], src), k1 = __shfl_sync(0xffffffffu, x[1], src);
+            const uint32_t k2 = __shfl_sync(0xffffffffu, x[2], src), k3 = __shfl_sync(0xffffffffu, x[3], src);
+            r = p26_words(k0 & 0x0fffffffu, k1 & 0x0ffffffcu, k2 & 0x0ffffffcu, k3 & 0x0ffffffcu, 0u);
+#pragma unroll
+            for (int i = 0; i < 4; i++) pad[i] = __shfl_sync(0xffffffffu, x[4 + i], src);
+        }
+        if (works) {
+            const int in_left = (int)in_len - (int)base;
+            const int body_left = (int)body - (int)base;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t o[4];
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const int k = 16 * c + 4 * w;
+                    const uint32_t in_w = keep_bytes(d[4 * c + w], in_left - k);
+                    o[w] = keep_bytes(in_w ^ x[4 * c + w], body_left - k);
+                    ct[4 * c + w] = OPEN ? in_w : o[w];
+                }
+                if (16 * c + 16 <= body_left) {
+                    *reinterpret_cast<uint4 *>(data + base + 16u * c) = make_uint4(o[0], o[1], o[2], o[3]);
+                } else if (16 * c < body_left) {
+                    uint8_t *dst = data + base + 16u * c;
+                    const int tail = body_left - 16 * c;
+#pragma unroll
+                    for (int k = 0; k < 15; k++)
+                        if (k < tail) dst[k] = (uint8_t)(o[k >> 2] >> (8 * (k & 3)));
+                }
+            }
+        }
+        // Horner over the lane's own four blocks (chunk lanes), or the state carried in (carry lane)
+        P26 V = p26_zero();
+        if (is_chunk) {
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                V = p26_mul(p26_add(V, p26_words(ct[4 * c], ct[4 * c + 1], ct[4 * c + 2], ct[4 * c + 3], 1u)), r);
+        }
+        if (is_carry) V = state;
+        // fold lanes 0..30 (tree positions 1..31) with r^4, r^8, ..., r^64
+        P26 pw = p26_mul(r, r);
+        pw = p26_mul(pw, pw);
+#pragma unroll
+        for (int k = 0; k < 5; k++) {
+            P26 left = p26_shfl_up(V, 1 << k);
+            if (lane < (1u << k)) left = p26_zero();
+            const P26 t = p26_add(p26_mul(left, pw), V);
+            const uint32_t mask = (2u << k) - 1u;
+            if (((lane + 1u) & mask) == mask && lane != 31u) V = t;
+            if (k < 4) pw = p26_mul(pw, pw);
+        }
+        state = p26_shfl(V, 30);
+        done += F;
+        first = false;
+    } while (!last_round);
+
+    // lane 31: the blocks behind the last whole chunk, the length block, the tag
+    uint32_t verdict = 0; // open: 1 = tag mismatch
+    if (lane == 31u) {
+        P26 h = state;
+        const uint32_t nb = (tail_bytes + 15u) >> 4;
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+            if ((uint32_t)c < nb) h = p26_mul(p26_add(h, p26_words(ct[4 * c], ct[4 * c + 1], ct[4 * c + 2], ct[4 * c + 3], 1u)), r);
+        h = p26_mul(p26_add(h, p26_words(0u, 0u, body, 0u, 1u)), r); // le64(0) | le64(body)
+        uint32_t tag[4];
+        p26_finish(h, pad, tag);
+        uint8_t *tagp = data + body;
+        if (!OPEN) {
+#pragma unroll
+            for (int w = 0; w < 4; w++)
+#pragma unroll
+                for (int k = 0; k < 4; k++) tagp[4 * w + k] = (uint8_t)(tag[w] >> (8 * k));
+        } else {
+            uint32_t diff = 0;
+#pragma unroll
+            for (int w = 0; w < 4; w++)
+#pragma unroll
+                for (int k = 0; k < 4; k++) diff |= (uint32_t)(tagp[4 * w + k] ^ (uint8_t)(tag[w] >> (8 * k)));
+            verdict = diff != 0;
+        }
+    }
+    if (!OPEN) {
+        if (lane == 0) {
+            *reinterpret_cast<uint4 *>(a.ring + dsc.off) = make_uint4(4u, a.remote_index[dsc.slot], dsc.n_lo, dsc.n_hi);
+            a.status[pkt] = BNK_PKT_OK;
+            a.out_len[pkt] = BNK_WG_HEADER + body + BNK_WG_TAG;
+        }
+    } else {
+        verdict = __shfl_sync(0xffffffffu, verdict, 31);
+        if (verdict) { // forged or damaged: wipe what the fused pass wrote
+            for (uint32_t k = lane * 16u; k + 16u <= body; k += 512u) *reinterpret_cast<uint4 *>(data + k) = make_uint4(0, 0, 0, 0);
+            if (lane == 0)
+                for (uint32_t k = body & ~15u; k < body; k++) data[k] = 0;
+        }
+        if (lane == 0) {
+            a.status[pkt] = verdict ? BNK_PKT_AUTH_FAIL : (body ? BNK_PKT_OK : BNK_PKT_KEEPALIVE);
+            a.out_len[pkt] = verdict ? 0u : body;
+        }
+    }
+}
+
+// Below this many packets one-packet-per-thread leaves most of the GPU idle and its run time is that of one thread
+// walking one packet (~39 us for 1420 B) whatever the batch size; one warp per packet takes ~13 us up to 2,400
+// packets and then grows by ~14 us per 2,400 more.  Measured crossover on B200: between 6,000 and 7,000 packets.
+#ifndef BNK_WPP_MAX_PACKETS
+#define BNK_WPP_MAX_PACKETS 6144u
+#endif
+
 template <bool OPEN>
 cudaError_t launch_aead(const AeadArgs &a, cudaStream_t s, bnk_ctx *ctx) {
     if (a.n == 0) return cudaSuccess;
-    const uint32_t ctas = (a.n + kThreads - 1) / kThreads;
-    aead_kernel<OPEN><<<ctas, kThreads, 0, s>>>(a);
+    const bool wpp = ctx->aead_mode == 2 || (ctx->aead_mode == 0 && a.n <= BNK_WPP_MAX_PACKETS);
+    if (wpp) {
+        const uint32_t ctas = (a.n + 3) / 4; // 4 warps = 4 packets per CTA
+        aead_wpp_kernel<OPEN><<<ctas, 128, 0, s>>>(a);
+    } else {
+        // one CTA per 128 packets; the hardware hands CTAs to SMs as slots free up, which measured faster
+        // than persistent warps with an even static share of the packets
+        const uint32_t ctas = (a.n + kThreads - 1) / kThreads;
+        aead_kernel<OPEN><<<ctas, kThreads, 0, s>>>(a);
+    }
     ++ctx->launches;
     return cudaGetLastError();
 }

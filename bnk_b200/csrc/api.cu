@@ -3,6 +3,7 @@
 // host->device copies, the kernels and device->host copies on one CUDA stream per batch.
 #include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <thread>
@@ -144,6 +145,9 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     ctx->device = cfg->device_id;
     ctx->sm_count = prop.multiProcessorCount;
     ctx->launches = 0;
+    ctx->aead_mode = 0;
+    if (const char *m = getenv("BNK_AEAD_KERNEL")) // tuning and test aid: tpp | wpp
+        ctx->aead_mode = !strcmp(m, "tpp") ? 1 : (!strcmp(m, "wpp") ? 2 : 0);
     ctx->kt = KeypairTables{};
     ctx->ft = FilterTables{};
     const size_t k = cfg->max_keypairs;

@@ -66,6 +66,7 @@ struct bnk_ctx {
     cudaStream_t admin_stream;
     cudaEvent_t timer_start;
     int sm_count;
+    int aead_mode; // 0 = choose by batch size, 1 = always thread per packet, 2 = always warp per packet (BNK_AEAD_KERNEL)
     std::atomic<uint64_t> launches;
     std::mutex mu;
     std::string last_error;

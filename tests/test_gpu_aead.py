@@ -7,8 +7,18 @@ from tests import helpers as H
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(scope="module", params=["tpp", "wpp"], autouse=True)
+def aead_kernel(request):
+    """Every case runs against both seal/open kernels: thread per packet (throughput) and warp per packet (latency)."""
+    import os
+
+    os.environ["BNK_AEAD_KERNEL"] = request.param  # read when a context is created
+    yield request.param
+    os.environ.pop("BNK_AEAD_KERNEL", None)
+
+
 @pytest.fixture(scope="module")
-def ctx(gpu_lib):
+def ctx(gpu_lib, aead_kernel):
     from bnk_b200 import Context
 
     c = Context(max_keypairs=300, replay_ring_blocks=128, mtu=1420, flow_capacity=1 << 12)
