@@ -218,6 +218,97 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(SortKeySrc 
     }
 }
 
+// --- the whole sort in one CTA, for batches of up to 1024 packets ----------------------
+// Same three steps per digit as above, but keys and indices ping-pong between shared-memory buffers
+// and all passes run inside one launch: a 128-packet batch pays one launch instead of six.
+constexpr uint32_t kSmallMax = 1024;
+__global__ void __launch_bounds__(kSortThreads) group_small_kernel(SortKeySrc src, uint32_t n, uint32_t passes,
+                                                                   uint32_t digit_bits, uint32_t *keys_out,
+                                                                   uint32_t *vals_out) {
+    constexpr uint32_t TILES = kSmallMax / kSortThreads; // 4
+    __shared__ uint32_t kbuf[2][kSmallMax], vbuf[2][kSmallMax];
+    __shared__ uint32_t cur[kSortWarps][kMaxBins];
+    __shared__ uint32_t base_of[kMaxBins];
+    __shared__ uint32_t warp_sum[kSortWarps];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t bins = 1u << digit_bits;
+    const uint32_t begin = warp * (32 * TILES);
+    const uint32_t lt = (1u << lane) - 1u;
+    for (uint32_t p = 0; p < passes; p++) {
+        const uint32_t shift = p * digit_bits;
+        const uint32_t *kin = kbuf[p & 1], *vin = vbuf[p & 1];
+        uint32_t *kout = kbuf[(p + 1) & 1], *vout = vbuf[(p + 1) & 1];
+        for (uint32_t d = tid; d < kSortWarps * kMaxBins; d += kSortThreads) (&cur[0][0])[d] = 0;
+        __syncthreads();
+        uint32_t key[TILES], val[TILES];
+#pragma unroll
+        for (uint32_t t = 0; t < TILES; t++) {
+            const uint32_t i = begin + t * 32 + lane;
+            const bool have = i < n;
+            key[t] = have ? (p == 0 ? slot_key(src, i) : kin[i]) : 0xffffffffu;
+            val[t] = have ? (p == 0 ? i : vin[i]) : 0u;
+            warp_hist_add(cur[warp], (key[t] >> shift) & (bins - 1), have);
+        }
+        __syncthreads();
+        {   // digit bases: exclusive prefix over the digit totals, two digits per thread
+            const uint32_t d0 = 2 * tid, d1 = 2 * tid + 1;
+            uint32_t v0 = 0, v1 = 0;
+            for (uint32_t w = 0; w < kSortWarps; w++) {
+                if (d0 < bins) v0 += cur[w][d0];
+                if (d1 < bins) v1 += cur[w][d1];
+            }
+            uint32_t incl = v0 + v1;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= (uint32_t)o) incl += t;
+            }
+            if (lane == 31) warp_sum[warp] = incl;
+            __syncthreads();
+            uint32_t before = 0;
+            for (uint32_t w = 0; w < warp; w++) before += warp_sum[w];
+            const uint32_t excl = before + incl - (v0 + v1);
+            if (d0 < bins) base_of[d0] = excl;
+            if (d1 < bins) base_of[d1] = excl + v0;
+        }
+        __syncthreads();
+        for (uint32_t d = tid; d < bins; d += kSortThreads) {
+            uint32_t run = base_of[d];
+#pragma unroll
+            for (uint32_t w = 0; w < kSortWarps; w++) {
+                const uint32_t c = cur[w][d];
+                cur[w][d] = run;
+                run += c;
+            }
+        }
+        __syncthreads();
+        const bool final_pass = p + 1 == passes;
+        uint32_t *mine = cur[warp];
+#pragma unroll
+        for (uint32_t t = 0; t < TILES; t++) {
+            const bool have = begin + t * 32 + lane < n;
+            const uint32_t digit = have ? ((key[t] >> shift) & (bins - 1)) : 0xffffffffu;
+            const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+            const uint32_t rank = __popc(peers & lt);
+            uint32_t pos = 0;
+            if (have) pos = mine[digit] + rank;
+            __syncwarp();
+            if (have && rank == 0) mine[digit] += __popc(peers);
+            __syncwarp();
+            if (have) {
+                if (final_pass) {
+                    keys_out[pos] = key[t];
+                    vals_out[pos] = val[t];
+                } else {
+                    kout[pos] = key[t];
+                    vout[pos] = val[t];
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // --- send counters ----------------------------------------------------------------------
 // One thread per slot segment: packets of the slot get base, base+1, ... in batch order and
 // the slot's counter moves past them, saturating at Reject-After-Messages (packets at or
@@ -359,6 +450,10 @@ void sort_pass(const SortKeySrc &src, const uint32_t *kin, const uint32_t *vin, 
 // Stable sort of packet indices 0..n-1 by key.  Returns the number of kernel launches.
 uint32_t group_sort(const SortKeySrc &src, uint32_t n, uint32_t max_chunks, const SortBuffers &sb, cudaStream_t s) {
     const SortPlan plan = plan_for(src.max_slots);
+    if (n <= kSmallMax) {
+        group_small_kernel<<<1, kSortThreads, 0, s>>>(src, n, plan.passes, plan.digit_bits, sb.keys_b, sb.order);
+        return 1;
+    }
     const uint32_t bins = 1u << plan.digit_bits;
     const uint32_t tiles = tiles_for(n, max_chunks);
     const uint32_t chunks = chunks_for(n, tiles);

@@ -165,3 +165,35 @@ def test_send_counters_assigned_in_batch_order(gpu_lib, oracle):
         b.close()
     finally:
         c.close()
+
+
+@pytest.mark.parametrize("n", [1, 2, 31, 33, 257, 1000, 1024, 1025])
+def test_send_counters_small_batches(gpu_lib, n):
+    """Batches of up to 1024 packets group by keypair in a single launch; the nonces must come out the same way."""
+    from bnk_b200 import Context
+    from bnk_b200.device import F_ASSIGN_COUNTERS, PKT_OK
+
+    rng = np.random.default_rng(n)
+    n_peers = 70000
+    c = Context(max_keypairs=n_peers, mtu=1420, flow_capacity=0)
+    try:
+        keys = np.zeros((n_peers, 32), np.uint8)
+        c.set_keypairs(0, keys, keys, np.zeros(n_peers, np.uint32))
+        hot = np.array([3, 65535, 65536, 69999], np.uint32)
+        b = c.batch(n, n * 64)
+        b.off[:n] = H.layout_fixed(n, 64)
+        b.len[:n] = 0
+        nxt = {}
+        for rep in range(3):
+            slots = np.where(rng.random(n) < 0.6, rng.choice(hot, n), rng.integers(0, n_peers, n)).astype(np.uint32)
+            want = np.zeros(n, np.uint64)
+            for i, s in enumerate(slots):
+                want[i] = nxt.get(int(s), 0)
+                nxt[int(s)] = int(want[i]) + 1
+            b.slot[:n] = slots
+            b.seal(n, F_ASSIGN_COUNTERS)
+            assert np.array_equal(b.counter[:n], want), rep
+            assert (b.status[:n] == PKT_OK).all()
+        b.close()
+    finally:
+        c.close()
