@@ -69,6 +69,29 @@ int end_submit(bnk_batch *b) {
     return BNK_SUCCESS;
 }
 
+// Descriptor fields in slab order.  A run of fields moves as one copy when that is cheap (a batch that is mostly
+// full, or a slab prefix of a few KB); otherwise each field moves its first n entries.
+enum { D_OFF = 0, D_LEN, D_SLOT, D_COUNTER, D_OUT_LEN, D_STATUS };
+const uint32_t kDescOff[7] = {0, 4, 8, 12, 20, 24, 25};   // bytes per entry before each field
+cudaError_t desc_copy(bnk_batch *b, size_t n, int first, int last, bool to_device, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    const size_t np = b->npad;
+    const size_t lo = kDescOff[first] * np;
+    const size_t hi = kDescOff[last] * np + (size_t)(kDescOff[last + 1] - kDescOff[last]) * n;
+    const cudaMemcpyKind kind = to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost;
+    if (first == last || hi - lo <= 65536 || 2 * n >= np) {
+        return to_device ? cudaMemcpyAsync(b->d_desc + lo, b->h_desc + lo, hi - lo, kind, s)
+                         : cudaMemcpyAsync(b->h_desc + lo, b->d_desc + lo, hi - lo, kind, s);
+    }
+    for (int f = first; f <= last; f++) {
+        const size_t at = kDescOff[f] * np, bytes = (size_t)(kDescOff[f + 1] - kDescOff[f]) * n;
+        cudaError_t e = to_device ? cudaMemcpyAsync(b->d_desc + at, b->h_desc + at, bytes, kind, s)
+                                  : cudaMemcpyAsync(b->h_desc + at, b->d_desc + at, bytes, kind, s);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
 AeadArgs aead_args(bnk_batch *b, uint32_t n, bool open, const uint32_t *order) {
     bnk_ctx *ctx = b->ctx;
     AeadArgs a{};
@@ -404,23 +427,13 @@ int bnk_batch_destroy(bnk_batch *b) {
     cudaSetDevice(b->ctx->device);
     if (b->stream) cudaStreamSynchronize(b->stream);
     cudaFreeHost(b->host.ring);
-    cudaFreeHost(b->host.off);
-    cudaFreeHost(b->host.len);
-    cudaFreeHost(b->host.slot);
-    cudaFreeHost(b->host.counter);
-    cudaFreeHost(b->host.out_len);
-    cudaFreeHost(b->host.status);
     cudaFreeHost(b->host.src_addr);
+    cudaFreeHost(b->h_desc);
+    cudaFree(b->d_desc);
     cudaFreeHost(b->h_flow_error);
     cudaFreeHost(b->h_gso);
     DeviceBatch &d = b->dev;
     cudaFree(d.ring);
-    cudaFree(d.off);
-    cudaFree(d.len);
-    cudaFree(d.slot);
-    cudaFree(d.out_len);
-    cudaFree(d.counter);
-    cudaFree(d.status);
     cudaFree(d.src_addr);
     cudaFree(d.order);
     cudaFree(d.order_tmp);
@@ -465,12 +478,18 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
         if (e == cudaSuccess) e = cudaMemset(*p, 0, bytes);
     };
     H((void **)&b->host.ring, ring_bytes);
-    H((void **)&b->host.off, n * 4);
-    H((void **)&b->host.len, n * 4);
-    H((void **)&b->host.slot, n * 4);
-    H((void **)&b->host.counter, n * 8);
-    H((void **)&b->host.out_len, n * 4);
-    H((void **)&b->host.status, n);
+    // descriptor arrays share one slab per side so that a small batch moves them with one copy each way
+    b->npad = (max_pkts + 15u) & ~15u;
+    const size_t np = b->npad;
+    H((void **)&b->h_desc, 25 * np);
+    if (e == cudaSuccess) {
+        b->host.off = reinterpret_cast<uint32_t *>(b->h_desc);
+        b->host.len = reinterpret_cast<uint32_t *>(b->h_desc + 4 * np);
+        b->host.slot = reinterpret_cast<uint32_t *>(b->h_desc + 8 * np);
+        b->host.counter = reinterpret_cast<uint64_t *>(b->h_desc + 12 * np);
+        b->host.out_len = reinterpret_cast<uint32_t *>(b->h_desc + 20 * np);
+        b->host.status = b->h_desc + 24 * np;
+    }
     H((void **)&b->host.src_addr, n * BNK_SRC_ADDR_STRIDE);
     H((void **)&b->h_flow_error, sizeof(int));
     H((void **)&b->h_gso, n * sizeof(bnk_gso_super));
@@ -478,12 +497,15 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     b->host.max_pkts = max_pkts;
     DeviceBatch &d = b->dev;
     D((void **)&d.ring, ring_bytes);
-    D((void **)&d.off, n * 4);
-    D((void **)&d.len, n * 4);
-    D((void **)&d.slot, n * 4);
-    D((void **)&d.out_len, n * 4);
-    D((void **)&d.counter, n * 8);
-    D((void **)&d.status, n);
+    D((void **)&b->d_desc, 25 * np);
+    if (e == cudaSuccess) {
+        d.off = reinterpret_cast<uint32_t *>(b->d_desc);
+        d.len = reinterpret_cast<uint32_t *>(b->d_desc + 4 * np);
+        d.slot = reinterpret_cast<uint32_t *>(b->d_desc + 8 * np);
+        d.counter = reinterpret_cast<uint64_t *>(b->d_desc + 12 * np);
+        d.out_len = reinterpret_cast<uint32_t *>(b->d_desc + 20 * np);
+        d.status = b->d_desc + 24 * np;
+    }
     D((void **)&d.src_addr, n * BNK_SRC_ADDR_STRIDE);
     D((void **)&d.order, n * 4);
     D((void **)&d.order_tmp, n * 4);
@@ -526,10 +548,7 @@ int bnk_batch_upload(bnk_batch *b, uint32_t npkts) {
     const uint64_t ext = ring_extent(b, npkts, 64);
     if (ext) CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, b->stream));
     if (n) {
-        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, b->stream));
-        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, b->stream));
-        CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, b->stream));
-        CK(ctx, cudaMemcpyAsync(b->dev.counter, b->host.counter, n * 8, cudaMemcpyHostToDevice, b->stream));
+        CK(ctx, desc_copy(b, n, D_OFF, D_COUNTER, true, b->stream));
     }
     return end_submit(b);
 }
@@ -542,9 +561,7 @@ int bnk_batch_download(bnk_batch *b, uint32_t npkts) {
     const uint64_t ext = ring_extent(b, npkts, 64);
     if (ext) CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, b->stream));
     if (n) {
-        CK(ctx, cudaMemcpyAsync(b->host.counter, b->dev.counter, n * 8, cudaMemcpyDeviceToHost, b->stream));
-        CK(ctx, cudaMemcpyAsync(b->host.out_len, b->dev.out_len, n * 4, cudaMemcpyDeviceToHost, b->stream));
-        CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, b->stream));
+        CK(ctx, desc_copy(b, n, D_COUNTER, D_STATUS, false, b->stream));
     }
     return end_submit(b);
 }
@@ -560,11 +577,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     const uint64_t ext = device_only ? 0 : ring_extent(b, npkts, 16 + 16 + 16);
     if (!(flags & BNK_F_NO_H2D) && n) {
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, s));
-        if (!(flags & BNK_F_ASSIGN_COUNTERS))
-            CK(ctx, cudaMemcpyAsync(b->dev.counter, b->host.counter, n * 8, cudaMemcpyHostToDevice, s));
+        CK(ctx, desc_copy(b, n, D_OFF, (flags & BNK_F_ASSIGN_COUNTERS) ? D_SLOT : D_COUNTER, true, s));
     }
     CK(ctx, cudaEventRecord(b->k_begin, s));
     if (flags & BNK_F_NOTE_OUTBOUND) {
@@ -585,9 +598,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     b->aead_timed = true;
     if (!(flags & BNK_F_NO_D2H) && n) {
         CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
-        CK(ctx, cudaMemcpyAsync(b->host.counter, b->dev.counter, n * 8, cudaMemcpyDeviceToHost, s));
-        CK(ctx, cudaMemcpyAsync(b->host.out_len, b->dev.out_len, n * 4, cudaMemcpyDeviceToHost, s));
-        CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
+        CK(ctx, desc_copy(b, n, D_COUNTER, D_STATUS, false, s));
     }
     return end_submit(b);
 }
@@ -602,10 +613,7 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     const uint64_t ext = device_only ? 0 : ring_extent(b, npkts, (flags & BNK_F_USE_OUT_LEN) ? 48 : 0);
     if (!(flags & BNK_F_NO_H2D) && n) {
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
-        if (!(flags & BNK_F_DEMUX_INDEX))
-            CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, s));
+        CK(ctx, desc_copy(b, n, D_OFF, (flags & BNK_F_DEMUX_INDEX) ? D_LEN : D_SLOT, true, s));
     }
     CK(ctx, cudaEventRecord(b->k_begin, s));
     const uint32_t *order = nullptr;
@@ -637,12 +645,8 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = true;
     if (!(flags & BNK_F_NO_D2H) && n) {
-        if (flags & BNK_F_DEMUX_INDEX)
-            CK(ctx, cudaMemcpyAsync(b->host.slot, b->dev.slot, n * 4, cudaMemcpyDeviceToHost, s));
         CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
-        CK(ctx, cudaMemcpyAsync(b->host.counter, b->dev.counter, n * 8, cudaMemcpyDeviceToHost, s));
-        CK(ctx, cudaMemcpyAsync(b->host.out_len, b->dev.out_len, n * 4, cudaMemcpyDeviceToHost, s));
-        CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
+        CK(ctx, desc_copy(b, n, (flags & BNK_F_DEMUX_INDEX) ? D_SLOT : D_COUNTER, D_STATUS, false, s));
     }
     return end_submit(b);
 }

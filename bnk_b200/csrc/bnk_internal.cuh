@@ -104,6 +104,8 @@ struct bnk_batch {
     bool kernel_timed;
     bool aead_timed;
     bnk_gso_super *h_gso; // pinned staging for the super-packet descriptors
+    uint8_t *h_desc, *d_desc; // descriptor slabs: off | len | slot | counter | out_len | status, each npad entries
+    uint32_t npad;
     int *h_flow_error; // pinned copy of the flow-table overflow flag, refreshed by filter work
 };
 
