@@ -47,9 +47,13 @@ class SplitMix64:
         return int(self.below(1, bound)[0])
 
 
-def splitmix_fill(seed: int, nbytes: int) -> np.ndarray:
-    """Bytes the device-side fill (bnk_batch_fill_random) writes for the same seed."""
-    return SplitMix64(seed).bytes(nbytes)
+def splitmix_fill(seed: int, nbytes: int, byte_offset: int = 0) -> np.ndarray:
+    """Bytes [byte_offset, byte_offset + nbytes) of what the device-side fill (bnk_batch_fill_random) writes for
+    the same seed: word k of the ring is output k of SplitMix64(seed)."""
+    first = byte_offset // 8
+    g = SplitMix64((seed + first * _GAMMA) & _M64)
+    lead = byte_offset - first * 8
+    return g.bytes(lead + nbytes)[lead:]
 
 
 # ---------------------------------------------------------------------------------------
