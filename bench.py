@@ -424,6 +424,35 @@ def run_ours(args, rank, world, local_rank):
         for b in batches:
             b.close()
 
+    # ---- one upstream-sized batch (128 packets, the reference's conn.IdealBatchSize): latency through the C ABI ----
+    small = None
+    if rank == 0 and not args.no_e2e:
+        sn = 128
+        sb = setup_batch(ctx, sn, stride, 32, first_peer=0)
+        sb.ring[:] = 0x5A
+        for _ in range(30):
+            sb.len[:sn] = SIZE
+            sb.seal(sn, F_ASSIGN_COUNTERS)
+            sb.len[:sn] = sb.out_len[:sn]
+            sb.open(sn, F_REPLAY)
+        seal_t, open_t = [], []
+        for _ in range(200):
+            sb.len[:sn] = SIZE
+            t0 = time.perf_counter()
+            sb.seal(sn, F_ASSIGN_COUNTERS)
+            t1 = time.perf_counter()
+            sb.len[:sn] = sb.out_len[:sn]
+            t2 = time.perf_counter()
+            sb.open(sn, F_REPLAY)
+            t3 = time.perf_counter()
+            seal_t.append(t1 - t0)
+            open_t.append(t3 - t2)
+        small_ok = bool((sb.status[:sn] == 0).all())
+        small = {"packets": sn, "payload_bytes": SIZE, "seal_us": statistics.median(seal_t) * 1e6,
+                 "open_us": statistics.median(open_t) * 1e6, "verified": small_ok,
+                 "note": "host wall clock per submit+wait (H2D, counters or replay, warp-per-packet kernel, D2H)"}
+        sb.close()
+
     sampler.stop()
     clocks = sampler.summary(windows)
     ok = dist.all_true(verified and e2e_ok and (imix is None or imix["verified"]))
@@ -448,7 +477,7 @@ def run_ours(args, rank, world, local_rank):
                 "value": e2e_value, "unit": "Gbit/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / K, "batches_in_flight": nb, "mpps": world * 2.0 * n * K / (e2e_ms * 1e-3) / 1e6,
                 "pcie_gbs_each_way": (h2d + d2h) / 2 / (e2e_ms / K * 1e-3) / 1e9},
-            "gpu_launches": int(launches), "roofline": roofline, "alu": alu, "imix": imix, "cpu_baseline": cpu,
+            "gpu_launches": int(launches), "roofline": roofline, "alu": alu, "imix": imix, "small_batch": small, "cpu_baseline": cpu,
             "clocks": clocks, "verified": ok,
         }
         print(json.dumps(line), flush=True)
