@@ -424,6 +424,59 @@ def run_ours(args, rank, world, local_rank):
         for b in batches:
             b.close()
 
+    # ---- ACL filter, configuration 3: 10,000 rules, 300,000 noted flows, 1,000,000 inbound headers, device resident ----
+    filt = None
+    if rank == 0 and not args.no_filter:
+        from bnk_b200.filter import flatten_rule_arrays
+
+        w3 = gen.config3()
+        fctx = Context(device_id=local_rank, max_keypairs=4, flow_capacity=1 << 20)
+        tuples = flatten_rule_arrays(w3.rules, w3.srcs, w3.ports)
+        fctx.acl_set(True, tuples)
+        n_out, n_in = len(w3.outbound_len), len(w3.inbound_len)
+        fb = fctx.batch(n_in, n_in * gen.HDR_STRIDE)
+
+        def load(hdr, lens):
+            m = len(lens)
+            view = fb.ring[:m * gen.HDR_STRIDE].reshape(m, gen.HDR_STRIDE)
+            view[:, 16:16 + hdr.shape[1]] = hdr
+            fb.off[:m] = (np.arange(m, dtype=np.uint64) * gen.HDR_STRIDE).astype(np.uint32)
+            fb.len[:m] = lens
+            fb.upload(m)
+
+        load(w3.outbound, w3.outbound_len)
+        fb.filter_note(n_out, w3.t0_ns, F_NO_H2D)
+        note_ms = fb.last_kernel_ms()
+        load(w3.inbound, w3.inbound_len)
+        check_ms = []
+        for _ in range(W + K):
+            fb.filter_check(n_in, w3.t0_ns + 10**9, F_NO_H2D | F_NO_D2H)
+            check_ms.append(fb.last_kernel_ms())
+        fb.download(n_in)
+        allowed = int((fb.status[:n_in] == 0).sum())
+        cms = statistics.mean(check_ms[W:])
+        filt = {"mverdicts_per_s": n_in / (cms * 1e-3) / 1e6, "check_ms": cms, "headers": n_in, "rules": len(w3.rules),
+                "allowances": int(len(tuples)), "noted_flows": n_out, "note_ms": note_ms, "allowed": allowed,
+                "hbm_gbs": n_in * 29 / (cms * 1e-3) / 1e9,
+                "note": "29 algorithmic bytes per header: latency-bound hash probes, HBM-trivial"}
+        if not args.no_cpu:
+            # the reference walks every rule for every packet under one mutex: one host thread, a sample of the headers
+            from oracle import oracle as O
+
+            of = O.Filter()
+            of.set_rules_arrays(w3.rules.astype(O.RULE_DTYPE), w3.srcs.astype(O.PREFIX_DTYPE), w3.ports.astype(O.PORT_DTYPE))
+            of.note_batch(np.ascontiguousarray(w3.outbound), 28, w3.outbound_len, w3.t0_ns)
+            sample = 20000
+            t0 = time.perf_counter()
+            ov = of.check_batch(np.ascontiguousarray(w3.inbound[:sample]), 28, np.ascontiguousarray(w3.inbound_len[:sample]),
+                                w3.t0_ns + 10**9)
+            dt = time.perf_counter() - t0
+            same = bool(np.array_equal(ov, (fb.status[:sample] == 0).astype(np.uint8)))
+            filt["cpu_baseline"] = {"mverdicts_per_s": sample / dt / 1e6, "cores": 1, "kind": "port", "sample": f"{sample} headers",
+                                    "verdicts_equal_gpu": same}
+        fb.close()
+        fctx.close()
+
     # ---- one upstream-sized batch (128 packets, the reference's conn.IdealBatchSize): latency through the C ABI ----
     small = None
     if rank == 0 and not args.no_e2e:
@@ -477,7 +530,7 @@ def run_ours(args, rank, world, local_rank):
                 "value": e2e_value, "unit": "Gbit/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / K, "batches_in_flight": nb, "mpps": world * 2.0 * n * K / (e2e_ms * 1e-3) / 1e6,
                 "pcie_gbs_each_way": (h2d + d2h) / 2 / (e2e_ms / K * 1e-3) / 1e9},
-            "gpu_launches": int(launches), "roofline": roofline, "alu": alu, "imix": imix, "small_batch": small, "cpu_baseline": cpu,
+            "gpu_launches": int(launches), "roofline": roofline, "alu": alu, "imix": imix, "filter": filt, "small_batch": small, "cpu_baseline": cpu,
             "clocks": clocks, "verified": ok,
         }
         print(json.dumps(line), flush=True)
@@ -497,6 +550,7 @@ def main():
     ap.add_argument("--no-imix", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-probe", action="store_true")
+    ap.add_argument("--no-filter", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the host-ring leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and args.packets == N_PACKETS else args.warmup
