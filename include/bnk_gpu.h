@@ -5,8 +5,9 @@
  * the ACL packet filter with reply-flow tracking.
  *
  * The reference (a Go program) has no FFI.  Each entry point below names the
- * reference interface whose per-packet work it takes over; a cgo binding for
- * them is shown in INTEGRATION.md.  Paths are relative to the reference tree;
+ * reference interface whose per-packet work it takes over (a cgo binding for
+ * them ships with the integration notes of this repository).  Paths are
+ * relative to the reference tree;
  * "wireguard-go" is golang.zx2c4.com/wireguard (go.mod:10) and "x/crypto" is
  * golang.org/x/crypto (go.mod:7), both entered through device.NewDevice at
  * internal/dataplane/engine.go:51.

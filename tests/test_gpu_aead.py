@@ -189,3 +189,81 @@ def test_seal_open_round_trip_mixed_sizes_sorted(ctx, oracle):
     for i in range(0, n, 17):
         assert b.payload(i)[:len(w.payloads[i])] == w.payloads[i]
     b.close()
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_descriptor_fuzz(ctx, oracle, seed):
+    """Random descriptors, many of them invalid (misaligned, out of range, absurd lengths, unknown keypairs): valid
+    packets come out bit-exact, invalid ones are refused with BAD_DESC / MALFORMED and nothing outside a valid packet's
+    own slot changes."""
+    from bnk_b200.device import PKT_BAD_DESC, PKT_MALFORMED
+
+    rng = np.random.default_rng(seed)
+    keys = rng.integers(0, 256, (300, 32), dtype=np.uint8)
+    ridx = rng.integers(0, 2**32, 300, dtype=np.uint64).astype(np.uint32)
+    ctx.set_keypairs(0, keys, keys, ridx)
+    n, slot_bytes = 400, 4096
+    ring_bytes = n * slot_bytes
+    b = ctx.batch(n, ring_bytes)
+    base = rng.integers(0, 256, ring_bytes, dtype=np.uint8)
+    for mode in ("seal", "open"):
+        b.ring[:] = base
+        off = (np.arange(n, dtype=np.uint64) * slot_bytes).astype(np.uint32)
+        length = rng.choice([0, 1, 15, 16, 17, 63, 64, 65, 100, 576, 1420, 1421, 2000, 3000, 4000], n).astype(np.uint32)
+        slot = rng.integers(0, 300, n).astype(np.uint32)
+        counter = rng.integers(0, 2**62, n, dtype=np.uint64)
+        kind = rng.integers(0, 10, n)
+        valid = np.ones(n, bool)
+        for i in range(n):
+            if kind[i] == 0:
+                off[i] += int(rng.choice([1, 4, 8, 12]))           # misaligned
+                valid[i] = False
+            elif kind[i] == 1:
+                slot[i] = int(rng.choice([300, 301, 2**31, 2**32 - 1]))  # no such keypair
+                valid[i] = False
+            elif kind[i] == 2:
+                length[i] = int(rng.choice([2**31, 2**32 - 1, ring_bytes, ring_bytes - 8]))  # runs far past the ring
+                off[i] = int(rng.integers(0, n)) * slot_bytes
+                valid[i] = False
+            elif kind[i] == 3 and i == n - 1:
+                length[i] = slot_bytes                              # last slot: a seal's header/tag room would pass the ring end
+        if mode == "open":
+            # put real messages into the valid slots (payload length such that the message is `length` long when possible)
+            for i in range(n):
+                if valid[i] and length[i] >= 32:
+                    pt = rng.integers(0, 256, int(length[i]) - 32, dtype=np.uint8).tobytes()
+                    m = oracle.wg_seal(keys[slot[i]].tobytes(), 1, int(counter[i]), pt, 0)
+                    if len(m) != length[i]:     # padding made it longer: open the padded message instead
+                        length[i] = len(m)
+                    o = int(off[i])
+                    b.ring[o:o + len(m)] = np.frombuffer(m, np.uint8)
+        seal_fits = lambda i: int(off[i]) + 16 + oracle.wg_padded_len(int(length[i]), 1420) + 16 <= ring_bytes  # noqa: E731
+        before = np.array(b.ring)
+        b.off[:n], b.len[:n], b.slot[:n], b.counter[:n] = off, length, slot, counter
+        if mode == "seal":
+            b.seal(n)
+        else:
+            b.open(n)
+        after = np.array(b.ring)
+        st = np.array(b.status[:n])
+        touched = np.zeros(ring_bytes, bool)
+        for i in range(n):
+            ok_desc = valid[i] and (seal_fits(i) if mode == "seal" else int(off[i]) + int(length[i]) <= ring_bytes)
+            if not ok_desc:
+                assert st[i] == PKT_BAD_DESC, (mode, i, st[i], off[i], length[i], slot[i])
+                continue
+            o, l = int(off[i]), int(length[i])
+            if mode == "seal":
+                want = oracle.wg_seal(keys[slot[i]].tobytes(), int(ridx[slot[i]]), int(counter[i]), before[o + 16:o + 16 + l].tobytes(), 1420)
+                assert st[i] == 0 and after[o:o + len(want)].tobytes() == want, (mode, i)
+                touched[o:o + len(want)] = True
+            else:
+                if l < 32:
+                    assert st[i] == PKT_MALFORMED
+                    continue
+                wst, pt, ctr, _ = oracle.wg_open(keys[slot[i]].tobytes(), before[o:o + l].tobytes())
+                assert st[i] == wst and b.counter[i] == ctr, (mode, i, st[i], wst)
+                assert after[o + 16:o + 16 + len(pt)].tobytes() == pt
+                touched[o + 16:o + l - 16] = True
+        assert np.array_equal(after[~touched], before[~touched]), "bytes outside valid packets changed"
+    b.close()
