@@ -477,6 +477,61 @@ def run_ours(args, rank, world, local_rank):
         fb.close()
         fctx.close()
 
+    # ---- configuration 5 as a loopback pipeline on one context, device resident:
+    #      GSO split -> NoteOutbound -> counters -> seal, then demux -> open -> replay -> inner check -> CheckInbound ----
+    pipe = None
+    if rank == 0 and not args.no_pipeline:
+        from bnk_b200.device import (F_CHECK_INBOUND, F_DEMUX_INDEX, F_INNER_CHECK, F_NOTE_OUTBOUND, GSO_SUPER_DTYPE,
+                                     PKT_FILTER_DENY, PKT_OK)
+        from bnk_b200.filter import flatten_rule_arrays
+
+        n_super, n_seg, mss, p_peers = 2048, 47, 1380, 10_000
+        w5 = gen.config5(n_super=n_super, n_peers=p_peers)
+        f5 = gen.config3(n_rules=2000, n_nodes=5000, n_out=16, n_in=16, seed=gen.seed_for(5) + 1)
+        hit = np.flatnonzero(f5.rules["proto"] == 6)[:3]
+        for rr in hit:
+            f5.srcs["addr"][f5.rules["src_begin"][rr]] = w5.self_ip
+        pctx = Context(device_id=local_rank, max_keypairs=p_peers, mtu=SIZE, flow_capacity=1 << 16)
+        pctx.set_keypairs(0, w5.keys, w5.keys, (0x1000 + np.arange(p_peers)).astype(np.uint32))
+        for p_ in sorted(set(w5.peer.tolist())):
+            pctx.index_set(0x1000 + p_, p_)
+            pctx.set_allowed_ip(p_, w5.self_ip)
+        pctx.acl_set(True, flatten_rule_arrays(f5.rules, f5.srcs, f5.ports))
+        n_pkts = n_super * n_seg
+        sup = np.zeros(n_super, GSO_SUPER_DTYPE)
+        sup_stride = (len(w5.supers[0]) + 15) & ~15
+        pb = pctx.batch(n_pkts, n_pkts * stride + n_super * sup_stride)
+        for j, pkt in enumerate(w5.supers):
+            o = n_pkts * stride + j * sup_stride
+            pb.ring[o:o + len(pkt)] = np.frombuffer(pkt, np.uint8)
+            sup[j] = (o, len(pkt), j * n_seg, n_seg, 40, mss, 20, 16, 6, (0, 0, 0))
+        pb.off[:n_pkts] = (np.arange(n_pkts, dtype=np.uint64) * np.uint64(stride)).astype(np.uint32)
+        pb.len[:n_pkts] = 40 + mss
+        pb.slot[:n_pkts] = np.repeat(w5.peer, n_seg)
+        pb.gso_split(sup, n_pkts)  # uploads the ring once
+        split_ms, seal5_ms, open5_ms = [], [], []
+        now = 1_700_000_000 * 10**9
+        for it in range(W + K):
+            pb.gso_split(sup, n_pkts, F_NO_H2D)
+            split_ms.append(pb.last_kernel_ms())
+            pb.seal(n_pkts, F_NO_H2D | F_NO_D2H | F_NOTE_OUTBOUND | F_ASSIGN_COUNTERS, now_ns=now + it)
+            seal5_ms.append(pb.last_kernel_ms())
+            pb.open(n_pkts, F_NO_H2D | F_NO_D2H | F_USE_OUT_LEN | F_DEMUX_INDEX | F_REPLAY | F_INNER_CHECK | F_CHECK_INBOUND,
+                    now_ns=now + it)
+            open5_ms.append(pb.last_kernel_ms())
+        pb.download(n_pkts)
+        st5 = np.array(pb.status[:n_pkts])
+        t5 = statistics.mean(split_ms[W:]) + statistics.mean(seal5_ms[W:]) + statistics.mean(open5_ms[W:])
+        pipe = {"segments": n_pkts, "super_packets": n_super, "peers": p_peers, "rules": 2000,
+                "split_ms": statistics.mean(split_ms[W:]), "seal_side_ms": statistics.mean(seal5_ms[W:]),
+                "open_side_ms": statistics.mean(open5_ms[W:]),
+                "gbps": 2.0 * n_pkts * (40 + mss) * 8 / (t5 * 1e-3) / 1e9, "mpps": 2.0 * n_pkts / (t5 * 1e-3) / 1e6,
+                "allowed": int((st5 == PKT_OK).sum()), "filter_deny": int((st5 == PKT_FILTER_DENY).sum()),
+                "verified": bool(((st5 == PKT_OK) | (st5 == PKT_FILTER_DENY)).all()),
+                "note": "one context plays sender and receiver (loopback); Zipf(1.1) peers, 47 x 1420 B per super-packet"}
+        pb.close()
+        pctx.close()
+
     # ---- one upstream-sized batch (128 packets, the reference's conn.IdealBatchSize): latency through the C ABI ----
     small = None
     if rank == 0 and not args.no_e2e:
@@ -530,7 +585,7 @@ def run_ours(args, rank, world, local_rank):
                 "value": e2e_value, "unit": "Gbit/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / K, "batches_in_flight": nb, "mpps": world * 2.0 * n * K / (e2e_ms * 1e-3) / 1e6,
                 "pcie_gbs_each_way": (h2d + d2h) / 2 / (e2e_ms / K * 1e-3) / 1e9},
-            "gpu_launches": int(launches), "roofline": roofline, "alu": alu, "imix": imix, "filter": filt, "small_batch": small, "cpu_baseline": cpu,
+            "gpu_launches": int(launches), "roofline": roofline, "alu": alu, "imix": imix, "filter": filt, "pipeline5": pipe, "small_batch": small, "cpu_baseline": cpu,
             "clocks": clocks, "verified": ok,
         }
         print(json.dumps(line), flush=True)
@@ -551,6 +606,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-probe", action="store_true")
     ap.add_argument("--no-filter", action="store_true")
+    ap.add_argument("--no-pipeline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the host-ring leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and args.packets == N_PACKETS else args.warmup

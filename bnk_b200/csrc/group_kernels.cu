@@ -6,8 +6,10 @@
 // Why a stable grouping: both the send counter (packets of one peer get
 // consecutive nonces in batch order) and the replay window (verdicts depend on
 // the arrival order of a peer's authenticated packets) are defined by a
-// sequential walk per peer.  Different peers are independent, so after grouping
-// one thread walks one peer's packets and all peers proceed in parallel.
+// sequential walk per peer.  Different peers are independent, and inside a peer
+// the walk has a parallel form: a packet's nonce is the peer's counter plus its
+// rank in the peer's run, and the window's verdicts over a stretch of packets
+// follow in closed form from the state at the start of the stretch.
 #include "bnk_internal.cuh"
 
 namespace {
@@ -310,71 +312,121 @@ __global__ void __launch_bounds__(kSortThreads) group_small_kernel(SortKeySrc sr
 }
 
 // --- send counters ----------------------------------------------------------------------
-// One thread per slot segment: packets of the slot get base, base+1, ... in batch order and
-// the slot's counter moves past them, saturating at Reject-After-Messages (packets at or
-// beyond it are refused by the seal kernel).
-__global__ void assign_counters_kernel(const uint32_t *keys, const uint32_t *order, const uint32_t *head,
-                                       uint32_t n, uint32_t max_slots, uint64_t *send_counter,
-                                       uint64_t *counter_out) {
+// Packets of a slot get base, base+1, ... in batch order and the slot's counter moves past them, saturating
+// at Reject-After-Messages (packets at or beyond it are refused by the seal kernel).  One thread per packet:
+// in the sorted order a packet's rank inside its run is its position minus the start of the run, found by
+// binary search, so a peer that owns most of a batch costs no more than any other.  The counters are read
+// by the first kernel and advanced by the second, so no thread can see a counter that already moved.
+__device__ __forceinline__ uint32_t run_start(const uint32_t *keys, uint32_t j) {
+    const uint32_t key = keys[j];
+    uint32_t lo = 0, hi = j; // first index in [0, j] whose key equals keys[j]
+    while (lo < hi) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (keys[mid] < key) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+__device__ __forceinline__ uint64_t saturating_counter(uint64_t base, uint32_t k) {
+    const uint64_t c = base + k;
+    return (c < base || c > BNK_REJECT_AFTER_MESSAGES) ? BNK_REJECT_AFTER_MESSAGES : c;
+}
+__global__ void assign_counters_kernel(const uint32_t *keys, const uint32_t *order, uint32_t n, uint32_t max_slots,
+                                       const uint64_t *send_counter, uint64_t *counter_out) {
     const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= n) return;
     const uint32_t slot = keys[j];
-    if (head ? !head[j] : (j != 0 && keys[j - 1] == slot)) return; // only the first packet of a run walks it
     if (slot >= max_slots) return;
-    const uint64_t base = send_counter[slot];
-    uint32_t k = j;
-    for (; k < n && keys[k] == slot; k++) {
-        uint64_t c = base + (uint64_t)(k - j);
-        if (c < base || c > BNK_REJECT_AFTER_MESSAGES) c = BNK_REJECT_AFTER_MESSAGES;
-        counter_out[order[k]] = c;
-    }
-    uint64_t next = base + (uint64_t)(k - j);
-    if (next < base || next > BNK_REJECT_AFTER_MESSAGES) next = BNK_REJECT_AFTER_MESSAGES;
-    send_counter[slot] = next;
+    counter_out[order[j]] = saturating_counter(send_counter[slot], j - run_start(keys, j));
+}
+__global__ void advance_counters_kernel(const uint32_t *keys, uint32_t n, uint32_t max_slots, uint64_t *send_counter) {
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const uint32_t slot = keys[j];
+    if (slot >= max_slots || (j + 1 < n && keys[j + 1] == slot)) return; // the last packet of a run moves the counter
+    send_counter[slot] = saturating_counter(send_counter[slot], j - run_start(keys, j) + 1);
 }
 
 // --- anti-replay window, RFC 6479 -------------------------------------------------------
-// One thread per slot segment walks the slot's packets in arrival order; only packets the open
-// kernel authenticated (status OK or KEEPALIVE) reach the window, the others are stepped over.
-__global__ void replay_kernel(const uint32_t *keys, const uint32_t *order, const uint32_t *head, uint32_t n,
-                              uint32_t max_slots, uint32_t ring_blocks, uint64_t *replay_last,
-                              uint64_t *replay_ring, const uint64_t *counter, uint8_t *status) {
-    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n) return;
-    const uint32_t slot = keys[j];
-    if (head ? !head[j] : (j != 0 && keys[j - 1] == slot)) return;
-    if (slot >= max_slots) return;
-    uint64_t *ring = replay_ring + (size_t)slot * ring_blocks;
-    const uint64_t mask = ring_blocks - 1;
+// The window is defined by a sequential walk over a peer's authenticated packets in arrival order.  For any
+// stretch of that walk the verdicts have a closed form in terms of the state (last, ring) at its start:
+// with M_j = max(last, counters of the earlier packets of the stretch), packet j is accepted iff its counter
+// is below the limit and either exceeds M_j, or lies within the window behind M_j, was not marked in the ring
+// at the start (only counters <= last can be) and does not repeat an earlier counter of the stretch.  (A ring
+// block that the walk would have cleared before reaching j lies more than a window behind M_j.)  Afterwards
+// last = max, the blocks the top moved over are cleared, and the bit of every packet that reached the window
+// is set unless the top has moved a whole ring past it.
+// One warp handles a peer: 32 packets at a time through the closed form (prefix max and duplicate search by
+// shuffle / match), the stretches one after the other.  Warp w looks at sorted positions [32w, 32w+32) and
+// handles the peers whose run starts there, so a peer that owns most of a batch is 32-wide instead of serial.
+__global__ void __launch_bounds__(256) replay_kernel(const uint32_t *keys, const uint32_t *order, uint32_t n,
+                                                     uint32_t max_slots, uint32_t ring_blocks, uint64_t *replay_last,
+                                                     uint64_t *replay_ring, const uint64_t *counter, uint8_t *status) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t first = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 32u;
+    if (first >= n) return;
+    const uint32_t mine = first + lane;
+    const bool is_head = mine < n && (mine == 0 || keys[mine - 1] != keys[mine]);
+    uint32_t heads = __ballot_sync(0xffffffffu, is_head);
+    const uint64_t rmask = ring_blocks - 1;
     const uint64_t window = (uint64_t)(ring_blocks - 1) * 64u;
-    uint64_t last = replay_last[slot];
-    for (uint32_t k = j; k < n && keys[k] == slot; k++) {
-        const uint32_t pkt = order[k];
-        const uint8_t st = status[pkt];
-        if (st != BNK_PKT_OK && st != BNK_PKT_KEEPALIVE) continue;
-        const uint64_t c = counter[pkt];
-        bool ok = c < BNK_REJECT_AFTER_MESSAGES;
-        if (ok) {
-            const uint64_t block = c >> 6;
-            if (c > last) {
-                const uint64_t top = last >> 6;
-                uint64_t steps = block - top;
-                if (steps > ring_blocks) steps = ring_blocks;
-                for (uint64_t s = 1; s <= steps; s++) ring[(top + s) & mask] = 0;
-                last = c;
-            } else if (last - c > window) {
-                ok = false;
+    const uint32_t lt = (1u << lane) - 1u;
+    while (heads) {
+        const uint32_t h = first + (__ffs(heads) - 1);
+        heads &= heads - 1;
+        const uint32_t slot = keys[h];
+        if (slot >= max_slots) continue; // packets that take no part
+        unsigned long long *ring = reinterpret_cast<unsigned long long *>(replay_ring) + (size_t)slot * ring_blocks;
+        uint64_t last = replay_last[slot];
+        for (uint32_t base = h;; base += 32) {
+            const uint32_t pos = base + lane;
+            const bool in = pos < n && keys[pos] == slot;
+            const uint32_t inmask = __ballot_sync(0xffffffffu, in);
+            if (!inmask) break;
+            uint32_t pkt = 0;
+            bool auth = false;
+            uint64_t c = 0;
+            if (in) {
+                pkt = order[pos];
+                const uint8_t st = status[pkt];
+                auth = st == BNK_PKT_OK || st == BNK_PKT_KEEPALIVE;
+                if (auth) c = counter[pkt];
             }
-            if (ok) {
-                const uint64_t bit = 1ull << (c & 63u);
-                const uint64_t w = ring[block & mask];
-                if (w & bit) ok = false;
-                else ring[block & mask] = w | bit;
+            const bool live = auth && c < BNK_REJECT_AFTER_MESSAGES;
+            // M: highest counter before this lane's packet
+            uint64_t incl = live ? c : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint64_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= (uint32_t)o && t > incl) incl = t;
             }
+            uint64_t excl = __shfl_up_sync(0xffffffffu, incl, 1);
+            if (lane == 0) excl = 0;
+            const uint64_t M = excl > last ? excl : last;
+            const uint64_t stretch_max = __shfl_sync(0xffffffffu, incl, 31);
+            // an earlier packet of the stretch with the same counter?
+            const unsigned long long probe = live ? c : (BNK_REJECT_AFTER_MESSAGES + 1ull + lane);
+            const bool repeated = (__match_any_sync(0xffffffffu, probe) & lt) != 0;
+            const bool behind = live && c <= M;
+            const bool too_old = behind && (M - c > window);
+            bool seen = false;
+            if (behind && !too_old && c <= last) seen = (__ldcg(&ring[(c >> 6) & rmask]) >> (c & 63u)) & 1ull; // L2: the word may have just been updated by atomics
+            const bool accept = live && (c > M || (!too_old && !seen && !repeated));
+            if (auth && !accept) status[pkt] = BNK_PKT_REPLAY;
+            __syncwarp();
+            const uint64_t new_last = stretch_max > last ? stretch_max : last;
+            const uint64_t top = last >> 6, ntop = new_last >> 6;
+            uint64_t steps = ntop - top;
+            if (steps > ring_blocks) steps = ring_blocks;
+            for (uint64_t i = lane; i < steps; i += 32) __stcg(&ring[(top + 1 + i) & rmask], 0ull);
+            __syncwarp();
+            if (live && !too_old && ntop - (c >> 6) < ring_blocks) atomicOr(&ring[(c >> 6) & rmask], 1ull << (c & 63u));
+            __syncwarp();
+            last = new_last;
+            if (inmask != 0xffffffffu) break;
         }
-        if (!ok) status[pkt] = BNK_PKT_REPLAY;
+        if (lane == 0) replay_last[slot] = last;
     }
-    replay_last[slot] = last;
 }
 
 // --- scheduling order by length class (mixed packet sizes) ------------------------------
@@ -503,10 +555,12 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
     cudaError_t e = launch_group_by_slot(b, n, false, s);
     if (e != cudaSuccess) return e;
     DeviceBatch &d = b->dev;
-    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, nullptr, n,
+    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, n,
                                                           b->ctx->cfg.max_keypairs, b->ctx->kt.send_counter,
                                                           d.counter);
-    b->ctx->launches += 1;
+    advance_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, n, b->ctx->cfg.max_keypairs,
+                                                           b->ctx->kt.send_counter);
+    b->ctx->launches += 2;
     return cudaGetLastError();
 }
 
@@ -515,7 +569,7 @@ cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     DeviceBatch &d = b->dev;
     bnk_ctx *ctx = b->ctx;
-    replay_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, nullptr, n,
+    replay_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, n,
                                                  ctx->cfg.max_keypairs, ctx->cfg.replay_ring_blocks,
                                                  ctx->kt.replay_last, ctx->kt.replay_ring, d.counter, d.status);
     ctx->launches += 1;
@@ -614,9 +668,10 @@ extern "C" int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uin
     SortKeySrc src{dev_slot, nullptr, ctx->cfg.max_keypairs, 0};
     SortBuffers sb{keys_a, keys_b, vals_a, order, hist + kMaxBins, hist};
     const uint32_t sort_launches = group_sort(src, n, kNoAllocMaxChunks, sb, s);
-    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, order, nullptr, n, ctx->cfg.max_keypairs,
+    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, order, n, ctx->cfg.max_keypairs,
                                                           ctx->kt.send_counter, dev_counter);
-    ctx->launches += sort_launches + 1;
+    advance_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, n, ctx->cfg.max_keypairs, ctx->kt.send_counter);
+    ctx->launches += sort_launches + 2;
     if ((e = cudaGetLastError()) != cudaSuccess) return noalloc_fail(ctx, BNK_ECUDA, "kernel launch", e);
     return BNK_SUCCESS;
 }
