@@ -157,6 +157,32 @@ def measured_hbm_peak():
         return 6650.0, "fallback (earlier measurement on this pool)"
 
 
+def bind_to_gpu_numa_node(local_rank: int) -> str:
+    """Pins this rank to the CPUs of the NUMA node its GPU hangs off, so that the pinned packet rings are
+    allocated in that node's memory and the host<->device copies do not cross sockets.  Best effort."""
+    try:
+        bus = subprocess.run(["nvidia-smi", "-i", str(local_rank), "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=20).stdout.strip().lower()
+        if not bus:
+            return "no bus id"
+        if bus.startswith("00000000:"):
+            bus = bus[4:]
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read().strip())
+        if node < 0:
+            return f"gpu {bus}: no numa node"
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return f"gpu {bus}: node {node} has no allowed cpu"
+        os.sched_setaffinity(0, allowed)
+        return f"gpu {bus}: numa node {node}, {len(allowed)} cpus"
+    except Exception as e:  # noqa: BLE001 - placement is an optimisation, never a failure
+        return f"not bound ({type(e).__name__})"
+
+
 def host_threads() -> int:
     try:
         return len(os.sched_getaffinity(0))
@@ -257,6 +283,7 @@ def run_ours(args, rank, world, local_rank):
     from bnk_b200.device import (F_ASSIGN_COUNTERS, F_NO_D2H, F_NO_H2D, F_REPLAY, F_SORT_BY_LENGTH, F_USE_OUT_LEN,
                                  slot_size)
 
+    placement = bind_to_gpu_numa_node(local_rank) if world > 1 else "single rank: not bound"
     dist = Dist(rank, world, local_rank)
     K, W = args.steps, args.warmup
     n, peers = args.packets, min(N_PEERS, max(1, args.packets // 16))
@@ -586,7 +613,7 @@ def run_ours(args, rank, world, local_rank):
                 "ms_per_step": e2e_ms / K, "batches_in_flight": nb, "mpps": world * 2.0 * n * K / (e2e_ms * 1e-3) / 1e6,
                 "pcie_gbs_each_way": (h2d + d2h) / 2 / (e2e_ms / K * 1e-3) / 1e9},
             "gpu_launches": int(launches), "roofline": roofline, "alu": alu, "imix": imix, "filter": filt, "pipeline5": pipe, "small_batch": small, "cpu_baseline": cpu,
-            "clocks": clocks, "verified": ok,
+            "clocks": clocks, "verified": ok, "placement": placement,
         }
         print(json.dumps(line), flush=True)
     ctx.close()
