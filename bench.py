@@ -280,7 +280,7 @@ def setup_batch(ctx, n, stride, peers, first_peer=0):
 
 def run_ours(args, rank, world, local_rank):
     from bnk_b200 import Context, gen
-    from bnk_b200.device import (F_ASSIGN_COUNTERS, F_NO_D2H, F_NO_H2D, F_REPLAY, F_SORT_BY_LENGTH, F_USE_OUT_LEN,
+    from bnk_b200.device import (F_ASSIGN_COUNTERS, F_NO_D2H, F_NO_H2D, F_REPLAY, F_SORT_BY_LENGTH, F_TIMED, F_USE_OUT_LEN,
                                  slot_size)
 
     placement = bind_to_gpu_numa_node(local_rank) if world > 1 else "single rank: not bound"
@@ -335,9 +335,9 @@ def run_ours(args, rank, world, local_rank):
     seal_ms, open_ms = [], []
     t_begin = time.time()
     for _ in range(max(K, 3)):
-        dev.seal(n, SEAL, wait=False)
+        dev.seal(n, SEAL | F_TIMED, wait=False)
         seal_ms.append(dev.last_aead_ms())
-        dev.open(n, OPEN, wait=False)
+        dev.open(n, OPEN | F_TIMED, wait=False)
         open_ms.append(dev.last_aead_ms())
     dev.wait()
     windows.append((t_begin, time.time()))
@@ -472,12 +472,12 @@ def run_ours(args, rank, world, local_rank):
             fb.upload(m)
 
         load(w3.outbound, w3.outbound_len)
-        fb.filter_note(n_out, w3.t0_ns, F_NO_H2D)
+        fb.filter_note(n_out, w3.t0_ns, F_NO_H2D | F_TIMED)
         note_ms = fb.last_kernel_ms()
         load(w3.inbound, w3.inbound_len)
         check_ms = []
         for _ in range(W + K):
-            fb.filter_check(n_in, w3.t0_ns + 10**9, F_NO_H2D | F_NO_D2H)
+            fb.filter_check(n_in, w3.t0_ns + 10**9, F_NO_H2D | F_NO_D2H | F_TIMED)
             check_ms.append(fb.last_kernel_ms())
         fb.download(n_in)
         allowed = int((fb.status[:n_in] == 0).sum())
@@ -539,11 +539,11 @@ def run_ours(args, rank, world, local_rank):
         split_ms, seal5_ms, open5_ms = [], [], []
         now = 1_700_000_000 * 10**9
         for it in range(W + K):
-            pb.gso_split(sup, n_pkts, F_NO_H2D)
+            pb.gso_split(sup, n_pkts, F_NO_H2D | F_TIMED)
             split_ms.append(pb.last_kernel_ms())
-            pb.seal(n_pkts, F_NO_H2D | F_NO_D2H | F_NOTE_OUTBOUND | F_ASSIGN_COUNTERS, now_ns=now + it)
+            pb.seal(n_pkts, F_NO_H2D | F_NO_D2H | F_NOTE_OUTBOUND | F_ASSIGN_COUNTERS | F_TIMED, now_ns=now + it)
             seal5_ms.append(pb.last_kernel_ms())
-            pb.open(n_pkts, F_NO_H2D | F_NO_D2H | F_USE_OUT_LEN | F_DEMUX_INDEX | F_REPLAY | F_INNER_CHECK | F_CHECK_INBOUND,
+            pb.open(n_pkts, F_NO_H2D | F_NO_D2H | F_USE_OUT_LEN | F_DEMUX_INDEX | F_REPLAY | F_INNER_CHECK | F_CHECK_INBOUND | F_TIMED,
                     now_ns=now + it)
             open5_ms.append(pb.last_kernel_ms())
         pb.download(n_pkts)

@@ -25,6 +25,7 @@ F_SORT_BY_LENGTH = 1 << 6
 F_USE_OUT_LEN = 1 << 7
 F_DEMUX_INDEX = 1 << 8
 F_INNER_CHECK = 1 << 9
+F_TIMED = 1 << 10
 
 WG_HEADER = 16
 WG_TAG = 16

@@ -63,11 +63,16 @@ int begin_submit(bnk_batch *b, uint32_t npkts, bool touches_host = true) {
     return BNK_SUCCESS;
 }
 
-int end_submit(bnk_batch *b) {
-    CK(b->ctx, cudaEventRecord(b->done, b->stream));
-    b->in_flight = true;
-    return BNK_SUCCESS;
-}
+// Closes a submit on every path out of it: whatever was queued before an error is still covered by the
+// batch's completion event, so a later bnk_wait really waits for it before the host touches the ring.
+struct SubmitScope {
+    bnk_batch *b;
+    explicit SubmitScope(bnk_batch *batch) : b(batch) {}
+    ~SubmitScope() {
+        cudaEventRecord(b->done, b->stream);
+        b->in_flight = true;
+    }
+};
 
 // Descriptor fields in slab order.  A run of fields moves as one copy when that is cheap (a batch that is mostly
 // full, or a slab prefix of a few KB); otherwise each field moves its first n entries.
@@ -543,6 +548,7 @@ int bnk_batch_view_get(bnk_batch *b, bnk_batch_view *out) {
 int bnk_batch_upload(bnk_batch *b, uint32_t npkts) {
     int rc = begin_submit(b, npkts);
     if (rc) return rc;
+    SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     const size_t n = npkts;
     const uint64_t ext = ring_extent(b, npkts, 64);
@@ -550,12 +556,13 @@ int bnk_batch_upload(bnk_batch *b, uint32_t npkts) {
     if (n) {
         CK(ctx, desc_copy(b, n, D_OFF, D_COUNTER, true, b->stream));
     }
-    return end_submit(b);
+    return BNK_SUCCESS;
 }
 
 int bnk_batch_download(bnk_batch *b, uint32_t npkts) {
     int rc = begin_submit(b, npkts);
     if (rc) return rc;
+    SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     const size_t n = npkts;
     const uint64_t ext = ring_extent(b, npkts, 64);
@@ -563,15 +570,17 @@ int bnk_batch_download(bnk_batch *b, uint32_t npkts) {
     if (n) {
         CK(ctx, desc_copy(b, n, D_COUNTER, D_STATUS, false, b->stream));
     }
-    return end_submit(b);
+    return BNK_SUCCESS;
 }
 
 int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
     const bool device_only = (flags & BNK_F_NO_H2D) && (flags & BNK_F_NO_D2H);
     int rc = begin_submit(b, npkts, !device_only);
     if (rc) return rc;
+    SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
+    const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
     // header room + payload + padding (< 16) + tag
     const uint64_t ext = device_only ? 0 : ring_extent(b, npkts, 16 + 16 + 16);
@@ -579,7 +588,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
         CK(ctx, desc_copy(b, n, D_OFF, (flags & BNK_F_ASSIGN_COUNTERS) ? D_SLOT : D_COUNTER, true, s));
     }
-    CK(ctx, cudaEventRecord(b->k_begin, s));
+    if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     if (flags & BNK_F_NOTE_OUTBOUND) {
         CK(ctx, launch_filter_note(b, npkts, now_unix_ns, s));
         CK(ctx, cudaMemcpyAsync(b->h_flow_error, ctx->ft.flow_error, sizeof(int), cudaMemcpyDeviceToHost, s));
@@ -590,32 +599,34 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         CK(ctx, launch_length_order(b, npkts, b->dev.len, false, s));
         order = b->dev.len_order;
     }
-    CK(ctx, cudaEventRecord(b->a_begin, s));
+    if (timed) CK(ctx, cudaEventRecord(b->a_begin, s));
     CK(ctx, launch_seal(aead_args(b, npkts, false, order), s, ctx));
-    CK(ctx, cudaEventRecord(b->a_end, s));
-    CK(ctx, cudaEventRecord(b->k_end, s));
-    b->kernel_timed = true;
-    b->aead_timed = true;
+    if (timed) CK(ctx, cudaEventRecord(b->a_end, s));
+    if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = timed;
+    b->aead_timed = timed;
     if (!(flags & BNK_F_NO_D2H) && n) {
         CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
         CK(ctx, desc_copy(b, n, D_COUNTER, D_STATUS, false, s));
     }
-    return end_submit(b);
+    return BNK_SUCCESS;
 }
 
 int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
     const bool device_only = (flags & BNK_F_NO_H2D) && (flags & BNK_F_NO_D2H);
     int rc = begin_submit(b, npkts, !device_only);
     if (rc) return rc;
+    SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
+    const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
     const uint64_t ext = device_only ? 0 : ring_extent(b, npkts, (flags & BNK_F_USE_OUT_LEN) ? 48 : 0);
     if (!(flags & BNK_F_NO_H2D) && n) {
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
         CK(ctx, desc_copy(b, n, D_OFF, (flags & BNK_F_DEMUX_INDEX) ? D_LEN : D_SLOT, true, s));
     }
-    CK(ctx, cudaEventRecord(b->k_begin, s));
+    if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     const uint32_t *order = nullptr;
     AeadArgs oa = aead_args(b, npkts, true, nullptr);
     if (flags & BNK_F_USE_OUT_LEN) oa.len = b->dev.out_len;
@@ -632,30 +643,32 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         CK(ctx, launch_group_by_slot(b, npkts, false, b->aux_stream));
         CK(ctx, cudaEventRecord(b->ev_join, b->aux_stream));
     }
-    CK(ctx, cudaEventRecord(b->a_begin, s));
+    if (timed) CK(ctx, cudaEventRecord(b->a_begin, s));
     CK(ctx, launch_open(oa, s, ctx));
-    CK(ctx, cudaEventRecord(b->a_end, s));
-    b->aead_timed = true;
+    if (timed) CK(ctx, cudaEventRecord(b->a_end, s));
+    b->aead_timed = timed;
     if (flags & BNK_F_REPLAY) {
         CK(ctx, cudaStreamWaitEvent(s, b->ev_join, 0));
         CK(ctx, launch_replay(b, npkts, s));
     }
     if (flags & BNK_F_INNER_CHECK) CK(ctx, launch_inner_check(b, npkts, s));
     if (flags & BNK_F_CHECK_INBOUND) CK(ctx, launch_filter_check(b, npkts, now_unix_ns, true, s));
-    CK(ctx, cudaEventRecord(b->k_end, s));
-    b->kernel_timed = true;
+    if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = timed;
     if (!(flags & BNK_F_NO_D2H) && n) {
         CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
         CK(ctx, desc_copy(b, n, (flags & BNK_F_DEMUX_INDEX) ? D_SLOT : D_COUNTER, D_STATUS, false, s));
     }
-    return end_submit(b);
+    return BNK_SUCCESS;
 }
 
 int bnk_filter_note_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
     int rc = begin_submit(b, npkts);
     if (rc) return rc;
+    SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
+    const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
     if (!(flags & BNK_F_NO_H2D) && n) {
         const uint64_t ext = ring_extent(b, npkts, 16);
@@ -663,19 +676,21 @@ int bnk_filter_note_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t
         CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
         CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
     }
-    CK(ctx, cudaEventRecord(b->k_begin, s));
+    if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     CK(ctx, launch_filter_note(b, npkts, now_unix_ns, s));
-    CK(ctx, cudaEventRecord(b->k_end, s));
-    b->kernel_timed = true;
+    if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = timed;
     CK(ctx, cudaMemcpyAsync(b->h_flow_error, ctx->ft.flow_error, sizeof(int), cudaMemcpyDeviceToHost, s));
-    return end_submit(b);
+    return BNK_SUCCESS;
 }
 
 int bnk_filter_check_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
     int rc = begin_submit(b, npkts);
     if (rc) return rc;
+    SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
+    const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
     if (!(flags & BNK_F_NO_H2D) && n) {
         const uint64_t ext = ring_extent(b, npkts, 16);
@@ -683,20 +698,22 @@ int bnk_filter_check_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_
         CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
         CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
     }
-    CK(ctx, cudaEventRecord(b->k_begin, s));
+    if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     CK(ctx, launch_filter_check(b, npkts, now_unix_ns, false, s));
-    CK(ctx, cudaEventRecord(b->k_end, s));
-    b->kernel_timed = true;
+    if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = timed;
     if (!(flags & BNK_F_NO_D2H) && n)
         CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
-    return end_submit(b);
+    return BNK_SUCCESS;
 }
 
 int bnk_classify_submit(bnk_batch *b, uint32_t npkts, uint32_t flags) {
     int rc = begin_submit(b, npkts);
     if (rc) return rc;
+    SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
+    const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
     if (!(flags & BNK_F_NO_H2D) && n) {
         const uint64_t ext = ring_extent(b, npkts, 0);
@@ -705,23 +722,25 @@ int bnk_classify_submit(bnk_batch *b, uint32_t npkts, uint32_t flags) {
         CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
         CK(ctx, cudaMemcpyAsync(b->dev.src_addr, b->host.src_addr, n * BNK_SRC_ADDR_STRIDE, cudaMemcpyHostToDevice, s));
     }
-    CK(ctx, cudaEventRecord(b->k_begin, s));
+    if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     CK(ctx, launch_classify(b, npkts, s));
-    CK(ctx, cudaEventRecord(b->k_end, s));
-    b->kernel_timed = true;
+    if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = timed;
     if (!(flags & BNK_F_NO_D2H) && n) {
         CK(ctx, cudaMemcpyAsync(b->host.slot, b->dev.slot, n * 4, cudaMemcpyDeviceToHost, s));
         CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
     }
-    return end_submit(b);
+    return BNK_SUCCESS;
 }
 
 int bnk_gso_split_submit(bnk_batch *b, const bnk_gso_super *supers, uint32_t n_super, uint32_t n_pkts,
                          uint32_t flags) {
     int rc = begin_submit(b, n_pkts, true); // the descriptor staging area is host memory in any case
     if (rc) return rc;
+    SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
+    const bool timed = (flags & BNK_F_TIMED) != 0;
     if (n_super > b->max_pkts || (n_super && !supers)) return fail(ctx, BNK_EINVAL, "bad super-packet list");
     const size_t n = n_pkts;
     if (!(flags & BNK_F_NO_H2D)) {
@@ -745,11 +764,11 @@ int bnk_gso_split_submit(bnk_batch *b, const bnk_gso_super *supers, uint32_t n_s
         memcpy(b->h_gso, supers, (size_t)n_super * sizeof(bnk_gso_super));
         CK(ctx, cudaMemcpyAsync(b->dev.gso, b->h_gso, (size_t)n_super * sizeof(bnk_gso_super), cudaMemcpyHostToDevice, s));
     }
-    CK(ctx, cudaEventRecord(b->k_begin, s));
+    if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     CK(ctx, launch_gso_split(b, n_super, n_pkts, s));
-    CK(ctx, cudaEventRecord(b->k_end, s));
-    b->kernel_timed = true;
-    return end_submit(b);
+    if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
+    b->kernel_timed = timed;
+    return BNK_SUCCESS;
 }
 
 int bnk_wait(bnk_batch *b, uint64_t timeout_ns) {

@@ -21,6 +21,7 @@ from ._lib import (  # noqa: F401  (re-exported)
     F_NOTE_OUTBOUND,
     F_REPLAY,
     F_SORT_BY_LENGTH,
+    F_TIMED,
     F_USE_OUT_LEN,
     PKT_AUTH_FAIL,
     PKT_BAD_DESC,

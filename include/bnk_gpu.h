@@ -80,6 +80,7 @@ extern "C" {
 #define BNK_F_USE_OUT_LEN (1u << 7)     /* open: message lengths are the out_len[] a seal left on the device */
 #define BNK_F_DEMUX_INDEX (1u << 8)     /* open: slot[] is an output, looked up from each header's receiver index */
 #define BNK_F_INNER_CHECK (1u << 9)     /* open: cut the plaintext to its IPv4 total length and check its source */
+#define BNK_F_TIMED (1u << 10)          /* record the CUDA events bnk_batch_last_kernel_ms / _aead_ms read */
 
 typedef struct bnk_ctx bnk_ctx;
 typedef struct bnk_batch bnk_batch;
@@ -270,7 +271,7 @@ int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uint32_t *dev_
  * start-to-end span in milliseconds. */
 int bnk_timer_start(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n);
 int bnk_timer_stop(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n, float *ms);
-/* Duration of the kernels of the batch's most recent submit (excluding copies), milliseconds. */
+/* Duration of the kernels of the batch's most recent submit made with BNK_F_TIMED (excluding copies), milliseconds. */
 int bnk_batch_last_kernel_ms(bnk_batch *b, float *ms);
 /* Duration of the seal or open kernel alone in the batch's most recent seal/open submit, milliseconds. */
 int bnk_batch_last_aead_ms(bnk_batch *b, float *ms);
