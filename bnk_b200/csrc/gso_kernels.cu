@@ -39,7 +39,8 @@ __global__ void __launch_bounds__(256) gso_split_kernel(const bnk_gso_super *sup
     const uint32_t data_at = hdr + k * sp.gso_size;
     bool ok = (sp.proto == 6 || sp.proto == 17) && iph >= 20 && hdr > iph && sp.gso_size > 0 && data_at < sp.src_len &&
               (sp.src_off & 3u) == 0 && (uint64_t)sp.src_off + sp.src_len <= ring_bytes &&
-              sp.csum_offset + 2u <= hdr - iph && hdr - iph >= (sp.proto == 6 ? 20u : 8u);
+              sp.csum_offset + 2u <= hdr - iph && hdr - iph >= (sp.proto == 6 ? 20u : 8u) && ((hdr | iph) & 3u) == 0 &&
+              (sp.csum_offset & 1u) == 0;
     uint32_t seg_len = 0, total = 0;
     const uint32_t o = off[pkt];
     if (ok) {
@@ -55,37 +56,54 @@ __global__ void __launch_bounds__(256) gso_split_kernel(const bnk_gso_super *sup
     uint8_t *out = ring + o + BNK_WG_HEADER;
     const bool last = data_at + seg_len == sp.src_len;
 
-    // headers: copied and patched by lane 0 (at most 120 bytes), payload by the whole warp
+    // headers: lane 0 reads them as 32-bit words (both are multiples of 4 bytes long), patches the fields and
+    // sums them from registers; the payload is left to the whole warp
+    uint64_t hdr_sum = 0; // transport header + pseudo header, checksum field zero
     if (lane == 0) {
-        for (uint32_t i = 0; i < hdr; i++) out[i] = in[i];
-        uint32_t id = be16(in + 4) + k;
-        out[4] = (uint8_t)(id >> 8);
-        out[5] = (uint8_t)id;
-        out[2] = (uint8_t)(total >> 8);
-        out[3] = (uint8_t)total;
-        out[10] = 0;
-        out[11] = 0;
-        uint64_t s = 0;
-        for (uint32_t i = 0; i < iph; i += 2) s += be16(out + i);
-        const uint32_t c = ~fold16(s) & 0xffffu;
-        out[10] = (uint8_t)(c >> 8);
-        out[11] = (uint8_t)c;
-        uint8_t *t = out + iph;
-        if (sp.proto == 6) {
-            const uint32_t seq = (((uint32_t)in[iph + 4] << 24) | ((uint32_t)in[iph + 5] << 16) | ((uint32_t)in[iph + 6] << 8) |
-                                  in[iph + 7]) + k * sp.gso_size;
-            t[4] = (uint8_t)(seq >> 24);
-            t[5] = (uint8_t)(seq >> 16);
-            t[6] = (uint8_t)(seq >> 8);
-            t[7] = (uint8_t)seq;
-            if (!last) t[13] &= (uint8_t)~(0x01u | 0x08u); // FIN, PSH
-        } else {
-            const uint32_t ulen = hdr - iph + seg_len;
-            t[4] = (uint8_t)(ulen >> 8);
-            t[5] = (uint8_t)ulen;
+        const uint32_t *in32 = reinterpret_cast<const uint32_t *>(in);
+        uint32_t *out32 = reinterpret_cast<uint32_t *>(out);
+        const uint32_t ipw = iph >> 2, hw = hdr >> 2;
+        // IPv4 header: words 0 (ver/ihl/tos/total length), 1 (id/flags/frag), 2 (ttl/proto/checksum), 3 src, 4 dst, options
+        uint64_t ips = 0;
+        uint32_t w_src = 0, w_dst = 0;
+        for (uint32_t i = 0; i < ipw; i++) {
+            uint32_t w = in32[i];
+            if (i == 0) w = (w & 0x0000ffffu) | ((total >> 8) << 16) | ((total & 0xffu) << 24);
+            else if (i == 1) {
+                const uint32_t id = (((w & 0xffu) << 8) | ((w >> 8) & 0xffu)) + k; // big-endian field in a little-endian word
+                w = (w & 0xffff0000u) | ((id >> 8) & 0xffu) | ((id & 0xffu) << 8);
+            } else if (i == 2) w &= 0x0000ffffu; // checksum field cleared
+            else if (i == 3) w_src = w;
+            else if (i == 4) w_dst = w;
+            ips += (uint64_t)__byte_perm(w, 0, 0x4401) + (uint64_t)__byte_perm(w, 0, 0x4423);
+            out32[i] = w; // word 2 gets its checksum bytes below
         }
-        t[sp.csum_offset] = 0;
-        t[sp.csum_offset + 1] = 0;
+        const uint32_t ipc = ~fold16(ips) & 0xffffu;
+        out[10] = (uint8_t)(ipc >> 8);
+        out[11] = (uint8_t)ipc;
+        // transport header
+        const uint32_t csum_word = sp.csum_offset >> 2, csum_hi = (sp.csum_offset & 2u) ? 1u : 0u; // which half of which word
+        for (uint32_t i = ipw; i < hw; i++) {
+            uint32_t w = in32[i];
+            const uint32_t t = i - ipw;
+            if (sp.proto == 6) {
+                if (t == 1) {
+                    const uint32_t seq = __byte_perm(w, 0, 0x0123) + k * sp.gso_size;
+                    w = __byte_perm(seq, 0, 0x0123);
+                } else if (t == 3 && !last) {
+                    w &= ~(0x09u << 8); // flags are byte 13: FIN | PSH survive on the last segment only
+                }
+            } else if (t == 1) {
+                const uint32_t ulen = hdr - iph + seg_len;
+                w = (w & 0xffff0000u) | (ulen >> 8) | ((ulen & 0xffu) << 8);
+            }
+            if (t == csum_word) w &= csum_hi ? 0x0000ffffu : 0xffff0000u;
+            hdr_sum += (uint64_t)__byte_perm(w, 0, 0x4401) + (uint64_t)__byte_perm(w, 0, 0x4423);
+            out32[i] = w;
+        }
+        hdr_sum += (uint64_t)__byte_perm(w_src, 0, 0x4401) + (uint64_t)__byte_perm(w_src, 0, 0x4423) +
+                   (uint64_t)__byte_perm(w_dst, 0, 0x4401) + (uint64_t)__byte_perm(w_dst, 0, 0x4423) + sp.proto +
+                   (hdr - iph + seg_len);
     }
     __syncwarp();
 
@@ -99,10 +117,23 @@ __global__ void __launch_bounds__(256) gso_split_kernel(const bnk_gso_super *sup
         const uint32_t words = seg_len >> 2;
         const uint32_t *s32 = reinterpret_cast<const uint32_t *>(src);
         uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
-        for (uint32_t i = lane; i < words; i += 32) {
+        // four loads in flight per lane: the copy is latency-bound otherwise
+        uint32_t i = lane;
+        for (; i + 96 < words; i += 128) {
+            const uint32_t w0 = s32[i], w1 = s32[i + 32], w2 = s32[i + 64], w3 = s32[i + 96];
+            d32[i] = w0;
+            d32[i + 32] = w1;
+            d32[i + 64] = w2;
+            d32[i + 96] = w3;
+            // little-endian load of bytes b0 b1 b2 b3 -> big-endian words b0b1 + b2b3
+            sum += (uint64_t)__byte_perm(w0, 0, 0x4401) + (uint64_t)__byte_perm(w0, 0, 0x4423) +
+                   (uint64_t)__byte_perm(w1, 0, 0x4401) + (uint64_t)__byte_perm(w1, 0, 0x4423) +
+                   (uint64_t)__byte_perm(w2, 0, 0x4401) + (uint64_t)__byte_perm(w2, 0, 0x4423) +
+                   (uint64_t)__byte_perm(w3, 0, 0x4401) + (uint64_t)__byte_perm(w3, 0, 0x4423);
+        }
+        for (; i < words; i += 32) {
             const uint32_t w = s32[i];
             d32[i] = w;
-            // little-endian load of bytes b0 b1 b2 b3 -> big-endian words b0b1 + b2b3
             sum += (uint64_t)__byte_perm(w, 0, 0x4401) + (uint64_t)__byte_perm(w, 0, 0x4423);
         }
         for (uint32_t i = (words << 2) + lane; i < seg_len; i += 32) {
@@ -120,14 +151,7 @@ __global__ void __launch_bounds__(256) gso_split_kernel(const bnk_gso_super *sup
 #pragma unroll
     for (int d = 16; d; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
     if (lane == 0) {
-        const uint8_t *t = out + iph;
-        const uint32_t tlen = hdr - iph + seg_len;
-        // pseudo header: source, destination, protocol, transport length
-        uint64_t s = sum + be16(out + 12) + be16(out + 14) + be16(out + 16) + be16(out + 18) + sp.proto + tlen;
-        const uint32_t th = hdr - iph;
-        for (uint32_t i = 0; i + 1 < th; i += 2) s += be16(t + i);
-        if (th & 1u) s += (uint32_t)t[th - 1] << 8;
-        const uint32_t c = ~fold16(s) & 0xffffu;
+        const uint32_t c = ~fold16(sum + hdr_sum) & 0xffffu;
         out[iph + sp.csum_offset] = (uint8_t)(c >> 8);
         out[iph + sp.csum_offset + 1] = (uint8_t)c;
     }
