@@ -191,6 +191,7 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     if ((e = dev_alloc_zero(&ctx->kt.remote_index, k)) != cudaSuccess) return bail("remote_index", e);
     if ((e = dev_alloc_zero(&ctx->kt.send_counter, k)) != cudaSuccess) return bail("send_counter", e);
     if ((e = dev_alloc_zero(&ctx->kt.replay_last, k)) != cudaSuccess) return bail("replay_last", e);
+    if ((e = dev_alloc_zero(&ctx->kt.replay_next, k)) != cudaSuccess) return bail("replay_next", e);
     if ((e = dev_alloc_zero(&ctx->kt.replay_ring, k * cfg->replay_ring_blocks)) != cudaSuccess) return bail("replay_ring", e);
     if ((e = dev_alloc_zero(&ctx->kt.allowed_ip, k)) != cudaSuccess) return bail("allowed_ip", e);
     uint32_t islots = 16;
@@ -217,6 +218,7 @@ int bnk_ctx_destroy(bnk_ctx *ctx) {
     cudaFree(ctx->kt.remote_index);
     cudaFree(ctx->kt.send_counter);
     cudaFree(ctx->kt.replay_last);
+    cudaFree(ctx->kt.replay_next);
     cudaFree(ctx->kt.replay_ring);
     cudaFree(ctx->kt.allowed_ip);
     cudaFree(ctx->kt.index_keys);
@@ -443,6 +445,12 @@ int bnk_batch_destroy(bnk_batch *b) {
     cudaFree(d.order);
     cudaFree(d.order_tmp);
     cudaFree(d.keys_tmp);
+    cudaFree(d.sorted_counter);
+    cudaFree(d.replay_state);
+    cudaFree(d.replay_hash);
+    cudaFree(d.replay_tile_head);
+    cudaFree(d.replay_tile_max);
+    cudaFree(d.replay_tile_carry);
     cudaFree(d.hist);
     cudaFree(d.len_order);
     cudaFree(d.counters32);
@@ -515,6 +523,12 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     D((void **)&d.order, n * 4);
     D((void **)&d.order_tmp, n * 4);
     D((void **)&d.keys_tmp, 2 * n * 4);
+    D((void **)&d.sorted_counter, n * 8);
+    D((void **)&d.replay_state, n);
+    D((void **)&d.replay_hash, (size_t)replay_hash_capacity(max_pkts) * 4);
+    D((void **)&d.replay_tile_head, ((size_t)replay_scan_tiles(max_pkts) + 1) * 4);
+    D((void **)&d.replay_tile_max, (size_t)replay_scan_tiles(max_pkts) * 8);
+    D((void **)&d.replay_tile_carry, (size_t)replay_scan_tiles(max_pkts) * 8);
     D((void **)&d.hist, (size_t)512 * group_sort_chunks(max_pkts) * 4); // histogram columns + one row of totals
     D((void **)&d.len_order, n * 4);
     D((void **)&d.counters32, 2048 * 4);

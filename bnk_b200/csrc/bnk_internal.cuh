@@ -23,6 +23,7 @@ struct KeypairTables {
     uint32_t *remote_index; // [max_keypairs] receiver index written into sealed headers
     uint64_t *send_counter; // [max_keypairs] next nonce to hand out
     uint64_t *replay_last;  // [max_keypairs] highest counter accepted
+    uint64_t *replay_next;  // [max_keypairs] scratch: the value replay_last takes after the batch in flight
     uint64_t *replay_ring;  // [max_keypairs][ring_blocks] RFC 6479 bitmap ring
     uint32_t *allowed_ip;   // [max_keypairs] the peer's tunnel address, host order (0 = none)
     // receiver index -> slot: open addressing, key = 1<<32 | index (0 = empty, 2<<32 = deleted)
@@ -84,6 +85,13 @@ struct DeviceBatch {
     uint32_t *order;      // [max_pkts] packet indices, stable by slot
     uint32_t *order_tmp;  // [max_pkts]
     uint32_t *keys_tmp;   // [2][max_pkts] radix keys ping-pong
+    // scratch of the replay window in its scan form (group_kernels.cu)
+    uint64_t *sorted_counter;    // [max_pkts] counters in grouped order
+    uint8_t *replay_state;       // [max_pkts] verdict per grouped position
+    uint32_t *replay_hash;       // [replay_hash_capacity(max_pkts)] lowest position per (peer, counter)
+    uint32_t *replay_tile_head;  // [tiles + 1] a run starts inside the tile; last entry: some packet needs the hash
+    uint64_t *replay_tile_max;   // [tiles]
+    uint64_t *replay_tile_carry; // [tiles]
     uint32_t *hist;       // [512 * chunks] digit-major histograms
     uint32_t *len_order;  // [max_pkts] packet indices ordered by length class
     uint32_t *counters32; // small scratch (bins)
@@ -138,6 +146,8 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s);
 cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s);
 cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, bool open_side, cudaStream_t s);
 uint32_t group_sort_chunks(uint32_t max_pkts);
+uint32_t replay_scan_tiles(uint32_t max_pkts);     // tiles of the running-maximum scan
+uint32_t replay_hash_capacity(uint32_t max_pkts);  // entries of the duplicate-counter table
 
 // filter_kernels.cu
 cudaError_t launch_filter_note(bnk_batch *b, uint32_t n, long long now_ns, cudaStream_t s);

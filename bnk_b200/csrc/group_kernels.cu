@@ -378,20 +378,33 @@ __global__ void __launch_bounds__(256) replay_kernel(const uint32_t *keys, const
         if (slot >= max_slots) continue; // packets that take no part
         unsigned long long *ring = reinterpret_cast<unsigned long long *>(replay_ring) + (size_t)slot * ring_blocks;
         uint64_t last = replay_last[slot];
-        for (uint32_t base = h;; base += 32) {
+        // the next stretch's descriptors are fetched while this one goes through the window
+        struct Fetched {
+            bool in, auth;
+            uint32_t pkt;
+            uint64_t c;
+        };
+        auto fetch = [&](uint32_t base) {
+            Fetched f{false, false, 0u, 0ull};
             const uint32_t pos = base + lane;
-            const bool in = pos < n && keys[pos] == slot;
-            const uint32_t inmask = __ballot_sync(0xffffffffu, in);
-            if (!inmask) break;
-            uint32_t pkt = 0;
-            bool auth = false;
-            uint64_t c = 0;
-            if (in) {
-                pkt = order[pos];
-                const uint8_t st = status[pkt];
-                auth = st == BNK_PKT_OK || st == BNK_PKT_KEEPALIVE;
-                if (auth) c = counter[pkt];
+            f.in = pos < n && keys[pos] == slot;
+            if (f.in) {
+                f.pkt = order[pos];
+                const uint8_t st = status[f.pkt];
+                f.auth = st == BNK_PKT_OK || st == BNK_PKT_KEEPALIVE;
+                if (f.auth) f.c = counter[f.pkt];
             }
+            return f;
+        };
+        Fetched nxt = fetch(h);
+        for (uint32_t base = h;; base += 32) {
+            const Fetched cur = nxt;
+            const uint32_t inmask = __ballot_sync(0xffffffffu, cur.in);
+            if (!inmask) break;
+            if (inmask == 0xffffffffu) nxt = fetch(base + 32);
+            const uint32_t pkt = cur.pkt;
+            const bool auth = cur.auth;
+            const uint64_t c = cur.c;
             const bool live = auth && c < BNK_REJECT_AFTER_MESSAGES;
             // M: highest counter before this lane's packet
             uint64_t incl = live ? c : 0;
@@ -426,6 +439,299 @@ __global__ void __launch_bounds__(256) replay_kernel(const uint32_t *keys, const
             if (inmask != 0xffffffffu) break;
         }
         if (lane == 0) replay_last[slot] = last;
+    }
+}
+
+// --- the same window without the walk -----------------------------------------------------
+// A warp walking a run costs about a microsecond per 32 packets, one stretch after the other, so a peer that
+// owns a large batch would hold the whole batch up.  Taking the whole run as one stretch, every term of the
+// closed form can be had without walking:
+//   M_j                         a segmented exclusive running maximum over the grouped order (a scan),
+//   "marked at the start"       a read of the ring as it was before the batch,
+//   "repeats an earlier one"    the lowest grouped position holding the same (peer, counter), found with a
+//                               hash table of positions; built only when some packet of the batch lies behind
+//                               its M_j inside the window, which in-order traffic never does,
+//   the new state               last = M at the end of the run; the words the top moved over are cleared; the
+//                               accepted packets within a ring of the new top are marked.
+// Kernels, in stream order: scan_tiles (also lays the counters out in grouped order), scan_carry, classify,
+// advance (new last, clears), hash_clear, hash_insert, finish (duplicate look-up, verdicts, marks).
+constexpr uint32_t kScanTile = 1024; // grouped positions per CTA: 256 threads x 4
+constexpr uint64_t kReplayNoPart = ~0ull; // grouped-order counter of a packet that takes no part
+constexpr uint32_t kHashEmpty = 0xffffffffu;
+enum : uint8_t { RP_NOPART = 0, RP_ACCEPT = 1, RP_REJECT = 2, RP_PENDING = 3 };
+
+struct SegMax { // running maximum that restarts at every run head
+    uint32_t f; // a head lies inside the span
+    uint64_t m; // maximum since the last head (or over the whole span)
+};
+__device__ __forceinline__ SegMax seg_combine(SegMax a, SegMax b) { // a: earlier span, b: the span after it
+    return SegMax{a.f | b.f, (b.f || b.m > a.m) ? b.m : a.m};
+}
+__device__ __forceinline__ SegMax seg_shfl_up(SegMax v, int o) {
+    return SegMax{__shfl_up_sync(0xffffffffu, v.f, o), __shfl_up_sync(0xffffffffu, v.m, o)};
+}
+// Inclusive scan of one value per thread over a CTA of NW warps; returns the exclusive prefix of the calling
+// thread and the total of the CTA.  `part` is NW entries of shared memory.
+template <int NW>
+__device__ __forceinline__ SegMax seg_block_exclusive(SegMax mine, SegMax *part, SegMax &total) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    SegMax inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const SegMax t = seg_shfl_up(inc, o);
+        if (lane >= (uint32_t)o) inc = seg_combine(t, inc);
+    }
+    SegMax ex = seg_shfl_up(inc, 1);
+    if (lane == 0) ex = SegMax{0u, 0ull};
+    __syncthreads(); // `part` may still be read from an earlier call
+    if (lane == 31) part[warp] = inc;
+    __syncthreads();
+    SegMax before{0u, 0ull};
+    total = SegMax{0u, 0ull};
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+        if ((uint32_t)w == warp) before = total;
+        total = seg_combine(total, part[w]);
+    }
+    return seg_combine(before, ex);
+}
+// Four consecutive grouped positions per thread.  e[k] = maximum of the values of the same run that lie in
+// front of item k (`carry` stands for what lies in front of the tile); total = the tile as one span.
+__device__ __forceinline__ void tile_running_max(const bool head[4], const uint64_t v[4], uint64_t carry,
+                                                 uint64_t e[4], SegMax *part, SegMax &total) {
+    SegMax run{0u, 0ull};
+    uint32_t headed = 0; // bit k: a head lies at or before item k inside this thread
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (head[k]) run = SegMax{1u, 0ull};
+        e[k] = run.m;
+        headed |= run.f << k;
+        if (v[k] > run.m) run.m = v[k];
+    }
+    const SegMax ex = seg_block_exclusive<8>(run, part, total);
+    const uint64_t front = ex.f ? ex.m : (carry > ex.m ? carry : ex.m);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        if (!((headed >> k) & 1u) && front > e[k]) e[k] = front;
+}
+
+__global__ void __launch_bounds__(256) replay_scan_tiles_kernel(const uint32_t *keys, const uint32_t *order, uint32_t n,
+                                                                uint32_t max_slots, const uint64_t *counter,
+                                                                uint8_t *status, uint64_t *sorted_counter,
+                                                                uint32_t *tile_head, uint64_t *tile_max,
+                                                                uint32_t *pending_flag) {
+    __shared__ SegMax part[8];
+    const uint32_t base = blockIdx.x * kScanTile + threadIdx.x * 4u;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *pending_flag = 0u;
+    bool head[4];
+    uint64_t v[4], e[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t p = base + k;
+        head[k] = false;
+        v[k] = 0;
+        if (p < n) {
+            const uint32_t slot = keys[p];
+            head[k] = p == 0 || keys[p - 1] != slot;
+            uint64_t c = kReplayNoPart;
+            if (slot < max_slots) {
+                const uint32_t pkt = order[p];
+                const uint8_t st = status[pkt];
+                if (st == BNK_PKT_OK || st == BNK_PKT_KEEPALIVE) {
+                    c = counter[pkt];
+                    if (c >= BNK_REJECT_AFTER_MESSAGES) { // beyond the message limit: rejected whatever the window holds
+                        status[pkt] = BNK_PKT_REPLAY;
+                        c = kReplayNoPart;
+                    }
+                }
+            }
+            sorted_counter[p] = c;
+            if (c != kReplayNoPart) v[k] = c;
+        }
+    }
+    SegMax total;
+    tile_running_max(head, v, 0ull, e, part, total);
+    if (threadIdx.x == 0) {
+        tile_head[blockIdx.x] = total.f;
+        tile_max[blockIdx.x] = total.m;
+    }
+}
+// One CTA: carry[t] = running maximum that reaches tile t from the tiles in front of it.
+__global__ void __launch_bounds__(1024) replay_scan_carry_kernel(const uint32_t *tile_head, const uint64_t *tile_max,
+                                                                 uint32_t tiles, uint64_t *tile_carry) {
+    __shared__ SegMax part[32];
+    SegMax reached{0u, 0ull};
+    for (uint32_t base = 0; base < tiles; base += 1024u) {
+        const uint32_t t = base + threadIdx.x;
+        SegMax mine{0u, 0ull};
+        if (t < tiles) mine = SegMax{tile_head[t], tile_max[t]};
+        SegMax total;
+        const SegMax ex = seg_block_exclusive<32>(mine, part, total);
+        if (t < tiles) tile_carry[t] = seg_combine(reached, ex).m;
+        reached = seg_combine(reached, total);
+    }
+}
+__global__ void __launch_bounds__(256) replay_classify_kernel(const uint32_t *keys, uint32_t n, uint32_t max_slots,
+                                                              uint32_t ring_blocks, const uint64_t *replay_last,
+                                                              const uint64_t *replay_ring, const uint64_t *sorted_counter,
+                                                              const uint64_t *tile_carry, uint64_t *replay_next,
+                                                              uint8_t *state, uint32_t *pending_flag) {
+    __shared__ SegMax part[8];
+    const uint32_t base = blockIdx.x * kScanTile + threadIdx.x * 4u;
+    const uint64_t rmask = ring_blocks - 1;
+    const uint64_t window = (uint64_t)(ring_blocks - 1) * 64u;
+    bool head[4];
+    uint32_t slot[4];
+    uint64_t c[4], v[4], e[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t p = base + k;
+        head[k] = false;
+        v[k] = 0;
+        c[k] = kReplayNoPart;
+        slot[k] = 0xffffffffu;
+        if (p < n) {
+            slot[k] = keys[p];
+            head[k] = p == 0 || keys[p - 1] != slot[k];
+            c[k] = sorted_counter[p];
+            if (c[k] != kReplayNoPart) v[k] = c[k];
+        }
+    }
+    SegMax total;
+    tile_running_max(head, v, tile_carry[blockIdx.x], e, part, total);
+    bool pending = false;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t p = base + k;
+        if (p >= n) continue;
+        uint8_t st = RP_NOPART;
+        if (slot[k] < max_slots) {
+            const uint64_t last = replay_last[slot[k]];
+            const uint64_t M = e[k] > last ? e[k] : last;
+            const uint64_t ck = c[k];
+            if (ck != kReplayNoPart) {
+                if (ck > M) st = RP_ACCEPT;
+                else if (M - ck > window) st = RP_REJECT;
+                else if (ck <= last &&
+                         ((replay_ring[(size_t)slot[k] * ring_blocks + ((ck >> 6) & rmask)] >> (ck & 63u)) & 1ull))
+                    st = RP_REJECT;
+                else {
+                    st = RP_PENDING;
+                    pending = true;
+                }
+            }
+            if (p + 1 == n || keys[p + 1] != slot[k]) replay_next[slot[k]] = v[k] > M ? v[k] : M;
+        }
+        state[p] = st;
+    }
+    if (__syncthreads_or(pending) && threadIdx.x == 0) *pending_flag = 1u;
+}
+// The warp that holds the last packet of a run moves the peer's window: clears, then the new last.
+__global__ void __launch_bounds__(256) replay_advance_kernel(const uint32_t *keys, uint32_t n, uint32_t max_slots,
+                                                             uint32_t ring_blocks, uint64_t *replay_last,
+                                                             uint64_t *replay_ring, const uint64_t *replay_next) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool is_tail = p < n && keys[p] < max_slots && (p + 1 == n || keys[p + 1] != keys[p]);
+    uint32_t tails = __ballot_sync(0xffffffffu, is_tail);
+    const uint64_t rmask = ring_blocks - 1;
+    while (tails) {
+        const uint32_t src = __ffs(tails) - 1;
+        tails &= tails - 1;
+        const uint32_t slot = __shfl_sync(0xffffffffu, p < n ? keys[p] : 0u, src);
+        unsigned long long *ring = reinterpret_cast<unsigned long long *>(replay_ring) + (size_t)slot * ring_blocks;
+        const uint64_t last = replay_last[slot], next = replay_next[slot];
+        const uint64_t top = last >> 6;
+        uint64_t steps = (next >> 6) - top;
+        if (steps > ring_blocks) steps = ring_blocks;
+        for (uint64_t i = lane; i < steps; i += 32) ring[(top + 1 + i) & rmask] = 0ull;
+        __syncwarp();
+        if (lane == 0) replay_last[slot] = next;
+    }
+}
+__device__ __forceinline__ uint32_t replay_hash(uint32_t slot, uint64_t c) {
+    uint64_t x = c * 0x9E3779B97F4A7C15ull + slot;
+    x ^= x >> 29;
+    x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 32;
+    return (uint32_t)x;
+}
+__global__ void __launch_bounds__(256) replay_hash_clear_kernel(uint32_t *table, uint32_t cap, const uint32_t *pending_flag) {
+    if (*pending_flag == 0u) return;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < cap; i += gridDim.x * blockDim.x) table[i] = kHashEmpty;
+}
+// table[h] = lowest grouped position that holds the key (peer, counter); the key of an entry is read through
+// the position it holds and never changes, so a probe may compare against whatever position it sees.
+__global__ void __launch_bounds__(256) replay_hash_insert_kernel(const uint32_t *keys, const uint64_t *sorted_counter,
+                                                                 const uint8_t *state, uint32_t n, uint32_t *table,
+                                                                 uint32_t mask, const uint32_t *pending_flag) {
+    if (*pending_flag == 0u) return;
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n || state[p] == RP_NOPART) return;
+    const uint32_t slot = keys[p];
+    const uint64_t c = sorted_counter[p];
+    uint32_t h = replay_hash(slot, c) & mask;
+    for (uint32_t probes = 0; probes <= mask; ++probes, h = (h + 1) & mask) {
+        uint32_t cur = __ldcg(&table[h]);
+        if (cur == kHashEmpty) {
+            cur = atomicCAS(&table[h], kHashEmpty, p);
+            if (cur == kHashEmpty) return;
+        }
+        if (keys[cur] == slot && sorted_counter[cur] == c) {
+            atomicMin(&table[h], p);
+            return;
+        }
+    }
+}
+__global__ void __launch_bounds__(256) replay_finish_kernel(const uint32_t *keys, const uint32_t *order,
+                                                            const uint64_t *sorted_counter, const uint8_t *state,
+                                                            uint32_t n, uint32_t ring_blocks, const uint64_t *replay_last,
+                                                            uint64_t *replay_ring, const uint32_t *table, uint32_t mask,
+                                                            uint8_t *status) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    uint8_t st = p < n ? state[p] : (uint8_t)RP_NOPART;
+    uint32_t slot = 0;
+    uint64_t c = 0;
+    if (st != RP_NOPART) {
+        slot = keys[p];
+        c = sorted_counter[p];
+    }
+    if (st == RP_PENDING) {
+        st = RP_ACCEPT;
+        uint32_t h = replay_hash(slot, c) & mask;
+        for (uint32_t probes = 0; probes <= mask; ++probes, h = (h + 1) & mask) {
+            const uint32_t cur = table[h];
+            if (cur == kHashEmpty) break;
+            if (keys[cur] == slot && sorted_counter[cur] == c) {
+                if (cur < p) st = RP_REJECT;
+                break;
+            }
+        }
+    }
+    if (st == RP_REJECT) status[order[p]] = BNK_PKT_REPLAY;
+    // marks: lanes that hit the same ring word hand their bits to the lowest of them
+    const uint64_t rmask = ring_blocks - 1;
+    const bool mark = st == RP_ACCEPT && (replay_last[slot] >> 6) - (c >> 6) < ring_blocks;
+    const unsigned long long word = mark ? (unsigned long long)slot * ring_blocks + ((c >> 6) & rmask) : ~0ull - lane;
+    const uint32_t group = __match_any_sync(0xffffffffu, word);
+    const bool leader = mark && (uint32_t)(__ffs(group) - 1) == lane;
+    uint32_t leaders = __ballot_sync(0xffffffffu, leader);
+    const uint32_t bit_lo = mark && (c & 32u) == 0 ? 1u << (c & 31u) : 0u;
+    const uint32_t bit_hi = mark && (c & 32u) != 0 ? 1u << (c & 31u) : 0u;
+    unsigned long long *ring = reinterpret_cast<unsigned long long *>(replay_ring);
+    if (__popc(leaders) <= 4) {
+        while (leaders) {
+            const uint32_t src = __ffs(leaders) - 1;
+            leaders &= leaders - 1;
+            const uint32_t members = __shfl_sync(0xffffffffu, group, src);
+            const bool in = (members >> lane) & 1u;
+            const uint32_t lo = __reduce_or_sync(0xffffffffu, in ? bit_lo : 0u);
+            const uint32_t hi = __reduce_or_sync(0xffffffffu, in ? bit_hi : 0u);
+            if (lane == src) atomicOr(&ring[word], ((unsigned long long)hi << 32) | lo);
+        }
+    } else if (mark) {
+        atomicOr(&ring[word], ((unsigned long long)bit_hi << 32) | bit_lo);
     }
 }
 
@@ -565,14 +871,41 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
 }
 
 // Expects launch_group_by_slot(b, n, false, ...) to have completed before this point of stream s.
+constexpr uint32_t kReplayWalkUpTo = 2048;
+uint32_t replay_scan_tiles(uint32_t max_pkts) { return (max_pkts + kScanTile - 1) / kScanTile; }
+uint32_t replay_hash_capacity(uint32_t max_pkts) {
+    uint32_t cap = 1024;
+    while (cap < 2u * max_pkts && cap < 0x80000000u) cap <<= 1;
+    return cap;
+}
 cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     DeviceBatch &d = b->dev;
     bnk_ctx *ctx = b->ctx;
-    replay_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, n,
-                                                 ctx->cfg.max_keypairs, ctx->cfg.replay_ring_blocks,
-                                                 ctx->kt.replay_last, ctx->kt.replay_ring, d.counter, d.status);
-    ctx->launches += 1;
+    const uint32_t *keys = d.keys_tmp + b->max_pkts;
+    const uint32_t slots = ctx->cfg.max_keypairs, blocks = ctx->cfg.replay_ring_blocks;
+    KeypairTables &kt = ctx->kt;
+    if (n <= kReplayWalkUpTo) { // one launch; runs are short enough to walk
+        replay_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys, d.order, n, slots, blocks, kt.replay_last, kt.replay_ring,
+                                                     d.counter, d.status);
+        ctx->launches += 1;
+        return cudaGetLastError();
+    }
+    const uint32_t tiles = (n + kScanTile - 1) / kScanTile, grid = (n + 255) / 256;
+    uint32_t cap = 1024;
+    while (cap < 2u * n) cap <<= 1; // at most half full
+    uint32_t *flag = d.replay_tile_head + replay_scan_tiles(b->max_pkts);
+    replay_scan_tiles_kernel<<<tiles, 256, 0, s>>>(keys, d.order, n, slots, d.counter, d.status, d.sorted_counter,
+                                                  d.replay_tile_head, d.replay_tile_max, flag);
+    replay_scan_carry_kernel<<<1, 1024, 0, s>>>(d.replay_tile_head, d.replay_tile_max, tiles, d.replay_tile_carry);
+    replay_classify_kernel<<<tiles, 256, 0, s>>>(keys, n, slots, blocks, kt.replay_last, kt.replay_ring, d.sorted_counter,
+                                                d.replay_tile_carry, kt.replay_next, d.replay_state, flag);
+    replay_advance_kernel<<<grid, 256, 0, s>>>(keys, n, slots, blocks, kt.replay_last, kt.replay_ring, kt.replay_next);
+    replay_hash_clear_kernel<<<148 * 4, 256, 0, s>>>(d.replay_hash, cap, flag);
+    replay_hash_insert_kernel<<<grid, 256, 0, s>>>(keys, d.sorted_counter, d.replay_state, n, d.replay_hash, cap - 1, flag);
+    replay_finish_kernel<<<grid, 256, 0, s>>>(keys, d.order, d.sorted_counter, d.replay_state, n, blocks, kt.replay_last,
+                                             kt.replay_ring, d.replay_hash, cap - 1, d.status);
+    ctx->launches += 7;
     return cudaGetLastError();
 }
 

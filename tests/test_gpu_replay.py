@@ -15,15 +15,16 @@ def _sealed_ring(oracle, keys, slots, counters, sizes, rng):
     return msgs, lengths, off
 
 
-@pytest.mark.parametrize("blocks", [32, 128])
-def test_replay_verdicts_follow_arrival_order(gpu_lib, oracle, blocks):
+# 256 blocks: too large for the walk in shared memory; 1500 packets: the walk without the gather pass
+@pytest.mark.parametrize("blocks,n", [(32, 3000), (128, 3000), (256, 3000), (128, 1500)])
+def test_replay_verdicts_follow_arrival_order(gpu_lib, oracle, blocks, n):
     """Many peers, heavy reordering, duplicates, stale counters, forged packets in between, across
     several batches so the window state carries over."""
     from bnk_b200 import Context
     from bnk_b200.device import F_REPLAY
 
     rng = np.random.default_rng(blocks)
-    n_peers, n = 37, 3000
+    n_peers = 37
     window = (blocks - 1) * 64
     keys = rng.integers(0, 256, (n_peers, 32), dtype=np.uint8)
     c = Context(max_keypairs=n_peers, replay_ring_blocks=blocks, mtu=0, flow_capacity=0)
@@ -70,6 +71,69 @@ def test_replay_verdicts_follow_arrival_order(gpu_lib, oracle, blocks):
         for s, r in state.items():
             last, ring = c.replay_export(s)
             assert last == r.last and np.array_equal(ring, r.ring()), s
+    finally:
+        c.close()
+
+
+@pytest.mark.parametrize("blocks", [32, 128])
+def test_replay_dominant_peer_large_batch(gpu_lib, oracle, blocks):
+    """One peer owns most of a 120,000-packet batch (the scan form of the window): reordering inside the
+    window, repeats of earlier counters far apart in the batch, stale counters at the window's edge, and
+    jumps of several rings; two batches so the second starts from the state the first left."""
+    from bnk_b200 import Context
+    from bnk_b200.device import F_REPLAY
+
+    rng = np.random.default_rng(1000 + blocks)
+    n_peers, n, size = 41, 120_000, 16
+    window = (blocks - 1) * 64
+    keys = rng.integers(0, 256, (n_peers, 32), dtype=np.uint8)
+    stride = 16 + size + 16
+    off = (np.arange(n, dtype=np.uint64) * stride).astype(np.uint32)
+    lengths = np.full(n, size, np.uint32)
+    c = Context(max_keypairs=n_peers, replay_ring_blocks=blocks, mtu=0, flow_capacity=0)
+    state = {}
+    top = rng.integers(1 << 20, 1 << 40, n_peers).astype(np.uint64)
+    try:
+        c.set_keypairs(0, keys, keys, np.ones(n_peers, np.uint32))
+        b = c.batch(n, n * stride + 64)
+        for batch_no in range(2):
+            slots = np.where(rng.random(n) < 0.7, 0, rng.integers(1, n_peers, n)).astype(np.uint32)
+            counters = np.zeros(n, np.uint64)
+            for s in range(n_peers):
+                idx = np.flatnonzero(slots == s)
+                m = len(idx)
+                kind = rng.random(m)
+                step = np.where(kind < 0.90, rng.integers(1, 3, m), 0)
+                step = np.where(kind > 0.995, rng.integers(window // 2, 3 * window + 200, m), step)
+                tops = top[s] + np.cumsum(step).astype(np.uint64)
+                back = np.zeros(m, np.int64)
+                r2 = rng.random(m)
+                back = np.where(r2 < 0.25, rng.integers(0, 100, m), back)                       # reordered / repeated
+                back = np.where(r2 < 0.04, rng.integers(window - 70, window + 70, m), back)     # the window's edge
+                back = np.where(r2 < 0.01, rng.integers(0, 6000, m), back)                      # far repeats
+                counters[idx] = tops - np.minimum(back.astype(np.uint64), tops)
+                if m:
+                    top[s] = tops[-1]
+            ring = np.zeros(n * stride + 64, np.uint8)
+            body = rng.integers(0, 256, (n, size), dtype=np.uint8)
+            ring[: n * stride].reshape(n, stride)[:, 16:16 + size] = body
+            st, out_len = oracle.wg_seal_batch(keys, np.ones(n_peers, np.uint32), 0, ring, off, lengths, slots, counters)
+            assert (st == oracle.OK).all()
+            forged = np.flatnonzero(rng.random(n) < 0.01)
+            ring[off[forged].astype(np.int64) + 20] ^= 1
+            b.ring[: len(ring)] = ring
+            b.off[:n], b.len[:n], b.slot[:n] = off, out_len, slots
+            _, ost, ctr, _ = H.oracle_open(oracle, keys, ring, off, out_len, slots)
+            want, state = H.oracle_replay(oracle, blocks, slots, ctr, ost, state)
+            b.open(n, F_REPLAY)
+            got = np.array(b.status[:n])
+            assert np.array_equal(got, want), f"batch {batch_no}: {np.flatnonzero(got != want)[:8]}"
+            assert (want == oracle.REPLAY).sum() > 5000 and (want == oracle.AUTH_FAIL).sum() > 500
+            assert (want == oracle.OK).sum() > n // 2
+        b.close()
+        for s, r in state.items():
+            last, ring_words = c.replay_export(s)
+            assert last == r.last and np.array_equal(ring_words, r.ring()), s
     finally:
         c.close()
 
