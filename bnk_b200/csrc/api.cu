@@ -58,7 +58,8 @@ uint64_t ring_extent(const bnk_batch *b, uint32_t n, uint32_t slack) {
 int begin_submit(bnk_batch *b, uint32_t npkts, bool touches_host = true) {
     if (!b) return BNK_EINVAL;
     if (npkts > b->max_pkts) return fail(b->ctx, BNK_EINVAL, "npkts exceeds the batch capacity");
-    if (b->in_flight && touches_host) return fail(b->ctx, BNK_EBUSY, "batch has work in flight; call bnk_wait first");
+    if (b->in_flight && (touches_host || b->dev_stale))
+        return fail(b->ctx, BNK_EBUSY, "batch has work in flight; call bnk_wait first");
     CK(b->ctx, cudaSetDevice(b->ctx->device));
     return BNK_SUCCESS;
 }
@@ -71,6 +72,42 @@ struct SubmitScope {
     ~SubmitScope() {
         cudaEventRecord(b->done, b->stream);
         b->in_flight = true;
+    }
+};
+
+// Small batches skip the copy engines: the kernels read the caller's pinned ring and descriptors through the
+// bus and write the results straight back (pinned memory has the same address on the device).  For a batch of
+// a few hundred KB the four copies and the engine hand-overs either side of the kernels cost more than the
+// kernels themselves.  While a HostAlias lives, the launchers see the host arrays where the device copies
+// would be; the device copies fall behind (dev_stale) until the next full upload.
+// Reads through the bus come at roughly 10 GB/s from a kernel this small (about 20 us for 128 full-size
+// packets), so the mode pays up to a ring extent of about a hundred KB: measured 23 against 35 us for one
+// packet and 30 against 42 us for 64, seal submit to wait; level at 128.  Serving only the descriptors this
+// way and the ring by copy was measured too and gained nothing.
+constexpr uint32_t kHostDirectMaxPkts = 1024;
+bool host_direct(const bnk_batch *b, uint32_t npkts, uint32_t flags, uint64_t ext) {
+    return b->ctx->host_direct_bytes != 0 && npkts != 0 && npkts <= kHostDirectMaxPkts &&
+           !(flags & (BNK_F_NO_H2D | BNK_F_NO_D2H | BNK_F_USE_OUT_LEN)) && ext <= b->ctx->host_direct_bytes;
+}
+struct HostAlias {
+    bnk_batch *b;
+    DeviceBatch saved;
+    bool on;
+    HostAlias(bnk_batch *batch, bool enable) : b(batch), saved(batch->dev), on(enable) {
+        if (!on) return;
+        DeviceBatch &d = b->dev;
+        const bnk_batch_view &h = b->host;
+        d.ring = h.ring;
+        d.off = h.off;
+        d.len = h.len;
+        d.slot = h.slot;
+        d.counter = h.counter;
+        d.out_len = h.out_len;
+        d.status = h.status;
+        b->dev_stale = true;
+    }
+    ~HostAlias() {
+        if (on) b->dev = saved;
     }
 };
 
@@ -176,6 +213,9 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     ctx->aead_mode = 0;
     if (const char *m = getenv("BNK_AEAD_KERNEL")) // tuning and test aid: tpp | wpp
         ctx->aead_mode = !strcmp(m, "tpp") ? 1 : (!strcmp(m, "wpp") ? 2 : 0);
+    ctx->host_direct_bytes = 128u << 10;
+    if (const char *m = getenv("BNK_HOST_DIRECT_BYTES")) // largest ring extent served without copies; 0 = never
+        ctx->host_direct_bytes = strtoull(m, nullptr, 0);
     ctx->kt = KeypairTables{};
     ctx->ft = FilterTables{};
     const size_t k = cfg->max_keypairs;
@@ -568,8 +608,9 @@ int bnk_batch_upload(bnk_batch *b, uint32_t npkts) {
     const uint64_t ext = ring_extent(b, npkts, 64);
     if (ext) CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, b->stream));
     if (n) {
-        CK(ctx, desc_copy(b, n, D_OFF, D_COUNTER, true, b->stream));
+        CK(ctx, desc_copy(b, n, D_OFF, b->dev_stale ? D_STATUS : D_COUNTER, true, b->stream));
     }
+    b->dev_stale = false;
     return BNK_SUCCESS;
 }
 
@@ -579,6 +620,7 @@ int bnk_batch_download(bnk_batch *b, uint32_t npkts) {
     SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     const size_t n = npkts;
+    if (b->dev_stale) return BNK_SUCCESS; // the last submit already left its results in the host arrays
     const uint64_t ext = ring_extent(b, npkts, 64);
     if (ext) CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, b->stream));
     if (n) {
@@ -597,10 +639,14 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
     // header room + payload + padding (< 16) + tag
-    const uint64_t ext = device_only ? 0 : ring_extent(b, npkts, 16 + 16 + 16);
-    if (!(flags & BNK_F_NO_H2D) && n) {
+    const bool refresh = b->dev_stale; // the device copies are behind the host arrays: upload whatever the flags say
+    const uint64_t ext = (device_only && !refresh) ? 0 : ring_extent(b, npkts, 16 + 16 + 16);
+    const bool direct = host_direct(b, npkts, flags, ext);
+    HostAlias alias(b, direct);
+    if (!direct && (!(flags & BNK_F_NO_H2D) || refresh) && n) {
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        CK(ctx, desc_copy(b, n, D_OFF, (flags & BNK_F_ASSIGN_COUNTERS) ? D_SLOT : D_COUNTER, true, s));
+        CK(ctx, desc_copy(b, n, D_OFF, refresh ? D_STATUS : (flags & BNK_F_ASSIGN_COUNTERS) ? D_SLOT : D_COUNTER, true, s));
+        b->dev_stale = false;
     }
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     if (flags & BNK_F_NOTE_OUTBOUND) {
@@ -619,7 +665,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
     b->aead_timed = timed;
-    if (!(flags & BNK_F_NO_D2H) && n) {
+    if (!direct && !(flags & BNK_F_NO_D2H) && n) {
         CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
         CK(ctx, desc_copy(b, n, D_COUNTER, D_STATUS, false, s));
     }
@@ -635,10 +681,14 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     cudaStream_t s = b->stream;
     const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
-    const uint64_t ext = device_only ? 0 : ring_extent(b, npkts, (flags & BNK_F_USE_OUT_LEN) ? 48 : 0);
-    if (!(flags & BNK_F_NO_H2D) && n) {
+    const bool refresh = b->dev_stale;
+    const uint64_t ext = (device_only && !refresh) ? 0 : ring_extent(b, npkts, (flags & BNK_F_USE_OUT_LEN) ? 48 : 0);
+    const bool direct = host_direct(b, npkts, flags, ext);
+    HostAlias alias(b, direct);
+    if (!direct && (!(flags & BNK_F_NO_H2D) || refresh) && n) {
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        CK(ctx, desc_copy(b, n, D_OFF, (flags & BNK_F_DEMUX_INDEX) ? D_LEN : D_SLOT, true, s));
+        CK(ctx, desc_copy(b, n, D_OFF, refresh ? D_STATUS : (flags & BNK_F_DEMUX_INDEX) ? D_LEN : D_SLOT, true, s));
+        b->dev_stale = false;
     }
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     const uint32_t *order = nullptr;
@@ -650,7 +700,8 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         order = b->dev.len_order;
     }
     oa.order = order;
-    if (flags & BNK_F_REPLAY) {
+    const bool replay_fused = (flags & BNK_F_REPLAY) && replay_is_one_launch(npkts);
+    if ((flags & BNK_F_REPLAY) && !replay_fused) {
         // grouping by keypair needs only the descriptors: it runs on the side stream beside the open kernel
         CK(ctx, cudaEventRecord(b->ev_fork, s));
         CK(ctx, cudaStreamWaitEvent(b->aux_stream, b->ev_fork, 0));
@@ -661,7 +712,9 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     CK(ctx, launch_open(oa, s, ctx));
     if (timed) CK(ctx, cudaEventRecord(b->a_end, s));
     b->aead_timed = timed;
-    if (flags & BNK_F_REPLAY) {
+    if (replay_fused) { // small batch: one launch sorts and walks; the stream hand-over would cost more than it hides
+        CK(ctx, launch_group_and_replay(b, npkts, s));
+    } else if (flags & BNK_F_REPLAY) {
         CK(ctx, cudaStreamWaitEvent(s, b->ev_join, 0));
         CK(ctx, launch_replay(b, npkts, s));
     }
@@ -669,7 +722,7 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     if (flags & BNK_F_CHECK_INBOUND) CK(ctx, launch_filter_check(b, npkts, now_unix_ns, true, s));
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
-    if (!(flags & BNK_F_NO_D2H) && n) {
+    if (!direct && !(flags & BNK_F_NO_D2H) && n) {
         CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
         CK(ctx, desc_copy(b, n, (flags & BNK_F_DEMUX_INDEX) ? D_SLOT : D_COUNTER, D_STATUS, false, s));
     }
@@ -684,11 +737,20 @@ int bnk_filter_note_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t
     cudaStream_t s = b->stream;
     const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
-    if (!(flags & BNK_F_NO_H2D) && n) {
-        const uint64_t ext = ring_extent(b, npkts, 16);
+    const bool refresh = b->dev_stale;
+    const uint64_t ext = (!(flags & BNK_F_NO_H2D) || refresh) ? ring_extent(b, npkts, 16) : 0;
+    // the filter reads at most 28 bytes of a packet: always cheaper through the bus than a copy of the ring
+    const bool direct = host_direct(b, npkts, flags, 0);
+    HostAlias alias(b, direct);
+    if (!direct && (!(flags & BNK_F_NO_H2D) || refresh) && n) {
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+        if (refresh) {
+            CK(ctx, desc_copy(b, n, D_OFF, D_STATUS, true, s));
+            b->dev_stale = false;
+        } else {
+            CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
+            CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+        }
     }
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     CK(ctx, launch_filter_note(b, npkts, now_unix_ns, s));
@@ -706,17 +768,26 @@ int bnk_filter_check_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_
     cudaStream_t s = b->stream;
     const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
-    if (!(flags & BNK_F_NO_H2D) && n) {
-        const uint64_t ext = ring_extent(b, npkts, 16);
+    const bool refresh = b->dev_stale;
+    const uint64_t ext = (!(flags & BNK_F_NO_H2D) || refresh) ? ring_extent(b, npkts, 16) : 0;
+    // the filter reads at most 28 bytes of a packet: always cheaper through the bus than a copy of the ring
+    const bool direct = host_direct(b, npkts, flags, 0);
+    HostAlias alias(b, direct);
+    if (!direct && (!(flags & BNK_F_NO_H2D) || refresh) && n) {
         CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+        if (refresh) {
+            CK(ctx, desc_copy(b, n, D_OFF, D_STATUS, true, s));
+            b->dev_stale = false;
+        } else {
+            CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
+            CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+        }
     }
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     CK(ctx, launch_filter_check(b, npkts, now_unix_ns, false, s));
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
-    if (!(flags & BNK_F_NO_D2H) && n)
+    if (!direct && !(flags & BNK_F_NO_D2H) && n)
         CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
     return BNK_SUCCESS;
 }
@@ -729,7 +800,8 @@ int bnk_classify_submit(bnk_batch *b, uint32_t npkts, uint32_t flags) {
     cudaStream_t s = b->stream;
     const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
-    if (!(flags & BNK_F_NO_H2D) && n) {
+    if ((!(flags & BNK_F_NO_H2D) || b->dev_stale) && n) {
+        b->dev_stale = false;
         const uint64_t ext = ring_extent(b, npkts, 0);
         if (ext) CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
         CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
@@ -757,7 +829,8 @@ int bnk_gso_split_submit(bnk_batch *b, const bnk_gso_super *supers, uint32_t n_s
     const bool timed = (flags & BNK_F_TIMED) != 0;
     if (n_super > b->max_pkts || (n_super && !supers)) return fail(ctx, BNK_EINVAL, "bad super-packet list");
     const size_t n = n_pkts;
-    if (!(flags & BNK_F_NO_H2D)) {
+    if (!(flags & BNK_F_NO_H2D) || b->dev_stale) {
+        b->dev_stale = false;
         // the ring span holds the segments' slots and the super-packets
         uint64_t ext = ring_extent(b, n_pkts, 16 + 16 + 16);
         for (uint32_t j = 0; j < n_super; j++) {

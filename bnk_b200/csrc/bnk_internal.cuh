@@ -67,6 +67,7 @@ struct bnk_ctx {
     cudaStream_t admin_stream;
     cudaEvent_t timer_start;
     int sm_count;
+    uint64_t host_direct_bytes; // batches up to this ring extent run on the caller's pinned buffers (BNK_HOST_DIRECT_BYTES)
     int aead_mode; // 0 = choose by batch size, 1 = always thread per packet, 2 = always warp per packet (BNK_AEAD_KERNEL)
     std::atomic<uint64_t> launches;
     std::mutex mu;
@@ -109,6 +110,7 @@ struct bnk_batch {
     cudaEvent_t ev_fork, ev_join;
     cudaEvent_t done, k_begin, k_end, t_end, a_begin, a_end;
     bool in_flight;
+    bool dev_stale; // a submit ran on the host arrays: the device copies of ring and descriptors are behind
     bool kernel_timed;
     bool aead_timed;
     bnk_gso_super *h_gso; // pinned staging for the super-packet descriptors
@@ -144,6 +146,8 @@ cudaError_t launch_open(const AeadArgs &a, cudaStream_t s, bnk_ctx *ctx);
 cudaError_t launch_group_by_slot(bnk_batch *b, uint32_t n, bool only_status_ok, cudaStream_t s);
 cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s);
 cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s);
+bool replay_is_one_launch(uint32_t n); // small batches: grouping and walk fit one CTA
+cudaError_t launch_group_and_replay(bnk_batch *b, uint32_t n, cudaStream_t s); // after the open kernel
 cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, bool open_side, cudaStream_t s);
 uint32_t group_sort_chunks(uint32_t max_pkts);
 uint32_t replay_scan_tiles(uint32_t max_pkts);     // tiles of the running-maximum scan

@@ -220,13 +220,393 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(SortKeySrc 
     }
 }
 
+// --- send counters ----------------------------------------------------------------------
+// Packets of a slot get base, base+1, ... in batch order and the slot's counter moves past them, saturating
+// at Reject-After-Messages (packets at or beyond it are refused by the seal kernel).  One thread per packet:
+// in the sorted order a packet's rank inside its run is its position minus the start of the run, found by
+// binary search, so a peer that owns most of a batch costs no more than any other.  The counters are read
+// by the first kernel and advanced by the second, so no thread can see a counter that already moved.
+__device__ __forceinline__ uint32_t run_start(const uint32_t *keys, uint32_t j) {
+    const uint32_t key = keys[j];
+    uint32_t lo = 0, hi = j; // first index in [0, j] whose key equals keys[j]
+    while (lo < hi) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (keys[mid] < key) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+__device__ __forceinline__ uint64_t saturating_counter(uint64_t base, uint32_t k) {
+    const uint64_t c = base + k;
+    return (c < base || c > BNK_REJECT_AFTER_MESSAGES) ? BNK_REJECT_AFTER_MESSAGES : c;
+}
+__global__ void assign_counters_kernel(const uint32_t *keys, const uint32_t *order, uint32_t n, uint32_t max_slots,
+                                       const uint64_t *send_counter, uint64_t *counter_out) {
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const uint32_t slot = keys[j];
+    if (slot >= max_slots) return;
+    counter_out[order[j]] = saturating_counter(send_counter[slot], j - run_start(keys, j));
+}
+__global__ void advance_counters_kernel(const uint32_t *keys, uint32_t n, uint32_t max_slots, uint64_t *send_counter) {
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const uint32_t slot = keys[j];
+    if (slot >= max_slots || (j + 1 < n && keys[j + 1] == slot)) return; // the last packet of a run moves the counter
+    send_counter[slot] = saturating_counter(send_counter[slot], j - run_start(keys, j) + 1);
+}
+
+// --- anti-replay window, RFC 6479 -------------------------------------------------------
+// The window is defined by a sequential walk over a peer's authenticated packets in arrival order: a counter
+// above `last` moves the window (clearing the ring words the top passes), one more than a window behind is
+// refused, and one in between is accepted unless its bit is already marked.  A GPU cannot afford the walk: a
+// peer that owns a large batch would hold the batch up for about a microsecond per 32 packets, and a small
+// batch of many peers would pay one dependent chain of loads per peer.  The verdicts have a closed form in
+// terms of the state (last, ring) at the start of the batch.  With M_j = max(last, counters of the peer's
+// earlier packets of the batch), packet j is accepted iff its counter is below the message limit and either
+// exceeds M_j, or lies within the window behind M_j, was not marked in the ring at the start (only counters
+// <= last can be) and does not repeat the counter of an earlier packet.  (A ring word that the walk would have
+// cleared before reaching j lies more than a window behind M_j; an earlier packet with the same counter that
+// was itself refused was refused for a reason that still holds at j.)  Afterwards last = M at the end of the
+// run, the words the top moved over are cleared, and the accepted packets within a ring of the new top are
+// marked.  Every term is data-parallel over the grouped order:
+//   M_j                         a segmented exclusive running maximum (a scan),
+//   "marked at the start"       a read of the ring as it was before the batch,
+//   "repeats an earlier one"    the lowest grouped position holding the same (peer, counter), found with a
+//                               hash table of positions; built only when some packet of the batch lies behind
+//                               its M_j inside the window, which in-order traffic never does.
+// Up to 1024 packets all of this runs in the CTA that sorted them (group_small_kernel); beyond, as kernels in
+// stream order: scan_tiles (also lays the counters out in grouped order), scan_carry, classify, advance (new
+// last, clears), hash_clear, hash_insert, finish (duplicate look-up, verdicts, marks).
+constexpr uint32_t kScanTile = 1024; // grouped positions per CTA: 256 threads x 4
+constexpr uint64_t kReplayNoPart = ~0ull; // grouped-order counter of a packet that takes no part
+constexpr uint32_t kHashEmpty = 0xffffffffu;
+enum : uint8_t { RP_NOPART = 0, RP_ACCEPT = 1, RP_REJECT = 2, RP_PENDING = 3 };
+
+struct ReplayArgs {
+    const uint32_t *keys;  // [n] keypair slots in grouped order
+    const uint32_t *order; // [n] packet index of each grouped position
+    uint32_t n, max_slots, ring_blocks;
+    uint64_t *replay_last, *replay_next, *replay_ring;
+    const uint64_t *counter; // per packet, as the open kernel left it
+    uint8_t *status;         // per packet
+    uint64_t *sorted_counter; // [n] scratch
+    uint8_t *state;           // [n] scratch
+    uint32_t *table;          // hash table of positions, `mask` + 1 entries
+    uint32_t mask;
+};
+
+struct SegMax { // running maximum that restarts at every run head
+    uint32_t f; // a head lies inside the span
+    uint64_t m; // maximum since the last head (or over the whole span)
+};
+__device__ __forceinline__ SegMax seg_combine(SegMax a, SegMax b) { // a: earlier span, b: the span after it
+    return SegMax{a.f | b.f, (b.f || b.m > a.m) ? b.m : a.m};
+}
+__device__ __forceinline__ SegMax seg_shfl_up(SegMax v, int o) {
+    return SegMax{__shfl_up_sync(0xffffffffu, v.f, o), __shfl_up_sync(0xffffffffu, v.m, o)};
+}
+// Inclusive scan of one value per thread over a CTA of NW warps; returns the exclusive prefix of the calling
+// thread and the total of the CTA.  `part` is NW entries of shared memory.
+template <int NW>
+__device__ __forceinline__ SegMax seg_block_exclusive(SegMax mine, SegMax *part, SegMax &total) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    SegMax inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const SegMax t = seg_shfl_up(inc, o);
+        if (lane >= (uint32_t)o) inc = seg_combine(t, inc);
+    }
+    SegMax ex = seg_shfl_up(inc, 1);
+    if (lane == 0) ex = SegMax{0u, 0ull};
+    __syncthreads(); // `part` may still be read from an earlier call
+    if (lane == 31) part[warp] = inc;
+    __syncthreads();
+    SegMax before{0u, 0ull};
+    total = SegMax{0u, 0ull};
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+        if ((uint32_t)w == warp) before = total;
+        total = seg_combine(total, part[w]);
+    }
+    return seg_combine(before, ex);
+}
+// Four consecutive grouped positions per thread.  e[k] = maximum of the values of the same run that lie in
+// front of item k (`carry` stands for what lies in front of the tile); total = the tile as one span.
+__device__ __forceinline__ void tile_running_max(const bool head[4], const uint64_t v[4], uint64_t carry,
+                                                 uint64_t e[4], SegMax *part, SegMax &total) {
+    SegMax run{0u, 0ull};
+    uint32_t headed = 0; // bit k: a head lies at or before item k inside this thread
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (head[k]) run = SegMax{1u, 0ull};
+        e[k] = run.m;
+        headed |= run.f << k;
+        if (v[k] > run.m) run.m = v[k];
+    }
+    const SegMax ex = seg_block_exclusive<8>(run, part, total);
+    const uint64_t front = ex.f ? ex.m : (carry > ex.m ? carry : ex.m);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        if (!((headed >> k) & 1u) && front > e[k]) e[k] = front;
+}
+
+// Counter of grouped position p, or kReplayNoPart.  Authenticated packets at or beyond the message limit are
+// refused here: their verdict does not depend on the window and they leave no trace in it.
+__device__ __forceinline__ uint64_t replay_gather(const ReplayArgs &a, uint32_t p, uint32_t slot) {
+    uint64_t c = kReplayNoPart;
+    if (slot < a.max_slots) {
+        const uint32_t pkt = a.order[p];
+        const uint8_t st = a.status[pkt];
+        if (st == BNK_PKT_OK || st == BNK_PKT_KEEPALIVE) {
+            c = a.counter[pkt];
+            if (c >= BNK_REJECT_AFTER_MESSAGES) {
+                a.status[pkt] = BNK_PKT_REPLAY;
+                c = kReplayNoPart;
+            }
+        }
+    }
+    a.sorted_counter[p] = c;
+    return c;
+}
+// Verdict of position p as far as it can be told without the duplicate search; the last packet of a run also
+// leaves the peer's next `last`.  e = running maximum of the run in front of p.
+__device__ __forceinline__ uint8_t replay_classify(const ReplayArgs &a, uint32_t p, uint32_t slot, uint64_t c, uint64_t e) {
+    if (slot >= a.max_slots) return RP_NOPART;
+    const uint64_t rmask = a.ring_blocks - 1, window = (uint64_t)(a.ring_blocks - 1) * 64u;
+    const uint64_t last = a.replay_last[slot];
+    const uint64_t M = e > last ? e : last;
+    uint8_t st = RP_NOPART;
+    uint64_t top = M;
+    if (c != kReplayNoPart) {
+        if (c > M) {
+            st = RP_ACCEPT;
+            top = c;
+        } else if (M - c > window) st = RP_REJECT;
+        else if (c <= last && ((a.replay_ring[(size_t)slot * a.ring_blocks + ((c >> 6) & rmask)] >> (c & 63u)) & 1ull))
+            st = RP_REJECT;
+        else st = RP_PENDING;
+    }
+    if (p + 1 == a.n || a.keys[p + 1] != slot) a.replay_next[slot] = top;
+    return st;
+}
+// Warp-wide over 32 consecutive positions (p = this lane's): the peers whose run ends here move their window.
+__device__ __forceinline__ void replay_advance_warp(const ReplayArgs &a, uint32_t p) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t key = p < a.n ? a.keys[p] : 0xffffffffu;
+    const bool is_tail = p < a.n && key < a.max_slots && (p + 1 == a.n || a.keys[p + 1] != key);
+    uint32_t tails = __ballot_sync(0xffffffffu, is_tail);
+    const uint64_t rmask = a.ring_blocks - 1;
+    while (tails) {
+        const uint32_t src = __ffs(tails) - 1;
+        tails &= tails - 1;
+        const uint32_t slot = __shfl_sync(0xffffffffu, key, src);
+        uint64_t *ring = a.replay_ring + (size_t)slot * a.ring_blocks;
+        const uint64_t last = a.replay_last[slot], next = a.replay_next[slot];
+        const uint64_t top = last >> 6;
+        uint64_t steps = (next >> 6) - top;
+        if (steps > a.ring_blocks) steps = a.ring_blocks;
+        for (uint64_t i = lane; i < steps; i += 32) ring[(top + 1 + i) & rmask] = 0ull;
+        __syncwarp();
+        if (lane == 0) a.replay_last[slot] = next;
+    }
+}
+__device__ __forceinline__ uint32_t replay_hash(uint32_t slot, uint64_t c) {
+    uint64_t x = c * 0x9E3779B97F4A7C15ull + slot;
+    x ^= x >> 29;
+    x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 32;
+    return (uint32_t)x;
+}
+// table[h] = lowest grouped position that holds the key (peer, counter); the key of an entry is read through
+// the position it holds and never changes, so a probe may compare against whatever position it sees.
+__device__ __forceinline__ void replay_hash_insert(const ReplayArgs &a, uint32_t p) {
+    const uint32_t slot = a.keys[p];
+    const uint64_t c = a.sorted_counter[p];
+    uint32_t h = replay_hash(slot, c) & a.mask;
+    for (uint32_t probes = 0; probes <= a.mask; ++probes, h = (h + 1) & a.mask) {
+        uint32_t cur = *(volatile uint32_t *)&a.table[h];
+        if (cur == kHashEmpty) {
+            cur = atomicCAS(&a.table[h], kHashEmpty, p);
+            if (cur == kHashEmpty) return;
+        }
+        if (a.keys[cur] == slot && a.sorted_counter[cur] == c) {
+            atomicMin(&a.table[h], p);
+            return;
+        }
+    }
+}
+__device__ __forceinline__ bool replay_hash_has_earlier(const ReplayArgs &a, uint32_t p, uint32_t slot, uint64_t c) {
+    uint32_t h = replay_hash(slot, c) & a.mask;
+    for (uint32_t probes = 0; probes <= a.mask; ++probes, h = (h + 1) & a.mask) {
+        const uint32_t cur = *(volatile uint32_t *)&a.table[h];
+        if (cur == kHashEmpty) return false;
+        if (a.keys[cur] == slot && a.sorted_counter[cur] == c) return cur < p;
+    }
+    return false;
+}
+// Warp-wide over 32 consecutive positions: settles the pending verdicts, writes the refusals and marks the
+// ring.  Lanes that hit the same ring word hand their bits to the lowest of them.
+__device__ __forceinline__ void replay_finish_warp(const ReplayArgs &a, uint32_t p) {
+    const uint32_t lane = threadIdx.x & 31;
+    uint8_t st = p < a.n ? a.state[p] : (uint8_t)RP_NOPART;
+    uint32_t slot = 0;
+    uint64_t c = 0;
+    if (st != RP_NOPART) {
+        slot = a.keys[p];
+        c = a.sorted_counter[p];
+    }
+    if (st == RP_PENDING) st = replay_hash_has_earlier(a, p, slot, c) ? RP_REJECT : RP_ACCEPT;
+    if (st == RP_REJECT) a.status[a.order[p]] = BNK_PKT_REPLAY;
+    const uint64_t rmask = a.ring_blocks - 1;
+    const bool mark = st == RP_ACCEPT && (a.replay_last[slot] >> 6) - (c >> 6) < a.ring_blocks;
+    const unsigned long long word = mark ? (unsigned long long)slot * a.ring_blocks + ((c >> 6) & rmask) : ~0ull - lane;
+    const uint32_t group = __match_any_sync(0xffffffffu, word);
+    const bool leader = mark && (uint32_t)(__ffs(group) - 1) == lane;
+    uint32_t leaders = __ballot_sync(0xffffffffu, leader);
+    const uint32_t bit_lo = mark && (c & 32u) == 0 ? 1u << (c & 31u) : 0u;
+    const uint32_t bit_hi = mark && (c & 32u) != 0 ? 1u << (c & 31u) : 0u;
+    unsigned long long *ring = reinterpret_cast<unsigned long long *>(a.replay_ring);
+    if (__popc(leaders) <= 4) {
+        while (leaders) {
+            const uint32_t src = __ffs(leaders) - 1;
+            leaders &= leaders - 1;
+            const uint32_t members = __shfl_sync(0xffffffffu, group, src);
+            const bool in = (members >> lane) & 1u;
+            const uint32_t lo = __reduce_or_sync(0xffffffffu, in ? bit_lo : 0u);
+            const uint32_t hi = __reduce_or_sync(0xffffffffu, in ? bit_hi : 0u);
+            if (lane == src) atomicOr(&ring[word], ((unsigned long long)hi << 32) | lo);
+        }
+    } else if (mark) {
+        atomicOr(&ring[word], ((unsigned long long)bit_hi << 32) | bit_lo);
+    }
+}
+// The tile of the calling CTA (thread t: positions base..base+3): counters gathered when GATHER, else read
+// back; running maximum with `carry` in front; returns the tile as one span.
+template <bool GATHER>
+__device__ __forceinline__ SegMax replay_tile(const ReplayArgs &a, uint32_t base, uint64_t carry, uint32_t slot[4],
+                                              uint64_t c[4], uint64_t e[4], SegMax *part) {
+    bool head[4];
+    uint64_t v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t p = base + k;
+        head[k] = false;
+        v[k] = 0;
+        c[k] = kReplayNoPart;
+        slot[k] = 0xffffffffu;
+        if (p < a.n) {
+            slot[k] = a.keys[p];
+            head[k] = p == 0 || a.keys[p - 1] != slot[k];
+            c[k] = GATHER ? replay_gather(a, p, slot[k]) : a.sorted_counter[p];
+            if (c[k] != kReplayNoPart) v[k] = c[k];
+        }
+    }
+    SegMax total;
+    tile_running_max(head, v, carry, e, part, total);
+    return total;
+}
+
+__global__ void __launch_bounds__(256) replay_scan_tiles_kernel(ReplayArgs a, uint32_t *tile_head, uint64_t *tile_max,
+                                                                uint32_t *pending_flag) {
+    __shared__ SegMax part[8];
+    if (blockIdx.x == 0 && threadIdx.x == 0) *pending_flag = 0u;
+    uint32_t slot[4];
+    uint64_t c[4], e[4];
+    const SegMax total = replay_tile<true>(a, blockIdx.x * kScanTile + threadIdx.x * 4u, 0ull, slot, c, e, part);
+    if (threadIdx.x == 0) {
+        tile_head[blockIdx.x] = total.f;
+        tile_max[blockIdx.x] = total.m;
+    }
+}
+// One CTA: carry[t] = running maximum that reaches tile t from the tiles in front of it.
+__global__ void __launch_bounds__(1024) replay_scan_carry_kernel(const uint32_t *tile_head, const uint64_t *tile_max,
+                                                                 uint32_t tiles, uint64_t *tile_carry) {
+    __shared__ SegMax part[32];
+    SegMax reached{0u, 0ull};
+    for (uint32_t base = 0; base < tiles; base += 1024u) {
+        const uint32_t t = base + threadIdx.x;
+        SegMax mine{0u, 0ull};
+        if (t < tiles) mine = SegMax{tile_head[t], tile_max[t]};
+        SegMax total;
+        const SegMax ex = seg_block_exclusive<32>(mine, part, total);
+        if (t < tiles) tile_carry[t] = seg_combine(reached, ex).m;
+        reached = seg_combine(reached, total);
+    }
+}
+__global__ void __launch_bounds__(256) replay_classify_kernel(ReplayArgs a, const uint64_t *tile_carry,
+                                                              uint32_t *pending_flag) {
+    __shared__ SegMax part[8];
+    const uint32_t base = blockIdx.x * kScanTile + threadIdx.x * 4u;
+    uint32_t slot[4];
+    uint64_t c[4], e[4];
+    replay_tile<false>(a, base, tile_carry[blockIdx.x], slot, c, e, part);
+    bool pending = false;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (base + k >= a.n) continue;
+        const uint8_t st = replay_classify(a, base + k, slot[k], c[k], e[k]);
+        a.state[base + k] = st;
+        pending |= st == RP_PENDING;
+    }
+    if (__syncthreads_or(pending) && threadIdx.x == 0) *pending_flag = 1u;
+}
+__global__ void __launch_bounds__(256) replay_advance_kernel(ReplayArgs a) {
+    replay_advance_warp(a, blockIdx.x * blockDim.x + threadIdx.x);
+}
+__global__ void __launch_bounds__(256) replay_hash_clear_kernel(ReplayArgs a, const uint32_t *pending_flag) {
+    if (*pending_flag == 0u) return;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i <= a.mask; i += gridDim.x * blockDim.x) a.table[i] = kHashEmpty;
+}
+__global__ void __launch_bounds__(256) replay_hash_insert_kernel(ReplayArgs a, const uint32_t *pending_flag) {
+    if (*pending_flag == 0u) return;
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < a.n && a.state[p] != RP_NOPART) replay_hash_insert(a, p);
+}
+__global__ void __launch_bounds__(256) replay_finish_kernel(ReplayArgs a) {
+    replay_finish_warp(a, blockIdx.x * blockDim.x + threadIdx.x);
+}
+// All of the above for one tile, by the CTA that holds it (n <= kScanTile, 256 threads).
+__device__ __forceinline__ void replay_one_cta(const ReplayArgs &a, SegMax *part) {
+    const uint32_t tid = threadIdx.x;
+    uint32_t slot[4];
+    uint64_t c[4], e[4];
+    replay_tile<true>(a, tid * 4u, 0ull, slot, c, e, part);
+    bool pending = false;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (tid * 4u + k >= a.n) continue;
+        const uint8_t st = replay_classify(a, tid * 4u + k, slot[k], c[k], e[k]);
+        a.state[tid * 4u + k] = st;
+        pending |= st == RP_PENDING;
+    }
+    const bool any_pending = __syncthreads_or(pending); // also: every verdict and next `last` is written
+    for (uint32_t p = tid; p < kScanTile; p += 256u) replay_advance_warp(a, p);
+    if (any_pending) {
+        for (uint32_t i = tid; i <= a.mask; i += 256u) a.table[i] = kHashEmpty;
+        __syncthreads();
+        for (uint32_t p = tid; p < a.n; p += 256u)
+            if (a.state[p] != RP_NOPART) replay_hash_insert(a, p);
+    }
+    __syncthreads(); // clears before marks, inserts before look-ups
+    for (uint32_t p = tid; p < kScanTile; p += 256u) replay_finish_warp(a, p);
+}
+
 // --- the whole sort in one CTA, for batches of up to 1024 packets ----------------------
 // Same three steps per digit as above, but keys and indices ping-pong between shared-memory buffers
 // and all passes run inside one launch: a 128-packet batch pays one launch instead of six.
 constexpr uint32_t kSmallMax = 1024;
+// Send counters in the same launch (counter_out != nullptr): with one CTA a barrier separates the reads of
+// the peers' counters from their advance, which takes two launches for larger batches.
+// The replay window of a small batch can follow in the same launch as well (replay_last != nullptr).
+struct SmallCounters {
+    uint64_t *send_counter; // [max_slots]
+    uint64_t *counter_out;  // per packet
+    uint32_t max_slots;
+};
 __global__ void __launch_bounds__(kSortThreads) group_small_kernel(SortKeySrc src, uint32_t n, uint32_t passes,
                                                                    uint32_t digit_bits, uint32_t *keys_out,
-                                                                   uint32_t *vals_out) {
+                                                                   uint32_t *vals_out, SmallCounters sc, ReplayArgs rp) {
     constexpr uint32_t TILES = kSmallMax / kSortThreads; // 4
     __shared__ uint32_t kbuf[2][kSmallMax], vbuf[2][kSmallMax];
     __shared__ uint32_t cur[kSortWarps][kMaxBins];
@@ -309,430 +689,32 @@ __global__ void __launch_bounds__(kSortThreads) group_small_kernel(SortKeySrc sr
         }
         __syncthreads();
     }
-}
-
-// --- send counters ----------------------------------------------------------------------
-// Packets of a slot get base, base+1, ... in batch order and the slot's counter moves past them, saturating
-// at Reject-After-Messages (packets at or beyond it are refused by the seal kernel).  One thread per packet:
-// in the sorted order a packet's rank inside its run is its position minus the start of the run, found by
-// binary search, so a peer that owns most of a batch costs no more than any other.  The counters are read
-// by the first kernel and advanced by the second, so no thread can see a counter that already moved.
-__device__ __forceinline__ uint32_t run_start(const uint32_t *keys, uint32_t j) {
-    const uint32_t key = keys[j];
-    uint32_t lo = 0, hi = j; // first index in [0, j] whose key equals keys[j]
-    while (lo < hi) {
-        const uint32_t mid = (lo + hi) >> 1;
-        if (keys[mid] < key) lo = mid + 1;
-        else hi = mid;
+    if (rp.replay_last != nullptr) { // the barrier that closed the last pass makes the sorted arrays visible
+        __shared__ SegMax part[8];
+        replay_one_cta(rp, part);
     }
-    return lo;
-}
-__device__ __forceinline__ uint64_t saturating_counter(uint64_t base, uint32_t k) {
-    const uint64_t c = base + k;
-    return (c < base || c > BNK_REJECT_AFTER_MESSAGES) ? BNK_REJECT_AFTER_MESSAGES : c;
-}
-__global__ void assign_counters_kernel(const uint32_t *keys, const uint32_t *order, uint32_t n, uint32_t max_slots,
-                                       const uint64_t *send_counter, uint64_t *counter_out) {
-    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n) return;
-    const uint32_t slot = keys[j];
-    if (slot >= max_slots) return;
-    counter_out[order[j]] = saturating_counter(send_counter[slot], j - run_start(keys, j));
-}
-__global__ void advance_counters_kernel(const uint32_t *keys, uint32_t n, uint32_t max_slots, uint64_t *send_counter) {
-    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n) return;
-    const uint32_t slot = keys[j];
-    if (slot >= max_slots || (j + 1 < n && keys[j + 1] == slot)) return; // the last packet of a run moves the counter
-    send_counter[slot] = saturating_counter(send_counter[slot], j - run_start(keys, j) + 1);
-}
-
-// --- anti-replay window, RFC 6479 -------------------------------------------------------
-// The window is defined by a sequential walk over a peer's authenticated packets in arrival order.  For any
-// stretch of that walk the verdicts have a closed form in terms of the state (last, ring) at its start:
-// with M_j = max(last, counters of the earlier packets of the stretch), packet j is accepted iff its counter
-// is below the limit and either exceeds M_j, or lies within the window behind M_j, was not marked in the ring
-// at the start (only counters <= last can be) and does not repeat an earlier counter of the stretch.  (A ring
-// block that the walk would have cleared before reaching j lies more than a window behind M_j.)  Afterwards
-// last = max, the blocks the top moved over are cleared, and the bit of every packet that reached the window
-// is set unless the top has moved a whole ring past it.
-// One warp handles a peer: 32 packets at a time through the closed form (prefix max and duplicate search by
-// shuffle / match), the stretches one after the other.  Warp w looks at sorted positions [32w, 32w+32) and
-// handles the peers whose run starts there, so a peer that owns most of a batch is 32-wide instead of serial.
-__global__ void __launch_bounds__(256) replay_kernel(const uint32_t *keys, const uint32_t *order, uint32_t n,
-                                                     uint32_t max_slots, uint32_t ring_blocks, uint64_t *replay_last,
-                                                     uint64_t *replay_ring, const uint64_t *counter, uint8_t *status) {
-    const uint32_t lane = threadIdx.x & 31;
-    const uint32_t first = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 32u;
-    if (first >= n) return;
-    const uint32_t mine = first + lane;
-    const bool is_head = mine < n && (mine == 0 || keys[mine - 1] != keys[mine]);
-    uint32_t heads = __ballot_sync(0xffffffffu, is_head);
-    const uint64_t rmask = ring_blocks - 1;
-    const uint64_t window = (uint64_t)(ring_blocks - 1) * 64u;
-    const uint32_t lt = (1u << lane) - 1u;
-    while (heads) {
-        const uint32_t h = first + (__ffs(heads) - 1);
-        heads &= heads - 1;
-        const uint32_t slot = keys[h];
-        if (slot >= max_slots) continue; // packets that take no part
-        unsigned long long *ring = reinterpret_cast<unsigned long long *>(replay_ring) + (size_t)slot * ring_blocks;
-        uint64_t last = replay_last[slot];
-        // the next stretch's descriptors are fetched while this one goes through the window
-        struct Fetched {
-            bool in, auth;
-            uint32_t pkt;
-            uint64_t c;
-        };
-        auto fetch = [&](uint32_t base) {
-            Fetched f{false, false, 0u, 0ull};
-            const uint32_t pos = base + lane;
-            f.in = pos < n && keys[pos] == slot;
-            if (f.in) {
-                f.pkt = order[pos];
-                const uint8_t st = status[f.pkt];
-                f.auth = st == BNK_PKT_OK || st == BNK_PKT_KEEPALIVE;
-                if (f.auth) f.c = counter[f.pkt];
-            }
-            return f;
-        };
-        Fetched nxt = fetch(h);
-        for (uint32_t base = h;; base += 32) {
-            const Fetched cur = nxt;
-            const uint32_t inmask = __ballot_sync(0xffffffffu, cur.in);
-            if (!inmask) break;
-            if (inmask == 0xffffffffu) nxt = fetch(base + 32);
-            const uint32_t pkt = cur.pkt;
-            const bool auth = cur.auth;
-            const uint64_t c = cur.c;
-            const bool live = auth && c < BNK_REJECT_AFTER_MESSAGES;
-            // M: highest counter before this lane's packet
-            uint64_t incl = live ? c : 0;
+    if (sc.counter_out == nullptr) return;
+    uint64_t next[TILES];
+    uint32_t tail_slot[TILES];
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint64_t t = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= (uint32_t)o && t > incl) incl = t;
-            }
-            uint64_t excl = __shfl_up_sync(0xffffffffu, incl, 1);
-            if (lane == 0) excl = 0;
-            const uint64_t M = excl > last ? excl : last;
-            const uint64_t stretch_max = __shfl_sync(0xffffffffu, incl, 31);
-            // an earlier packet of the stretch with the same counter?
-            const unsigned long long probe = live ? c : (BNK_REJECT_AFTER_MESSAGES + 1ull + lane);
-            const bool repeated = (__match_any_sync(0xffffffffu, probe) & lt) != 0;
-            const bool behind = live && c <= M;
-            const bool too_old = behind && (M - c > window);
-            bool seen = false;
-            if (behind && !too_old && c <= last) seen = (__ldcg(&ring[(c >> 6) & rmask]) >> (c & 63u)) & 1ull; // L2: the word may have just been updated by atomics
-            const bool accept = live && (c > M || (!too_old && !seen && !repeated));
-            if (auth && !accept) status[pkt] = BNK_PKT_REPLAY;
-            __syncwarp();
-            const uint64_t new_last = stretch_max > last ? stretch_max : last;
-            const uint64_t top = last >> 6, ntop = new_last >> 6;
-            uint64_t steps = ntop - top;
-            if (steps > ring_blocks) steps = ring_blocks;
-            for (uint64_t i = lane; i < steps; i += 32) __stcg(&ring[(top + 1 + i) & rmask], 0ull);
-            __syncwarp();
-            if (live && !too_old && ntop - (c >> 6) < ring_blocks) atomicOr(&ring[(c >> 6) & rmask], 1ull << (c & 63u));
-            __syncwarp();
-            last = new_last;
-            if (inmask != 0xffffffffu) break;
+    for (uint32_t t = 0; t < TILES; t++) {
+        const uint32_t j = t * kSortThreads + tid;
+        tail_slot[t] = 0xffffffffu;
+        if (j >= n) continue;
+        const uint32_t slot = keys_out[j];
+        if (slot >= sc.max_slots) continue;
+        const uint32_t rank = j - run_start(keys_out, j);
+        const uint64_t base = sc.send_counter[slot];
+        sc.counter_out[vals_out[j]] = saturating_counter(base, rank);
+        if (j + 1 == n || keys_out[j + 1] != slot) {
+            tail_slot[t] = slot;
+            next[t] = saturating_counter(base, rank + 1);
         }
-        if (lane == 0) replay_last[slot] = last;
     }
-}
-
-// --- the same window without the walk -----------------------------------------------------
-// A warp walking a run costs about a microsecond per 32 packets, one stretch after the other, so a peer that
-// owns a large batch would hold the whole batch up.  Taking the whole run as one stretch, every term of the
-// closed form can be had without walking:
-//   M_j                         a segmented exclusive running maximum over the grouped order (a scan),
-//   "marked at the start"       a read of the ring as it was before the batch,
-//   "repeats an earlier one"    the lowest grouped position holding the same (peer, counter), found with a
-//                               hash table of positions; built only when some packet of the batch lies behind
-//                               its M_j inside the window, which in-order traffic never does,
-//   the new state               last = M at the end of the run; the words the top moved over are cleared; the
-//                               accepted packets within a ring of the new top are marked.
-// Kernels, in stream order: scan_tiles (also lays the counters out in grouped order), scan_carry, classify,
-// advance (new last, clears), hash_clear, hash_insert, finish (duplicate look-up, verdicts, marks).
-constexpr uint32_t kScanTile = 1024; // grouped positions per CTA: 256 threads x 4
-constexpr uint64_t kReplayNoPart = ~0ull; // grouped-order counter of a packet that takes no part
-constexpr uint32_t kHashEmpty = 0xffffffffu;
-enum : uint8_t { RP_NOPART = 0, RP_ACCEPT = 1, RP_REJECT = 2, RP_PENDING = 3 };
-
-struct SegMax { // running maximum that restarts at every run head
-    uint32_t f; // a head lies inside the span
-    uint64_t m; // maximum since the last head (or over the whole span)
-};
-__device__ __forceinline__ SegMax seg_combine(SegMax a, SegMax b) { // a: earlier span, b: the span after it
-    return SegMax{a.f | b.f, (b.f || b.m > a.m) ? b.m : a.m};
-}
-__device__ __forceinline__ SegMax seg_shfl_up(SegMax v, int o) {
-    return SegMax{__shfl_up_sync(0xffffffffu, v.f, o), __shfl_up_sync(0xffffffffu, v.m, o)};
-}
-// Inclusive scan of one value per thread over a CTA of NW warps; returns the exclusive prefix of the calling
-// thread and the total of the CTA.  `part` is NW entries of shared memory.
-template <int NW>
-__device__ __forceinline__ SegMax seg_block_exclusive(SegMax mine, SegMax *part, SegMax &total) {
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    SegMax inc = mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const SegMax t = seg_shfl_up(inc, o);
-        if (lane >= (uint32_t)o) inc = seg_combine(t, inc);
-    }
-    SegMax ex = seg_shfl_up(inc, 1);
-    if (lane == 0) ex = SegMax{0u, 0ull};
-    __syncthreads(); // `part` may still be read from an earlier call
-    if (lane == 31) part[warp] = inc;
     __syncthreads();
-    SegMax before{0u, 0ull};
-    total = SegMax{0u, 0ull};
 #pragma unroll
-    for (int w = 0; w < NW; ++w) {
-        if ((uint32_t)w == warp) before = total;
-        total = seg_combine(total, part[w]);
-    }
-    return seg_combine(before, ex);
-}
-// Four consecutive grouped positions per thread.  e[k] = maximum of the values of the same run that lie in
-// front of item k (`carry` stands for what lies in front of the tile); total = the tile as one span.
-__device__ __forceinline__ void tile_running_max(const bool head[4], const uint64_t v[4], uint64_t carry,
-                                                 uint64_t e[4], SegMax *part, SegMax &total) {
-    SegMax run{0u, 0ull};
-    uint32_t headed = 0; // bit k: a head lies at or before item k inside this thread
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        if (head[k]) run = SegMax{1u, 0ull};
-        e[k] = run.m;
-        headed |= run.f << k;
-        if (v[k] > run.m) run.m = v[k];
-    }
-    const SegMax ex = seg_block_exclusive<8>(run, part, total);
-    const uint64_t front = ex.f ? ex.m : (carry > ex.m ? carry : ex.m);
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-        if (!((headed >> k) & 1u) && front > e[k]) e[k] = front;
-}
-
-__global__ void __launch_bounds__(256) replay_scan_tiles_kernel(const uint32_t *keys, const uint32_t *order, uint32_t n,
-                                                                uint32_t max_slots, const uint64_t *counter,
-                                                                uint8_t *status, uint64_t *sorted_counter,
-                                                                uint32_t *tile_head, uint64_t *tile_max,
-                                                                uint32_t *pending_flag) {
-    __shared__ SegMax part[8];
-    const uint32_t base = blockIdx.x * kScanTile + threadIdx.x * 4u;
-    if (blockIdx.x == 0 && threadIdx.x == 0) *pending_flag = 0u;
-    bool head[4];
-    uint64_t v[4], e[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const uint32_t p = base + k;
-        head[k] = false;
-        v[k] = 0;
-        if (p < n) {
-            const uint32_t slot = keys[p];
-            head[k] = p == 0 || keys[p - 1] != slot;
-            uint64_t c = kReplayNoPart;
-            if (slot < max_slots) {
-                const uint32_t pkt = order[p];
-                const uint8_t st = status[pkt];
-                if (st == BNK_PKT_OK || st == BNK_PKT_KEEPALIVE) {
-                    c = counter[pkt];
-                    if (c >= BNK_REJECT_AFTER_MESSAGES) { // beyond the message limit: rejected whatever the window holds
-                        status[pkt] = BNK_PKT_REPLAY;
-                        c = kReplayNoPart;
-                    }
-                }
-            }
-            sorted_counter[p] = c;
-            if (c != kReplayNoPart) v[k] = c;
-        }
-    }
-    SegMax total;
-    tile_running_max(head, v, 0ull, e, part, total);
-    if (threadIdx.x == 0) {
-        tile_head[blockIdx.x] = total.f;
-        tile_max[blockIdx.x] = total.m;
-    }
-}
-// One CTA: carry[t] = running maximum that reaches tile t from the tiles in front of it.
-__global__ void __launch_bounds__(1024) replay_scan_carry_kernel(const uint32_t *tile_head, const uint64_t *tile_max,
-                                                                 uint32_t tiles, uint64_t *tile_carry) {
-    __shared__ SegMax part[32];
-    SegMax reached{0u, 0ull};
-    for (uint32_t base = 0; base < tiles; base += 1024u) {
-        const uint32_t t = base + threadIdx.x;
-        SegMax mine{0u, 0ull};
-        if (t < tiles) mine = SegMax{tile_head[t], tile_max[t]};
-        SegMax total;
-        const SegMax ex = seg_block_exclusive<32>(mine, part, total);
-        if (t < tiles) tile_carry[t] = seg_combine(reached, ex).m;
-        reached = seg_combine(reached, total);
-    }
-}
-__global__ void __launch_bounds__(256) replay_classify_kernel(const uint32_t *keys, uint32_t n, uint32_t max_slots,
-                                                              uint32_t ring_blocks, const uint64_t *replay_last,
-                                                              const uint64_t *replay_ring, const uint64_t *sorted_counter,
-                                                              const uint64_t *tile_carry, uint64_t *replay_next,
-                                                              uint8_t *state, uint32_t *pending_flag) {
-    __shared__ SegMax part[8];
-    const uint32_t base = blockIdx.x * kScanTile + threadIdx.x * 4u;
-    const uint64_t rmask = ring_blocks - 1;
-    const uint64_t window = (uint64_t)(ring_blocks - 1) * 64u;
-    bool head[4];
-    uint32_t slot[4];
-    uint64_t c[4], v[4], e[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const uint32_t p = base + k;
-        head[k] = false;
-        v[k] = 0;
-        c[k] = kReplayNoPart;
-        slot[k] = 0xffffffffu;
-        if (p < n) {
-            slot[k] = keys[p];
-            head[k] = p == 0 || keys[p - 1] != slot[k];
-            c[k] = sorted_counter[p];
-            if (c[k] != kReplayNoPart) v[k] = c[k];
-        }
-    }
-    SegMax total;
-    tile_running_max(head, v, tile_carry[blockIdx.x], e, part, total);
-    bool pending = false;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const uint32_t p = base + k;
-        if (p >= n) continue;
-        uint8_t st = RP_NOPART;
-        if (slot[k] < max_slots) {
-            const uint64_t last = replay_last[slot[k]];
-            const uint64_t M = e[k] > last ? e[k] : last;
-            const uint64_t ck = c[k];
-            if (ck != kReplayNoPart) {
-                if (ck > M) st = RP_ACCEPT;
-                else if (M - ck > window) st = RP_REJECT;
-                else if (ck <= last &&
-                         ((replay_ring[(size_t)slot[k] * ring_blocks + ((ck >> 6) & rmask)] >> (ck & 63u)) & 1ull))
-                    st = RP_REJECT;
-                else {
-                    st = RP_PENDING;
-                    pending = true;
-                }
-            }
-            if (p + 1 == n || keys[p + 1] != slot[k]) replay_next[slot[k]] = v[k] > M ? v[k] : M;
-        }
-        state[p] = st;
-    }
-    if (__syncthreads_or(pending) && threadIdx.x == 0) *pending_flag = 1u;
-}
-// The warp that holds the last packet of a run moves the peer's window: clears, then the new last.
-__global__ void __launch_bounds__(256) replay_advance_kernel(const uint32_t *keys, uint32_t n, uint32_t max_slots,
-                                                             uint32_t ring_blocks, uint64_t *replay_last,
-                                                             uint64_t *replay_ring, const uint64_t *replay_next) {
-    const uint32_t lane = threadIdx.x & 31;
-    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
-    const bool is_tail = p < n && keys[p] < max_slots && (p + 1 == n || keys[p + 1] != keys[p]);
-    uint32_t tails = __ballot_sync(0xffffffffu, is_tail);
-    const uint64_t rmask = ring_blocks - 1;
-    while (tails) {
-        const uint32_t src = __ffs(tails) - 1;
-        tails &= tails - 1;
-        const uint32_t slot = __shfl_sync(0xffffffffu, p < n ? keys[p] : 0u, src);
-        unsigned long long *ring = reinterpret_cast<unsigned long long *>(replay_ring) + (size_t)slot * ring_blocks;
-        const uint64_t last = replay_last[slot], next = replay_next[slot];
-        const uint64_t top = last >> 6;
-        uint64_t steps = (next >> 6) - top;
-        if (steps > ring_blocks) steps = ring_blocks;
-        for (uint64_t i = lane; i < steps; i += 32) ring[(top + 1 + i) & rmask] = 0ull;
-        __syncwarp();
-        if (lane == 0) replay_last[slot] = next;
-    }
-}
-__device__ __forceinline__ uint32_t replay_hash(uint32_t slot, uint64_t c) {
-    uint64_t x = c * 0x9E3779B97F4A7C15ull + slot;
-    x ^= x >> 29;
-    x *= 0xBF58476D1CE4E5B9ull;
-    x ^= x >> 32;
-    return (uint32_t)x;
-}
-__global__ void __launch_bounds__(256) replay_hash_clear_kernel(uint32_t *table, uint32_t cap, const uint32_t *pending_flag) {
-    if (*pending_flag == 0u) return;
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < cap; i += gridDim.x * blockDim.x) table[i] = kHashEmpty;
-}
-// table[h] = lowest grouped position that holds the key (peer, counter); the key of an entry is read through
-// the position it holds and never changes, so a probe may compare against whatever position it sees.
-__global__ void __launch_bounds__(256) replay_hash_insert_kernel(const uint32_t *keys, const uint64_t *sorted_counter,
-                                                                 const uint8_t *state, uint32_t n, uint32_t *table,
-                                                                 uint32_t mask, const uint32_t *pending_flag) {
-    if (*pending_flag == 0u) return;
-    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= n || state[p] == RP_NOPART) return;
-    const uint32_t slot = keys[p];
-    const uint64_t c = sorted_counter[p];
-    uint32_t h = replay_hash(slot, c) & mask;
-    for (uint32_t probes = 0; probes <= mask; ++probes, h = (h + 1) & mask) {
-        uint32_t cur = __ldcg(&table[h]);
-        if (cur == kHashEmpty) {
-            cur = atomicCAS(&table[h], kHashEmpty, p);
-            if (cur == kHashEmpty) return;
-        }
-        if (keys[cur] == slot && sorted_counter[cur] == c) {
-            atomicMin(&table[h], p);
-            return;
-        }
-    }
-}
-__global__ void __launch_bounds__(256) replay_finish_kernel(const uint32_t *keys, const uint32_t *order,
-                                                            const uint64_t *sorted_counter, const uint8_t *state,
-                                                            uint32_t n, uint32_t ring_blocks, const uint64_t *replay_last,
-                                                            uint64_t *replay_ring, const uint32_t *table, uint32_t mask,
-                                                            uint8_t *status) {
-    const uint32_t lane = threadIdx.x & 31;
-    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
-    uint8_t st = p < n ? state[p] : (uint8_t)RP_NOPART;
-    uint32_t slot = 0;
-    uint64_t c = 0;
-    if (st != RP_NOPART) {
-        slot = keys[p];
-        c = sorted_counter[p];
-    }
-    if (st == RP_PENDING) {
-        st = RP_ACCEPT;
-        uint32_t h = replay_hash(slot, c) & mask;
-        for (uint32_t probes = 0; probes <= mask; ++probes, h = (h + 1) & mask) {
-            const uint32_t cur = table[h];
-            if (cur == kHashEmpty) break;
-            if (keys[cur] == slot && sorted_counter[cur] == c) {
-                if (cur < p) st = RP_REJECT;
-                break;
-            }
-        }
-    }
-    if (st == RP_REJECT) status[order[p]] = BNK_PKT_REPLAY;
-    // marks: lanes that hit the same ring word hand their bits to the lowest of them
-    const uint64_t rmask = ring_blocks - 1;
-    const bool mark = st == RP_ACCEPT && (replay_last[slot] >> 6) - (c >> 6) < ring_blocks;
-    const unsigned long long word = mark ? (unsigned long long)slot * ring_blocks + ((c >> 6) & rmask) : ~0ull - lane;
-    const uint32_t group = __match_any_sync(0xffffffffu, word);
-    const bool leader = mark && (uint32_t)(__ffs(group) - 1) == lane;
-    uint32_t leaders = __ballot_sync(0xffffffffu, leader);
-    const uint32_t bit_lo = mark && (c & 32u) == 0 ? 1u << (c & 31u) : 0u;
-    const uint32_t bit_hi = mark && (c & 32u) != 0 ? 1u << (c & 31u) : 0u;
-    unsigned long long *ring = reinterpret_cast<unsigned long long *>(replay_ring);
-    if (__popc(leaders) <= 4) {
-        while (leaders) {
-            const uint32_t src = __ffs(leaders) - 1;
-            leaders &= leaders - 1;
-            const uint32_t members = __shfl_sync(0xffffffffu, group, src);
-            const bool in = (members >> lane) & 1u;
-            const uint32_t lo = __reduce_or_sync(0xffffffffu, in ? bit_lo : 0u);
-            const uint32_t hi = __reduce_or_sync(0xffffffffu, in ? bit_hi : 0u);
-            if (lane == src) atomicOr(&ring[word], ((unsigned long long)hi << 32) | lo);
-        }
-    } else if (mark) {
-        atomicOr(&ring[word], ((unsigned long long)bit_hi << 32) | bit_lo);
-    }
+    for (uint32_t t = 0; t < TILES; t++)
+        if (tail_slot[t] != 0xffffffffu) sc.send_counter[tail_slot[t]] = next[t];
 }
 
 // --- scheduling order by length class (mixed packet sizes) ------------------------------
@@ -809,7 +791,8 @@ void sort_pass(const SortKeySrc &src, const uint32_t *kin, const uint32_t *vin, 
 uint32_t group_sort(const SortKeySrc &src, uint32_t n, uint32_t max_chunks, const SortBuffers &sb, cudaStream_t s) {
     const SortPlan plan = plan_for(src.max_slots);
     if (n <= kSmallMax) {
-        group_small_kernel<<<1, kSortThreads, 0, s>>>(src, n, plan.passes, plan.digit_bits, sb.keys_b, sb.order);
+        group_small_kernel<<<1, kSortThreads, 0, s>>>(src, n, plan.passes, plan.digit_bits, sb.keys_b, sb.order,
+                                                      SmallCounters{nullptr, nullptr, 0}, ReplayArgs{});
         return 1;
     }
     const uint32_t bins = 1u << plan.digit_bits;
@@ -858,6 +841,17 @@ cudaError_t launch_group_by_slot(bnk_batch *b, uint32_t n, bool only_status_ok, 
 
 cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
+    if (n <= kSmallMax) { // sort and counters in one launch
+        bnk_ctx *ctx = b->ctx;
+        DeviceBatch &d = b->dev;
+        const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
+        group_small_kernel<<<1, kSortThreads, 0, s>>>(SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n,
+                                                      plan.passes, plan.digit_bits, d.keys_tmp + b->max_pkts, d.order,
+                                                      SmallCounters{ctx->kt.send_counter, d.counter, ctx->cfg.max_keypairs},
+                                                      ReplayArgs{});
+        ctx->launches += 1;
+        return cudaGetLastError();
+    }
     cudaError_t e = launch_group_by_slot(b, n, false, s);
     if (e != cudaSuccess) return e;
     DeviceBatch &d = b->dev;
@@ -870,42 +864,62 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-// Expects launch_group_by_slot(b, n, false, ...) to have completed before this point of stream s.
-constexpr uint32_t kReplayWalkUpTo = 2048;
 uint32_t replay_scan_tiles(uint32_t max_pkts) { return (max_pkts + kScanTile - 1) / kScanTile; }
 uint32_t replay_hash_capacity(uint32_t max_pkts) {
     uint32_t cap = 1024;
     while (cap < 2u * max_pkts && cap < 0x80000000u) cap <<= 1;
     return cap;
 }
+static ReplayArgs replay_args(bnk_batch *b, uint32_t n) {
+    bnk_ctx *ctx = b->ctx;
+    DeviceBatch &d = b->dev;
+    uint32_t cap = 1024;
+    while (cap < 2u * n) cap <<= 1; // at most half full
+    ReplayArgs a{};
+    a.keys = d.keys_tmp + b->max_pkts;
+    a.order = d.order;
+    a.n = n;
+    a.max_slots = ctx->cfg.max_keypairs;
+    a.ring_blocks = ctx->cfg.replay_ring_blocks;
+    a.replay_last = ctx->kt.replay_last;
+    a.replay_next = ctx->kt.replay_next;
+    a.replay_ring = ctx->kt.replay_ring;
+    a.counter = d.counter;
+    a.status = d.status;
+    a.sorted_counter = d.sorted_counter;
+    a.state = d.replay_state;
+    a.table = d.replay_hash;
+    a.mask = cap - 1;
+    return a;
+}
+// Grouping and replay window of a small batch in one launch, for after the open kernel.
+bool replay_is_one_launch(uint32_t n) { return n <= kSmallMax; }
+cudaError_t launch_group_and_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    bnk_ctx *ctx = b->ctx;
+    DeviceBatch &d = b->dev;
+    const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
+    group_small_kernel<<<1, kSortThreads, 0, s>>>(SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n, plan.passes,
+                                                  plan.digit_bits, d.keys_tmp + b->max_pkts, d.order,
+                                                  SmallCounters{nullptr, nullptr, 0}, replay_args(b, n));
+    ctx->launches += 1;
+    return cudaGetLastError();
+}
+// Expects launch_group_by_slot(b, n, false, ...) to have completed before this point of stream s.
 cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     DeviceBatch &d = b->dev;
-    bnk_ctx *ctx = b->ctx;
-    const uint32_t *keys = d.keys_tmp + b->max_pkts;
-    const uint32_t slots = ctx->cfg.max_keypairs, blocks = ctx->cfg.replay_ring_blocks;
-    KeypairTables &kt = ctx->kt;
-    if (n <= kReplayWalkUpTo) { // one launch; runs are short enough to walk
-        replay_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys, d.order, n, slots, blocks, kt.replay_last, kt.replay_ring,
-                                                     d.counter, d.status);
-        ctx->launches += 1;
-        return cudaGetLastError();
-    }
+    const ReplayArgs a = replay_args(b, n);
     const uint32_t tiles = (n + kScanTile - 1) / kScanTile, grid = (n + 255) / 256;
-    uint32_t cap = 1024;
-    while (cap < 2u * n) cap <<= 1; // at most half full
     uint32_t *flag = d.replay_tile_head + replay_scan_tiles(b->max_pkts);
-    replay_scan_tiles_kernel<<<tiles, 256, 0, s>>>(keys, d.order, n, slots, d.counter, d.status, d.sorted_counter,
-                                                  d.replay_tile_head, d.replay_tile_max, flag);
+    replay_scan_tiles_kernel<<<tiles, 256, 0, s>>>(a, d.replay_tile_head, d.replay_tile_max, flag);
     replay_scan_carry_kernel<<<1, 1024, 0, s>>>(d.replay_tile_head, d.replay_tile_max, tiles, d.replay_tile_carry);
-    replay_classify_kernel<<<tiles, 256, 0, s>>>(keys, n, slots, blocks, kt.replay_last, kt.replay_ring, d.sorted_counter,
-                                                d.replay_tile_carry, kt.replay_next, d.replay_state, flag);
-    replay_advance_kernel<<<grid, 256, 0, s>>>(keys, n, slots, blocks, kt.replay_last, kt.replay_ring, kt.replay_next);
-    replay_hash_clear_kernel<<<148 * 4, 256, 0, s>>>(d.replay_hash, cap, flag);
-    replay_hash_insert_kernel<<<grid, 256, 0, s>>>(keys, d.sorted_counter, d.replay_state, n, d.replay_hash, cap - 1, flag);
-    replay_finish_kernel<<<grid, 256, 0, s>>>(keys, d.order, d.sorted_counter, d.replay_state, n, blocks, kt.replay_last,
-                                             kt.replay_ring, d.replay_hash, cap - 1, d.status);
-    ctx->launches += 7;
+    replay_classify_kernel<<<tiles, 256, 0, s>>>(a, d.replay_tile_carry, flag);
+    replay_advance_kernel<<<grid, 256, 0, s>>>(a);
+    replay_hash_clear_kernel<<<148 * 4, 256, 0, s>>>(a, flag);
+    replay_hash_insert_kernel<<<grid, 256, 0, s>>>(a, flag);
+    replay_finish_kernel<<<grid, 256, 0, s>>>(a);
+    b->ctx->launches += 7;
     return cudaGetLastError();
 }
 
