@@ -23,6 +23,10 @@
  *     of that batch to have been waited for (BNK_EBUSY otherwise).  Submits with
  *     both BNK_F_NO_H2D and BNK_F_NO_D2H only queue kernels on the batch's stream
  *     and may be issued back to back.
+ *   - Between a submit and its bnk_wait the batch's host arrays belong to the
+ *     library.  Small batches (up to 1024 packets and a ring extent of 128 KiB,
+ *     environment BNK_HOST_DIRECT_BYTES, 0 = never) are not copied: the kernels
+ *     read and write the pinned arrays in place.  The results are the same bytes.
  *   - Send counters and replay windows are per keypair and ordered: batches that
  *     are in flight at the same time must not carry packets of the same keypair
  *     slot when BNK_F_ASSIGN_COUNTERS or BNK_F_REPLAY is used (give each peer's
