@@ -565,13 +565,13 @@ def run_ours(args, rank, world, local_rank):
         def small_latency(sn):
             sb = setup_batch(ctx, sn, stride, 32, first_peer=0)
             sb.ring[:] = 0x5A
-            for _ in range(30):
+            for _ in range(min(30, args.small_rounds)):
                 sb.len[:sn] = SIZE
                 sb.seal(sn, F_ASSIGN_COUNTERS)
                 sb.len[:sn] = sb.out_len[:sn]
                 sb.open(sn, F_REPLAY)
             seal_t, open_t = [], []
-            for _ in range(200):
+            for _ in range(args.small_rounds):
                 sb.len[:sn] = SIZE
                 t0 = time.perf_counter()
                 sb.seal(sn, F_ASSIGN_COUNTERS)
@@ -586,7 +586,7 @@ def run_ours(args, rank, world, local_rank):
             sb.close()
             return statistics.median(seal_t) * 1e6, statistics.median(open_t) * 1e6, ok
 
-        def small_pipelined(sn, nb, rounds=60):
+        def small_pipelined(sn, nb, rounds=max(1, args.small_rounds // 3)):
             """nb batches of sn packets in flight from this one host thread, each with its own peers."""
             bs = [setup_batch(ctx, sn, stride, 32, first_peer=64 * k) for k in range(nb)]
             for x in bs:
@@ -601,7 +601,7 @@ def run_ours(args, rank, world, local_rank):
                     x.open(sn, F_REPLAY, wait=False)
                 for x in bs:
                     x.wait()
-            for _ in range(10):
+            for _ in range(min(10, rounds)):
                 one_round()
             t0 = time.perf_counter()
             for _ in range(rounds):
@@ -671,6 +671,7 @@ def main():
     ap.add_argument("--no-filter", action="store_true")
     ap.add_argument("--no-pipeline", action="store_true")
     ap.add_argument("--no-small", action="store_true", help="skip the small-batch latency section (thousands of launches)")
+    ap.add_argument("--small-rounds", type=int, default=200, help="timed rounds of the small-batch section (few, for profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the host-ring leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and args.packets == N_PACKETS else args.warmup

@@ -1,5 +1,9 @@
-"""Generates the golden vectors under tests/golden/ from implementations that are independent of
-this repository: OpenSSL (through the `cryptography` package) and libsodium (through PyNaCl).
+"""Generates the golden vectors under tests/golden/.  The AEAD vectors and the sealed messages of
+configurations 1, 2 and 5 come from implementations that are independent of this repository: OpenSSL
+(through the `cryptography` package) and libsodium (through PyNaCl).  Configuration 3 (filter verdicts) and
+the segment bytes of configuration 5 have no independent implementation in this container: their digests are
+taken from the CPU checker under oracle/ (itself pinned to the reference's own test cases) and serve as a
+regression pin for checker and generator together.
 
 Run from the repository root:  python tests/golden/make_golden.py
 The output is committed; the tests only read it.  Inputs come from the seeded generators in
@@ -39,6 +43,52 @@ def padded(n: int, mtu: int) -> int:
     return n + (p - last)
 
 
+SEC = 1_000_000_000
+
+
+def filter_and_gso_digests():
+    import numpy as np
+
+    from oracle import oracle as O
+
+    out = {}
+    # (d) configuration 3 at a size the scalar checker walks in a second: digests of the generated tables and
+    # headers, and of the checker's verdicts at t0 + 1 s, of the late replies at t0 + 10 min and again at t0 + 2 s
+    w = gen.config3(500, 2000, 6000, 20000)
+    f = O.Filter()
+    f.set_rules_arrays(w.rules.astype(O.RULE_DTYPE), w.srcs.astype(O.PREFIX_DTYPE), w.ports.astype(O.PORT_DTYPE))
+    f.note_batch(np.ascontiguousarray(w.outbound), 28, w.outbound_len, w.t0_ns)
+    v1 = f.check_batch(np.ascontiguousarray(w.inbound), 28, np.ascontiguousarray(w.inbound_len), w.t0_ns + SEC)
+    v2 = f.check_batch(np.ascontiguousarray(w.late), 28, w.late_len, w.t0_ns + 600 * SEC)
+    v3 = f.check_batch(np.ascontiguousarray(w.late), 28, w.late_len, w.t0_ns + 2 * SEC)
+    sha = lambda *arrays: hashlib.sha256(b"".join(np.ascontiguousarray(a).tobytes() for a in arrays)).hexdigest()
+    out["config3"] = {"sizes": [500, 2000, 6000, 20000],
+                      "tables_sha256": sha(w.rules, w.srcs, w.ports),
+                      "headers_sha256": sha(w.outbound, w.outbound_len, w.inbound, w.inbound_len, w.late, w.late_len),
+                      "verdicts_sha256": sha(v1.astype(np.uint8), v2.astype(np.uint8), v3.astype(np.uint8)),
+                      "allowed": [int(v1.sum()), int(v2.sum()), int(v3.sum())], "flows": int(f.flow_count),
+                      "source": "oracle/ (CPU checker)"}
+    # (e) configuration 5, eight super-packets: the checker's segments, each then sealed by the library AEAD with
+    # the peer's key and consecutive counters per peer in batch order
+    w5 = gen.config5(n_super=8)
+    segs, msgs, nxt = [], [], {}
+    for j, sp in enumerate(w5.supers):
+        parts = O.gso_split(sp, w5.hdr_len, w5.mss, w5.csum_start, w5.csum_offset, 6)
+        assert parts is not None and len(parts) == 47
+        p = int(w5.peer[j])
+        for seg in parts:
+            c = nxt.get(p, 0)
+            nxt[p] = c + 1
+            segs.append(seg)
+            msgs.append(wg_message(w5.keys[p].tobytes(), p + 1, c, seg, padded(len(seg), 1420)))
+    out["config5"] = {"n_super": 8, "supers_sha256": hashlib.sha256(b"".join(w5.supers)).hexdigest(),
+                      "segments_sha256": hashlib.sha256(b"".join(segs)).hexdigest(),
+                      "sealed_sha256": hashlib.sha256(b"".join(msgs)).hexdigest(),
+                      "peers": [int(x) for x in w5.peer],
+                      "source": "segments: oracle/ (CPU checker); sealing: cryptography + PyNaCl; remote index = peer + 1"}
+    return out
+
+
 def main():
     out = {"source": "cryptography (OpenSSL) cross-checked with PyNaCl (libsodium)", "aead": [], "config1": {},
            "config2": {}}
@@ -66,6 +116,7 @@ def main():
     out["config2"] = {"sha256": hashlib.sha256(b"".join(msgs2)).hexdigest(), "n_base": len(msgs2),
                       "n_arrivals": int(len(w2.arrival)),
                       "arrival_sha256": hashlib.sha256(w2.arrival.astype("<i8").tobytes()).hexdigest()}
+    out.update(filter_and_gso_digests())
     with open(os.path.join(HERE, "aead_golden.json"), "w") as f:
         json.dump(out, f, indent=1)
     print("wrote aead_golden.json:", len(out["aead"]), "vectors")
