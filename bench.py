@@ -612,16 +612,34 @@ def run_ours(args, rank, world, local_rank):
                 x.close()
             return 2.0 * sn * nb * rounds * SIZE * 8 / dt / 1e9, ok
 
+        def threaded(threads, packets, rounds):
+            """bnk_b200/host/apps/mt_stress: host threads with two batches in flight each, one context, through the
+            C ABI; it checks statuses, plaintext and replay verdicts itself.  -> Gbit/s or None"""
+            import re
+            import subprocess
+            from bnk_b200 import _build
+            exe = os.path.join(_build.HOST, "apps", "mt_stress")
+            if not os.path.exists(exe):
+                return None
+            res = subprocess.run([exe, str(threads), str(rounds), str(packets), str(SIZE), "2"], capture_output=True,
+                                 text=True, timeout=300)
+            m = re.search(r"gbps=([0-9.]+)", res.stdout)
+            return float(m.group(1)) if res.returncode == 0 and res.stdout.startswith("OK") and m else None
+
         s128, o128, ok128 = small_latency(128)
         pipe_gbps, pipe_ok = small_pipelined(128, 16)
         s16, o16, ok16 = small_latency(16)
         small = {"packets": 128, "payload_bytes": SIZE, "seal_us": s128, "open_us": o128,
                  "seal_us_16_packets": s16, "open_us_16_packets": o16, "verified": ok128 and ok16 and pipe_ok,
                  "gbps_16_batches_in_flight": pipe_gbps,
+                 "gbps_8_threads_128_packets": threaded(8, 128, max(20, args.small_rounds)),
+                 "gbps_8_threads_1024_packets": threaded(8, 1024, max(10, args.small_rounds // 2)),
                  "note": "host wall clock per submit+wait; seal = group+counters launch, seal launch; open = open "
                          "launch, group+replay launch; 128 x 1420 B goes through the copy engines, 16 x 1420 B (under "
                          "128 KiB) runs on the pinned host arrays without copies; gbps_16_batches_in_flight: sixteen "
-                         "128-packet batches submitted round-robin by this one Python thread, seal then open"}
+                         "128-packet batches submitted round-robin by this one Python thread, seal then open; "
+                         "gbps_8_threads_*: eight C++ host threads, two batches in flight each, same context "
+                         "(bnk_b200/host/apps/mt_stress.cpp)"}
 
     sampler.stop()
     clocks = sampler.summary(windows)

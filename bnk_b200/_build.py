@@ -65,22 +65,31 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
-def build_host_test(force: bool = False) -> str:
-    """Compiles tests/cpp/host_test.cpp (the reference's Go tests restated in C++) against libbnkgpu.so."""
-    root = os.path.dirname(PKG_DIR)
-    src = os.path.join(root, "tests", "cpp", "host_test.cpp")
-    exe = os.path.join(root, "tests", "cpp", "host_test")
+def _build_cpp(src: str, exe: str, force: bool) -> str:
     build()
-    deps = [src, LIB_PATH, os.path.join(HOST, "bnk_host.hpp")]
+    deps = [src, LIB_PATH, os.path.join(HOST, "bnk_host.hpp"), os.path.join(os.path.dirname(PKG_DIR), "include", "bnk_gpu.h")]
     if not force and os.path.exists(exe) and all(os.path.getmtime(d) <= os.path.getmtime(exe) for d in deps):
         return exe
     cxx = shutil.which("g++") or "g++"
-    cmd = [cxx, "-O2", "-std=c++17", "-Wall", "-o", exe, src, "-L" + PKG_DIR, "-lbnkgpu",
-           "-Wl,-rpath," + PKG_DIR, "-Wl,-rpath,$ORIGIN/../../bnk_b200"]
+    rel = os.path.relpath(PKG_DIR, os.path.dirname(exe))
+    cmd = [cxx, "-O2", "-std=c++17", "-Wall", "-pthread", "-o", exe, src, "-L" + PKG_DIR, "-lbnkgpu",
+           "-Wl,-rpath," + PKG_DIR, "-Wl,-rpath,$ORIGIN/" + rel]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
     return exe
+
+
+def build_host_test(force: bool = False) -> str:
+    """Compiles tests/cpp/host_test.cpp (the reference's Go tests restated in C++) against libbnkgpu.so."""
+    root = os.path.dirname(PKG_DIR)
+    return _build_cpp(os.path.join(root, "tests", "cpp", "host_test.cpp"), os.path.join(root, "tests", "cpp", "host_test"), force)
+
+
+def build_mt_stress(force: bool = False) -> str:
+    """Compiles bnk_b200/host/apps/mt_stress.cpp: several host threads driving one context through the C ABI, with
+    its own checks; used by the tests and by the benchmark's small-batch section."""
+    return _build_cpp(os.path.join(HOST, "apps", "mt_stress.cpp"), os.path.join(HOST, "apps", "mt_stress"), force)
 
 
 if __name__ == "__main__":

@@ -473,14 +473,12 @@ int bnk_batch_destroy(bnk_batch *b) {
     if (!b) return BNK_EINVAL;
     cudaSetDevice(b->ctx->device);
     if (b->stream) cudaStreamSynchronize(b->stream);
-    cudaFreeHost(b->host.ring);
     cudaFreeHost(b->host.src_addr);
     cudaFreeHost(b->h_desc);
     cudaFree(b->d_desc);
     cudaFreeHost(b->h_flow_error);
     cudaFreeHost(b->h_gso);
     DeviceBatch &d = b->dev;
-    cudaFree(d.ring);
     cudaFree(d.src_addr);
     cudaFree(d.order);
     cudaFree(d.order_tmp);
@@ -530,12 +528,16 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
         if (e == cudaSuccess) e = cudaMalloc(p, bytes);
         if (e == cudaSuccess) e = cudaMemset(*p, 0, bytes);
     };
-    H((void **)&b->host.ring, ring_bytes);
-    // descriptor arrays share one slab per side so that a small batch moves them with one copy each way
+    // One slab per side: the descriptor arrays, then the ring.  A batch whose descriptor slab is small moves
+    // descriptors and ring with one copy each way (joint_copy); otherwise the descriptor fields a call needs
+    // move as one run or field by field (desc_copy).
     b->npad = (max_pkts + 15u) & ~15u;
     const size_t np = b->npad;
-    H((void **)&b->h_desc, 25 * np);
+    b->desc_room = (25 * np + 255) & ~(size_t)255;
+    b->joint_copy = b->desc_room <= 64u * 1024;
+    H((void **)&b->h_desc, b->desc_room + ring_bytes);
     if (e == cudaSuccess) {
+        b->host.ring = b->h_desc + b->desc_room;
         b->host.off = reinterpret_cast<uint32_t *>(b->h_desc);
         b->host.len = reinterpret_cast<uint32_t *>(b->h_desc + 4 * np);
         b->host.slot = reinterpret_cast<uint32_t *>(b->h_desc + 8 * np);
@@ -549,9 +551,9 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     b->host.ring_bytes = ring_bytes;
     b->host.max_pkts = max_pkts;
     DeviceBatch &d = b->dev;
-    D((void **)&d.ring, ring_bytes);
-    D((void **)&b->d_desc, 25 * np);
+    D((void **)&b->d_desc, b->desc_room + ring_bytes);
     if (e == cudaSuccess) {
+        d.ring = b->d_desc + b->desc_room;
         d.off = reinterpret_cast<uint32_t *>(b->d_desc);
         d.len = reinterpret_cast<uint32_t *>(b->d_desc + 4 * np);
         d.slot = reinterpret_cast<uint32_t *>(b->d_desc + 8 * np);
@@ -644,8 +646,12 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     const bool direct = host_direct(b, npkts, flags, ext);
     HostAlias alias(b, direct);
     if (!direct && (!(flags & BNK_F_NO_H2D) || refresh) && n) {
-        CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        CK(ctx, desc_copy(b, n, D_OFF, refresh ? D_STATUS : (flags & BNK_F_ASSIGN_COUNTERS) ? D_SLOT : D_COUNTER, true, s));
+        if (b->joint_copy) {
+            CK(ctx, cudaMemcpyAsync(b->d_desc, b->h_desc, b->desc_room + ext, cudaMemcpyHostToDevice, s));
+        } else {
+            CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
+            CK(ctx, desc_copy(b, n, D_OFF, refresh ? D_STATUS : (flags & BNK_F_ASSIGN_COUNTERS) ? D_SLOT : D_COUNTER, true, s));
+        }
         b->dev_stale = false;
     }
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
@@ -666,8 +672,12 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     b->kernel_timed = timed;
     b->aead_timed = timed;
     if (!direct && !(flags & BNK_F_NO_D2H) && n) {
-        CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
-        CK(ctx, desc_copy(b, n, D_COUNTER, D_STATUS, false, s));
+        if (b->joint_copy) {
+            CK(ctx, cudaMemcpyAsync(b->h_desc, b->d_desc, b->desc_room + ext, cudaMemcpyDeviceToHost, s));
+        } else {
+            CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
+            CK(ctx, desc_copy(b, n, D_COUNTER, D_STATUS, false, s));
+        }
     }
     return BNK_SUCCESS;
 }
@@ -685,9 +695,15 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     const uint64_t ext = (device_only && !refresh) ? 0 : ring_extent(b, npkts, (flags & BNK_F_USE_OUT_LEN) ? 48 : 0);
     const bool direct = host_direct(b, npkts, flags, ext);
     HostAlias alias(b, direct);
+    // (a joint upload carries out_len from the host as well: BNK_F_USE_OUT_LEN together with an upload means
+    // the host array, which the seal that wrote the ring also wrote)
     if (!direct && (!(flags & BNK_F_NO_H2D) || refresh) && n) {
-        CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        CK(ctx, desc_copy(b, n, D_OFF, refresh ? D_STATUS : (flags & BNK_F_DEMUX_INDEX) ? D_LEN : D_SLOT, true, s));
+        if (b->joint_copy && !((flags & BNK_F_USE_OUT_LEN) && !refresh)) {
+            CK(ctx, cudaMemcpyAsync(b->d_desc, b->h_desc, b->desc_room + ext, cudaMemcpyHostToDevice, s));
+        } else {
+            CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
+            CK(ctx, desc_copy(b, n, D_OFF, refresh ? D_STATUS : (flags & BNK_F_DEMUX_INDEX) ? D_LEN : D_SLOT, true, s));
+        }
         b->dev_stale = false;
     }
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
@@ -723,8 +739,12 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
     if (!direct && !(flags & BNK_F_NO_D2H) && n) {
-        CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
-        CK(ctx, desc_copy(b, n, (flags & BNK_F_DEMUX_INDEX) ? D_SLOT : D_COUNTER, D_STATUS, false, s));
+        if (b->joint_copy) {
+            CK(ctx, cudaMemcpyAsync(b->h_desc, b->d_desc, b->desc_room + ext, cudaMemcpyDeviceToHost, s));
+        } else {
+            CK(ctx, cudaMemcpyAsync(b->host.ring, b->dev.ring, ext, cudaMemcpyDeviceToHost, s));
+            CK(ctx, desc_copy(b, n, (flags & BNK_F_DEMUX_INDEX) ? D_SLOT : D_COUNTER, D_STATUS, false, s));
+        }
     }
     return BNK_SUCCESS;
 }

@@ -114,8 +114,10 @@ struct bnk_batch {
     bool kernel_timed;
     bool aead_timed;
     bnk_gso_super *h_gso; // pinned staging for the super-packet descriptors
-    uint8_t *h_desc, *d_desc; // descriptor slabs: off | len | slot | counter | out_len | status, each npad entries
+    uint8_t *h_desc, *d_desc; // one slab per side: off | len | slot | counter | out_len | status (npad entries each), then the ring
     uint32_t npad;
+    size_t desc_room;  // bytes of the descriptor slab in front of the ring (same on both sides)
+    bool joint_copy;   // descriptors and ring move as one copy
     int *h_flow_error; // pinned copy of the flow-table overflow flag, refreshed by filter work
 };
 
