@@ -695,8 +695,8 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     const uint64_t ext = (device_only && !refresh) ? 0 : ring_extent(b, npkts, (flags & BNK_F_USE_OUT_LEN) ? 48 : 0);
     const bool direct = host_direct(b, npkts, flags, ext);
     HostAlias alias(b, direct);
-    // (a joint upload carries out_len from the host as well: BNK_F_USE_OUT_LEN together with an upload means
-    // the host array, which the seal that wrote the ring also wrote)
+    // BNK_F_USE_OUT_LEN reads the lengths a seal left on the device: an upload beside it must not bring the
+    // host's out_len along, so it moves the fields one by one instead of the whole slab.
     if (!direct && (!(flags & BNK_F_NO_H2D) || refresh) && n) {
         if (b->joint_copy && !((flags & BNK_F_USE_OUT_LEN) && !refresh)) {
             CK(ctx, cudaMemcpyAsync(b->d_desc, b->h_desc, b->desc_room + ext, cudaMemcpyHostToDevice, s));
