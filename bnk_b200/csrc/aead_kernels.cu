@@ -44,10 +44,12 @@ __device__ __forceinline__ uint32_t rotl8(uint32_t x) { return __byte_perm(x, 0,
 __device__ __forceinline__ uint32_t rotl12(uint32_t x) { return __funnelshift_l(x, x, 12); }
 __device__ __forceinline__ uint32_t rotl7(uint32_t x) { return __funnelshift_l(x, x, 7); }
 
-// 12 instructions; the four rotations issue at half rate on sm_100 (byte permute and funnel shift
-// both measure 64 lanes/clk/SM), which makes a quarter round cost ~17 issue cycles per warp.
-// Issuing the additions as multiply-adds on the FMA pipe was measured and does not help: the
-// issue slots, not the ALU pipe, are what runs out.
+// 12 instructions.  Exclusive-or, funnel shift and byte permute run on the ALU pipe only, at 64 lanes/clk/SM
+// (two cycles per warp instruction per scheduler): 8 of them make a quarter round cost 16-17 cycles per warp,
+// with the four additions riding along on the FMA pipe (the compiler already issues them there, so writing
+// them as multiply-adds changes nothing).  The profiler agrees: issue slots 66 % busy, ALU pipe 75 %, top stall
+// "math pipe throttle".  Moving a rotation to the multiplier (x * 2^n as a 64-bit product, low + high word) was
+// measured too: each of the four rotations moved costs 9 % more time, the wide multiply being slower still.
 #define BNK_QR(a, b, c, d) \
     a += b;                \
     d = rotl16(d ^ a);     \
@@ -312,6 +314,9 @@ __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const Aead
         poly_init(poly, 0, 0, 0, 0);
     }
 
+    // (Splitting off a branch-free loop over the whole blocks so that the Poly1305 multiplies can be scheduled
+    // into the ChaCha20 rounds of the same thread, with the seal side absorbing the previous block's ciphertext,
+    // was measured: no gain for seal, 10 % slower for open.  The warps of an SM already overlap the two phases.)
     for (uint32_t b = 0; b < nblk; b++) {
         const uint32_t base = b * 64u;
         uint32_t d[16];
