@@ -659,9 +659,19 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         CK(ctx, launch_filter_note(b, npkts, now_unix_ns, s));
         CK(ctx, cudaMemcpyAsync(b->h_flow_error, ctx->ft.flow_error, sizeof(int), cudaMemcpyDeviceToHost, s));
     }
-    if (flags & BNK_F_ASSIGN_COUNTERS) CK(ctx, launch_assign_counters(b, npkts, s));
     const uint32_t *order = nullptr;
-    if (flags & BNK_F_SORT_BY_LENGTH) {
+    const bool side_order = (flags & BNK_F_SORT_BY_LENGTH) && (flags & BNK_F_ASSIGN_COUNTERS) && npkts > 4096;
+    if (side_order) { // the length classes need only len[]: they are built beside the grouping for the counters
+        CK(ctx, cudaEventRecord(b->ev_fork, s));
+        CK(ctx, cudaStreamWaitEvent(b->aux_stream, b->ev_fork, 0));
+        CK(ctx, launch_length_order(b, npkts, b->dev.len, false, b->aux_stream));
+        CK(ctx, cudaEventRecord(b->ev_join, b->aux_stream));
+        order = b->dev.len_order;
+    }
+    if (flags & BNK_F_ASSIGN_COUNTERS) CK(ctx, launch_assign_counters(b, npkts, s));
+    if (side_order) {
+        CK(ctx, cudaStreamWaitEvent(s, b->ev_join, 0));
+    } else if (flags & BNK_F_SORT_BY_LENGTH) {
         CK(ctx, launch_length_order(b, npkts, b->dev.len, false, s));
         order = b->dev.len_order;
     }
