@@ -19,7 +19,10 @@ constexpr uint32_t kSortWarps = kSortThreads / 32;
 constexpr uint32_t kMaxTiles = 32;     // a lane keeps up to 32 keys in registers
 constexpr uint32_t kMaxDigitBits = 9;
 constexpr uint32_t kMaxBins = 1u << kMaxDigitBits;
-constexpr uint32_t kBatchMaxChunks = 320; // ~2 CTAs per SM: enough to fill the GPU, few enough to scan quickly
+#ifndef BNK_SORT_MAX_CHUNKS
+#define BNK_SORT_MAX_CHUNKS 320
+#endif
+constexpr uint32_t kBatchMaxChunks = BNK_SORT_MAX_CHUNKS; // ~2 CTAs per SM: enough to fill the GPU, few enough to scan quickly
 
 struct SortKeySrc {
     const uint32_t *slot;

@@ -75,6 +75,12 @@ void Context::Check(int rc) const {
     if (rc < 0) throw Error(rc, std::string(bnk_strerror(rc)) + ": " + bnk_last_error_string(ctx_));
 }
 
+uint64_t Context::LaunchCount() const {
+    uint64_t n = 0;
+    Check(bnk_kernel_launch_count(ctx_, &n));
+    return n;
+}
+
 Batch::Batch(Context &ctx, uint32_t max_pkts, uint32_t slot_bytes) : ctx_(ctx), slot_((slot_bytes + 15u) & ~15u) {
     ctx_.Check(bnk_batch_create(ctx_.raw(), max_pkts, (uint64_t)max_pkts * slot_, &b_));
     ctx_.Check(bnk_batch_view_get(b_, &v_));
@@ -198,8 +204,10 @@ std::unique_ptr<TunDevice> WrapTUN(TunDevice *inner, Filter *f, std::function<Ti
 }
 
 // ---- Device ----
-Device::Device(Context &ctx, TunDevice *tun, Bind *bind, uint32_t batch_pkts)
-    : ctx_(ctx), tun_(tun), bind_(bind), batch_(ctx, batch_pkts, 16 + ((ctx.mtu() ? ctx.mtu() : 1500) + 15) / 16 * 16 + 32) {}
+Device::Device(Context &ctx, TunDevice *tun, Bind *bind, uint32_t batch_pkts, uint32_t coalesce)
+    : ctx_(ctx), tun_(tun), bind_(bind),
+      batch_(ctx, batch_pkts * std::max(1u, coalesce), 16 + ((ctx.mtu() ? ctx.mtu() : 1500) + 15) / 16 * 16 + 32),
+      read_pkts_(batch_pkts), coalesce_(std::max(1u, coalesce)) {}
 
 void Device::SetPeer(uint32_t slot, const uint8_t send_key[32], const uint8_t recv_key[32], uint32_t remote_index,
                      uint32_t local_index, uint32_t allowed_ip) {
@@ -228,70 +236,82 @@ void Device::AttachFilter(Filter *f, std::function<TimeNs()> clock) {
 }
 
 int Device::PumpOutbound() {
-    const int cap = std::min<int>(batch_.capacity(), std::max(1, tun_->BatchSize()));
+    // One GPU submit per pump: up to `coalesce` reads of the TUN, as long as each comes back full, go into the
+    // same batch (packets of different reads are as independent as packets of one read; order is kept).
+    const int cap = std::min<int>(read_pkts_, std::max(1, tun_->BatchSize()));
     const size_t room = (size_t)kOffset + (ctx_.mtu() ? ctx_.mtu() : 1500) + 32;
-    std::vector<Packet> bufs(cap, Packet(room));
-    std::vector<int> sizes(cap, 0);
-    const int n = tun_->Read(bufs, sizes, kOffset);
+    if ((int)tx_bufs_.size() != cap) {
+        tx_bufs_.assign(cap, Packet(room));
+        tx_sizes_.assign(cap, 0);
+    }
     uint32_t m = 0;
     std::vector<uint32_t> peer_of;
-    for (int i = 0; i < n; i++) {
-        const uint8_t *p = bufs[i].data() + kOffset;
-        // outbound routing: destination address -> peer (allowed-IPs, one /32 per peer)
-        if (sizes[i] < 20 || (p[0] >> 4) != 4) {
-            stats_.no_route++;
-            continue;
+    for (uint32_t r = 0; r < coalesce_ && m + cap <= batch_.capacity(); r++) {
+        const int n = tun_->Read(tx_bufs_, tx_sizes_, kOffset);
+        for (int i = 0; i < n; i++) {
+            const uint8_t *p = tx_bufs_[i].data() + kOffset;
+            // outbound routing: destination address -> peer (allowed-IPs, one /32 per peer)
+            if (tx_sizes_[i] < 20 || (p[0] >> 4) != 4) {
+                stats_.no_route++;
+                continue;
+            }
+            const uint32_t dst = ((uint32_t)p[16] << 24) | ((uint32_t)p[17] << 16) | ((uint32_t)p[18] << 8) | p[19];
+            auto it = route_.find(dst);
+            if (it == route_.end()) {
+                stats_.no_route++;
+                continue;
+            }
+            batch_.Put(m++, p, (size_t)tx_sizes_[i], kOffset, it->second);
+            peer_of.push_back(it->second);
         }
-        const uint32_t dst = ((uint32_t)p[16] << 24) | ((uint32_t)p[17] << 16) | ((uint32_t)p[18] << 8) | p[19];
-        auto it = route_.find(dst);
-        if (it == route_.end()) {
-            stats_.no_route++;
-            continue;
-        }
-        batch_.Put(m++, p, (size_t)sizes[i], kOffset, it->second);
-        peer_of.push_back(it->second);
+        if (n < cap) break; // the TUN ran dry
     }
     if (m == 0) return 0;
     uint32_t flags = BNK_F_ASSIGN_COUNTERS;
     if (filter_) flags |= BNK_F_NOTE_OUTBOUND;
     ctx_.Check(bnk_seal_submit(batch_.raw(), m, flags, clock_()));
     batch_.Wait();
-    // per-peer sends, batch order kept inside each peer (bind.go:296, called once per peer by the device)
+    // per-peer sends, batch order kept inside each peer (bind.go:296, called once per peer by the device);
+    // peers in the order of their first packet
     int sent = 0;
-    std::vector<uint8_t> done(m, 0);
-    for (uint32_t i = 0; i < m; i++) {
-        if (done[i]) continue;
-        std::vector<Packet> out;
-        for (uint32_t j = i; j < m; j++) {
-            if (done[j] || peer_of[j] != peer_of[i]) continue;
-            done[j] = 1;
-            if (batch_.view().status[j] != BNK_PKT_OK) continue; // counter exhausted: dropped, a rekey is due
-            const uint8_t *msg = batch_.slot(j);
-            out.emplace_back(msg, msg + batch_.view().out_len[j]);
-            stats_.sealed++;
+    std::unordered_map<uint32_t, size_t> group_of;
+    std::vector<std::pair<uint32_t, std::vector<Packet>>> groups;
+    for (uint32_t j = 0; j < m; j++) {
+        if (batch_.view().status[j] != BNK_PKT_OK) continue; // counter exhausted: dropped, a rekey is due
+        auto it = group_of.find(peer_of[j]);
+        if (it == group_of.end()) {
+            it = group_of.emplace(peer_of[j], groups.size()).first;
+            groups.emplace_back(peer_of[j], std::vector<Packet>());
         }
-        if (!out.empty()) {
-            bind_->Send(out, Endpoint{peer_of[i]});
-            sent += (int)out.size();
-        }
+        const uint8_t *msg = batch_.slot(j);
+        groups[it->second].second.emplace_back(msg, msg + batch_.view().out_len[j]);
+        stats_.sealed++;
+    }
+    for (auto &g : groups) {
+        bind_->Send(g.second, Endpoint{g.first});
+        sent += (int)g.second.size();
     }
     return sent;
 }
 
 int Device::PumpInbound() {
-    const int cap = std::min<int>(batch_.capacity(), std::max(1, bind_->BatchSize()));
-    std::vector<Packet> packets(cap, Packet(batch_.slot_bytes()));
-    std::vector<int> sizes(cap, 0);
-    std::vector<Endpoint> eps(cap);
-    const int n = bind_->Receive(packets, sizes, eps);
-    if (n <= 0) return 0;
+    const int cap = std::min<int>(read_pkts_, std::max(1, bind_->BatchSize()));
+    if ((int)rx_bufs_.size() != cap) {
+        rx_bufs_.assign(cap, Packet(batch_.slot_bytes()));
+        rx_sizes_.assign(cap, 0);
+        rx_eps_.assign(cap, Endpoint{});
+    }
     uint32_t m = 0;
-    for (int i = 0; i < n; i++) {
-        if ((size_t)sizes[i] + 32 > batch_.slot_bytes()) {
-            stats_.malformed++;
-            continue;
+    for (uint32_t r = 0; r < coalesce_ && m + cap <= batch_.capacity(); r++) {
+        const int n = bind_->Receive(rx_bufs_, rx_sizes_, rx_eps_);
+        for (int i = 0; i < n; i++) {
+            if ((size_t)rx_sizes_[i] + 32 > batch_.slot_bytes()) {
+                stats_.malformed++;
+                continue;
+            }
+            batch_.Put(m++, rx_bufs_[i].data(), (size_t)rx_sizes_[i], 0, 0);
         }
-        batch_.Put(m++, packets[i].data(), (size_t)sizes[i], 0, 0);
+        if (n < cap) break; // nothing more pending
     }
     if (m == 0) return 0;
     uint32_t flags = BNK_F_DEMUX_INDEX | BNK_F_REPLAY | BNK_F_INNER_CHECK;

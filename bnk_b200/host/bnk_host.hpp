@@ -58,6 +58,7 @@ class Context {
     bnk_ctx *raw() const { return ctx_; }
     uint32_t mtu() const { return mtu_; }
     void Check(int rc) const; // throws bnk::Error with the library's message
+    uint64_t LaunchCount() const; // kernels launched through this context so far
 
   private:
     bnk_ctx *ctx_ = nullptr;
@@ -152,7 +153,9 @@ class Device {
   public:
     static constexpr int kOffset = 16; // transport header room kept in front of every TUN packet
 
-    Device(Context &ctx, TunDevice *tun, Bind *bind, uint32_t batch_pkts = 128);
+    // `coalesce`: how many full reads of the TUN (or receive calls of the Bind) one pump may put into a single
+    // GPU submit.  1 keeps the reference's batch size; the GPU pays off from about a thousand packets per submit.
+    Device(Context &ctx, TunDevice *tun, Bind *bind, uint32_t batch_pkts = 128, uint32_t coalesce = 1);
     // keypair slot `slot`; `local_index` is the receiver index peers put in messages for us, `remote_index` the one
     // we put in messages for them; `allowed_ip` the peer's tunnel address (one /32 per peer, engine.go:294)
     void SetPeer(uint32_t slot, const uint8_t send_key[32], const uint8_t recv_key[32], uint32_t remote_index,
@@ -174,6 +177,10 @@ class Device {
     TunDevice *tun_;
     Bind *bind_;
     Batch batch_;
+    uint32_t read_pkts_, coalesce_;
+    std::vector<Packet> tx_bufs_, rx_bufs_; // reused between pumps
+    std::vector<int> tx_sizes_, rx_sizes_;
+    std::vector<Endpoint> rx_eps_;
     Filter *filter_ = nullptr;
     std::function<TimeNs()> clock_ = Now;
     std::unordered_map<uint32_t, uint32_t> route_;    // allowed ip -> keypair slot

@@ -291,6 +291,50 @@ static void TestTwoDevicesRoundTrip(Context &) {
     CHECK(tunA.written.size() == 1 && tunA.written[0] == tcp(ipB, ipA, 7777, 41000, false), "only the reply reaches A's TUN");
 }
 
+// One pump, several reads: 40 packets for three peers wait in a TUN that hands out 4 per read; a device that may
+// coalesce 16 reads seals them in one submit, counters still run in TUN order per peer, and the receiving device
+// (which coalesces its receive calls the same way) writes them to its TUN in order.
+static void TestCoalescedPumps(Context &) {
+    Context ctxA(0, 16, 1420, 1u << 12), ctxB(0, 16, 1420, 1u << 12);
+    std::deque<Packet> a2b, b2a;
+    WireBind bindA, bindB;
+    bindA.tx = &a2b; bindA.rx = &b2a;
+    bindB.tx = &b2a; bindB.rx = &a2b;
+    FakeTUN tunA, tunB;
+    Device A(ctxA, &tunA, &bindA, 4, 16), B(ctxB, &tunB, &bindB, 4, 16);
+    const uint32_t ipA = ip(100, 64, 0, 1);
+    uint8_t key[3][32];
+    for (int p = 0; p < 3; p++) {
+        for (int i = 0; i < 32; i++) key[p][i] = (uint8_t)(p * 50 + i);
+        A.SetPeer(p, key[p], key[p], 0x500 + p, 0x600 + p, ip(100, 64, 1, 1 + p));
+        B.SetPeer(p, key[p], key[p], 0x600 + p, 0x500 + p, ipA); // B plays all three peers of A
+    }
+    std::vector<Packet> sent;
+    for (int i = 0; i < 40; i++) sent.push_back(udp(ipA, ip(100, 64, 1, 1 + i % 3), 1000 + i, 53));
+    for (const Packet &p : sent) tunA.pending.push_back(p);
+    const uint64_t before = ctxA.LaunchCount();
+    CHECK(A.PumpOutbound() == 40 && tunA.pending.empty(), "one pump takes all ten reads");
+    CHECK(ctxA.LaunchCount() - before <= 3, "and seals them with one submit");
+    CHECK(a2b.size() == 40, "forty datagrams on the wire");
+    // per peer, the counters follow the order the packets had in the TUN
+    bool ordered = true;
+    uint64_t next[3] = {0, 0, 0};
+    for (const Packet &m : a2b) {
+        uint32_t idx;
+        uint64_t c;
+        memcpy(&idx, m.data() + 4, 4);
+        memcpy(&c, m.data() + 8, 8);
+        ordered = ordered && idx >= 0x500 && idx < 0x503 && c == next[idx - 0x500]++;
+    }
+    CHECK(ordered && next[0] == 14 && next[1] == 13 && next[2] == 13, "consecutive counters per peer");
+    CHECK(B.PumpInbound() == 40 && a2b.empty(), "one pump opens all of them");
+    // Send groups by peer, so B sees peer 0's packets first, then peer 1's, then peer 2's
+    std::vector<Packet> want;
+    for (int p = 0; p < 3; p++)
+        for (int i = p; i < 40; i += 3) want.push_back(sent[i]);
+    CHECK(tunB.written == want, "every plaintext arrives, in send order per peer");
+}
+
 int main() {
     try {
         Context ctx(0, /*max_keypairs=*/16, /*mtu=*/1420, /*flow_capacity=*/1u << 12);
@@ -312,6 +356,7 @@ int main() {
         RUN(TestWrapTUNDropsDeniedInboundWrites)
         RUN(TestWrapTUNReadRecordsOutboundFlows)
         RUN(TestTwoDevicesRoundTrip)
+        RUN(TestCoalescedPumps)
     } catch (const Error &e) {
         printf("FAIL %s: exception %d %s\n", g_test, e.code, e.what());
         return 2;
