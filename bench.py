@@ -566,7 +566,7 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- one upstream-sized batch (128 packets, the reference's conn.IdealBatchSize): latency through the C ABI ----
     small = None
-    if rank == 0 and not args.no_e2e and not args.no_small:
+    if rank == 0 and not args.no_small:
         def small_latency(sn):
             sb = setup_batch(ctx, sn, stride, 32, first_peer=0)
             sb.ring[:] = 0x5A

@@ -423,9 +423,19 @@ __device__ __forceinline__ uint32_t replay_hash(uint32_t slot, uint64_t c) {
 }
 // table[h] = lowest grouped position that holds the key (peer, counter); the key of an entry is read through
 // the position it holds and never changes, so a probe may compare against whatever position it sees.
-__device__ __forceinline__ void replay_hash_insert(const ReplayArgs &a, uint32_t p) {
-    const uint32_t slot = a.keys[p];
-    const uint64_t c = a.sorted_counter[p];
+// Warp-wide (32 consecutive positions, `active` per lane): of the lanes that hold the same key only the lowest,
+// which has the lowest position, goes to the table, so a burst of copies of one packet costs one atomic per
+// warp instead of one per copy.
+__device__ __forceinline__ void replay_hash_insert_warp(const ReplayArgs &a, uint32_t p, bool active) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t slot = active ? a.keys[p] : 0u;
+    const uint64_t c = active ? a.sorted_counter[p] : 0ull;
+    const unsigned long long tag = active ? (c * 0x9E3779B97F4A7C15ull + slot) : ~0ull - lane;
+    const uint32_t same_tag = __match_any_sync(0xffffffffu, tag);
+    const uint32_t first = __ffs(same_tag) - 1;
+    const uint32_t first_slot = __shfl_sync(0xffffffffu, slot, first);
+    const uint64_t first_c = __shfl_sync(0xffffffffu, c, first);
+    if (!active || (lane != first && first_slot == slot && first_c == c)) return; // a lower lane carries this key
     uint32_t h = replay_hash(slot, c) & a.mask;
     for (uint32_t probes = 0; probes <= a.mask; ++probes, h = (h + 1) & a.mask) {
         uint32_t cur = *(volatile uint32_t *)&a.table[h];
@@ -564,7 +574,7 @@ __global__ void __launch_bounds__(256) replay_hash_clear_kernel(ReplayArgs a, co
 __global__ void __launch_bounds__(256) replay_hash_insert_kernel(ReplayArgs a, const uint32_t *pending_flag) {
     if (*pending_flag == 0u) return;
     const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
-    if (p < a.n && a.state[p] != RP_NOPART) replay_hash_insert(a, p);
+    replay_hash_insert_warp(a, p, p < a.n && a.state[p] != RP_NOPART);
 }
 __global__ void __launch_bounds__(256) replay_finish_kernel(ReplayArgs a) {
     replay_finish_warp(a, blockIdx.x * blockDim.x + threadIdx.x);
@@ -588,8 +598,7 @@ __device__ __forceinline__ void replay_one_cta(const ReplayArgs &a, SegMax *part
     if (any_pending) {
         for (uint32_t i = tid; i <= a.mask; i += 256u) a.table[i] = kHashEmpty;
         __syncthreads();
-        for (uint32_t p = tid; p < a.n; p += 256u)
-            if (a.state[p] != RP_NOPART) replay_hash_insert(a, p);
+        for (uint32_t p = tid; p < kScanTile; p += 256u) replay_hash_insert_warp(a, p, p < a.n && a.state[p] != RP_NOPART);
     }
     __syncthreads(); // clears before marks, inserts before look-ups
     for (uint32_t p = tid; p < kScanTile; p += 256u) replay_finish_warp(a, p);

@@ -138,6 +138,45 @@ def test_replay_dominant_peer_large_batch(gpu_lib, oracle, blocks):
         c.close()
 
 
+def test_replay_burst_of_copies(gpu_lib, oracle):
+    """A captured packet sent over and over: 60 distinct counters of one peer, each repeated about 300 times in
+    shuffled order among other peers' traffic.  Only first occurrences may pass."""
+    from bnk_b200 import Context
+    from bnk_b200.device import F_REPLAY
+
+    rng = np.random.default_rng(4242)
+    n_peers, n, size, blocks = 7, 20_000, 16, 128
+    keys = rng.integers(0, 256, (n_peers, 32), dtype=np.uint8)
+    stride = 16 + size + 16
+    off = (np.arange(n, dtype=np.uint64) * stride).astype(np.uint32)
+    slots = np.where(rng.random(n) < 0.9, 3, rng.integers(0, n_peers, n)).astype(np.uint32)
+    counters = (1000 + rng.integers(0, 60, n)).astype(np.uint64)              # the copies
+    others = slots != 3
+    counters[others] = 5000 + np.arange(int(others.sum()), dtype=np.uint64)  # ordinary traffic of the rest
+    ring = np.zeros(n * stride + 64, np.uint8)
+    ring[: n * stride].reshape(n, stride)[:, 16:16 + size] = rng.integers(0, 256, (n, size), dtype=np.uint8)
+    st, out_len = oracle.wg_seal_batch(keys, np.ones(n_peers, np.uint32), 0, ring, off, np.full(n, size, np.uint32), slots, counters)
+    assert (st == oracle.OK).all()
+    c = Context(max_keypairs=n_peers, replay_ring_blocks=blocks, mtu=0, flow_capacity=0)
+    try:
+        c.set_keypairs(0, keys, keys, np.ones(n_peers, np.uint32))
+        b = c.batch(n, n * stride + 64)
+        b.ring[: len(ring)] = ring
+        b.off[:n], b.len[:n], b.slot[:n] = off, out_len, slots
+        _, ost, ctr, _ = H.oracle_open(oracle, keys, ring, off, out_len, slots)
+        want, state = H.oracle_replay(oracle, blocks, slots, ctr, ost)
+        b.open(n, F_REPLAY)
+        got = np.array(b.status[:n])
+        b.close()
+        assert np.array_equal(got, want), np.flatnonzero(got != want)[:8]
+        assert (want[slots == 3] == oracle.OK).sum() == 60
+        for s_, r in state.items():
+            last, ring_words = c.replay_export(s_)
+            assert last == r.last and np.array_equal(ring_words, r.ring()), s_
+    finally:
+        c.close()
+
+
 def test_replay_limit_and_state_import(gpu_lib, oracle):
     from bnk_b200 import Context
     from bnk_b200.device import F_REPLAY, PKT_KEEPALIVE, PKT_REPLAY
