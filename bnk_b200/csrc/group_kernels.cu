@@ -628,6 +628,25 @@ __global__ void __launch_bounds__(kSortThreads) group_small_kernel(SortKeySrc sr
     const uint32_t bins = 1u << digit_bits;
     const uint32_t begin = warp * (32 * TILES);
     const uint32_t lt = (1u << lane) - 1u;
+    if (n <= kSortThreads) {
+        // One packet per thread at most (the upstream batch is 128): the place of a packet is the number of
+        // packets with a lower key, or the same key and a lower index.  n broadcast reads from shared memory
+        // instead of two radix passes with five barriers each.
+        const uint32_t mine = tid < n ? slot_key(src, tid) : 0xffffffffu;
+        kbuf[0][tid] = mine;
+        __syncthreads();
+        uint32_t place = 0;
+        for (uint32_t j = 0; j < n; j++) {
+            const uint32_t other = kbuf[0][j];
+            place += (other < mine || (other == mine && j < tid)) ? 1u : 0u;
+        }
+        if (tid < n) {
+            keys_out[place] = mine;
+            vals_out[place] = tid;
+        }
+        __syncthreads();
+        passes = 0;
+    }
     for (uint32_t p = 0; p < passes; p++) {
         const uint32_t shift = p * digit_bits;
         const uint32_t *kin = kbuf[p & 1], *vin = vbuf[p & 1];

@@ -270,7 +270,7 @@ def test_send_counters_assigned_in_batch_order(gpu_lib, oracle):
         c.close()
 
 
-@pytest.mark.parametrize("n", [1, 2, 31, 33, 257, 1000, 1024, 1025])
+@pytest.mark.parametrize("n", [1, 2, 31, 33, 128, 255, 256, 257, 1000, 1024, 1025])
 def test_send_counters_small_batches(gpu_lib, n):
     """Batches of up to 1024 packets group by keypair in a single launch; the nonces must come out the same way."""
     from bnk_b200 import Context
