@@ -64,15 +64,13 @@ int begin_submit(bnk_batch *b, uint32_t npkts, bool touches_host = true) {
     return BNK_SUCCESS;
 }
 
-// Closes a submit on every path out of it: whatever was queued before an error is still covered by the
-// batch's completion event, so a later bnk_wait really waits for it before the host touches the ring.
+// Closes a submit on every path out of it: whatever was queued before an error is still on the batch's stream,
+// so a later bnk_wait really waits for it before the host touches the ring.  (Completion is that of the stream:
+// work on the side stream is always joined back before a submit returns, and no event is recorded per submit.)
 struct SubmitScope {
     bnk_batch *b;
     explicit SubmitScope(bnk_batch *batch) : b(batch) {}
-    ~SubmitScope() {
-        cudaEventRecord(b->done, b->stream);
-        b->in_flight = true;
-    }
+    ~SubmitScope() { b->in_flight = true; }
 };
 
 // Small batches skip the copy engines: the kernels read the caller's pinned ring and descriptors through the
@@ -493,7 +491,6 @@ int bnk_batch_destroy(bnk_batch *b) {
     cudaFree(d.len_order);
     cudaFree(d.counters32);
     cudaFree(d.gso);
-    if (b->done) cudaEventDestroy(b->done);
     if (b->k_begin) cudaEventDestroy(b->k_begin);
     if (b->k_end) cudaEventDestroy(b->k_end);
     if (b->a_begin) cudaEventDestroy(b->a_begin);
@@ -579,7 +576,6 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->aux_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_join, cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->done, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreate(&b->k_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&b->k_end);
     if (e == cudaSuccess) e = cudaEventCreate(&b->t_end);
@@ -894,13 +890,13 @@ int bnk_wait(bnk_batch *b, uint64_t timeout_ns) {
     bnk_ctx *ctx = b->ctx;
     CK(ctx, cudaSetDevice(ctx->device));
     if (timeout_ns == UINT64_MAX) {
-        CK(ctx, cudaEventSynchronize(b->done));
+        CK(ctx, cudaStreamSynchronize(b->stream));
     } else {
         const auto deadline = std::chrono::steady_clock::now() + std::chrono::nanoseconds(timeout_ns);
         for (;;) {
-            cudaError_t e = cudaEventQuery(b->done);
+            cudaError_t e = cudaStreamQuery(b->stream);
             if (e == cudaSuccess) break;
-            if (e != cudaErrorNotReady) return fail(ctx, BNK_ECUDA, "cudaEventQuery", e);
+            if (e != cudaErrorNotReady) return fail(ctx, BNK_ECUDA, "cudaStreamQuery", e);
             if (std::chrono::steady_clock::now() >= deadline) return BNK_ETIMEDOUT;
             std::this_thread::yield();
         }

@@ -108,7 +108,7 @@ struct bnk_batch {
     cudaStream_t stream;
     cudaStream_t aux_stream;   // grouping work that can run beside the open kernel
     cudaEvent_t ev_fork, ev_join;
-    cudaEvent_t done, k_begin, k_end, t_end, a_begin, a_end;
+    cudaEvent_t k_begin, k_end, t_end, a_begin, a_end;
     bool in_flight;
     bool dev_stale; // a submit ran on the host arrays: the device copies of ring and descriptors are behind
     bool kernel_timed;
