@@ -88,6 +88,8 @@ __device__ __forceinline__ unsigned long long flow_key(uint32_t remote, uint16_t
 }
 
 // any allowance matches?  acl.go:149-172 over the indexed table
+// (Fetching the first slot of four prefix lengths before looking at any of them, to overlap the round trips, was
+// measured: 10 % slower on configuration 3, where nearly half the packets match at one of the first lengths.)
 __device__ __forceinline__ bool rules_allow(const FilterTables &ft, const Parsed &p) {
     if (ft.rule_slots == 0) return false;
     uint64_t lens = ft.len_mask;
