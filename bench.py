@@ -626,10 +626,15 @@ def run_ours(args, rank, world, local_rank):
             exe = os.path.join(_build.HOST, "apps", "mt_stress")
             if not os.path.exists(exe):
                 return None
-            res = subprocess.run([exe, str(threads), str(rounds), str(packets), str(SIZE), "2"], capture_output=True,
-                                 text=True, timeout=300)
-            m = re.search(r"gbps=([0-9.]+)", res.stdout)
-            return float(m.group(1)) if res.returncode == 0 and res.stdout.startswith("OK") and m else None
+            rates = []
+            for _ in range(5):  # the rate is bimodal on shared hosts (some runs are several times slower): median of five
+                res = subprocess.run([exe, str(threads), str(rounds), str(packets), str(SIZE), "2"], capture_output=True,
+                                     text=True, timeout=300)
+                m = re.search(r"gbps=([0-9.]+)", res.stdout)
+                if res.returncode != 0 or not res.stdout.startswith("OK") or not m:
+                    return None
+                rates.append(float(m.group(1)))
+            return statistics.median(rates)
 
         s128, o128, ok128 = small_latency(128)
         pipe_gbps, pipe_ok = small_pipelined(128, 16)
@@ -644,7 +649,7 @@ def run_ours(args, rank, world, local_rank):
                          "128 KiB) runs on the pinned host arrays without copies; gbps_16_batches_in_flight: sixteen "
                          "128-packet batches submitted round-robin by this one Python thread, seal then open; "
                          "gbps_8_threads_*: eight C++ host threads, two batches in flight each, same context "
-                         "(bnk_b200/host/apps/mt_stress.cpp)"}
+                         "(bnk_b200/host/apps/mt_stress.cpp), median of five runs"}
 
     sampler.stop()
     clocks = sampler.summary(windows)
