@@ -525,6 +525,8 @@ constexpr uint32_t kWppFull = 30;
 
 template <bool OPEN>
 __global__ void __launch_bounds__(128) aead_wpp_kernel(const AeadArgs a) {
+    let_next_kernel_start();    // open side: the grouping + replay launch behind may take its place already
+    wait_for_kernel_in_front(); // seal side: the counters come from the grouping launch in front
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (idx >= a.n) return; // a whole warp at a time
@@ -686,7 +688,8 @@ cudaError_t launch_aead(const AeadArgs &a, cudaStream_t s, bnk_ctx *ctx) {
     const bool wpp = ctx->aead_mode == 2 || (ctx->aead_mode == 0 && a.n <= BNK_WPP_MAX_PACKETS);
     if (wpp) {
         const uint32_t ctas = (a.n + 3) / 4; // 4 warps = 4 packets per CTA
-        aead_wpp_kernel<OPEN><<<ctas, 128, 0, s>>>(a);
+        cudaError_t e = launch_after_kernel(aead_wpp_kernel<OPEN>, dim3(ctas), dim3(128), s, a);
+        if (e != cudaSuccess) return e;
     } else {
         // one CTA per 128 packets; the hardware hands CTAs to SMs as slots free up, which measured faster
         // than persistent warps with an even static share of the packets

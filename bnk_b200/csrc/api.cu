@@ -214,6 +214,7 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     ctx->host_direct_bytes = 128u << 10;
     if (const char *m = getenv("BNK_HOST_DIRECT_BYTES")) // largest ring extent served without copies; 0 = never
         ctx->host_direct_bytes = strtoull(m, nullptr, 0);
+    if (!prop.unifiedAddressing || !prop.canMapHostMemory) ctx->host_direct_bytes = 0; // pinned memory must have one address
     ctx->kt = KeypairTables{};
     ctx->ft = FilterTables{};
     const size_t k = cfg->max_keypairs;

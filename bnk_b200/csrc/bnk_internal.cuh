@@ -121,6 +121,29 @@ struct bnk_batch {
     int *h_flow_error; // pinned copy of the flow-table overflow flag, refreshed by filter work
 };
 
+// Small batches are two dependent launches with little work in each, so the gap between them counts.  A kernel
+// launched through launch_after_kernel may be scheduled while the kernel in front of it on the stream is still
+// running (programmatic dependent launch) and must call wait_for_kernel_in_front() before it touches anything
+// that kernel writes: the wait ends when that kernel has finished and its writes are visible.  The kernel in front
+// calls let_next_kernel_start() first thing, which allows the next one to be placed on the SMs (where it sits in
+// its wait) as soon as all of this kernel's CTAs are resident; that hides the launch latency of the second kernel
+// behind the first.  Launched the ordinary way, or with nothing of the kind behind it, both calls do nothing.
+__device__ __forceinline__ void wait_for_kernel_in_front() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;"); }
+template <typename... KArgs, typename... Args>
+cudaError_t launch_after_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---------------------------------------------------------------------------
 // Kernel launchers (each defined next to its kernels).  All are asynchronous on
 // `s` and return the cudaError_t of the launch.

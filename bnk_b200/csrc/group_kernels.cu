@@ -619,6 +619,8 @@ struct SmallCounters {
 __global__ void __launch_bounds__(kSortThreads) group_small_kernel(SortKeySrc src, uint32_t n, uint32_t passes,
                                                                    uint32_t digit_bits, uint32_t *keys_out,
                                                                    uint32_t *vals_out, SmallCounters sc, ReplayArgs rp) {
+    let_next_kernel_start();    // seal side: the seal launch behind may take its place already
+    wait_for_kernel_in_front(); // open side: statuses and counters come from the open launch in front
     constexpr uint32_t TILES = kSmallMax / kSortThreads; // 4
     __shared__ uint32_t kbuf[2][kSmallMax], vbuf[2][kSmallMax];
     __shared__ uint32_t cur[kSortWarps][kMaxBins];
@@ -848,7 +850,7 @@ void sort_pass(const SortKeySrc &src, const uint32_t *kin, const uint32_t *vin, 
 uint32_t group_sort(const SortKeySrc &src, uint32_t n, uint32_t max_chunks, const SortBuffers &sb, cudaStream_t s) {
     const SortPlan plan = plan_for(src.max_slots);
     if (n <= kSmallMax) {
-        group_small_kernel<<<1, kSortThreads, 0, s>>>(src, n, plan.passes, plan.digit_bits, sb.keys_b, sb.order,
+        launch_after_kernel(group_small_kernel, dim3(1), dim3(kSortThreads), s, src, n, plan.passes, plan.digit_bits, sb.keys_b, sb.order,
                                                       SmallCounters{nullptr, nullptr, 0}, ReplayArgs{});
         return 1;
     }
@@ -902,7 +904,7 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
         bnk_ctx *ctx = b->ctx;
         DeviceBatch &d = b->dev;
         const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
-        group_small_kernel<<<1, kSortThreads, 0, s>>>(SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n,
+        launch_after_kernel(group_small_kernel, dim3(1), dim3(kSortThreads), s, SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n,
                                                       plan.passes, plan.digit_bits, d.keys_tmp + b->max_pkts, d.order,
                                                       SmallCounters{ctx->kt.send_counter, d.counter, ctx->cfg.max_keypairs},
                                                       ReplayArgs{});
@@ -956,7 +958,7 @@ cudaError_t launch_group_and_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     bnk_ctx *ctx = b->ctx;
     DeviceBatch &d = b->dev;
     const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
-    group_small_kernel<<<1, kSortThreads, 0, s>>>(SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n, plan.passes,
+    launch_after_kernel(group_small_kernel, dim3(1), dim3(kSortThreads), s, SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n, plan.passes,
                                                   plan.digit_bits, d.keys_tmp + b->max_pkts, d.order,
                                                   SmallCounters{nullptr, nullptr, 0}, replay_args(b, n));
     ctx->launches += 1;
