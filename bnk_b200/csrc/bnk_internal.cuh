@@ -130,6 +130,10 @@ struct bnk_batch {
 // behind the first.  Launched the ordinary way, or with nothing of the kind behind it, both calls do nothing.
 __device__ __forceinline__ void wait_for_kernel_in_front() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;"); }
+// The chains of short kernels around a large batch (grouping, counters, replay window, length classes) are
+// launched the same way while they are short: measured on 96,256 packets both sides of the pipeline got 7 % faster,
+// on 1,048,576 packets 1 % slower, hence the limit.
+constexpr uint32_t kDependentLaunchUpTo = 1u << 18;
 template <typename... KArgs, typename... Args>
 cudaError_t launch_after_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -141,6 +145,16 @@ cudaError_t launch_after_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+// the same launch with the ordinary full dependency when `dependent` is false
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
+    if (dependent) return launch_after_kernel(kernel, grid, block, s, args...);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = s;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

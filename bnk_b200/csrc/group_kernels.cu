@@ -57,6 +57,8 @@ template <uint32_t TILES>
 __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(SortKeySrc src, const uint32_t *keys_in,
                                                                   uint32_t n, uint32_t shift, uint32_t bins,
                                                                   uint32_t chunks, uint32_t *hist) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     __shared__ uint32_t cnt[kMaxBins];
     const uint32_t tid = threadIdx.x, chunk = blockIdx.x;
     for (uint32_t d = tid; d < bins; d += kSortThreads) cnt[d] = 0;
@@ -80,6 +82,8 @@ __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(SortKeySrc src
 // scatter kernel turns them into digit bases on its own.
 __global__ void __launch_bounds__(kSortThreads) radix_rowscan_kernel(uint32_t *hist, uint32_t bins, uint32_t chunks,
                                                                      uint32_t *totals) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t d = (blockIdx.x * kSortThreads + threadIdx.x) >> 5;
     if (d >= bins) return;
@@ -102,6 +106,8 @@ __global__ void __launch_bounds__(kSortThreads) radix_rowscan_kernel(uint32_t *h
 
 // --- exclusive scan of a small array by one CTA (length-class bins) ---------------------
 __global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t *data, uint32_t n) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     __shared__ uint32_t warp_off[32];
     __shared__ uint32_t carry_s;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -157,6 +163,8 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(SortKeySrc 
                                                                      uint32_t shift, uint32_t bins, uint32_t chunks,
                                                                      const uint32_t *hist, const uint32_t *totals,
                                                                      uint32_t *keys_out, uint32_t *vals_out) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     __shared__ uint32_t cur[kSortWarps][kMaxBins];
     __shared__ uint32_t base_of[kMaxBins];
     __shared__ uint32_t warp_sum[kSortWarps];
@@ -245,6 +253,8 @@ __device__ __forceinline__ uint64_t saturating_counter(uint64_t base, uint32_t k
 }
 __global__ void assign_counters_kernel(const uint32_t *keys, const uint32_t *order, uint32_t n, uint32_t max_slots,
                                        const uint64_t *send_counter, uint64_t *counter_out) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= n) return;
     const uint32_t slot = keys[j];
@@ -252,6 +262,8 @@ __global__ void assign_counters_kernel(const uint32_t *keys, const uint32_t *ord
     counter_out[order[j]] = saturating_counter(send_counter[slot], j - run_start(keys, j));
 }
 __global__ void advance_counters_kernel(const uint32_t *keys, uint32_t n, uint32_t max_slots, uint64_t *send_counter) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= n) return;
     const uint32_t slot = keys[j];
@@ -522,6 +534,8 @@ __device__ __forceinline__ SegMax replay_tile(const ReplayArgs &a, uint32_t base
 
 __global__ void __launch_bounds__(256) replay_scan_tiles_kernel(ReplayArgs a, uint32_t *tile_head, uint64_t *tile_max,
                                                                 uint32_t *pending_flag) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     __shared__ SegMax part[8];
     if (blockIdx.x == 0 && threadIdx.x == 0) *pending_flag = 0u;
     uint32_t slot[4];
@@ -535,6 +549,8 @@ __global__ void __launch_bounds__(256) replay_scan_tiles_kernel(ReplayArgs a, ui
 // One CTA: carry[t] = running maximum that reaches tile t from the tiles in front of it.
 __global__ void __launch_bounds__(1024) replay_scan_carry_kernel(const uint32_t *tile_head, const uint64_t *tile_max,
                                                                  uint32_t tiles, uint64_t *tile_carry) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     __shared__ SegMax part[32];
     SegMax reached{0u, 0ull};
     for (uint32_t base = 0; base < tiles; base += 1024u) {
@@ -549,6 +565,8 @@ __global__ void __launch_bounds__(1024) replay_scan_carry_kernel(const uint32_t 
 }
 __global__ void __launch_bounds__(256) replay_classify_kernel(ReplayArgs a, const uint64_t *tile_carry,
                                                               uint32_t *pending_flag) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     __shared__ SegMax part[8];
     const uint32_t base = blockIdx.x * kScanTile + threadIdx.x * 4u;
     uint32_t slot[4];
@@ -565,18 +583,26 @@ __global__ void __launch_bounds__(256) replay_classify_kernel(ReplayArgs a, cons
     if (__syncthreads_or(pending) && threadIdx.x == 0) *pending_flag = 1u;
 }
 __global__ void __launch_bounds__(256) replay_advance_kernel(ReplayArgs a) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     replay_advance_warp(a, blockIdx.x * blockDim.x + threadIdx.x);
 }
 __global__ void __launch_bounds__(256) replay_hash_clear_kernel(ReplayArgs a, const uint32_t *pending_flag) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     if (*pending_flag == 0u) return;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i <= a.mask; i += gridDim.x * blockDim.x) a.table[i] = kHashEmpty;
 }
 __global__ void __launch_bounds__(256) replay_hash_insert_kernel(ReplayArgs a, const uint32_t *pending_flag) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     if (*pending_flag == 0u) return;
     const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
     replay_hash_insert_warp(a, p, p < a.n && a.state[p] != RP_NOPART);
 }
 __global__ void __launch_bounds__(256) replay_finish_kernel(ReplayArgs a) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     replay_finish_warp(a, blockIdx.x * blockDim.x + threadIdx.x);
 }
 // All of the above for one tile, by the CTA that holds it (n <= kScanTile, 256 threads).
@@ -788,6 +814,8 @@ __device__ __forceinline__ uint32_t len_tile_count(const uint32_t *len, uint32_t
 }
 __global__ void __launch_bounds__(256) len_hist_kernel(const uint32_t *len, uint32_t n, int open_side,
                                                        uint32_t *bins) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     __shared__ uint32_t h[kLenBins];
     uint32_t bin[kLenItems], rank[kLenItems];
     len_tile_count(len, n, open_side, h, bin, rank);
@@ -796,6 +824,8 @@ __global__ void __launch_bounds__(256) len_hist_kernel(const uint32_t *len, uint
 }
 __global__ void __launch_bounds__(256) len_scatter_kernel(const uint32_t *len, uint32_t n, int open_side,
                                                           uint32_t *bins, uint32_t *order) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     __shared__ uint32_t h[kLenBins];
     uint32_t bin[kLenItems], rank[kLenItems];
     const uint32_t first = len_tile_count(len, n, open_side, h, bin, rank);
@@ -839,10 +869,10 @@ struct SortBuffers {
 template <uint32_t TILES>
 void sort_pass(const SortKeySrc &src, const uint32_t *kin, const uint32_t *vin, uint32_t n, uint32_t shift,
                uint32_t bins, uint32_t chunks, const SortBuffers &sb, uint32_t *kout, uint32_t *vout, cudaStream_t s) {
-    radix_hist_kernel<TILES><<<chunks, kSortThreads, 0, s>>>(src, kin, n, shift, bins, chunks, sb.hist);
-    radix_rowscan_kernel<<<(bins * 32 + kSortThreads - 1) / kSortThreads, kSortThreads, 0, s>>>(sb.hist, bins, chunks,
+    launch_kernel(n <= kDependentLaunchUpTo, radix_hist_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src, kin, n, shift, bins, chunks, sb.hist);
+    launch_kernel(n <= kDependentLaunchUpTo, radix_rowscan_kernel, dim3((bins * 32 + kSortThreads - 1) / kSortThreads), dim3(kSortThreads), s, sb.hist, bins, chunks,
                                                                                                sb.totals);
-    radix_scatter_kernel<TILES><<<chunks, kSortThreads, 0, s>>>(src, kin, vin, n, shift, bins, chunks, sb.hist, sb.totals,
+    launch_kernel(n <= kDependentLaunchUpTo, radix_scatter_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src, kin, vin, n, shift, bins, chunks, sb.hist, sb.totals,
                                                                kout, vout);
 }
 
@@ -914,10 +944,10 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
     cudaError_t e = launch_group_by_slot(b, n, false, s);
     if (e != cudaSuccess) return e;
     DeviceBatch &d = b->dev;
-    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, d.order, n,
+    launch_kernel(n <= kDependentLaunchUpTo, assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s, d.keys_tmp + b->max_pkts, d.order, n,
                                                           b->ctx->cfg.max_keypairs, b->ctx->kt.send_counter,
                                                           d.counter);
-    advance_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(d.keys_tmp + b->max_pkts, n, b->ctx->cfg.max_keypairs,
+    launch_kernel(n <= kDependentLaunchUpTo, advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s, d.keys_tmp + b->max_pkts, n, b->ctx->cfg.max_keypairs,
                                                            b->ctx->kt.send_counter);
     b->ctx->launches += 2;
     return cudaGetLastError();
@@ -971,13 +1001,13 @@ cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     const ReplayArgs a = replay_args(b, n);
     const uint32_t tiles = (n + kScanTile - 1) / kScanTile, grid = (n + 255) / 256;
     uint32_t *flag = d.replay_tile_head + replay_scan_tiles(b->max_pkts);
-    replay_scan_tiles_kernel<<<tiles, 256, 0, s>>>(a, d.replay_tile_head, d.replay_tile_max, flag);
-    replay_scan_carry_kernel<<<1, 1024, 0, s>>>(d.replay_tile_head, d.replay_tile_max, tiles, d.replay_tile_carry);
-    replay_classify_kernel<<<tiles, 256, 0, s>>>(a, d.replay_tile_carry, flag);
-    replay_advance_kernel<<<grid, 256, 0, s>>>(a);
-    replay_hash_clear_kernel<<<148 * 4, 256, 0, s>>>(a, flag);
-    replay_hash_insert_kernel<<<grid, 256, 0, s>>>(a, flag);
-    replay_finish_kernel<<<grid, 256, 0, s>>>(a);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_scan_tiles_kernel, dim3(tiles), dim3(256), s, a, d.replay_tile_head, d.replay_tile_max, flag);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_scan_carry_kernel, dim3(1), dim3(1024), s, d.replay_tile_head, d.replay_tile_max, tiles, d.replay_tile_carry);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_classify_kernel, dim3(tiles), dim3(256), s, a, d.replay_tile_carry, flag);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_advance_kernel, dim3(grid), dim3(256), s, a);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_hash_clear_kernel, dim3(148 * 4), dim3(256), s, a, flag);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_hash_insert_kernel, dim3(grid), dim3(256), s, a, flag);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_finish_kernel, dim3(grid), dim3(256), s, a);
     b->ctx->launches += 7;
     return cudaGetLastError();
 }
@@ -987,9 +1017,9 @@ cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, b
     DeviceBatch &d = b->dev;
     cudaError_t e = cudaMemsetAsync(d.counters32, 0, kLenBins * sizeof(uint32_t), s);
     if (e != cudaSuccess) return e;
-    len_hist_kernel<<<(n + kLenTile - 1) / kLenTile, 256, 0, s>>>(len, n, open_side ? 1 : 0, d.counters32);
-    exclusive_scan_kernel<<<1, 1024, 0, s>>>(d.counters32, kLenBins);
-    len_scatter_kernel<<<(n + kLenTile - 1) / kLenTile, 256, 0, s>>>(len, n, open_side ? 1 : 0, d.counters32, d.len_order);
+    launch_kernel(n <= kDependentLaunchUpTo, len_hist_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s, len, n, open_side ? 1 : 0, d.counters32);
+    launch_kernel(n <= kDependentLaunchUpTo, exclusive_scan_kernel, dim3(1), dim3(1024), s, d.counters32, kLenBins);
+    launch_kernel(n <= kDependentLaunchUpTo, len_scatter_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s, len, n, open_side ? 1 : 0, d.counters32, d.len_order);
     b->ctx->launches += 3;
     return cudaGetLastError();
 }
@@ -1074,9 +1104,9 @@ extern "C" int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uin
     SortKeySrc src{dev_slot, nullptr, ctx->cfg.max_keypairs, 0};
     SortBuffers sb{keys_a, keys_b, vals_a, order, hist + kMaxBins, hist};
     const uint32_t sort_launches = group_sort(src, n, kNoAllocMaxChunks, sb, s);
-    assign_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, order, n, ctx->cfg.max_keypairs,
+    launch_kernel(n <= kDependentLaunchUpTo, assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b, order, n, ctx->cfg.max_keypairs,
                                                           ctx->kt.send_counter, dev_counter);
-    advance_counters_kernel<<<(n + 255) / 256, 256, 0, s>>>(keys_b, n, ctx->cfg.max_keypairs, ctx->kt.send_counter);
+    launch_kernel(n <= kDependentLaunchUpTo, advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b, n, ctx->cfg.max_keypairs, ctx->kt.send_counter);
     ctx->launches += sort_launches + 2;
     if ((e = cudaGetLastError()) != cudaSuccess) return noalloc_fail(ctx, BNK_ECUDA, "kernel launch", e);
     return BNK_SUCCESS;
