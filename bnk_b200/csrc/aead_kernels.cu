@@ -287,6 +287,8 @@ __device__ __forceinline__ Desc load_desc(const AeadArgs &a, uint32_t pkt, bool 
 // ---------------------------------------------------------------------------
 template <bool OPEN>
 __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const AeadArgs a) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t idx = blockIdx.x * kThreads + threadIdx.x;
     const bool have = idx < a.n;
     const uint32_t pkt = have ? (a.order ? a.order[idx] : idx) : 0u;
@@ -694,7 +696,7 @@ cudaError_t launch_aead(const AeadArgs &a, cudaStream_t s, bnk_ctx *ctx) {
         // one CTA per 128 packets; the hardware hands CTAs to SMs as slots free up, which measured faster
         // than persistent warps with an even static share of the packets
         const uint32_t ctas = (a.n + kThreads - 1) / kThreads;
-        aead_kernel<OPEN><<<ctas, kThreads, 0, s>>>(a);
+        launch_kernel(a.n <= kDependentLaunchUpTo, aead_kernel<OPEN>, dim3(ctas), dim3(kThreads), s, a);
     }
     ++ctx->launches;
     return cudaGetLastError();

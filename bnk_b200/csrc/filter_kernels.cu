@@ -121,6 +121,8 @@ __device__ __forceinline__ bool rules_allow(const FilterTables &ft, const Parsed
 // ---- NoteOutbound, filter.go:189-209 ----------------------------------------------------
 __global__ void filter_note_kernel(FilterTables ft, const uint8_t *ring, const uint32_t *off,
                                    const uint32_t *len, uint32_t n, uint64_t ring_bytes, long long now) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const uint32_t o = off[i], l = len[i];
@@ -157,10 +159,14 @@ __global__ void filter_note_kernel(FilterTables ft, const uint8_t *ring, const u
 // insert.  Within one batch (one `now`) that equals: insert everything, then sweep once if
 // the count exceeds the threshold.  A repeat sweep at an unchanged `now` finds nothing.
 __global__ void filter_sweep_decide_kernel(FilterTables ft, long long now) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     FlowCtl *ctl = reinterpret_cast<FlowCtl *>(ft.flow_live);
     ctl->sweep_now = (ctl->live > SWEEP_THRESHOLD && !(ctl->swept_valid && ctl->swept_at == now)) ? 1 : 0;
 }
 __global__ void filter_sweep_kernel(FilterTables ft, long long now) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     FlowCtl *ctl = reinterpret_cast<FlowCtl *>(ft.flow_live);
     if (!ctl->sweep_now) return;
     const size_t total = (size_t)3 * ft.flow_capacity;
@@ -176,6 +182,8 @@ __global__ void filter_sweep_kernel(FilterTables ft, long long now) {
     if (dropped) atomicAdd(&ctl->live, 0ull - dropped);
 }
 __global__ void filter_sweep_finish_kernel(FilterTables ft, long long now) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     FlowCtl *ctl = reinterpret_cast<FlowCtl *>(ft.flow_live);
     if (ctl->sweep_now) {
         ctl->swept_at = now;
@@ -189,6 +197,8 @@ __global__ void filter_sweep_finish_kernel(FilterTables ft, long long now) {
 __global__ void filter_check_kernel(FilterTables ft, const uint8_t *ring, const uint32_t *off,
                                     const uint32_t *len, uint8_t *status, uint32_t n, uint64_t ring_bytes,
                                     long long now, int only_status_ok) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     if (only_status_ok) {
@@ -383,11 +393,12 @@ int filter_acl_upload(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, si
 cudaError_t launch_filter_note(bnk_batch *b, uint32_t n, long long now_ns, cudaStream_t s) {
     bnk_ctx *ctx = b->ctx;
     if (n == 0 || !ctx->ft.enforce || ctx->ft.flow_capacity == 0) return cudaSuccess; // filter.go:192-194
-    filter_note_kernel<<<(n + 255) / 256, 256, 0, s>>>(ctx->ft, b->dev.ring, b->dev.off, b->dev.len, n,
-                                                      b->ring_bytes, now_ns);
-    filter_sweep_decide_kernel<<<1, 1, 0, s>>>(ctx->ft, now_ns);
-    filter_sweep_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(ctx->ft, now_ns);
-    filter_sweep_finish_kernel<<<1, 1, 0, s>>>(ctx->ft, now_ns);
+    launch_kernel(n <= kDependentLaunchUpTo, filter_note_kernel, dim3((n + 255) / 256), dim3(256), s, ctx->ft,
+        b->dev.ring, b->dev.off, b->dev.len, n, b->ring_bytes, now_ns);
+    launch_kernel(n <= kDependentLaunchUpTo, filter_sweep_decide_kernel, dim3(1), dim3(1), s, ctx->ft, now_ns);
+    launch_kernel(n <= kDependentLaunchUpTo, filter_sweep_kernel, dim3(ctx->sm_count * 4), dim3(256), s, ctx->ft,
+        now_ns);
+    launch_kernel(n <= kDependentLaunchUpTo, filter_sweep_finish_kernel, dim3(1), dim3(1), s, ctx->ft, now_ns);
     ctx->launches += 4;
     return cudaGetLastError();
 }
@@ -397,8 +408,8 @@ cudaError_t launch_filter_check(bnk_batch *b, uint32_t n, long long now_ns, bool
     if (n == 0) return cudaSuccess;
     // open pipeline: the packet handed to the filter is the decrypted payload of out_len bytes
     const uint32_t *lens = only_status_ok ? b->dev.out_len : b->dev.len;
-    filter_check_kernel<<<(n + 255) / 256, 256, 0, s>>>(ctx->ft, b->dev.ring, b->dev.off, lens, b->dev.status, n,
-                                                       b->ring_bytes, now_ns, only_status_ok ? 1 : 0);
+    launch_kernel(n <= kDependentLaunchUpTo, filter_check_kernel, dim3((n + 255) / 256), dim3(256), s, ctx->ft,
+        b->dev.ring, b->dev.off, lens, b->dev.status, n, b->ring_bytes, now_ns, only_status_ok ? 1 : 0);
     ctx->launches += 1;
     return cudaGetLastError();
 }

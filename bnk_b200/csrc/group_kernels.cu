@@ -869,19 +869,20 @@ struct SortBuffers {
 template <uint32_t TILES>
 void sort_pass(const SortKeySrc &src, const uint32_t *kin, const uint32_t *vin, uint32_t n, uint32_t shift,
                uint32_t bins, uint32_t chunks, const SortBuffers &sb, uint32_t *kout, uint32_t *vout, cudaStream_t s) {
-    launch_kernel(n <= kDependentLaunchUpTo, radix_hist_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src, kin, n, shift, bins, chunks, sb.hist);
-    launch_kernel(n <= kDependentLaunchUpTo, radix_rowscan_kernel, dim3((bins * 32 + kSortThreads - 1) / kSortThreads), dim3(kSortThreads), s, sb.hist, bins, chunks,
-                                                                                               sb.totals);
-    launch_kernel(n <= kDependentLaunchUpTo, radix_scatter_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src, kin, vin, n, shift, bins, chunks, sb.hist, sb.totals,
-                                                               kout, vout);
+    launch_kernel(n <= kDependentLaunchUpTo, radix_hist_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src, kin,
+        n, shift, bins, chunks, sb.hist);
+    launch_kernel(n <= kDependentLaunchUpTo, radix_rowscan_kernel,
+        dim3((bins * 32 + kSortThreads - 1) / kSortThreads), dim3(kSortThreads), s, sb.hist, bins, chunks, sb.totals);
+    launch_kernel(n <= kDependentLaunchUpTo, radix_scatter_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src,
+        kin, vin, n, shift, bins, chunks, sb.hist, sb.totals, kout, vout);
 }
 
 // Stable sort of packet indices 0..n-1 by key.  Returns the number of kernel launches.
 uint32_t group_sort(const SortKeySrc &src, uint32_t n, uint32_t max_chunks, const SortBuffers &sb, cudaStream_t s) {
     const SortPlan plan = plan_for(src.max_slots);
     if (n <= kSmallMax) {
-        launch_after_kernel(group_small_kernel, dim3(1), dim3(kSortThreads), s, src, n, plan.passes, plan.digit_bits, sb.keys_b, sb.order,
-                                                      SmallCounters{nullptr, nullptr, 0}, ReplayArgs{});
+        launch_after_kernel(group_small_kernel, dim3(1), dim3(kSortThreads), s, src, n, plan.passes, plan.digit_bits,
+            sb.keys_b, sb.order, SmallCounters{nullptr, nullptr, 0}, ReplayArgs{});
         return 1;
     }
     const uint32_t bins = 1u << plan.digit_bits;
@@ -934,21 +935,20 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
         bnk_ctx *ctx = b->ctx;
         DeviceBatch &d = b->dev;
         const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
-        launch_after_kernel(group_small_kernel, dim3(1), dim3(kSortThreads), s, SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n,
-                                                      plan.passes, plan.digit_bits, d.keys_tmp + b->max_pkts, d.order,
-                                                      SmallCounters{ctx->kt.send_counter, d.counter, ctx->cfg.max_keypairs},
-                                                      ReplayArgs{});
+        launch_after_kernel(group_small_kernel, dim3(1), dim3(kSortThreads), s,
+            SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n, plan.passes, plan.digit_bits,
+            d.keys_tmp + b->max_pkts, d.order, SmallCounters{ctx->kt.send_counter, d.counter, ctx->cfg.max_keypairs},
+            ReplayArgs{});
         ctx->launches += 1;
         return cudaGetLastError();
     }
     cudaError_t e = launch_group_by_slot(b, n, false, s);
     if (e != cudaSuccess) return e;
     DeviceBatch &d = b->dev;
-    launch_kernel(n <= kDependentLaunchUpTo, assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s, d.keys_tmp + b->max_pkts, d.order, n,
-                                                          b->ctx->cfg.max_keypairs, b->ctx->kt.send_counter,
-                                                          d.counter);
-    launch_kernel(n <= kDependentLaunchUpTo, advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s, d.keys_tmp + b->max_pkts, n, b->ctx->cfg.max_keypairs,
-                                                           b->ctx->kt.send_counter);
+    launch_kernel(n <= kDependentLaunchUpTo, assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s,
+        d.keys_tmp + b->max_pkts, d.order, n, b->ctx->cfg.max_keypairs, b->ctx->kt.send_counter, d.counter);
+    launch_kernel(n <= kDependentLaunchUpTo, advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s,
+        d.keys_tmp + b->max_pkts, n, b->ctx->cfg.max_keypairs, b->ctx->kt.send_counter);
     b->ctx->launches += 2;
     return cudaGetLastError();
 }
@@ -988,9 +988,9 @@ cudaError_t launch_group_and_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     bnk_ctx *ctx = b->ctx;
     DeviceBatch &d = b->dev;
     const SortPlan plan = plan_for(ctx->cfg.max_keypairs);
-    launch_after_kernel(group_small_kernel, dim3(1), dim3(kSortThreads), s, SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n, plan.passes,
-                                                  plan.digit_bits, d.keys_tmp + b->max_pkts, d.order,
-                                                  SmallCounters{nullptr, nullptr, 0}, replay_args(b, n));
+    launch_after_kernel(group_small_kernel, dim3(1), dim3(kSortThreads), s,
+        SortKeySrc{d.slot, d.status, ctx->cfg.max_keypairs, 0}, n, plan.passes, plan.digit_bits,
+        d.keys_tmp + b->max_pkts, d.order, SmallCounters{nullptr, nullptr, 0}, replay_args(b, n));
     ctx->launches += 1;
     return cudaGetLastError();
 }
@@ -1001,9 +1001,12 @@ cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     const ReplayArgs a = replay_args(b, n);
     const uint32_t tiles = (n + kScanTile - 1) / kScanTile, grid = (n + 255) / 256;
     uint32_t *flag = d.replay_tile_head + replay_scan_tiles(b->max_pkts);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_scan_tiles_kernel, dim3(tiles), dim3(256), s, a, d.replay_tile_head, d.replay_tile_max, flag);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_scan_carry_kernel, dim3(1), dim3(1024), s, d.replay_tile_head, d.replay_tile_max, tiles, d.replay_tile_carry);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_classify_kernel, dim3(tiles), dim3(256), s, a, d.replay_tile_carry, flag);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_scan_tiles_kernel, dim3(tiles), dim3(256), s, a,
+        d.replay_tile_head, d.replay_tile_max, flag);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_scan_carry_kernel, dim3(1), dim3(1024), s, d.replay_tile_head,
+        d.replay_tile_max, tiles, d.replay_tile_carry);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_classify_kernel, dim3(tiles), dim3(256), s, a,
+        d.replay_tile_carry, flag);
     launch_kernel(n <= kDependentLaunchUpTo, replay_advance_kernel, dim3(grid), dim3(256), s, a);
     launch_kernel(n <= kDependentLaunchUpTo, replay_hash_clear_kernel, dim3(148 * 4), dim3(256), s, a, flag);
     launch_kernel(n <= kDependentLaunchUpTo, replay_hash_insert_kernel, dim3(grid), dim3(256), s, a, flag);
@@ -1017,9 +1020,11 @@ cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, b
     DeviceBatch &d = b->dev;
     cudaError_t e = cudaMemsetAsync(d.counters32, 0, kLenBins * sizeof(uint32_t), s);
     if (e != cudaSuccess) return e;
-    launch_kernel(n <= kDependentLaunchUpTo, len_hist_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s, len, n, open_side ? 1 : 0, d.counters32);
+    launch_kernel(n <= kDependentLaunchUpTo, len_hist_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s, len,
+        n, open_side ? 1 : 0, d.counters32);
     launch_kernel(n <= kDependentLaunchUpTo, exclusive_scan_kernel, dim3(1), dim3(1024), s, d.counters32, kLenBins);
-    launch_kernel(n <= kDependentLaunchUpTo, len_scatter_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s, len, n, open_side ? 1 : 0, d.counters32, d.len_order);
+    launch_kernel(n <= kDependentLaunchUpTo, len_scatter_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s,
+        len, n, open_side ? 1 : 0, d.counters32, d.len_order);
     b->ctx->launches += 3;
     return cudaGetLastError();
 }
@@ -1104,9 +1109,10 @@ extern "C" int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uin
     SortKeySrc src{dev_slot, nullptr, ctx->cfg.max_keypairs, 0};
     SortBuffers sb{keys_a, keys_b, vals_a, order, hist + kMaxBins, hist};
     const uint32_t sort_launches = group_sort(src, n, kNoAllocMaxChunks, sb, s);
-    launch_kernel(n <= kDependentLaunchUpTo, assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b, order, n, ctx->cfg.max_keypairs,
-                                                          ctx->kt.send_counter, dev_counter);
-    launch_kernel(n <= kDependentLaunchUpTo, advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b, n, ctx->cfg.max_keypairs, ctx->kt.send_counter);
+    launch_kernel(n <= kDependentLaunchUpTo, assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b,
+        order, n, ctx->cfg.max_keypairs, ctx->kt.send_counter, dev_counter);
+    launch_kernel(n <= kDependentLaunchUpTo, advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b, n,
+        ctx->cfg.max_keypairs, ctx->kt.send_counter);
     ctx->launches += sort_launches + 2;
     if ((e = cudaGetLastError()) != cudaSuccess) return noalloc_fail(ctx, BNK_ECUDA, "kernel launch", e);
     return BNK_SUCCESS;

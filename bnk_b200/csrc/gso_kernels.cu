@@ -28,6 +28,8 @@ __device__ __forceinline__ uint32_t fold16(uint64_t s) {
 __global__ void __launch_bounds__(256) gso_split_kernel(const bnk_gso_super *supers, uint32_t n_super, uint8_t *ring,
                                                         const uint32_t *off, const uint32_t *len, uint32_t *slot,
                                                         uint32_t n_pkts, uint64_t ring_bytes, const uint32_t *seg_super) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_pkts) return;
     const uint32_t pkt = warp;
@@ -158,6 +160,8 @@ __global__ void __launch_bounds__(256) gso_split_kernel(const bnk_gso_super *sup
 
 // segment -> super-packet index (n_super for packets that belong to none)
 __global__ void gso_map_kernel(const bnk_gso_super *supers, uint32_t n_super, uint32_t n_pkts, uint32_t *seg_super) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= n_super) return;
     const bnk_gso_super sp = supers[j];
@@ -166,6 +170,8 @@ __global__ void gso_map_kernel(const bnk_gso_super *supers, uint32_t n_super, ui
 }
 
 __global__ void fill_u32_kernel(uint32_t *p, uint32_t n, uint32_t v) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = v;
 }
@@ -176,10 +182,12 @@ cudaError_t launch_gso_split(bnk_batch *b, uint32_t n_super, uint32_t n_pkts, cu
     if (n_pkts == 0 || n_super == 0) return cudaSuccess;
     DeviceBatch &d = b->dev;
     uint32_t *seg_super = d.order_tmp; // grouping scratch is idle here
-    fill_u32_kernel<<<(n_pkts + 255) / 256, 256, 0, s>>>(seg_super, n_pkts, n_super);
-    gso_map_kernel<<<(n_super + 127) / 128, 128, 0, s>>>(d.gso, n_super, n_pkts, seg_super);
-    gso_split_kernel<<<(n_pkts + 7) / 8, 256, 0, s>>>(d.gso, n_super, d.ring, d.off, d.len, d.slot, n_pkts, b->ring_bytes,
-                                                     seg_super);
+    launch_kernel(n_pkts <= kDependentLaunchUpTo, fill_u32_kernel, dim3((n_pkts + 255) / 256), dim3(256), s,
+        seg_super, n_pkts, n_super);
+    launch_kernel(n_pkts <= kDependentLaunchUpTo, gso_map_kernel, dim3((n_super + 127) / 128), dim3(128), s, d.gso,
+        n_super, n_pkts, seg_super);
+    launch_kernel(n_pkts <= kDependentLaunchUpTo, gso_split_kernel, dim3((n_pkts + 7) / 8), dim3(256), s, d.gso,
+        n_super, d.ring, d.off, d.len, d.slot, n_pkts, b->ring_bytes, seg_super);
     b->ctx->launches += 3;
     return cudaGetLastError();
 }

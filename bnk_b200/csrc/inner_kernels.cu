@@ -11,6 +11,8 @@ namespace {
 
 __global__ void demux_index_kernel(KeypairTables kt, const uint8_t *ring, const uint32_t *off, const uint32_t *len,
                                    uint32_t *slot, uint32_t n, uint64_t ring_bytes) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const uint32_t o = off[i], l = len[i];
@@ -38,6 +40,8 @@ __global__ void demux_index_kernel(KeypairTables kt, const uint8_t *ring, const 
 
 __global__ void inner_check_kernel(KeypairTables kt, const uint8_t *ring, const uint32_t *off, const uint32_t *slot,
                                    uint32_t *out_len, uint8_t *status, uint32_t n) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n || status[i] != BNK_PKT_OK) return;
     const uint8_t *p = ring + off[i] + BNK_WG_HEADER; // 16-byte aligned
@@ -61,6 +65,8 @@ __global__ void inner_check_kernel(KeypairTables kt, const uint8_t *ring, const 
 __global__ void classify_kernel(KeypairTables kt, const uint8_t *ring, const uint32_t *off, const uint32_t *len,
                                 const uint8_t *src_addr, uint32_t *slot, uint8_t *status, uint32_t n,
                                 uint64_t ring_bytes) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const uint32_t o = off[i], l = len[i];
@@ -116,24 +122,24 @@ __global__ void classify_kernel(KeypairTables kt, const uint8_t *ring, const uin
 
 cudaError_t launch_classify(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    classify_kernel<<<(n + 255) / 256, 256, 0, s>>>(b->ctx->kt, b->dev.ring, b->dev.off, b->dev.len, b->dev.src_addr,
-                                                   b->dev.slot, b->dev.status, n, b->ring_bytes);
+    launch_kernel(n <= kDependentLaunchUpTo, classify_kernel, dim3((n + 255) / 256), dim3(256), s, b->ctx->kt,
+        b->dev.ring, b->dev.off, b->dev.len, b->dev.src_addr, b->dev.slot, b->dev.status, n, b->ring_bytes);
     ++b->ctx->launches;
     return cudaGetLastError();
 }
 
 cudaError_t launch_demux_index(bnk_batch *b, uint32_t n, const uint32_t *len, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    demux_index_kernel<<<(n + 255) / 256, 256, 0, s>>>(b->ctx->kt, b->dev.ring, b->dev.off, len, b->dev.slot, n,
-                                                      b->ring_bytes);
+    launch_kernel(n <= kDependentLaunchUpTo, demux_index_kernel, dim3((n + 255) / 256), dim3(256), s, b->ctx->kt,
+        b->dev.ring, b->dev.off, len, b->dev.slot, n, b->ring_bytes);
     ++b->ctx->launches;
     return cudaGetLastError();
 }
 
 cudaError_t launch_inner_check(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    inner_check_kernel<<<(n + 255) / 256, 256, 0, s>>>(b->ctx->kt, b->dev.ring, b->dev.off, b->dev.slot, b->dev.out_len,
-                                                      b->dev.status, n);
+    launch_kernel(n <= kDependentLaunchUpTo, inner_check_kernel, dim3((n + 255) / 256), dim3(256), s, b->ctx->kt,
+        b->dev.ring, b->dev.off, b->dev.slot, b->dev.out_len, b->dev.status, n);
     ++b->ctx->launches;
     return cudaGetLastError();
 }
