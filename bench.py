@@ -40,7 +40,7 @@ INT_OPS_PER_PACKET = 24 * 992 + 90 * 40
 E2E_BATCHES = 8
 # dram__bytes_read.sum + dram__bytes_write.sum per packet of the seal kernel, from the ncu capture summarised in
 # profiles/ (captured on 131,072 packets; traffic grows in proportion to the packet count); None until measured
-NCU_DRAM_BYTES_PER_PACKET = 2593
+NCU_DRAM_BYTES_PER_PACKET = 2569
 
 
 # ----------------------------------------------------------------------------------------------
