@@ -9,6 +9,8 @@ import subprocess
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libbnkgpu.so")
+BENCH_CSRC = os.path.join(PKG_DIR, "bench_csrc")
+BENCH_LIB_PATH = os.path.join(PKG_DIR, "libbnkgpu_bench.so")  # measurement helpers, not part of the drop-in
 
 NVCC_FLAGS = [
     "-O3",
@@ -30,16 +32,30 @@ def sources() -> list[str]:
     return sorted(glob.glob(os.path.join(CSRC, "*.cu"))) + sorted(glob.glob(os.path.join(HOST, "*.cpp")))
 
 
+def bench_sources() -> list[str]:
+    return sorted(glob.glob(os.path.join(BENCH_CSRC, "*.cu")))
+
+
 def _deps() -> list[str]:
     inc = os.path.join(os.path.dirname(PKG_DIR), "include", "bnk_gpu.h")
     return sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(HOST, "*.hpp")) + [inc]
 
 
-def is_stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+def _bench_deps() -> list[str]:
+    inc = os.path.join(os.path.dirname(PKG_DIR), "include")
+    return bench_sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(inc, "bnk_gpu.h"),
+                                                                     os.path.join(inc, "bnk_gpu_bench.h")]
+
+
+def _stale(lib: str, deps: list[str]) -> bool:
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    return any(os.path.getmtime(p) > t for p in _deps())
+    t = os.path.getmtime(lib)
+    return any(os.path.getmtime(p) > t for p in deps)
+
+
+def is_stale() -> bool:
+    return _stale(LIB_PATH, _deps()) or _stale(BENCH_LIB_PATH, _bench_deps())
 
 
 def nvcc_path() -> str:
@@ -50,18 +66,20 @@ def nvcc_path() -> str:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every .cu under csrc/ into libbnkgpu.so.  Returns the library path."""
-    if not force and not is_stale():
-        return LIB_PATH
-    cmd = [nvcc_path(), *NVCC_FLAGS]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", LIB_PATH, *sources()]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        print(res.stderr)
+    """Compile every .cu under csrc/ into libbnkgpu.so and bench_csrc/ into libbnkgpu_bench.so.  Returns the
+    path of the former."""
+    for lib, srcs, deps in ((LIB_PATH, sources(), _deps()), (BENCH_LIB_PATH, bench_sources(), _bench_deps())):
+        if not force and not _stale(lib, deps):
+            continue
+        cmd = [nvcc_path(), *NVCC_FLAGS]
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+        cmd += ["-o", lib, *srcs]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+        if verbose:
+            print(res.stderr)
     return LIB_PATH
 
 

@@ -26,6 +26,7 @@ F_USE_OUT_LEN = 1 << 7
 F_DEMUX_INDEX = 1 << 8
 F_INNER_CHECK = 1 << 9
 F_TIMED = 1 << 10
+F_STATS = 1 << 11
 
 WG_HEADER = 16
 WG_TAG = 16
@@ -89,6 +90,22 @@ class BatchView(C.Structure):
     ]
 
 
+class BatchStats(C.Structure):
+    _fields_ = [("packets", C.c_uint64), ("bytes_out", C.c_uint64), ("by_status", C.c_uint64 * 16)]
+
+
+class TableStats(C.Structure):
+    _fields_ = [
+        ("flow_live", C.c_uint64),
+        ("flow_used", C.c_uint32 * 3),
+        ("flow_dead", C.c_uint32 * 3),
+        ("flow_capacity", C.c_uint32),
+        ("index_live", C.c_uint32), ("index_dead", C.c_uint32), ("index_slots", C.c_uint32),
+        ("addr_live", C.c_uint32), ("addr_dead", C.c_uint32), ("addr_slots", C.c_uint32),
+        ("reserved", C.c_uint32),
+    ]
+
+
 SRC_ADDR_STRIDE = 20
 CLASS_WIREGUARD, CLASS_DISCO, CLASS_STUN, CLASS_STRANGER = 0, 10, 11, 12
 
@@ -115,6 +132,7 @@ SYMBOLS = {
     "bnk_acl_set": (_i, [_vp, _i, _vp, _sz]),
     "bnk_flows_clear": (_i, [_vp]),
     "bnk_flows_count": (_i, [_vp, C.POINTER(_u64)]),
+    "bnk_table_stats_get": (_i, [_vp, C.POINTER(TableStats)]),
     "bnk_batch_create": (_i, [_vp, _u32, _u64, C.POINTER(_vp)]),
     "bnk_batch_destroy": (_i, [_vp]),
     "bnk_batch_view_get": (_i, [_vp, C.POINTER(BatchView)]),
@@ -127,19 +145,25 @@ SYMBOLS = {
     "bnk_classify_submit": (_i, [_vp, _u32, _u32]),
     "bnk_gso_split_submit": (_i, [_vp, _vp, _u32, _u32, _u32]),
     "bnk_wait": (_i, [_vp, _u64]),
+    "bnk_batch_stats_get": (_i, [_vp, C.POINTER(BatchStats)]),
     "bnk_batch_upload": (_i, [_vp, _u32]),
     "bnk_batch_download": (_i, [_vp, _u32]),
     "bnk_assign_counters_noalloc": (_i, [_vp, _vp, _vp, _u32, _vp]),
-    "bnk_timer_start": (_i, [_vp, C.POINTER(_vp), _u32]),
-    "bnk_timer_stop": (_i, [_vp, C.POINTER(_vp), _u32, C.POINTER(C.c_float)]),
     "bnk_batch_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "bnk_batch_last_aead_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "bnk_kernel_launch_count": (_i, [_vp, C.POINTER(_u64)]),
+}
+# include/bnk_gpu_bench.h, exported by libbnkgpu_bench.so
+BENCH_SYMBOLS = {
+    "bnk_timer_start": (_i, [_vp, C.POINTER(_vp), _u32]),
+    "bnk_timer_stop": (_i, [_vp, C.POINTER(_vp), _u32, C.POINTER(C.c_float)]),
     "bnk_probe_int_throughput": (_i, [_vp, _i, C.POINTER(C.c_double)]),
     "bnk_batch_fill_random": (_i, [_vp, _u64]),
+    "bnk_batch_copy_only": (_i, [_vp, _u32, _i, _i]),
 }
 
 _LIB = None
+_BENCH_LIB = None
 
 
 class BnkError(RuntimeError):
@@ -171,6 +195,24 @@ def lib() -> C.CDLL:
         fn.restype = res
         fn.argtypes = args
     _LIB = L
+    return L
+
+
+def bench_lib() -> C.CDLL:
+    """Loads libbnkgpu_bench.so (timers, probes, device-side fill, copy-only pass) after libbnkgpu.so."""
+    global _BENCH_LIB
+    if _BENCH_LIB is not None:
+        return _BENCH_LIB
+    lib()
+    path = os.environ.get("BNK_B200_BENCH_LIB") or _build.BENCH_LIB_PATH
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} is missing: build it with `python -m bnk_b200._build` (needs nvcc).")
+    L = C.CDLL(path)
+    for name, (res, args) in BENCH_SYMBOLS.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    _BENCH_LIB = L
     return L
 
 

@@ -1,7 +1,7 @@
 // Measurement helpers for sm_100a: the 32-bit integer issue-rate probe that gives the
 // seal/open kernels their ALU roofline denominator, and a seeded device-side fill for
 // synthetic payloads.
-#include "bnk_internal.cuh"
+#include "../csrc/bnk_internal.cuh"
 
 namespace {
 
@@ -148,12 +148,10 @@ __global__ void fill_random_kernel(uint64_t *dst, uint64_t words, uint64_t seed)
 
 } // namespace
 
-cudaError_t launch_fill_random(uint8_t *dst, uint64_t bytes, uint64_t seed, cudaStream_t s,
-                               std::atomic<uint64_t> *launches) {
+cudaError_t launch_fill_random(uint8_t *dst, uint64_t bytes, uint64_t seed, int sm_count, cudaStream_t s) {
     const uint64_t words = bytes / 8; // ring sizes are multiples of 16
     if (words == 0) return cudaSuccess;
-    fill_random_kernel<<<148 * 8, 256, 0, s>>>(reinterpret_cast<uint64_t *>(dst), words, seed);
-    if (launches) ++*launches;
+    fill_random_kernel<<<sm_count * 8, 256, 0, s>>>(reinterpret_cast<uint64_t *>(dst), words, seed);
     return cudaGetLastError();
 }
 

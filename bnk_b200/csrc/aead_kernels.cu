@@ -236,6 +236,11 @@ __device__ __forceinline__ Desc load_desc(const AeadArgs &a, uint32_t pkt, bool 
     if ((d.off & 15u) || d.slot >= a.max_slots) {
         st = (OPEN && d.slot == kSlotNoKeypair) ? BNK_PKT_NO_KEYPAIR : BNK_PKT_BAD_DESC;
         d.live = false;
+    } else if (!a.valid[d.slot]) {
+        // never set, or cleared: the zeroed key of such a slot is public knowledge, so nothing is sealed
+        // under it and nothing "authenticates" against it (wireguard-go drops traffic that has no keypair)
+        st = BNK_PKT_NO_KEYPAIR;
+        d.live = false;
     } else if (!OPEN) {
         d.body = wg_padded_len(len, a.mtu);
         d.in_len = len;

@@ -69,9 +69,17 @@ int begin_submit(bnk_batch *b, uint32_t npkts, bool touches_host = true) {
 // work on the side stream is always joined back before a submit returns, and no event is recorded per submit.)
 struct SubmitScope {
     bnk_batch *b;
-    explicit SubmitScope(bnk_batch *batch) : b(batch) {}
+    std::shared_lock<std::shared_mutex> tables; // see bnk_ctx::submit_mu
+    explicit SubmitScope(bnk_batch *batch) : b(batch), tables(batch->ctx->submit_mu) { b->stats_pending = false; }
     ~SubmitScope() { b->in_flight = true; }
 };
+
+// The counters of BNK_F_STATS: one launch behind the submit's last kernel, totals straight into pinned memory.
+cudaError_t tally_if_asked(bnk_batch *b, uint32_t npkts, uint32_t flags, cudaStream_t s) {
+    if (!(flags & BNK_F_STATS)) return cudaSuccess;
+    b->stats_pending = true;
+    return launch_tally(b, npkts, s);
+}
 
 // Small batches skip the copy engines: the kernels read the caller's pinned ring and descriptors through the
 // bus and write the results straight back (pinned memory has the same address on the device).  For a batch of
@@ -144,6 +152,7 @@ AeadArgs aead_args(bnk_batch *b, uint32_t n, bool open, const uint32_t *order) {
     a.status = b->dev.status;
     a.keys = open ? ctx->kt.recv_keys : ctx->kt.send_keys;
     a.remote_index = ctx->kt.remote_index;
+    a.valid = ctx->kt.valid;
     a.order = order;
     a.n = n;
     a.mtu = ctx->cfg.mtu;
@@ -233,10 +242,15 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     if ((e = dev_alloc_zero(&ctx->kt.replay_next, k)) != cudaSuccess) return bail("replay_next", e);
     if ((e = dev_alloc_zero(&ctx->kt.replay_ring, k * cfg->replay_ring_blocks)) != cudaSuccess) return bail("replay_ring", e);
     if ((e = dev_alloc_zero(&ctx->kt.allowed_ip, k)) != cudaSuccess) return bail("allowed_ip", e);
+    if ((e = dev_alloc_zero(&ctx->kt.valid, k)) != cudaSuccess) return bail("valid", e);
     uint32_t islots = 16;
     while (islots < 2 * k) islots <<= 1;
     ctx->kt.index_slots = islots;
     ctx->index_keys_host.assign(islots, 0);
+    ctx->index_vals_host.assign(islots, 0);
+    ctx->index_live = ctx->index_dead = ctx->addr_live = ctx->addr_dead = 0;
+    for (auto &h : ctx->flow_dead_hint) h = 0;
+    ctx->flow_errors_seen = 0;
     if ((e = dev_alloc_zero(&ctx->kt.index_keys, (size_t)islots)) != cudaSuccess) return bail("index_keys", e);
     if ((e = dev_alloc_zero(&ctx->kt.index_vals, (size_t)islots)) != cudaSuccess) return bail("index_vals", e);
     ctx->kt.addr_slots = islots;
@@ -260,6 +274,7 @@ int bnk_ctx_destroy(bnk_ctx *ctx) {
     cudaFree(ctx->kt.replay_next);
     cudaFree(ctx->kt.replay_ring);
     cudaFree(ctx->kt.allowed_ip);
+    cudaFree(ctx->kt.valid);
     cudaFree(ctx->kt.index_keys);
     cudaFree(ctx->kt.index_vals);
     cudaFree(ctx->kt.addr_tab);
@@ -292,6 +307,7 @@ int bnk_keypair_set_many(bnk_ctx *ctx, uint32_t first_slot, uint32_t n, const ui
     CK(ctx, cudaMemset(ctx->kt.replay_last + first_slot, 0, (size_t)n * 8));
     CK(ctx, cudaMemset(ctx->kt.replay_ring + (size_t)first_slot * rb, 0, (size_t)n * rb * 8));
     CK(ctx, cudaMemset(ctx->kt.allowed_ip + first_slot, 0, (size_t)n * 4));
+    CK(ctx, cudaMemset(ctx->kt.valid + first_slot, 1, (size_t)n));
     return BNK_SUCCESS;
 }
 
@@ -300,9 +316,15 @@ int bnk_keypair_set(bnk_ctx *ctx, uint32_t slot, const uint8_t send_key[32], con
     return bnk_keypair_set_many(ctx, slot, 1, send_key, recv_key, &remote_index);
 }
 
+static int index_drop_slot(bnk_ctx *ctx, uint32_t slot);
+
 int bnk_keypair_clear(bnk_ctx *ctx, uint32_t slot) {
     static const uint8_t zeros[32] = {0};
-    return bnk_keypair_set(ctx, slot, zeros, zeros, 0);
+    int rc = bnk_keypair_set(ctx, slot, zeros, zeros, 0);
+    if (rc != BNK_SUCCESS) return rc;
+    // no keys: seal and open refuse the slot with BNK_PKT_NO_KEYPAIR, and no receiver index leads to it any more
+    CK(ctx, cudaMemset(ctx->kt.valid + slot, 0, 1));
+    return index_drop_slot(ctx, slot);
 }
 
 int bnk_send_counter_get(bnk_ctx *ctx, uint32_t slot, uint64_t *counter) {
@@ -327,9 +349,33 @@ int bnk_keypair_set_allowed_ip(bnk_ctx *ctx, uint32_t slot, uint32_t ipv4) {
 }
 
 // The index table is edited in a host shadow and the touched entry is copied over: updates happen once per
-// handshake, lookups once per packet.
+// handshake, lookups once per packet.  A deleted entry keeps its slot as a tombstone so that probe chains stay
+// intact; every handshake brings a new random index, so tombstones pile up, and once a quarter of the table is
+// tombstones the table is rebuilt without them (otherwise a lookup of an unknown index, which anyone can send,
+// would end up walking the whole table).
+constexpr uint64_t kIndexLive = 1ull << 32, kIndexDead = 2ull << 32;
+static int index_rebuild(bnk_ctx *ctx) {
+    const uint32_t slots = ctx->kt.index_slots, mask = slots - 1;
+    std::vector<uint64_t> keys(slots, 0);
+    std::vector<uint32_t> vals(slots, 0);
+    for (uint32_t i = 0; i < slots; i++) {
+        const uint64_t k = ctx->index_keys_host[i];
+        if ((k >> 32) != 1) continue;
+        uint32_t h = index_hash((uint32_t)k) & mask;
+        while (keys[h]) h = (h + 1) & mask;
+        keys[h] = k;
+        vals[h] = ctx->index_vals_host[i];
+    }
+    ctx->index_keys_host.swap(keys);
+    ctx->index_vals_host.swap(vals);
+    ctx->index_dead = 0;
+    CK(ctx, cudaDeviceSynchronize()); // the whole table moves: not under a running lookup
+    CK(ctx, cudaMemcpy(ctx->kt.index_vals, ctx->index_vals_host.data(), (size_t)slots * 4, cudaMemcpyHostToDevice));
+    CK(ctx, cudaMemcpy(ctx->kt.index_keys, ctx->index_keys_host.data(), (size_t)slots * 8, cudaMemcpyHostToDevice));
+    return BNK_SUCCESS;
+}
 static int index_update(bnk_ctx *ctx, uint32_t local_index, bool insert, uint32_t slot) {
-    const uint64_t key = (1ull << 32) | local_index, dead = 2ull << 32;
+    const uint64_t key = kIndexLive | local_index;
     std::vector<uint64_t> &keys = ctx->index_keys_host;
     const uint32_t mask = ctx->kt.index_slots - 1;
     uint32_t h = index_hash(local_index) & mask;
@@ -339,7 +385,7 @@ static int index_update(bnk_ctx *ctx, uint32_t local_index, bool insert, uint32_
             at = h;
             break;
         }
-        if (keys[h] == dead && spare < 0) spare = h;
+        if (keys[h] == kIndexDead && spare < 0) spare = h;
         if (keys[h] == 0) {
             if (spare < 0) spare = h;
             break;
@@ -348,16 +394,39 @@ static int index_update(bnk_ctx *ctx, uint32_t local_index, bool insert, uint32_
     }
     if (!insert) {
         if (at < 0) return BNK_SUCCESS;
-        keys[at] = dead;
-        CK(ctx, cudaMemcpy(ctx->kt.index_keys + at, &dead, 8, cudaMemcpyHostToDevice));
+        keys[at] = kIndexDead;
+        ctx->index_live--;
+        ctx->index_dead++;
+        CK(ctx, cudaMemcpy(ctx->kt.index_keys + at, &kIndexDead, 8, cudaMemcpyHostToDevice));
+        if (ctx->index_dead >= ctx->kt.index_slots / 4) return index_rebuild(ctx);
         return BNK_SUCCESS;
     }
+    const bool fresh = at < 0;
     if (at < 0) at = spare;
     if (at < 0) return fail(ctx, BNK_EFULL, "receiver index table full");
+    if (fresh) {
+        if (keys[at] == kIndexDead) ctx->index_dead--;
+        ctx->index_live++;
+    }
     // value first, then the key that makes the entry visible
+    ctx->index_vals_host[at] = slot;
     CK(ctx, cudaMemcpy(ctx->kt.index_vals + at, &slot, 4, cudaMemcpyHostToDevice));
     keys[at] = key;
     CK(ctx, cudaMemcpy(ctx->kt.index_keys + at, &key, 8, cudaMemcpyHostToDevice));
+    return BNK_SUCCESS;
+}
+// bnk_keypair_clear: the indices that led to the slot lead nowhere now
+static int index_drop_slot(bnk_ctx *ctx, uint32_t slot) {
+    bool any = false;
+    for (uint32_t i = 0; i < ctx->kt.index_slots; i++) {
+        if ((ctx->index_keys_host[i] >> 32) != 1 || ctx->index_vals_host[i] != slot) continue;
+        ctx->index_keys_host[i] = kIndexDead;
+        ctx->index_live--;
+        ctx->index_dead++;
+        any = true;
+        CK(ctx, cudaMemcpy(ctx->kt.index_keys + i, &kIndexDead, 8, cudaMemcpyHostToDevice));
+    }
+    if (any && ctx->index_dead >= ctx->kt.index_slots / 4) return index_rebuild(ctx);
     return BNK_SUCCESS;
 }
 
@@ -373,12 +442,29 @@ int bnk_index_clear(bnk_ctx *ctx, uint32_t local_index) {
     return index_update(ctx, local_index, false, 0);
 }
 
-// byAddr: same host-shadow scheme as the receiver-index table
+// byAddr: same host-shadow scheme as the receiver-index table, tombstones reclaimed the same way
+constexpr uint32_t kAddrLive = 1u << 16, kAddrDead = 2u << 16;
+static int addr_rebuild(bnk_ctx *ctx) {
+    const uint32_t slots = ctx->kt.addr_slots, mask = slots - 1;
+    std::vector<KeypairTables::AddrEntry> tab(slots, KeypairTables::AddrEntry{});
+    for (const KeypairTables::AddrEntry &e : ctx->addr_host) {
+        if (!(e.port & kAddrLive)) continue;
+        uint32_t h = addr_hash(e.hi, e.lo, e.port & 0xffffu) & mask;
+        while (tab[h].port) h = (h + 1) & mask;
+        tab[h] = e;
+    }
+    ctx->addr_host.swap(tab);
+    ctx->addr_dead = 0;
+    CK(ctx, cudaDeviceSynchronize());
+    CK(ctx, cudaMemcpy(ctx->kt.addr_tab, ctx->addr_host.data(), (size_t)slots * sizeof(KeypairTables::AddrEntry),
+                       cudaMemcpyHostToDevice));
+    return BNK_SUCCESS;
+}
 static int addr_update(bnk_ctx *ctx, const uint8_t addr[16], uint16_t port, bool insert, uint32_t peer) {
     uint64_t hi, lo;
     memcpy(&hi, addr, 8);
     memcpy(&lo, addr + 8, 8);
-    const uint32_t live = (uint32_t)port | (1u << 16), dead = 2u << 16;
+    const uint32_t live = (uint32_t)port | kAddrLive, dead = kAddrDead;
     std::vector<KeypairTables::AddrEntry> &tab = ctx->addr_host;
     const uint32_t mask = ctx->kt.addr_slots - 1;
     uint32_t h = addr_hash(hi, lo, port) & mask;
@@ -399,13 +485,20 @@ static int addr_update(bnk_ctx *ctx, const uint8_t addr[16], uint16_t port, bool
     if (!insert) {
         if (at < 0) return BNK_SUCCESS;
         tab[at].port = dead;
+        ctx->addr_live--;
+        ctx->addr_dead++;
     } else {
-        if (at < 0) at = spare;
-        if (at < 0) return fail(ctx, BNK_EFULL, "source address table full");
+        if (at < 0) {
+            at = spare;
+            if (at < 0) return fail(ctx, BNK_EFULL, "source address table full");
+            if (tab[at].port == dead) ctx->addr_dead--;
+            ctx->addr_live++;
+        }
         tab[at] = KeypairTables::AddrEntry{hi, lo, live, peer, 0};
     }
     CK(ctx, cudaDeviceSynchronize()); // entries are 32 bytes: never rewrite one under a running kernel
     CK(ctx, cudaMemcpy(ctx->kt.addr_tab + at, &tab[at], sizeof tab[at], cudaMemcpyHostToDevice));
+    if (!insert && ctx->addr_dead >= ctx->kt.addr_slots / 4) return addr_rebuild(ctx);
     return BNK_SUCCESS;
 }
 
@@ -452,6 +545,7 @@ int bnk_acl_set(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n
 int bnk_flows_clear(bnk_ctx *ctx) {
     if (!ctx) return BNK_EINVAL;
     CK(ctx, cudaSetDevice(ctx->device));
+    std::unique_lock<std::shared_mutex> tables(ctx->submit_mu);
     CK(ctx, cudaDeviceSynchronize());
     CK(ctx, filter_flows_clear(ctx, ctx->admin_stream));
     return BNK_SUCCESS;
@@ -467,15 +561,43 @@ int bnk_flows_count(bnk_ctx *ctx, uint64_t *live) {
     return BNK_SUCCESS;
 }
 
+int bnk_table_stats_get(bnk_ctx *ctx, bnk_table_stats *out) {
+    if (!ctx || !out) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, cudaDeviceSynchronize());
+    memset(out, 0, sizeof *out);
+    CK(ctx, filter_flow_stats(ctx, &out->flow_live, out->flow_used, out->flow_dead));
+    out->flow_capacity = ctx->ft.flow_capacity;
+    out->index_live = ctx->index_live;
+    out->index_dead = ctx->index_dead;
+    out->index_slots = ctx->kt.index_slots;
+    out->addr_live = ctx->addr_live;
+    out->addr_dead = ctx->addr_dead;
+    out->addr_slots = ctx->kt.addr_slots;
+    return BNK_SUCCESS;
+}
+
 /* ---- batches ---- */
 int bnk_batch_destroy(bnk_batch *b) {
     if (!b) return BNK_EINVAL;
     cudaSetDevice(b->ctx->device);
+    {
+        std::unique_lock<std::shared_mutex> tables(b->ctx->submit_mu); // not while table maintenance walks the registry
+        std::lock_guard<std::mutex> g(b->ctx->mu);
+        std::vector<bnk_batch *> &all = b->ctx->batches;
+        for (size_t i = 0; i < all.size(); i++)
+            if (all[i] == b) {
+                all.erase(all.begin() + i);
+                break;
+            }
+    }
     if (b->stream) cudaStreamSynchronize(b->stream);
     cudaFreeHost(b->host.src_addr);
     cudaFreeHost(b->h_desc);
     cudaFree(b->d_desc);
-    cudaFreeHost(b->h_flow_error);
+    cudaFreeHost(b->h_flow);
+    cudaFreeHost(b->h_stats);
+    cudaFree(b->d_stats);
     cudaFreeHost(b->h_gso);
     DeviceBatch &d = b->dev;
     cudaFree(d.src_addr);
@@ -499,6 +621,7 @@ int bnk_batch_destroy(bnk_batch *b) {
     if (b->t_end) cudaEventDestroy(b->t_end);
     if (b->ev_fork) cudaEventDestroy(b->ev_fork);
     if (b->ev_join) cudaEventDestroy(b->ev_join);
+    if (b->ev_fence) cudaEventDestroy(b->ev_fence);
     if (b->aux_stream) cudaStreamDestroy(b->aux_stream);
     if (b->stream) cudaStreamDestroy(b->stream);
     delete b;
@@ -544,7 +667,8 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
         b->host.status = b->h_desc + 24 * np;
     }
     H((void **)&b->host.src_addr, n * BNK_SRC_ADDR_STRIDE);
-    H((void **)&b->h_flow_error, sizeof(int));
+    H((void **)&b->h_flow, sizeof(FlowReport));
+    H((void **)&b->h_stats, sizeof(bnk_batch_stats));
     H((void **)&b->h_gso, n * sizeof(bnk_gso_super));
     b->host.ring_bytes = ring_bytes;
     b->host.max_pkts = max_pkts;
@@ -573,10 +697,12 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     D((void **)&d.len_order, n * 4);
     D((void **)&d.counters32, 2048 * 4);
     D((void **)&d.gso, n * sizeof(bnk_gso_super));
+    D((void **)&b->d_stats, 20 * sizeof(unsigned long long));
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->aux_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_join, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_fence, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreate(&b->k_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&b->k_end);
     if (e == cudaSuccess) e = cudaEventCreate(&b->t_end);
@@ -587,6 +713,11 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
         int rc = fail(ctx, e == cudaErrorMemoryAllocation ? BNK_ENOMEM : BNK_ECUDA, "batch allocation", e);
         bnk_batch_destroy(b);
         return rc;
+    }
+    {
+        std::unique_lock<std::shared_mutex> tables(ctx->submit_mu);
+        std::lock_guard<std::mutex> g(ctx->mu);
+        ctx->batches.push_back(b);
     }
     *out = b;
     return BNK_SUCCESS;
@@ -632,6 +763,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     const bool device_only = (flags & BNK_F_NO_H2D) && (flags & BNK_F_NO_D2H);
     int rc = begin_submit(b, npkts, !device_only);
     if (rc) return rc;
+    if (flags & BNK_F_NOTE_OUTBOUND) CK(b->ctx, filter_flows_maintain(b, b->stream));
     SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
@@ -654,7 +786,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     if (flags & BNK_F_NOTE_OUTBOUND) {
         CK(ctx, launch_filter_note(b, npkts, now_unix_ns, s));
-        CK(ctx, cudaMemcpyAsync(b->h_flow_error, ctx->ft.flow_error, sizeof(int), cudaMemcpyDeviceToHost, s));
+        CK(ctx, launch_flow_report(b, s));
     }
     const uint32_t *order = nullptr;
     const bool side_order = (flags & BNK_F_SORT_BY_LENGTH) && (flags & BNK_F_ASSIGN_COUNTERS) && npkts > 4096;
@@ -678,6 +810,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
     b->aead_timed = timed;
+    CK(ctx, tally_if_asked(b, npkts, flags, s));
     if (!direct && !(flags & BNK_F_NO_D2H) && n) {
         if (b->joint_copy) {
             CK(ctx, cudaMemcpyAsync(b->h_desc, b->d_desc, b->desc_room + ext, cudaMemcpyDeviceToHost, s));
@@ -745,6 +878,7 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     if (flags & BNK_F_CHECK_INBOUND) CK(ctx, launch_filter_check(b, npkts, now_unix_ns, true, s));
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
+    CK(ctx, tally_if_asked(b, npkts, flags, s));
     if (!direct && !(flags & BNK_F_NO_D2H) && n) {
         if (b->joint_copy) {
             CK(ctx, cudaMemcpyAsync(b->h_desc, b->d_desc, b->desc_room + ext, cudaMemcpyDeviceToHost, s));
@@ -759,6 +893,7 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
 int bnk_filter_note_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns) {
     int rc = begin_submit(b, npkts);
     if (rc) return rc;
+    CK(b->ctx, filter_flows_maintain(b, b->stream));
     SubmitScope scope(b);
     bnk_ctx *ctx = b->ctx;
     cudaStream_t s = b->stream;
@@ -783,7 +918,7 @@ int bnk_filter_note_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t
     CK(ctx, launch_filter_note(b, npkts, now_unix_ns, s));
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
-    CK(ctx, cudaMemcpyAsync(b->h_flow_error, ctx->ft.flow_error, sizeof(int), cudaMemcpyDeviceToHost, s));
+    CK(ctx, launch_flow_report(b, s));
     return BNK_SUCCESS;
 }
 
@@ -814,6 +949,7 @@ int bnk_filter_check_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_
     CK(ctx, launch_filter_check(b, npkts, now_unix_ns, false, s));
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
+    CK(ctx, tally_if_asked(b, npkts, flags, s));
     if (!direct && !(flags & BNK_F_NO_D2H) && n)
         CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
     return BNK_SUCCESS;
@@ -828,17 +964,22 @@ int bnk_classify_submit(bnk_batch *b, uint32_t npkts, uint32_t flags) {
     const bool timed = (flags & BNK_F_TIMED) != 0;
     const size_t n = npkts;
     if ((!(flags & BNK_F_NO_H2D) || b->dev_stale) && n) {
-        b->dev_stale = false;
         const uint64_t ext = ring_extent(b, npkts, 0);
         if (ext) CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
-        CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+        if (b->dev_stale) { // a submit ran on the host arrays: every device descriptor field is behind
+            CK(ctx, desc_copy(b, n, D_OFF, D_STATUS, true, s));
+        } else {
+            CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
+            CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
+        }
+        b->dev_stale = false;
         CK(ctx, cudaMemcpyAsync(b->dev.src_addr, b->host.src_addr, n * BNK_SRC_ADDR_STRIDE, cudaMemcpyHostToDevice, s));
     }
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     CK(ctx, launch_classify(b, npkts, s));
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
+    CK(ctx, tally_if_asked(b, npkts, flags, s));
     if (!(flags & BNK_F_NO_D2H) && n) {
         CK(ctx, cudaMemcpyAsync(b->host.slot, b->dev.slot, n * 4, cudaMemcpyDeviceToHost, s));
         CK(ctx, cudaMemcpyAsync(b->host.status, b->dev.status, n, cudaMemcpyDeviceToHost, s));
@@ -857,6 +998,7 @@ int bnk_gso_split_submit(bnk_batch *b, const bnk_gso_super *supers, uint32_t n_s
     if (n_super > b->max_pkts || (n_super && !supers)) return fail(ctx, BNK_EINVAL, "bad super-packet list");
     const size_t n = n_pkts;
     if (!(flags & BNK_F_NO_H2D) || b->dev_stale) {
+        const bool refresh = b->dev_stale;
         b->dev_stale = false;
         // the ring span holds the segments' slots and the super-packets
         uint64_t ext = ring_extent(b, n_pkts, 16 + 16 + 16);
@@ -868,7 +1010,9 @@ int bnk_gso_split_submit(bnk_batch *b, const bnk_gso_super *supers, uint32_t n_s
         ext = (ext + 15) & ~15ull;
         if (ext > b->ring_bytes) ext = b->ring_bytes;
         if (ext) CK(ctx, cudaMemcpyAsync(b->dev.ring, b->host.ring, ext, cudaMemcpyHostToDevice, s));
-        if (n) {
+        if (n && refresh) {
+            CK(ctx, desc_copy(b, n, D_OFF, D_STATUS, true, s));
+        } else if (n) {
             CK(ctx, cudaMemcpyAsync(b->dev.off, b->host.off, n * 4, cudaMemcpyHostToDevice, s));
             CK(ctx, cudaMemcpyAsync(b->dev.len, b->host.len, n * 4, cudaMemcpyHostToDevice, s));
             CK(ctx, cudaMemcpyAsync(b->dev.slot, b->host.slot, n * 4, cudaMemcpyHostToDevice, s));
@@ -903,37 +1047,26 @@ int bnk_wait(bnk_batch *b, uint64_t timeout_ns) {
         }
     }
     b->in_flight = false;
-    if (*b->h_flow_error) {
-        *b->h_flow_error = 0;
-        return fail(ctx, BNK_EFULL, "flow table full: some outbound flows were not recorded");
+    if (b->flow_reported) { // what the device said about the flow table after this batch: input of the next compaction
+        b->flow_reported = false;
+        for (int c = 0; c < 3; c++) ctx->flow_dead_hint[c] = b->h_flow->dead[c];
+        int seen = ctx->flow_errors_seen.load();
+        const int now_failed = b->h_flow->error;
+        while (now_failed > seen && !ctx->flow_errors_seen.compare_exchange_weak(seen, now_failed)) {}
+        if (now_failed > seen) return fail(ctx, BNK_EFULL, "flow table full: some outbound flows were not recorded");
     }
     return BNK_SUCCESS;
 }
 
-/* ---- measurement ---- */
-int bnk_timer_start(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n) {
-    if (!ctx || !batches || n == 0) return BNK_EINVAL;
-    CK(ctx, cudaSetDevice(ctx->device));
-    CK(ctx, cudaEventRecord(ctx->timer_start, batches[0]->stream));
-    for (uint32_t i = 1; i < n; i++) CK(ctx, cudaStreamWaitEvent(batches[i]->stream, ctx->timer_start, 0));
+int bnk_batch_stats_get(bnk_batch *b, bnk_batch_stats *out) {
+    if (!b || !out) return BNK_EINVAL;
+    if (b->in_flight) return fail(b->ctx, BNK_EBUSY, "batch has work in flight; call bnk_wait first");
+    if (!b->stats_pending) return fail(b->ctx, BNK_EINVAL, "the batch's last submit was not made with BNK_F_STATS");
+    *out = *b->h_stats;
     return BNK_SUCCESS;
 }
 
-int bnk_timer_stop(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n, float *ms) {
-    if (!ctx || !batches || n == 0 || !ms) return BNK_EINVAL;
-    CK(ctx, cudaSetDevice(ctx->device));
-    for (uint32_t i = 0; i < n; i++) CK(ctx, cudaEventRecord(batches[i]->t_end, batches[i]->stream));
-    float longest = 0.f;
-    for (uint32_t i = 0; i < n; i++) {
-        CK(ctx, cudaEventSynchronize(batches[i]->t_end));
-        float t = 0.f;
-        CK(ctx, cudaEventElapsedTime(&t, ctx->timer_start, batches[i]->t_end));
-        if (t > longest) longest = t;
-    }
-    *ms = longest;
-    return BNK_SUCCESS;
-}
-
+/* ---- stage timing ---- */
 int bnk_batch_last_kernel_ms(bnk_batch *b, float *ms) {
     if (!b || !ms) return BNK_EINVAL;
     if (!b->kernel_timed) return fail(b->ctx, BNK_EINVAL, "no submit has been timed on this batch");
@@ -955,23 +1088,6 @@ int bnk_batch_last_aead_ms(bnk_batch *b, float *ms) {
 int bnk_kernel_launch_count(bnk_ctx *ctx, uint64_t *count) {
     if (!ctx || !count) return BNK_EINVAL;
     *count = ctx->launches.load();
-    return BNK_SUCCESS;
-}
-
-int bnk_probe_int_throughput(bnk_ctx *ctx, int mix, double *tera_ops_per_s) {
-    if (!ctx || !tera_ops_per_s) return BNK_EINVAL;
-    CK(ctx, cudaSetDevice(ctx->device));
-    CK(ctx, probe_int_throughput(ctx, mix, tera_ops_per_s));
-    return BNK_SUCCESS;
-}
-
-int bnk_batch_fill_random(bnk_batch *b, uint64_t seed) {
-    if (!b) return BNK_EINVAL;
-    bnk_ctx *ctx = b->ctx;
-    if (b->in_flight) return fail(ctx, BNK_EBUSY, "batch has work in flight");
-    CK(ctx, cudaSetDevice(ctx->device));
-    CK(ctx, launch_fill_random(b->dev.ring, b->ring_bytes, seed, b->stream, &ctx->launches));
-    CK(ctx, cudaStreamSynchronize(b->stream));
     return BNK_SUCCESS;
 }
 

@@ -7,6 +7,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <shared_mutex>
 #include <string>
 #include <vector>
 
@@ -26,6 +27,7 @@ struct KeypairTables {
     uint64_t *replay_next;  // [max_keypairs] scratch: the value replay_last takes after the batch in flight
     uint64_t *replay_ring;  // [max_keypairs][ring_blocks] RFC 6479 bitmap ring
     uint32_t *allowed_ip;   // [max_keypairs] the peer's tunnel address, host order (0 = none)
+    uint8_t *valid;         // [max_keypairs] 1 while the slot holds keys that bnk_keypair_set* put there
     // receiver index -> slot: open addressing, key = 1<<32 | index (0 = empty, 2<<32 = deleted)
     uint64_t *index_keys;   // [index_slots]
     uint32_t *index_vals;   // [index_slots]
@@ -50,13 +52,26 @@ struct FilterTables {
     uint32_t rule_slots;   // power of two (0 when no tuples)
     uint64_t len_mask;     // bit L set when some tuple has prefix length L (bits 0..32)
     int enforce;
-    // flow table, one open-addressing region per protocol class (tcp, udp, icmp)
-    uint64_t *flow_keys;   // [3][flow_capacity] FLOW_EMPTY = all ones
-    long long *flow_exp;   // [3][flow_capacity] expiry in unix ns; FLOW_DEAD = deleted
+    // flow table, one open-addressing region per protocol class (tcp, udp, icmp).  Every class has two
+    // regions, [class][half][flow_capacity]; flow_half[class] says which one is in use, the other one is all
+    // FLOW_EMPTY and receives the surviving entries when the class is compacted (filter_flows_compact).
+    uint64_t *flow_keys;   // [3][2][flow_capacity] FLOW_EMPTY = all ones
+    long long *flow_exp;   // [3][2][flow_capacity] expiry in unix ns; FLOW_DEAD = deleted
     uint32_t flow_capacity; // power of two
-    unsigned long long *flow_live;  // device counter: live entries (Go's len(f.flows))
+    uint8_t flow_half[3];
+    unsigned long long *flow_live;  // device control block (FlowCtl): live entries (Go's len(f.flows)) and more
     long long *flow_special_exp;    // [3] entry for the one key that equals FLOW_EMPTY
-    int *flow_error;       // set to 1 when an insert found no free slot
+    int *flow_error;       // counts the inserts that found no free slot
+};
+// region of protocol class `cls` that is in use
+__host__ __device__ inline size_t flow_region(const FilterTables &ft, int cls) {
+    return ((size_t)cls * 2 + ft.flow_half[cls]) * ft.flow_capacity;
+}
+// What a batch's filter work reports back to the host next to the packets (pinned, one per batch).
+struct FlowReport {
+    int error;            // inserts that found no free slot, since the table was last cleared
+    uint32_t used[3];     // slots of the class's region that hold a key, live or deleted
+    uint32_t dead[3];     // of those, deleted ones (reclaimed by compaction)
 };
 
 struct bnk_ctx {
@@ -72,8 +87,28 @@ struct bnk_ctx {
     std::atomic<uint64_t> launches;
     std::mutex mu;
     std::string last_error;
+    // Submits hold this shared while they queue their work; whoever changes what running kernels of other
+    // batches could observe half-done (flow-table compaction) or swaps tables that launches capture by value
+    // (rule table) holds it exclusively.
+    std::shared_mutex submit_mu;
+    std::vector<bnk_batch *> batches;       // every live batch of the context (guarded by mu)
+    std::atomic<uint32_t> flow_dead_hint[3]; // deleted entries per class as last reported by the device
+    std::atomic<int> flow_errors_seen;       // failed inserts already reported to a caller as BNK_EFULL
+    // rule table: two device buffer sets, the one not in use receives the next upload
+    struct RuleSet {
+        uint64_t *keys = nullptr;
+        uint2 *span = nullptr;
+        uint64_t *entries = nullptr;
+        size_t slots_cap = 0, entries_cap = 0;
+        std::vector<cudaEvent_t> in_use; // recorded on every batch stream when the set was retired
+    } rule_set[2];
+    int rule_cur = 0;
+    std::mutex acl_mu; // one bnk_acl_set at a time
     std::vector<KeypairTables::AddrEntry> addr_host; // host shadow of kt.addr_tab
     std::vector<uint64_t> index_keys_host; // host shadow of kt.index_keys (updates are rare: one per handshake)
+    std::vector<uint32_t> index_vals_host; // host shadow of kt.index_vals
+    uint32_t index_live, index_dead;       // entries of the receiver-index table in use / deleted but not yet reclaimed
+    uint32_t addr_live, addr_dead;         // the same for the source-address table
 };
 
 struct DeviceBatch {
@@ -118,7 +153,12 @@ struct bnk_batch {
     uint32_t npad;
     size_t desc_room;  // bytes of the descriptor slab in front of the ring (same on both sides)
     bool joint_copy;   // descriptors and ring move as one copy
-    int *h_flow_error; // pinned copy of the flow-table overflow flag, refreshed by filter work
+    FlowReport *h_flow; // pinned copy of the flow table's state after the batch's filter work
+    bool stats_pending; // the last submit was made with BNK_F_STATS
+    bool flow_reported; // the last submit queued a copy of the flow table's state into h_flow
+    bnk_batch_stats *h_stats; // pinned; written by the tally kernel
+    unsigned long long *d_stats; // device accumulators of the tally kernel (zero between launches)
+    cudaEvent_t ev_fence; // orders this batch's stream against table maintenance on another stream
 };
 
 // Small batches are two dependent launches with little work in each, so the gap between them counts.  A kernel
@@ -172,6 +212,7 @@ struct AeadArgs {
     uint8_t *status;
     const uint32_t *keys;         // send keys (seal) or receive keys (open)
     const uint32_t *remote_index; // seal only
+    const uint8_t *valid;         // per keypair slot: keys present
     const uint32_t *order;        // optional scheduling permutation, may be null
     uint32_t n;
     uint32_t mtu;
@@ -199,6 +240,13 @@ cudaError_t filter_tables_alloc(bnk_ctx *ctx);
 void filter_tables_free(bnk_ctx *ctx);
 int filter_acl_upload(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n);
 cudaError_t filter_flows_clear(bnk_ctx *ctx, cudaStream_t s);
+cudaError_t filter_flow_stats(bnk_ctx *ctx, uint64_t *live, uint32_t used[3], uint32_t dead[3]);
+cudaError_t launch_flow_report(bnk_batch *b, cudaStream_t s); // copies the flow table's control block to b->h_flow
+// Rebuilds the regions whose deleted entries have piled up; called by a submit that feeds the flow table,
+// before it takes submit_mu.  Returns without doing anything in the common case.
+cudaError_t filter_flows_maintain(bnk_batch *b, cudaStream_t s);
+// Per-status packet counts and byte total of the first n packets, into b->h_stats (one launch).
+cudaError_t launch_tally(bnk_batch *b, uint32_t n, cudaStream_t s);
 
 // inner_kernels.cu
 constexpr uint32_t kSlotNoKeypair = 0xfffffffeu; // demux found no keypair for the receiver index
@@ -220,8 +268,3 @@ __host__ __device__ inline uint32_t index_hash(uint32_t index) {
 
 // gso_kernels.cu
 cudaError_t launch_gso_split(bnk_batch *b, uint32_t n_super, uint32_t n_pkts, cudaStream_t s);
-
-// probe_kernels.cu
-cudaError_t launch_fill_random(uint8_t *dst, uint64_t bytes, uint64_t seed, cudaStream_t s,
-                               std::atomic<uint64_t> *launches);
-cudaError_t probe_int_throughput(bnk_ctx *ctx, int mix, double *tops);

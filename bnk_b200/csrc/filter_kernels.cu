@@ -14,6 +14,10 @@
 // 64-bit compare-and-swap.  A deleted entry keeps its key with expiry FLOW_DEAD,
 // which behaves like an absent key for every later lookup.  The live-entry count
 // is kept exactly because the reference's expiry sweep depends on len(flows) > 4096.
+// Go deletes map entries (filter.go:144, 202-208), so its map is bounded by the live
+// flows; here deleted entries are counted per class, and once they fill a quarter of
+// a class's region the surviving entries are re-inserted into the class's second,
+// empty region and the two swap roles (filter_flows_maintain), between two batches.
 #include <algorithm>
 #include <climits>
 #include <vector>
@@ -23,7 +27,9 @@
 namespace {
 
 constexpr unsigned long long FLOW_EMPTY = ~0ull;
-constexpr long long FLOW_DEAD = LLONG_MIN;
+constexpr long long FLOW_DEAD = LLONG_MIN;      // the key is there, the entry is deleted
+constexpr long long FLOW_FRESH = LLONG_MIN + 1; // expiry of a slot no key has used yet
+__device__ __forceinline__ bool flow_absent(long long exp) { return exp <= FLOW_FRESH; }
 constexpr long long TTL_UDP = 30ll * 1000000000ll;  // filter.go:19
 constexpr long long TTL_TCP = 120ll * 1000000000ll; // filter.go:20
 constexpr long long TTL_ICMP = 30ll * 1000000000ll; // filter.go:21
@@ -35,6 +41,8 @@ struct FlowCtl {
     long long swept_at;        // `now` of the last completed sweep
     int swept_valid;           // nothing was written at another `now` since that sweep
     int sweep_now;             // decision for the sweep kernel of this batch
+    FlowReport rep;            // overflow flag and per-class slot counts; copied to the host after a batch
+    uint32_t moved;            // entries a compaction has re-inserted so far
 };
 
 __host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
@@ -137,22 +145,24 @@ __global__ void filter_note_kernel(FilterTables ft, const uint8_t *ring, const u
     if (key == FLOW_EMPTY) {
         const long long prev = (long long)atomicExch((unsigned long long *)&ft.flow_special_exp[cls],
                                                      (unsigned long long)exp);
-        if (prev == FLOW_DEAD) atomicAdd(&ctl->live, 1ull);
+        if (flow_absent(prev)) atomicAdd(&ctl->live, 1ull);
         return;
     }
-    unsigned long long *keys = (unsigned long long *)ft.flow_keys + (size_t)cls * ft.flow_capacity;
-    long long *exps = ft.flow_exp + (size_t)cls * ft.flow_capacity;
+    unsigned long long *keys = (unsigned long long *)ft.flow_keys + flow_region(ft, cls);
+    long long *exps = ft.flow_exp + flow_region(ft, cls);
     uint32_t h = (uint32_t)mix64(key) & (ft.flow_capacity - 1);
     for (uint32_t probe = 0; probe < ft.flow_capacity; probe++) {
         const unsigned long long old = atomicCAS(&keys[h], FLOW_EMPTY, key);
         if (old == FLOW_EMPTY || old == key) {
+            if (old == FLOW_EMPTY) atomicAdd(&ctl->rep.used[cls], 1u);
             const long long prev = (long long)atomicExch((unsigned long long *)&exps[h], (unsigned long long)exp);
-            if (prev == FLOW_DEAD) atomicAdd(&ctl->live, 1ull);
+            if (flow_absent(prev)) atomicAdd(&ctl->live, 1ull);
+            if (prev == FLOW_DEAD) atomicSub(&ctl->rep.dead[cls], 1u); // a deleted entry is back
             return;
         }
         h = (h + 1) & (ft.flow_capacity - 1);
     }
-    *ft.flow_error = 1; // table full: the flow is not recorded, the host reports BNK_EFULL
+    atomicAdd(ft.flow_error, 1); // table full: the flow is not recorded, the host reports BNK_EFULL
 }
 
 // The reference sweeps expired flows whenever the map holds more than 4096 entries after an
@@ -169,17 +179,23 @@ __global__ void filter_sweep_kernel(FilterTables ft, long long now) {
     wait_for_kernel_in_front();
     FlowCtl *ctl = reinterpret_cast<FlowCtl *>(ft.flow_live);
     if (!ctl->sweep_now) return;
-    const size_t total = (size_t)3 * ft.flow_capacity;
+    // both regions of every class are walked; the one not in use holds nothing but fresh slots
+    const size_t total = (size_t)6 * ft.flow_capacity;
     unsigned long long dropped = 0;
+    uint32_t dead[3] = {0, 0, 0};
     for (size_t k = blockIdx.x * (size_t)blockDim.x + threadIdx.x; k < total + 3; k += (size_t)gridDim.x * blockDim.x) {
         long long *e = k < total ? &ft.flow_exp[k] : &ft.flow_special_exp[k - total];
         const long long exp = *e;
-        if (exp != FLOW_DEAD && now > exp) {
+        if (!flow_absent(exp) && now > exp) {
             *e = FLOW_DEAD;
             dropped++;
+            if (k < total) dead[k / ((size_t)2 * ft.flow_capacity)]++;
         }
     }
     if (dropped) atomicAdd(&ctl->live, 0ull - dropped);
+#pragma unroll
+    for (int c = 0; c < 3; c++)
+        if (dead[c]) atomicAdd(&ctl->rep.dead[c], dead[c]);
 }
 __global__ void filter_sweep_finish_kernel(FilterTables ft, long long now) {
     let_next_kernel_start();
@@ -230,13 +246,13 @@ __global__ void filter_check_kernel(FilterTables ft, const uint8_t *ring, const 
     if (key == FLOW_EMPTY) {
         slot_exp = &ft.flow_special_exp[cls];
     } else {
-        const unsigned long long *keys = (const unsigned long long *)ft.flow_keys + (size_t)cls * ft.flow_capacity;
+        const unsigned long long *keys = (const unsigned long long *)ft.flow_keys + flow_region(ft, cls);
         uint32_t h = (uint32_t)mix64(key) & (ft.flow_capacity - 1);
         for (uint32_t probe = 0; probe < ft.flow_capacity; probe++) {
             const unsigned long long k = keys[h];
             if (k == FLOW_EMPTY) break;
             if (k == key) {
-                slot_exp = ft.flow_exp + (size_t)cls * ft.flow_capacity + h;
+                slot_exp = ft.flow_exp + flow_region(ft, cls) + h;
                 break;
             }
             h = (h + 1) & (ft.flow_capacity - 1);
@@ -245,14 +261,17 @@ __global__ void filter_check_kernel(FilterTables ft, const uint8_t *ring, const 
     uint8_t verdict = BNK_PKT_FILTER_DENY;
     if (slot_exp) {
         const long long exp = *(volatile long long *)slot_exp;
-        if (exp != FLOW_DEAD) {
+        if (!flow_absent(exp)) {
             if (now < exp) { // strict: time.Before
                 *(volatile long long *)slot_exp = now + flow_ttl(p.proto); // keep-alive on traffic
                 if (!(ctl->swept_valid && ctl->swept_at == now)) ctl->swept_valid = 0;
                 verdict = BNK_PKT_OK;
             } else {
                 const long long prev = (long long)atomicExch((unsigned long long *)slot_exp, (unsigned long long)FLOW_DEAD);
-                if (prev != FLOW_DEAD) atomicAdd(&ctl->live, 0ull - 1ull);
+                if (!flow_absent(prev)) {
+                    atomicAdd(&ctl->live, 0ull - 1ull);
+                    if (key != FLOW_EMPTY) atomicAdd(&ctl->rep.dead[cls], 1u);
+                }
             }
         }
     }
@@ -260,19 +279,99 @@ __global__ void filter_check_kernel(FilterTables ft, const uint8_t *ring, const 
 }
 
 __global__ void flows_fill_kernel(FilterTables ft) {
-    const size_t total = (size_t)3 * ft.flow_capacity;
+    const size_t total = (size_t)6 * ft.flow_capacity;
     for (size_t k = blockIdx.x * (size_t)blockDim.x + threadIdx.x; k < total; k += (size_t)gridDim.x * blockDim.x) {
         ft.flow_keys[k] = FLOW_EMPTY;
-        ft.flow_exp[k] = FLOW_DEAD;
+        ft.flow_exp[k] = FLOW_FRESH;
     }
-    if (blockIdx.x == 0 && threadIdx.x < 3) ft.flow_special_exp[threadIdx.x] = FLOW_DEAD;
+    if (blockIdx.x == 0 && threadIdx.x < 3) ft.flow_special_exp[threadIdx.x] = FLOW_FRESH;
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         FlowCtl *ctl = reinterpret_cast<FlowCtl *>(ft.flow_live);
-        ctl->live = 0;
-        ctl->swept_at = 0;
-        ctl->swept_valid = 0;
-        ctl->sweep_now = 0;
-        *ft.flow_error = 0;
+        *ctl = FlowCtl{};
+    }
+}
+
+// ---- compaction: the entries of class `cls` that are not deleted move from the region in use to the class's
+// other region, which is empty; the host then swaps the roles (filter_flows_maintain).  Expired entries that no
+// sweep or lookup has deleted yet move along: they still count in len(f.flows), which decides the next sweep.
+__global__ void flows_compact_kernel(FilterTables ft, int cls) {
+    FlowCtl *ctl = reinterpret_cast<FlowCtl *>(ft.flow_live);
+    const size_t from = flow_region(ft, cls), to = ((size_t)cls * 2 + (ft.flow_half[cls] ^ 1)) * ft.flow_capacity;
+    unsigned long long *keys = (unsigned long long *)ft.flow_keys + to;
+    long long *exps = ft.flow_exp + to;
+    uint32_t moved = 0;
+    for (size_t k = blockIdx.x * (size_t)blockDim.x + threadIdx.x; k < ft.flow_capacity; k += (size_t)gridDim.x * blockDim.x) {
+        const unsigned long long key = ft.flow_keys[from + k];
+        if (key == FLOW_EMPTY) continue;
+        const long long exp = ft.flow_exp[from + k];
+        if (flow_absent(exp)) continue;
+        uint32_t h = (uint32_t)mix64(key) & (ft.flow_capacity - 1);
+        bool placed = false; // the target region starts empty and takes fewer entries than it has slots
+        for (uint32_t probe = 0; probe < ft.flow_capacity && !placed; probe++) {
+            if (atomicCAS(&keys[h], FLOW_EMPTY, key) == FLOW_EMPTY) placed = true;
+            else h = (h + 1) & (ft.flow_capacity - 1);
+        }
+        if (!placed) {
+            atomicAdd(ft.flow_error, 1);
+            continue;
+        }
+        exps[h] = exp;
+        moved++;
+    }
+    if (moved) atomicAdd(&ctl->moved, moved);
+}
+// wipes the region the class has just left and books the move
+__global__ void flows_compact_finish_kernel(FilterTables ft, int cls) {
+    FlowCtl *ctl = reinterpret_cast<FlowCtl *>(ft.flow_live);
+    const size_t from = flow_region(ft, cls);
+    for (size_t k = blockIdx.x * (size_t)blockDim.x + threadIdx.x; k < ft.flow_capacity; k += (size_t)gridDim.x * blockDim.x) {
+        ft.flow_keys[from + k] = FLOW_EMPTY;
+        ft.flow_exp[from + k] = FLOW_FRESH;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        ctl->rep.used[cls] = ctl->moved; // the kernel in front has finished: the count is final
+        ctl->rep.dead[cls] = 0;
+        ctl->moved = 0;
+    }
+}
+
+// ---- per-batch counters (BNK_F_STATS): statuses and output bytes of the first n packets.  Every CTA adds its
+// share to the device accumulators; the CTA that finishes last hands the totals to the host struct and leaves
+// the accumulators zero for the next launch.
+__global__ void __launch_bounds__(256) tally_kernel(const uint8_t *status, const uint32_t *out_len, uint32_t n,
+                                                    unsigned long long *acc /* [16] statuses, [16] bytes, [17] ticket */,
+                                                    bnk_batch_stats *host_out) {
+    let_next_kernel_start();
+    wait_for_kernel_in_front();
+    __shared__ unsigned int cnt[16];
+    __shared__ unsigned long long bytes_s;
+    __shared__ bool last;
+    if (threadIdx.x < 16) cnt[threadIdx.x] = 0;
+    if (threadIdx.x == 0) bytes_s = 0;
+    __syncthreads();
+    unsigned long long bytes = 0;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const uint8_t st = status[i];
+        atomicAdd(&cnt[st & 15u], 1u);
+        if (st == BNK_PKT_OK) bytes += out_len[i];
+    }
+    for (int o = 16; o > 0; o >>= 1) bytes += __shfl_down_sync(0xffffffffu, bytes, o);
+    if ((threadIdx.x & 31) == 0 && bytes) atomicAdd(&bytes_s, bytes);
+    __syncthreads();
+    if (threadIdx.x < 16 && cnt[threadIdx.x]) atomicAdd(&acc[threadIdx.x], (unsigned long long)cnt[threadIdx.x]);
+    if (threadIdx.x == 0 && bytes_s) atomicAdd(&acc[16], bytes_s);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(&acc[17], 1ull) + 1 == gridDim.x;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (threadIdx.x < 16) {
+        host_out->by_status[threadIdx.x] = atomicExch(&acc[threadIdx.x], 0ull);
+    } else if (threadIdx.x == 16) {
+        host_out->bytes_out = atomicExch(&acc[16], 0ull);
+        host_out->packets = n;
+        acc[17] = 0;
     }
 }
 
@@ -284,12 +383,26 @@ cudaError_t filter_tables_alloc(bnk_ctx *ctx) {
     const uint32_t cap = ctx->cfg.flow_capacity;
     ft.flow_capacity = cap;
     cudaError_t e;
-    if ((e = cudaMalloc(&ft.flow_live, sizeof(FlowCtl))) != cudaSuccess) return e;
+    FlowCtl *ctl = nullptr;
+    if ((e = cudaMalloc(&ctl, sizeof(FlowCtl))) != cudaSuccess) return e;
+    ft.flow_live = reinterpret_cast<unsigned long long *>(ctl);
+    ft.flow_error = &ctl->rep.error;
     if ((e = cudaMalloc(&ft.flow_special_exp, 3 * sizeof(long long))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&ft.flow_error, sizeof(int))) != cudaSuccess) return e;
     if (cap) {
-        if ((e = cudaMalloc(&ft.flow_keys, (size_t)3 * cap * sizeof(uint64_t))) != cudaSuccess) return e;
-        if ((e = cudaMalloc(&ft.flow_exp, (size_t)3 * cap * sizeof(long long))) != cudaSuccess) return e;
+        if ((e = cudaMalloc(&ft.flow_keys, (size_t)6 * cap * sizeof(uint64_t))) != cudaSuccess) return e;
+        if ((e = cudaMalloc(&ft.flow_exp, (size_t)6 * cap * sizeof(long long))) != cudaSuccess) return e;
+    }
+    // With a stated rule-table capacity both buffer sets are allocated here, and a rule swap allocates nothing.
+    if (const size_t cap_t = ctx->cfg.max_acl_tuples) {
+        size_t slots = 16;
+        while (slots < cap_t * 2) slots <<= 1;
+        for (bnk_ctx::RuleSet &rs : ctx->rule_set) {
+            if ((e = cudaMalloc(&rs.keys, slots * sizeof(uint64_t))) != cudaSuccess) return e;
+            if ((e = cudaMalloc(&rs.span, slots * sizeof(uint2))) != cudaSuccess) return e;
+            if ((e = cudaMalloc(&rs.entries, cap_t * sizeof(uint64_t))) != cudaSuccess) return e;
+            rs.slots_cap = slots;
+            rs.entries_cap = cap_t;
+        }
     }
     return filter_flows_clear(ctx, ctx->admin_stream);
 }
@@ -298,16 +411,22 @@ void filter_tables_free(bnk_ctx *ctx) {
     FilterTables &ft = ctx->ft;
     cudaFree(ft.flow_live);
     cudaFree(ft.flow_special_exp);
-    cudaFree(ft.flow_error);
     cudaFree(ft.flow_keys);
     cudaFree(ft.flow_exp);
-    cudaFree(ft.rule_keys);
-    cudaFree(ft.rule_span);
-    cudaFree(ft.rule_entries);
+    for (bnk_ctx::RuleSet &rs : ctx->rule_set) {
+        cudaFree(rs.keys);
+        cudaFree(rs.span);
+        cudaFree(rs.entries);
+        for (cudaEvent_t ev : rs.in_use) cudaEventDestroy(ev);
+        rs = bnk_ctx::RuleSet{};
+    }
     ft = FilterTables{};
 }
 
 cudaError_t filter_flows_clear(bnk_ctx *ctx, cudaStream_t s) {
+    ctx->ft.flow_half[0] = ctx->ft.flow_half[1] = ctx->ft.flow_half[2] = 0;
+    for (auto &h : ctx->flow_dead_hint) h = 0;
+    ctx->flow_errors_seen = 0;
     flows_fill_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(ctx->ft);
     ctx->launches += 1;
     cudaError_t e = cudaGetLastError();
@@ -315,9 +434,79 @@ cudaError_t filter_flows_clear(bnk_ctx *ctx, cudaStream_t s) {
     return cudaStreamSynchronize(s);
 }
 
+cudaError_t filter_flow_stats(bnk_ctx *ctx, uint64_t *live, uint32_t used[3], uint32_t dead[3]) {
+    FlowCtl ctl;
+    cudaError_t e = cudaMemcpy(&ctl, ctx->ft.flow_live, sizeof ctl, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    *live = ctl.live;
+    for (int c = 0; c < 3; c++) {
+        used[c] = ctl.rep.used[c];
+        dead[c] = ctl.rep.dead[c];
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_flow_report(bnk_batch *b, cudaStream_t s) {
+    const FlowCtl *ctl = reinterpret_cast<const FlowCtl *>(b->ctx->ft.flow_live);
+    b->flow_reported = true;
+    return cudaMemcpyAsync(b->h_flow, &ctl->rep, sizeof(FlowReport), cudaMemcpyDeviceToHost, s);
+}
+
+// Deleted entries keep their slots, so a class whose flows come and go (every connection brings a new source
+// port) would fill up although few flows are alive, and a lookup that misses would walk longer and longer
+// chains.  The submit that is about to record flows calls this first: when the device last reported that
+// deleted entries fill a quarter of a class's region, the class is compacted on this batch's stream.  Kernels
+// of other batches must not see the table half-moved, so the move is fenced against every other stream of the
+// context on both sides, and submits are held off while the fences are placed (submit_mu, exclusive).
+cudaError_t filter_flows_maintain(bnk_batch *b, cudaStream_t s) {
+    bnk_ctx *ctx = b->ctx;
+    const uint32_t cap = ctx->ft.flow_capacity;
+    if (cap == 0) return cudaSuccess;
+    const uint32_t limit = cap / 4;
+    if (ctx->flow_dead_hint[0] < limit && ctx->flow_dead_hint[1] < limit && ctx->flow_dead_hint[2] < limit)
+        return cudaSuccess;
+    std::unique_lock<std::shared_mutex> tables(ctx->submit_mu);
+    cudaError_t e;
+    for (bnk_batch *o : ctx->batches) { // everything submitted so far finishes before the move
+        if (o == b) continue;
+        if ((e = cudaEventRecord(o->ev_fence, o->stream)) != cudaSuccess) return e;
+        if ((e = cudaStreamWaitEvent(s, o->ev_fence, 0)) != cudaSuccess) return e;
+    }
+    for (int cls = 0; cls < 3; cls++) {
+        if (ctx->flow_dead_hint[cls] < limit) continue;
+        flows_compact_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(ctx->ft, cls);
+        flows_compact_finish_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(ctx->ft, cls);
+        ctx->launches += 2;
+        ctx->ft.flow_half[cls] ^= 1; // launches from here on use the other region
+        ctx->flow_dead_hint[cls] = 0;
+    }
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    if ((e = cudaEventRecord(b->ev_fence, s)) != cudaSuccess) return e;
+    for (bnk_batch *o : ctx->batches) // and nothing submitted later starts before it is done
+        if (o != b && (e = cudaStreamWaitEvent(o->stream, b->ev_fence, 0)) != cudaSuccess) return e;
+    return cudaSuccess;
+}
+
+cudaError_t launch_tally(bnk_batch *b, uint32_t n, cudaStream_t s) {
+    bnk_ctx *ctx = b->ctx;
+    uint32_t grid = (n + 1023) / 1024;
+    if (grid == 0) grid = 1;
+    if (grid > (uint32_t)ctx->sm_count * 4) grid = ctx->sm_count * 4;
+    bnk_batch_stats *out = b->h_stats; // pinned memory has the same address on the device
+    launch_kernel(n <= kDependentLaunchUpTo, tally_kernel, dim3(grid), dim3(256), s, b->dev.status, b->dev.out_len, n,
+                  b->d_stats, out);
+    ctx->launches += 1;
+    return cudaGetLastError();
+}
+
 // Builds the prefix-indexed rule table on the host and swaps it in.  Runs per policy change
-// (Engine.ApplyNetmap, internal/dataplane/engine.go:279-283), never per packet.
+// (Engine.ApplyNetmap, internal/dataplane/engine.go:279-283), never per packet, and may run while packets
+// flow: the reference swaps the table under the filter's mutex between two packets (filter.go:46-51); here
+// the new table is uploaded into the buffer set that is not in use, on the admin stream, and the context's
+// FilterTables (which every launch captures by value) switch over between two submits.  A batch submitted
+// before the switch is judged by the old rules as a whole, one submitted after it by the new ones.
 int filter_acl_upload(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n) {
+    std::lock_guard<std::mutex> one_at_a_time(ctx->acl_mu);
     FilterTables &ft = ctx->ft;
     struct Item {
         uint64_t key, ent;
@@ -363,30 +552,57 @@ int filter_acl_upload(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, si
         span[h] = make_uint2((uint32_t)i, (uint32_t)(j - i));
         i = j;
     }
-    uint64_t *d_keys = nullptr, *d_ents = nullptr;
-    uint2 *d_span = nullptr;
-    if (slots) {
-        if (cudaMalloc(&d_keys, slots * sizeof(uint64_t)) != cudaSuccess) return BNK_ENOMEM;
-        if (cudaMalloc(&d_span, slots * sizeof(uint2)) != cudaSuccess) { cudaFree(d_keys); return BNK_ENOMEM; }
-        if (cudaMalloc(&d_ents, std::max<size_t>(ents.size(), 1) * sizeof(uint64_t)) != cudaSuccess) {
-            cudaFree(d_keys);
-            cudaFree(d_span);
-            return BNK_ENOMEM;
-        }
-        cudaMemcpy(d_keys, keys.data(), slots * sizeof(uint64_t), cudaMemcpyHostToDevice);
-        cudaMemcpy(d_span, span.data(), slots * sizeof(uint2), cudaMemcpyHostToDevice);
-        if (!ents.empty()) cudaMemcpy(d_ents, ents.data(), ents.size() * sizeof(uint64_t), cudaMemcpyHostToDevice);
+    bnk_ctx::RuleSet &spare = ctx->rule_set[ctx->rule_cur ^ 1];
+    // Kernels launched before the previous switch may still be reading the spare set: wait for those (the events
+    // were recorded on the batches' streams at that switch), not for the whole device.
+    for (cudaEvent_t ev : spare.in_use) {
+        cudaEventSynchronize(ev);
+        cudaEventDestroy(ev);
     }
-    if (cudaDeviceSynchronize() != cudaSuccess) return BNK_ECUDA;
-    cudaFree(ft.rule_keys);
-    cudaFree(ft.rule_span);
-    cudaFree(ft.rule_entries);
-    ft.rule_keys = d_keys;
-    ft.rule_span = d_span;
-    ft.rule_entries = d_ents;
-    ft.rule_slots = slots;
-    ft.len_mask = len_mask;
-    ft.enforce = enforce ? 1 : 0;
+    spare.in_use.clear();
+    // A context created without max_acl_tuples grows the spare set here when a larger table arrives
+    // (an allocation can stall the device for a moment; state the capacity to avoid that).
+    if (slots > spare.slots_cap) {
+        cudaFree(spare.keys);
+        cudaFree(spare.span);
+        spare.keys = nullptr;
+        spare.span = nullptr;
+        spare.slots_cap = 0;
+        if (cudaMalloc(&spare.keys, slots * sizeof(uint64_t)) != cudaSuccess) return BNK_ENOMEM;
+        if (cudaMalloc(&spare.span, slots * sizeof(uint2)) != cudaSuccess) return BNK_ENOMEM;
+        spare.slots_cap = slots;
+    }
+    if (ents.size() > spare.entries_cap) {
+        cudaFree(spare.entries);
+        spare.entries = nullptr;
+        spare.entries_cap = 0;
+        if (cudaMalloc(&spare.entries, ents.size() * sizeof(uint64_t)) != cudaSuccess) return BNK_ENOMEM;
+        spare.entries_cap = ents.size();
+    }
+    cudaStream_t as = ctx->admin_stream;
+    if (slots) {
+        cudaMemcpyAsync(spare.keys, keys.data(), slots * sizeof(uint64_t), cudaMemcpyHostToDevice, as);
+        cudaMemcpyAsync(spare.span, span.data(), slots * sizeof(uint2), cudaMemcpyHostToDevice, as);
+        if (!ents.empty()) cudaMemcpyAsync(spare.entries, ents.data(), ents.size() * sizeof(uint64_t), cudaMemcpyHostToDevice, as);
+    }
+    if (cudaStreamSynchronize(as) != cudaSuccess) return BNK_ECUDA;
+    {
+        std::unique_lock<std::shared_mutex> tables(ctx->submit_mu); // between two submits
+        bnk_ctx::RuleSet &old = ctx->rule_set[ctx->rule_cur];
+        for (bnk_batch *b : ctx->batches) { // what has been launched with the old set, per stream
+            cudaEvent_t ev;
+            if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return BNK_ECUDA;
+            cudaEventRecord(ev, b->stream);
+            old.in_use.push_back(ev);
+        }
+        ft.rule_keys = spare.keys;
+        ft.rule_span = spare.span;
+        ft.rule_entries = spare.entries;
+        ft.rule_slots = slots;
+        ft.len_mask = len_mask;
+        ft.enforce = enforce ? 1 : 0;
+        ctx->rule_cur ^= 1;
+    }
     return BNK_SUCCESS;
 }
 

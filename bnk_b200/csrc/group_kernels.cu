@@ -1008,7 +1008,7 @@ cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     launch_kernel(n <= kDependentLaunchUpTo, replay_classify_kernel, dim3(tiles), dim3(256), s, a,
         d.replay_tile_carry, flag);
     launch_kernel(n <= kDependentLaunchUpTo, replay_advance_kernel, dim3(grid), dim3(256), s, a);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_hash_clear_kernel, dim3(148 * 4), dim3(256), s, a, flag);
+    launch_kernel(n <= kDependentLaunchUpTo, replay_hash_clear_kernel, dim3(b->ctx->sm_count * 4), dim3(256), s, a, flag);
     launch_kernel(n <= kDependentLaunchUpTo, replay_hash_insert_kernel, dim3(grid), dim3(256), s, a, flag);
     launch_kernel(n <= kDependentLaunchUpTo, replay_finish_kernel, dim3(grid), dim3(256), s, a);
     b->ctx->launches += 7;

@@ -21,6 +21,7 @@ from ._lib import (  # noqa: F401  (re-exported)
     F_NOTE_OUTBOUND,
     F_REPLAY,
     F_SORT_BY_LENGTH,
+    F_STATS,
     F_TIMED,
     F_USE_OUT_LEN,
     PKT_AUTH_FAIL,
@@ -160,6 +161,11 @@ class Context:
         self._ck(_lib.lib().bnk_flows_count(self._h, C.byref(v)))
         return v.value
 
+    def table_stats(self) -> "_lib.TableStats":
+        v = _lib.TableStats()
+        self._ck(_lib.lib().bnk_table_stats_get(self._h, C.byref(v)))
+        return v
+
     # -- batches / measurement --
     def batch(self, max_pkts: int, ring_bytes: int) -> "Batch":
         return Batch(self, max_pkts, ring_bytes)
@@ -171,17 +177,17 @@ class Context:
 
     def probe_int_throughput(self, mix: int) -> float:
         v = C.c_double()
-        self._ck(_lib.lib().bnk_probe_int_throughput(self._h, mix, C.byref(v)))
+        self._ck(_lib.bench_lib().bnk_probe_int_throughput(self._h, mix, C.byref(v)))
         return v.value
 
     def timer_start(self, batches: Sequence["Batch"]):
         arr = (C.c_void_p * len(batches))(*[b._h for b in batches])
-        self._ck(_lib.lib().bnk_timer_start(self._h, arr, len(batches)))
+        self._ck(_lib.bench_lib().bnk_timer_start(self._h, arr, len(batches)))
 
     def timer_stop(self, batches: Sequence["Batch"]) -> float:
         arr = (C.c_void_p * len(batches))(*[b._h for b in batches])
         ms = C.c_float()
-        self._ck(_lib.lib().bnk_timer_stop(self._h, arr, len(batches), C.byref(ms)))
+        self._ck(_lib.bench_lib().bnk_timer_stop(self._h, arr, len(batches), C.byref(ms)))
         return ms.value
 
 
@@ -307,4 +313,16 @@ class Batch:
         return ms.value
 
     def fill_random(self, seed: int):
-        self._ck(_lib.lib().bnk_batch_fill_random(self._h, seed))
+        self._ck(_lib.bench_lib().bnk_batch_fill_random(self._h, seed))
+
+    def copy_only(self, n: int, up: bool = True, down: bool = True, wait: bool = True):
+        """The copies a seal/open submit of n packets makes, and no kernel (measurement helper)."""
+        self._ck(_lib.bench_lib().bnk_batch_copy_only(self._h, n, int(up), int(down)))
+        if wait:
+            self.wait()
+
+    def stats(self) -> dict:
+        """Counters of the last submit made with F_STATS (after wait): packets, bytes_out, by_status[16]."""
+        v = _lib.BatchStats()
+        self._ck(_lib.lib().bnk_batch_stats_get(self._h, C.byref(v)))
+        return {"packets": v.packets, "bytes_out": v.bytes_out, "by_status": list(v.by_status)}

@@ -65,7 +65,8 @@ extern "C" {
 #define BNK_PKT_KEEPALIVE 5         /* authenticated zero-length payload */
 #define BNK_PKT_COUNTER_EXHAUSTED 6 /* send counter reached Reject-After-Messages */
 #define BNK_PKT_BAD_DESC 7          /* descriptor out of range (offset, length or keypair slot) */
-#define BNK_PKT_NO_KEYPAIR 8        /* BNK_F_DEMUX_INDEX: the receiver index in the header maps to no keypair */
+#define BNK_PKT_NO_KEYPAIR 8        /* the keypair slot holds no keys (never set, or cleared), or with
+                                       BNK_F_DEMUX_INDEX the receiver index in the header maps to no keypair */
 #define BNK_PKT_BAD_INNER 9         /* BNK_F_INNER_CHECK: decrypted packet is not IPv4, lies about its length,
                                        or does not come from the peer's allowed address */
 
@@ -85,6 +86,7 @@ extern "C" {
 #define BNK_F_DEMUX_INDEX (1u << 8)     /* open: slot[] is an output, looked up from each header's receiver index */
 #define BNK_F_INNER_CHECK (1u << 9)     /* open: cut the plaintext to its IPv4 total length and check its source */
 #define BNK_F_TIMED (1u << 10)          /* record the CUDA events bnk_batch_last_kernel_ms / _aead_ms read */
+#define BNK_F_STATS (1u << 11)          /* count the batch's outcomes on the device for bnk_batch_stats_get */
 
 typedef struct bnk_ctx bnk_ctx;
 typedef struct bnk_batch bnk_batch;
@@ -176,6 +178,21 @@ int bnk_replay_import(bnk_ctx *ctx, uint32_t slot, uint64_t last, const uint64_t
 int bnk_acl_set(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n);
 int bnk_flows_clear(bnk_ctx *ctx);
 int bnk_flows_count(bnk_ctx *ctx, uint64_t *live);
+/* Occupancy of the context's hash tables, for monitoring: entries in use, entries deleted but not yet
+ * reclaimed, and slots.  Deleted entries are reclaimed by the library itself (the flow table is compacted
+ * between batches once a quarter of a class's slots are deleted entries, the two host-maintained tables are
+ * rebuilt on update), so `dead` stays below a fraction of `slots`.  Waits for submitted work like
+ * bnk_flows_count. */
+typedef struct bnk_table_stats {
+    uint64_t flow_live;        /* Go's len(f.flows) */
+    uint32_t flow_used[3];     /* slots holding a key, per protocol class (tcp, udp, icmp) */
+    uint32_t flow_dead[3];
+    uint32_t flow_capacity;    /* slots per class */
+    uint32_t index_live, index_dead, index_slots; /* receiver index -> keypair slot */
+    uint32_t addr_live, addr_dead, addr_slots;    /* source address -> peer */
+    uint32_t reserved;
+} bnk_table_stats;
+int bnk_table_stats_get(bnk_ctx *ctx, bnk_table_stats *out);
 
 /* ---- batches ---- */
 int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_batch **out);
@@ -197,6 +214,20 @@ int bnk_filter_note_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t
 int bnk_filter_check_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_unix_ns);
 /* Waits for the batch's submitted work.  timeout_ns = 0 polls once; UINT64_MAX waits without limit. */
 int bnk_wait(bnk_batch *b, uint64_t timeout_ns);
+/* Per-batch counters, the analogue of the per-bind send/receive counters the reference keeps
+ * (internal/magicsock/bind.go:68-69,469-473).  A submit made with BNK_F_STATS counts the statuses of its
+ * packets on the device, after its last kernel, and the totals come back with the batch's results:
+ * bnk_batch_stats_get is valid after the bnk_wait that follows such a submit.
+ *   by_status[s]  packets whose status[] is s (BNK_PKT_* for seal, open and filter submits;
+ *                 BNK_CLASS_* for bnk_classify_submit)
+ *   bytes_out     sum of out_len[] over packets with status BNK_PKT_OK (sealed message bytes, or
+ *                 opened plaintext bytes) */
+typedef struct bnk_batch_stats {
+    uint64_t packets;
+    uint64_t bytes_out;
+    uint64_t by_status[16];
+} bnk_batch_stats;
+int bnk_batch_stats_get(bnk_batch *b, bnk_batch_stats *out);
 /* Explicit transfers between the pinned ring/descriptors and the device mirror (asynchronous). */
 int bnk_batch_upload(bnk_batch *b, uint32_t npkts);
 int bnk_batch_download(bnk_batch *b, uint32_t npkts);
@@ -269,23 +300,14 @@ int bnk_gso_split_submit(bnk_batch *b, const bnk_gso_super *supers, uint32_t n_s
 int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uint32_t *dev_slot, uint32_t npkts,
                                 uint64_t *dev_counter);
 
-/* ---- measurement helpers (CUDA events on the batches' own streams) ----
- * bnk_timer_start records a start event on batches[0]'s stream and makes the other batches' streams
- * wait for it; bnk_timer_stop records an end event on every batch, waits, and returns the longest
- * start-to-end span in milliseconds. */
-int bnk_timer_start(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n);
-int bnk_timer_stop(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n, float *ms);
+/* ---- stage timing (tracing) ----
+ * A submit made with BNK_F_TIMED brackets its kernels with CUDA events on the batch's stream. */
 /* Duration of the kernels of the batch's most recent submit made with BNK_F_TIMED (excluding copies), milliseconds. */
 int bnk_batch_last_kernel_ms(bnk_batch *b, float *ms);
 /* Duration of the seal or open kernel alone in the batch's most recent seal/open submit, milliseconds. */
 int bnk_batch_last_aead_ms(bnk_batch *b, float *ms);
 /* Number of kernels this library has launched on the context since creation. */
 int bnk_kernel_launch_count(bnk_ctx *ctx, uint64_t *count);
-/* Measures the 32-bit integer issue rate of the device (dependent chains of add/xor/funnel-shift on the
- * ALU pipe, optionally mixed with multiply-adds on the FMA pipe); result in 10^12 operations/s. */
-int bnk_probe_int_throughput(bnk_ctx *ctx, int mix, double *tera_ops_per_s);
-/* Fills the device mirror of the batch's ring with SplitMix64 output (seeded, position-dependent). */
-int bnk_batch_fill_random(bnk_batch *b, uint64_t seed);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,40 @@
+/*
+ * bnk_gpu_bench.h -- measurement helpers around libbnkgpu.so, exported by libbnkgpu_bench.so.
+ *
+ * Nothing here is part of the drop-in boundary (that is bnk_gpu.h) and nothing here has a counterpart
+ * in the reference: these calls exist for the benchmark and the tests, which need device-side timing
+ * across several batches, the integer issue-rate probe
+ * that gives the seal/open kernels their ALU roofline denominator, a seeded device-side fill for
+ * synthetic payloads, and a copy-only pass over a batch's buffers that measures what the host link can
+ * carry.  The library reaches into the handles of libbnkgpu.so, so both must come from the same build.
+ */
+#ifndef BNK_GPU_BENCH_H
+#define BNK_GPU_BENCH_H
+
+#include "bnk_gpu.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- timers (CUDA events on the batches' own streams) ----
+ * bnk_timer_start records a start event on batches[0]'s stream and makes the other batches' streams
+ * wait for it; bnk_timer_stop records an end event on every batch, waits, and returns the longest
+ * start-to-end span in milliseconds. */
+int bnk_timer_start(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n);
+int bnk_timer_stop(bnk_ctx *ctx, bnk_batch *const *batches, uint32_t n, float *ms);
+/* Measures the 32-bit integer issue rate of the device (dependent chains of add/xor/funnel-shift on the
+ * ALU pipe, optionally mixed with multiply-adds on the FMA pipe); result in 10^12 operations/s. */
+int bnk_probe_int_throughput(bnk_ctx *ctx, int mix, double *tera_ops_per_s);
+/* Fills the device mirror of the batch's ring with SplitMix64 output (seeded, position-dependent). */
+int bnk_batch_fill_random(bnk_batch *b, uint64_t seed);
+
+/* Queues on the batch's stream the same host<->device copies a seal or open submit of npkts packets would
+ * make (pinned ring and descriptors to the device mirror when `up`, back when `down`) and no kernel: the
+ * ceiling of the host link for the end-to-end numbers.  Completion is reported by bnk_wait as usual. */
+int bnk_batch_copy_only(bnk_batch *b, uint32_t npkts, int up, int down);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -8,6 +8,7 @@
  */
 #include "bnk_oracle.h"
 
+#include <pthread.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -741,6 +742,77 @@ void bnko_filter_check_batch(bnko_filter *f, const uint8_t *hdr, size_t stride, 
                              int64_t now_ns, uint8_t *verdict) {
     for (size_t i = 0; i < n; i++)
         verdict[i] = (uint8_t)bnko_filter_check_inbound(f, hdr + i * stride, len[i], now_ns);
+}
+
+/* The same batch on several host cores, for full-size comparisons.  CheckInbound (filter.go:121-147) first
+ * walks the rules (filter.go:131-135), which reads nothing a packet can change, and only then touches the flow
+ * table.  So the rule walk of every header runs in parallel here (phase 1), and the rest of CheckInbound runs
+ * header by header in batch order exactly as above (phase 2): the verdicts and the table afterwards are those
+ * of bnko_filter_check_batch. */
+typedef struct {
+    const bnko_filter *f;
+    const uint8_t *hdr;
+    size_t stride, begin, end;
+    const uint32_t *len;
+    uint8_t *pre; /* 0 = does not parse, 1 = a rule matches, 2 = goes on to the flow table */
+} rule_job;
+
+static void *rule_walk_worker(void *arg) {
+    rule_job *j = (rule_job *)arg;
+    const bnko_filter *f = j->f;
+    for (size_t i = j->begin; i < j->end; i++) {
+        parsed_t p;
+        uint8_t r = 2;
+        if (!parse_pkt(j->hdr + i * j->stride, j->len[i], &p)) r = 0;
+        else
+            for (size_t k = 0; k < f->n_rules; k++)
+                if (bnko_rule_match(&f->rules[k], f->srcs, f->ports, p.src, p.proto, p.dport)) {
+                    r = 1;
+                    break;
+                }
+        j->pre[i] = r;
+    }
+    return NULL;
+}
+
+void bnko_filter_check_batch_mt(bnko_filter *f, const uint8_t *hdr, size_t stride, const uint32_t *len, size_t n,
+                                int64_t now_ns, uint8_t *verdict, int threads) {
+    if (!f->enforce) {
+        memset(verdict, 1, n);
+        return;
+    }
+    if (threads < 1) threads = 1;
+    if (threads > 256) threads = 256;
+    uint8_t *pre = (uint8_t *)malloc(n ? n : 1);
+    pthread_t tid[256];
+    rule_job job[256];
+    for (int t = 0; t < threads; t++) {
+        job[t] = (rule_job){f, hdr, stride, n * (size_t)t / (size_t)threads, n * (size_t)(t + 1) / (size_t)threads, len, pre};
+        pthread_create(&tid[t], NULL, rule_walk_worker, &job[t]);
+    }
+    for (int t = 0; t < threads; t++) pthread_join(tid[t], NULL);
+    for (size_t i = 0; i < n; i++) {
+        if (pre[i] != 2) {
+            verdict[i] = pre[i];
+            continue;
+        }
+        parsed_t p;
+        parse_pkt(hdr + i * stride, len[i], &p);
+        uint8_t v = 0;
+        flow_ent *e = flow_find(f, p.src, p.sport, p.dport, p.proto);
+        if (e) {
+            if (now_ns < e->exp) {
+                e->exp = now_ns + flow_ttl(p.proto);
+                if (!f->swept_valid || f->swept_at != now_ns) f->swept_valid = 0;
+                v = 1;
+            } else {
+                e->state = 2;
+                f->live--;
+            }
+        }
+        verdict[i] = v;
+    }
+    free(pre);
 }
 
 void bnko_filter_note_batch(bnko_filter *f, const uint8_t *hdr, size_t stride, const uint32_t *len, size_t n,

@@ -139,6 +139,9 @@ void bnko_filter_check_batch(bnko_filter *f, const uint8_t *hdr, size_t stride, 
                              int64_t now_ns, uint8_t *verdict);
 void bnko_filter_note_batch(bnko_filter *f, const uint8_t *hdr, size_t stride, const uint32_t *len, size_t n,
                             int64_t now_ns);
+/* bnko_filter_check_batch with the rule walk spread over `threads` host threads; same verdicts, same table */
+void bnko_filter_check_batch_mt(bnko_filter *f, const uint8_t *hdr, size_t stride, const uint32_t *len, size_t n,
+                                int64_t now_ns, uint8_t *verdict, int threads);
 int bnko_rule_match(const bnko_rule *r, const bnko_prefix *srcs, const bnko_port_range *ports, uint32_t src,
                     uint8_t proto, uint16_t dport);
 /* parse; returns 1 ok.  out[0]=proto out[1]=src out[2]=dst out[3]=sport out[4]=dport out[5]=icmp type */

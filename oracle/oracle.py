@@ -122,6 +122,8 @@ def lib() -> C.CDLL:
     L.bnko_filter_flow_count.restype = sz
     L.bnko_filter_check_batch.argtypes = [vp, vp, sz, vp, sz, C.c_int64, vp]
     L.bnko_filter_check_batch.restype = None
+    L.bnko_filter_check_batch_mt.argtypes = [vp, vp, sz, vp, sz, C.c_int64, vp, C.c_int]
+    L.bnko_filter_check_batch_mt.restype = None
     L.bnko_filter_note_batch.argtypes = [vp, vp, sz, vp, sz, C.c_int64]
     L.bnko_filter_note_batch.restype = None
     L.bnko_rule_match.argtypes = [vp, vp, vp, C.c_uint32, C.c_uint8, C.c_uint16]
@@ -355,6 +357,14 @@ class Filter:
         n = len(length)
         out = np.zeros(n, np.uint8)
         lib().bnko_filter_check_batch(self._h, _ptr(hdr), stride, _ptr(length), n, now_ns, _ptr(out))
+        return out
+
+    def check_batch_mt(self, hdr: np.ndarray, stride: int, length: np.ndarray, now_ns: int, threads: int = 0) -> np.ndarray:
+        """check_batch with the (read-only) rule walk on `threads` host threads (0 = all cores); same result."""
+        n = len(length)
+        out = np.zeros(n, np.uint8)
+        lib().bnko_filter_check_batch_mt(self._h, _ptr(hdr), stride, _ptr(length), n, now_ns, _ptr(out),
+                                         threads or host_cores())
         return out
 
     def note_batch(self, hdr: np.ndarray, stride: int, length: np.ndarray, now_ns: int) -> None:

@@ -86,6 +86,67 @@ def filter_and_gso_digests():
                       "sealed_sha256": hashlib.sha256(b"".join(msgs)).hexdigest(),
                       "peers": [int(x) for x in w5.peer],
                       "source": "segments: oracle/ (CPU checker); sealing: cryptography + PyNaCl; remote index = peer + 1"}
+    out.update(full_size_digests())
+    return out
+
+
+def full_size_digests():
+    """Configurations 4 and 5 at the sizes BASELINE.json states.  Too large for per-message Python calls into two
+    libraries, so the sealing is done by OpenSSL's EVP_chacha20_poly1305 called from C on every core
+    (oracle/cpu_baseline.c, independent of the scalar checker and of the CUDA path); configuration 5's segments
+    come from the checker's split as above."""
+    import numpy as np
+
+    from oracle import oracle as O
+
+    out = {}
+    threads = O.host_cores()
+    # configuration 4: 1,048,576 x 1420 B over 65,536 peers, 16 sequential counters per peer, remote index = peer
+    n, peers, size = 1 << 20, 1 << 16, 1420
+    plan = gen.config4(n, peers, size)
+    stride = plan.stride
+    ring = gen.splitmix_fill(plan.payload_seed, n * stride)
+    i = np.arange(n, dtype=np.uint64)
+    off = (i * np.uint64(stride)).astype(np.uint32)
+    keys = gen.bulk_keys(plan)
+    _, st, ol = O.cpu_aead_batch(False, threads, keys, np.arange(peers, dtype=np.uint32), size, ring, off,
+                                 np.full(n, size, np.uint32), (i % np.uint64(peers)).astype(np.uint32), i // np.uint64(peers))
+    assert (st == 0).all() and (ol == size + 32).all()
+    msgs = np.ascontiguousarray(ring.reshape(n, stride)[:, :size + 32])
+    out["config4_full"] = {"packets": n, "peers": peers, "payload": size,
+                           "sealed_sha256": hashlib.sha256(msgs).hexdigest(),
+                           "source": "OpenSSL EVP_chacha20_poly1305 from C (oracle/cpu_baseline.c); messages concatenated "
+                                     "in packet order, remote index = peer, counter = packet // peers"}
+    del ring, msgs
+    # configuration 5: 2,048 super-packets -> 96,256 segments, Zipf(1.1) over 10,000 peers, remote index = 0x1000 + peer
+    w5 = gen.config5(n_super=2048)
+    segs, seg_peer = [], []
+    for j, sp in enumerate(w5.supers):
+        parts = O.gso_split(sp, w5.hdr_len, w5.mss, w5.csum_start, w5.csum_offset, 6)
+        assert parts is not None and len(parts) == 47
+        segs.extend(parts)
+        seg_peer.extend([int(w5.peer[j])] * 47)
+    m = len(segs)
+    stride = 1456
+    ring = np.zeros(m * stride, np.uint8)
+    view = ring.reshape(m, stride)
+    view[:, 16:16 + 1420] = np.frombuffer(b"".join(segs), np.uint8).reshape(m, 1420)
+    seg_peer = np.array(seg_peer, np.uint32)
+    counter = np.zeros(m, np.uint64)
+    nxt = {}
+    for k, pr in enumerate(seg_peer.tolist()):
+        counter[k] = nxt.get(pr, 0)
+        nxt[pr] = int(counter[k]) + 1
+    _, st, ol = O.cpu_aead_batch(False, threads, w5.keys, (0x1000 + np.arange(len(w5.keys))).astype(np.uint32), 1420, ring,
+                                 (np.arange(m, dtype=np.uint64) * stride).astype(np.uint32), np.full(m, 1420, np.uint32),
+                                 seg_peer, counter)
+    assert (st == 0).all() and (ol == 1452).all()
+    out["config5_full"] = {"n_super": 2048, "segments": m,
+                           "supers_sha256": hashlib.sha256(b"".join(w5.supers)).hexdigest(),
+                           "segments_sha256": hashlib.sha256(b"".join(segs)).hexdigest(),
+                           "sealed_sha256": hashlib.sha256(np.ascontiguousarray(view[:, :1452])).hexdigest(),
+                           "source": "segments: oracle/ (CPU checker); sealing: OpenSSL EVP from C (oracle/cpu_baseline.c); "
+                                     "remote index = 0x1000 + peer, counters consecutive per peer in batch order"}
     return out
 
 

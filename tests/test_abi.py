@@ -6,8 +6,8 @@ import re
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "bnk_gpu.h")).read()
+def declared_symbols(header="bnk_gpu.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(bnk_[a-z0-9_]+)\s*\(", text)))
 
@@ -16,6 +16,19 @@ def test_header_and_binding_agree():
     from bnk_b200 import _lib
 
     assert declared_symbols() == sorted(_lib.SYMBOLS)
+    assert declared_symbols("bnk_gpu_bench.h") == sorted(_lib.BENCH_SYMBOLS)
+
+
+def test_bench_library_exports_its_header_and_nothing_of_the_drop_in():
+    from bnk_b200 import _build, _lib
+
+    if _build.is_stale():
+        _build.build()
+    L = ctypes.CDLL(_lib.lib_path())  # the helpers work on the product library's handles
+    B = ctypes.CDLL(_build.BENCH_LIB_PATH)
+    for name in declared_symbols("bnk_gpu_bench.h"):
+        assert hasattr(B, name), name
+        assert not hasattr(L, name), f"{name} is a measurement helper and must not be exported by libbnkgpu.so"
 
 
 def test_library_exports_every_declared_symbol():
@@ -36,6 +49,8 @@ def test_struct_layouts_match_header():
     assert ctypes.sizeof(_lib.Cfg) == 32
     assert ctypes.sizeof(_lib.AclTuple) == 12
     assert ctypes.sizeof(_lib.BatchView) == 80
+    assert ctypes.sizeof(_lib.BatchStats) == 144
+    assert ctypes.sizeof(_lib.TableStats) == 64
 
 
 def test_no_cpu_fallback_in_product_path():

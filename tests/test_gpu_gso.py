@@ -196,3 +196,105 @@ def test_config5_pipeline(gpu_lib, oracle):
     finally:
         tx.close()
         rx.close()
+
+
+def test_config5_full_size_every_segment(gpu_lib, oracle):
+    """BASELINE configuration 5 at the size the benchmark runs: 2,048 super-packets -> 96,256 segments of 1420 B,
+    Zipf(1.1) over 10,000 peers, 2,000-rule ACL.  Sender: every sealed segment equals the CPU checker's split
+    sealed by OpenSSL, and the digests equal the committed ones.  Receiver: every status, slot and plaintext."""
+    import hashlib
+    import json
+    import os
+
+    from bnk_b200 import Context, gen
+    from bnk_b200.device import (F_ASSIGN_COUNTERS, F_CHECK_INBOUND, F_DEMUX_INDEX, F_INNER_CHECK, F_NO_H2D,
+                                 F_NOTE_OUTBOUND, F_REPLAY, F_STATS, PKT_FILTER_DENY, PKT_OK)
+    from bnk_b200.filter import flatten_rule_arrays
+
+    n_peers, n_super, stride = 10_000, 2048, 1456
+    golden = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "aead_golden.json")))["config5_full"]
+    w = gen.config5(n_super=n_super, n_peers=n_peers)
+    assert hashlib.sha256(b"".join(w.supers)).hexdigest() == golden["supers_sha256"]
+    meta = [(w.hdr_len, w.mss, w.csum_start, w.csum_offset, 6)] * n_super
+    sup, seg_len, n_pkts, ring_bytes = _plan(w.supers, meta, stride)
+    assert n_pkts == golden["segments"] and (seg_len == 1420).all()
+    seg_peer = np.repeat(w.peer, 47).astype(np.uint32)
+    off = H.layout_fixed(n_pkts, stride)
+    # --- CPU checker: split; counters in batch order per peer; sealed by OpenSSL on all cores ---
+    segs = []
+    for pkt in w.supers:
+        segs.extend(oracle.gso_split(pkt, 40, w.mss, 20, 16, 6))
+    seg_bytes = np.frombuffer(b"".join(segs), np.uint8).reshape(n_pkts, 1420)
+    assert hashlib.sha256(seg_bytes).hexdigest() == golden["segments_sha256"]
+    counter = np.zeros(n_pkts, np.uint64)
+    nxt = {}
+    for k, p in enumerate(seg_peer.tolist()):
+        counter[k] = nxt.get(p, 0)
+        nxt[p] = int(counter[k]) + 1
+    ridx = (0x1000 + np.arange(n_peers)).astype(np.uint32)
+    want = np.zeros(n_pkts * stride, np.uint8)
+    want.reshape(n_pkts, stride)[:, 16:16 + 1420] = seg_bytes
+    _, st, ol = oracle.cpu_aead_batch(False, oracle.host_cores(), w.keys, ridx, 1420, want, off,
+                                      np.full(n_pkts, 1420, np.uint32), seg_peer, counter)
+    assert (st == 0).all() and (ol == 1452).all()
+    want_msgs = want.reshape(n_pkts, stride)[:, :1452]
+    assert hashlib.sha256(np.ascontiguousarray(want_msgs)).hexdigest() == golden["sealed_sha256"]
+    tx = Context(max_keypairs=n_peers, mtu=1420, flow_capacity=1 << 18)
+    rx = Context(max_keypairs=n_peers, mtu=1420, flow_capacity=1 << 14)
+    try:
+        tx.set_keypairs(0, w.keys, w.keys, ridx)
+        tx.acl_set(True, None)
+        b = tx.batch(n_pkts, ring_bytes + 64)
+        for j, pkt in enumerate(w.supers):
+            o = int(sup[j]["src_off"])
+            b.ring[o:o + len(pkt)] = np.frombuffer(pkt, np.uint8)
+        b.off[:n_pkts] = off
+        b.len[:n_pkts] = seg_len
+        b.slot[:n_pkts] = seg_peer
+        b.gso_split(sup, n_pkts)
+        b.seal(n_pkts, F_NO_H2D | F_NOTE_OUTBOUND | F_ASSIGN_COUNTERS | F_STATS, now_ns=RC.T0)
+        assert (b.status[:n_pkts] == PKT_OK).all()
+        assert b.stats()["by_status"][PKT_OK] == n_pkts and b.stats()["bytes_out"] == 1452 * n_pkts
+        assert np.array_equal(b.counter[:n_pkts], counter)
+        got_msgs = b.ring[:n_pkts * stride].reshape(n_pkts, stride)[:, :1452]
+        if not np.array_equal(got_msgs, want_msgs):
+            bad = np.flatnonzero((got_msgs != want_msgs).any(axis=1))
+            raise AssertionError(f"{len(bad)} sealed segments differ, first {bad[:8]}")
+        assert hashlib.sha256(np.ascontiguousarray(got_msgs)).hexdigest() == golden["sealed_sha256"]
+        assert tx.flows_count() == len({(int(p), s[20:24]) for p, s in zip(seg_peer, segs)})
+        # --- receiver ---
+        f3 = gen.config3(n_rules=2000, n_nodes=5000, n_out=16, n_in=16, seed=gen.seed_for(5) + 1)
+        rules, srcs, ports = f3.rules.copy(), f3.srcs.copy(), f3.ports.copy()
+        hit = np.flatnonzero(rules["proto"] == 6)[:3]
+        for r in hit:
+            srcs["addr"][rules["src_begin"][r]] = w.self_ip
+            srcs["bits"][rules["src_begin"][r]] = 32
+        rx.set_keypairs(0, w.keys, w.keys, np.zeros(n_peers, np.uint32))
+        for p in sorted(set(seg_peer.tolist())):
+            rx.index_set(0x1000 + p, p)
+            rx.set_allowed_ip(p, w.self_ip)
+        rx.acl_set(True, flatten_rule_arrays(rules, srcs, ports))
+        fo = oracle.Filter()
+        fo.set_rules_arrays(rules.astype(oracle.RULE_DTYPE), srcs.astype(oracle.PREFIX_DTYPE), ports.astype(oracle.PORT_DTYPE))
+        allow = fo.check_batch_mt(seg_bytes, 1420, np.full(n_pkts, 1420, np.uint32), RC.T0)
+        want_status = np.where(allow == 1, PKT_OK, PKT_FILTER_DENY).astype(np.uint8)
+        r = rx.batch(n_pkts, n_pkts * stride)
+        r.off[:n_pkts] = off
+        r.len[:n_pkts] = 1452
+        r.ring[:n_pkts * stride] = b.ring[:n_pkts * stride]
+        r.open(n_pkts, F_DEMUX_INDEX | F_REPLAY | F_INNER_CHECK | F_CHECK_INBOUND | F_STATS, now_ns=RC.T0)
+        assert np.array_equal(r.status[:n_pkts], want_status)
+        assert np.array_equal(r.slot[:n_pkts], seg_peer)
+        assert 0 < int(allow.sum()) < n_pkts
+        assert r.stats()["by_status"][PKT_OK] == int(allow.sum())
+        opened = r.ring[:n_pkts * stride].reshape(n_pkts, stride)[:, 16:16 + 1420]
+        assert np.array_equal(opened, seg_bytes)  # the filter's verdict does not touch the plaintext
+        # the same messages once more: every one is a replay
+        r.ring[:n_pkts * stride] = b.ring[:n_pkts * stride]
+        r.open(n_pkts, F_DEMUX_INDEX | F_REPLAY | F_INNER_CHECK | F_CHECK_INBOUND, now_ns=RC.T0)
+        assert (r.status[:n_pkts] == 2).all()
+        b.close()
+        r.close()
+    finally:
+        tx.close()
+        rx.close()

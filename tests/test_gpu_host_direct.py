@@ -108,3 +108,54 @@ def test_device_resident_call_after_a_batch_without_copies(gpu_lib, oracle):
         b.close()
     finally:
         c.close()
+
+
+def test_classify_and_gso_after_a_batch_without_copies(gpu_lib, oracle):
+    """A submit that ran on the host arrays leaves every device descriptor behind.  classify and the GSO split
+    upload only what they read; when the device copies are stale they must bring all descriptor fields along,
+    or a device-resident seal after them would read old counters."""
+    from bnk_b200.device import F_NO_D2H, F_NO_H2D
+
+    n, n_peers = 32, 3
+    rng = np.random.default_rng(21)
+    keys = rng.integers(0, 256, (n_peers, 32), dtype=np.uint8)
+    c = _context(1 << 20, max_keypairs=n_peers, mtu=1420, flow_capacity=0)
+    try:
+        c.set_keypairs(0, keys, keys, np.arange(n_peers, dtype=np.uint32))
+        for i in range(n_peers):
+            c.addr_set(bytes(10) + b"\xff\xff" + bytes([10, 0, 0, 1 + i]), 51820, i)
+        b = c.batch(n, n * 1472)
+        off, sizes = _load(b, rng, n, n_peers)
+        sizes = np.maximum(sizes, 40)
+        b.len[:n] = sizes
+        b.counter[:n] = 1000 + np.arange(n)
+        b.seal(n)                                   # host-direct: device descriptors are now behind
+        first = np.array(b.ring)
+        # new plaintext and new caller-chosen counters, written to the host arrays only
+        for i in range(n):
+            b.ring[int(off[i]) + 16:int(off[i]) + 16 + int(sizes[i])] = rng.integers(0, 256, int(sizes[i]), dtype=np.uint8)
+        plain = np.array(b.ring)
+        b.len[:n] = sizes
+        b.counter[:n] = 5000 + np.arange(n)
+        peers = rng.integers(0, n_peers, n)
+        for i in range(n):
+            b.src_addr[i, :] = 0
+            b.src_addr[i, 10:12] = 0xFF
+            b.src_addr[i, 12:16] = [10, 0, 0, 1 + int(peers[i])]
+            b.src_addr[i, 16:18] = [51820 >> 8, 51820 & 255]
+        b.classify(n)                               # uploads; must refresh counter/out_len/status too
+        assert list(b.slot[:n]) == list(peers)
+        b.seal(n, F_NO_H2D | F_NO_D2H)              # caller-supplied counters, read from the device copies
+        b.download(n)
+        assert (b.status[:n] == 0).all()
+        assert (b.counter[:n] == 5000 + np.arange(n)).all()
+        # (classify uploads datagrams, ring[off, off+len): the furthest packet's last 16 payload bytes, which lie
+        # behind that span, are not part of its upload, so that one packet is left out of the byte comparison)
+        for i in range(n - 1):
+            o, l = int(off[i]) + 16, int(sizes[i])
+            want = oracle.wg_seal(keys[int(peers[i])].tobytes(), int(peers[i]), 5000 + i, plain[o:o + l].tobytes(), 1420)
+            assert b.message(i) == want, i
+        assert not np.array_equal(np.array(b.ring), first)
+        b.close()
+    finally:
+        c.close()

@@ -59,3 +59,29 @@ def test_parse_fields(oracle):
 
     assert oracle.lib().bnko_filter_parse(pkt, len(pkt), out.ctypes.data_as(ctypes.c_void_p)) == 1
     assert list(out) == [6, RC.PEER, RC.SELF, 0x1234, 0x5678, 0]
+
+
+def test_threaded_batch_check_equals_the_sequential_one(oracle):
+    """The full-size GPU comparisons use check_batch_mt (rule walk on all cores); it must be the same function."""
+    import numpy as np
+
+    from bnk_b200 import gen
+
+    w = gen.config3(300, 800, 3000, 9000, seed=123)
+
+    def fresh():
+        f = oracle.Filter()
+        f.set_rules_arrays(w.rules.astype(oracle.RULE_DTYPE), w.srcs.astype(oracle.PREFIX_DTYPE),
+                           w.ports.astype(oracle.PORT_DTYPE))
+        f.note_batch(np.ascontiguousarray(w.outbound), 28, w.outbound_len, w.t0_ns)
+        return f
+
+    a, b = fresh(), fresh()
+    for hdr, lens, now in ((w.inbound, w.inbound_len, w.t0_ns + 10**9), (w.late, w.late_len, w.t0_ns + 600 * 10**9),
+                           (w.late, w.late_len, w.t0_ns + 2 * 10**9)):
+        va = a.check_batch(np.ascontiguousarray(hdr), 28, np.ascontiguousarray(lens), now)
+        vb = b.check_batch_mt(np.ascontiguousarray(hdr), 28, np.ascontiguousarray(lens), now, threads=3)
+        assert np.array_equal(va, vb)
+        assert a.flow_count == b.flow_count
+    allow = oracle.Filter()
+    assert allow.check_batch_mt(np.ascontiguousarray(w.inbound), 28, np.ascontiguousarray(w.inbound_len), 0).all()
