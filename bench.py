@@ -38,9 +38,14 @@ HBM_BYTES_PER_PACKET = 2 * SIZE + 32          # seal: read 1420 + write 1452; op
 # 32-bit integer operations per 1420-byte packet: (23 + 1) ChaCha20 blocks x 992 + 90 Poly1305 blocks x 40
 INT_OPS_PER_PACKET = 24 * 992 + 90 * 40
 E2E_BATCHES = 8
-# dram__bytes_read.sum + dram__bytes_write.sum per packet of the seal kernel, from the ncu capture summarised in
-# profiles/ (captured on 131,072 packets; traffic grows in proportion to the packet count); None until measured
-NCU_DRAM_BYTES_PER_PACKET = 2569
+DEVICE_BATCHES = 2  # device-resident legs: batches in flight, each with half of the step's packets
+REGIONS = 5  # timed regions of K steps each; the median one is reported
+# dram__bytes_read.sum + dram__bytes_write.sum of one seal launch, from the ncu captures summarised in profiles/:
+# (packets of the captured launch, bytes).  The figure is a LOWER bound of what a launch moves: whatever part of
+# the output is still dirty in the 126 MB L2 when the launch ends has not reached DRAM yet (about 50 MB, so the
+# larger the launch the smaller the share).  The capture closest in size to the benchmark's launch is used and
+# scaled by the packet count.
+NCU_DRAM_CAPTURES = [(131072, 131072 * 2569)]
 
 
 # ----------------------------------------------------------------------------------------------
@@ -79,6 +84,13 @@ class Dist:
             return v
         t = self.torch.tensor([v], dtype=self.torch.float64, device="cuda" if self.backend == "nccl" else "cpu")
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum(self, v: float) -> float:
+        if self.world == 1:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device="cuda" if self.backend == "nccl" else "cpu")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
         return float(t.item())
 
     def all_true(self, ok: bool) -> bool:
@@ -209,43 +221,63 @@ def cpu_sample(n: int, peers: int, seed: int):
     return ring, off, length, slot, counter, keys, ridx
 
 
-def cpu_seal_open(threads: int, n: int, passes: int):
-    """-> (Gbit/s over seal+open, seconds).  Output is checked against the input round trip."""
-    from oracle import oracle as O
+class CpuArm:
+    """The CPU arm's ring: built once, then sealed and opened in place over and over, as a forwarder's packet
+    buffers are.  One pass = seal all packets, then open them (which restores the plaintext)."""
 
-    ring, off, length, slot, counter, keys, ridx = cpu_sample(n, min(N_PEERS, n // 16), 0xB2000004)
-    first = ring[16:16 + SIZE].copy()
-    total = 0.0
-    for _ in range(passes):
-        s1, st, out_len = O.cpu_aead_batch(False, threads, keys, ridx, SIZE, ring, off, length, slot, counter)
-        ctr = np.zeros(n, np.uint64)
-        s2, st2, _ = O.cpu_aead_batch(True, threads, keys, ridx, SIZE, ring, off, out_len, slot, ctr)
-        assert (st == 0).all() and (st2 == 0).all() and np.array_equal(ctr, counter)
-        assert np.array_equal(ring[16:16 + SIZE], first)
-        total += s1 + s2
-    bits = 2.0 * n * SIZE * 8 * passes
-    return bits / total / 1e9, total
+    def __init__(self, threads: int, n: int):
+        self.threads, self.n = threads, n
+        self.peers = min(N_PEERS, max(1, n // 16))
+        (self.ring, self.off, self.length, self.slot, self.counter, self.keys, self.ridx) = cpu_sample(n, self.peers, 0xB2000004)
+        self.first = self.ring[16:16 + SIZE].copy()
+
+    def passes(self, count: int) -> float:
+        """-> seconds the worker threads took for `count` passes (checked against the round trip)."""
+        from oracle import oracle as O
+
+        total = 0.0
+        for _ in range(count):
+            s1, st, out_len = O.cpu_aead_batch(False, self.threads, self.keys, self.ridx, SIZE, self.ring, self.off,
+                                               self.length, self.slot, self.counter)
+            ctr = np.zeros(self.n, np.uint64)
+            s2, st2, _ = O.cpu_aead_batch(True, self.threads, self.keys, self.ridx, SIZE, self.ring, self.off, out_len,
+                                          self.slot, ctr)
+            assert (st == 0).all() and (st2 == 0).all() and np.array_equal(ctr, self.counter)
+            assert np.array_equal(self.ring[16:16 + SIZE], self.first)
+            total += s1 + s2
+        return total
+
+    def gbps(self, count: int, secs: float) -> float:
+        return 2.0 * self.n * SIZE * 8 * count / secs / 1e9
+
+
+REFERENCE_PASSES_PER_STEP = 3
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
     threads = host_threads()
-    # a bounded sample of the same workload: 16 packets per peer, 1420 B, sized for ~1-2 s per step
+    # a bounded sample of the same workload: 16 packets per peer, 1420 B; every step walks the same ring three
+    # times (the ring is warm, as in the GPU arm, where every step reuses its rings)
     n = 1 << 18
-    for _ in range(args.warmup):
-        cpu_seal_open(threads, 1 << 14, 1)
+    arm = CpuArm(threads, n)
+    for _ in range(max(1, args.warmup)):
+        arm.passes(1)
     t0 = time.time()
-    vals = [cpu_seal_open(threads, n, 1) for _ in range(args.steps)]
-    secs = sum(v[1] for v in vals)
-    gbps = 2.0 * n * SIZE * 8 * args.steps / secs / 1e9
-    sample = f"{n} packets x {SIZE} B sealed then opened per step (a quarter of the GPU arm's batch)"
+    per_step = [arm.passes(REFERENCE_PASSES_PER_STEP) for _ in range(args.steps)]
+    secs = sum(per_step)
+    gbps = arm.gbps(REFERENCE_PASSES_PER_STEP * args.steps, secs)
+    sample = (f"{n} packets x {SIZE} B sealed then opened, {REFERENCE_PASSES_PER_STEP} passes per step over one warm ring "
+              f"(a quarter of the GPU arm's batch)")
     line = {
         "impl": "reference", "metric": "aead_seal_open_gbps_1420B", "value": gbps, "unit": "Gbit/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": workload_config(args.gpus),
         "cpu_baseline": {"value": gbps, "unit": "Gbit/s", "cores": threads, "kind": "port", "sample": sample,
+                         "step_gbps_min_max": [arm.gbps(REFERENCE_PASSES_PER_STEP, max(per_step)),
+                                               arm.gbps(REFERENCE_PASSES_PER_STEP, min(per_step))],
                          "note": "OpenSSL EVP_chacha20_poly1305 (AVX2/AVX-512 assembly) standing in for x/crypto's "
                                  "assembly: the Go reference path cannot be built here (no Go toolchain or module cache)"},
         "e2e": {"value": gbps, "unit": "Gbit/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -254,7 +286,7 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus: int):
+def workload_config(n_gpus: int, device_batches: int = DEVICE_BATCHES):
     return {
         "workload": "bulk seal+open at scale (BASELINE configs[3]): 1,048,576 packets x 1420 B over 65,536 peers per GPU, "
                     "16 sequential counters per peer, MTU 1420, replay ring 128 blocks",
@@ -262,6 +294,7 @@ def workload_config(n_gpus: int):
         "sharding": f"peer index mod {n_gpus}, no inter-GPU traffic",
         "bits_counted": "payload bits sealed + payload bits opened",
         "l2": "inputs (1.5 GB per pass) are larger than L2, no flush needed",
+        "device_batches_in_flight": device_batches,
     }
 
 
@@ -276,6 +309,112 @@ def setup_batch(ctx, n, stride, peers, first_peer=0):
     b.slot[:] = (first_peer + (i % np.uint64(peers))).astype(np.uint32)
     b.counter[:] = 0
     return b
+
+
+PIPE5_SUPERS_PER_GPU, PIPE5_SEGS, PIPE5_MSS, PIPE5_PEERS = 2048, 47, 1380, 10_000
+
+
+def pipeline5_share(rank: int, world: int, supers_per_gpu: int = PIPE5_SUPERS_PER_GPU, n_peers: int = PIPE5_PEERS):
+    """Which super-packets of configuration 5's batch this rank works on.  Every rank computes the same placement
+    from the same measured loads (the peer draws of an earlier period of the same traffic), so no rank has to be
+    told.  -> (workload, indices of this rank's super-packets, gpu_of, slot_of, segments per GPU)"""
+    from bnk_b200 import gen
+    from bnk_b200.mgpu import place_peers
+
+    n_super = supers_per_gpu * world
+    earlier = gen.config5_peers(n_super, n_peers, seed=gen.seed_for(5) + 1000)
+    load = np.bincount(earlier, minlength=n_peers).astype(np.uint64)
+    gpu_of, slot_of, _ = place_peers(load, n_peers, world)
+    w5 = gen.config5(n_super=n_super, n_peers=n_peers)
+    per_gpu = np.bincount(gpu_of[w5.peer], minlength=world) * PIPE5_SEGS
+    mine = np.flatnonzero(gpu_of[w5.peer] == rank)
+    return w5, mine, gpu_of, slot_of, per_gpu
+
+
+def run_pipeline5(rank, world, local_rank, dist, W, K, windows):
+    from bnk_b200 import Context, gen
+    from bnk_b200.device import (F_ASSIGN_COUNTERS, F_CHECK_INBOUND, F_DEMUX_INDEX, F_INNER_CHECK, F_NO_D2H, F_NO_H2D,
+                                 F_NOTE_OUTBOUND, F_REPLAY, F_TIMED, F_USE_OUT_LEN, GSO_SUPER_DTYPE, PKT_FILTER_DENY, PKT_OK,
+                                 slot_size)
+    from bnk_b200.filter import flatten_rule_arrays
+
+    n_seg, mss, p_peers, stride = PIPE5_SEGS, PIPE5_MSS, PIPE5_PEERS, slot_size(SIZE)
+    w5, mine, gpu_of, slot_of, per_gpu = pipeline5_share(rank, world)
+    f5 = gen.config3(n_rules=2000, n_nodes=5000, n_out=16, n_in=16, seed=gen.seed_for(5) + 1)
+    hit = np.flatnonzero(f5.rules["proto"] == 6)[:3]
+    for rr in hit:
+        f5.srcs["addr"][f5.rules["src_begin"][rr]] = w5.self_ip
+    my_peers = np.flatnonzero(gpu_of == rank)
+    n_slots = max(1, int(slot_of[my_peers].max()) + 1) if len(my_peers) else 1
+    pctx = Context(device_id=local_rank, max_keypairs=n_slots, mtu=SIZE, flow_capacity=1 << 16)
+    # a peer's keypair slot on its GPU is the one the placement handed out
+    keys = np.zeros((n_slots, 32), np.uint8)
+    keys[slot_of[my_peers]] = w5.keys[my_peers]
+    ridx = np.zeros(n_slots, np.uint32)
+    ridx[slot_of[my_peers]] = (0x1000 + my_peers).astype(np.uint32)
+    pctx.set_keypairs(0, keys, keys, ridx)
+    for p_ in sorted(set(w5.peer[mine].tolist())):
+        pctx.index_set(0x1000 + p_, int(slot_of[p_]))
+        pctx.set_allowed_ip(int(slot_of[p_]), w5.self_ip)
+    pctx.acl_set(True, flatten_rule_arrays(f5.rules, f5.srcs, f5.ports))
+    n_super = len(mine)
+    n_pkts = n_super * n_seg
+    split_ms, seal5_ms, open5_ms = [], [], []
+    st5 = np.zeros(0, np.uint8)
+    if n_super:
+        sup = np.zeros(n_super, GSO_SUPER_DTYPE)
+        sup_stride = (len(w5.supers[0]) + 15) & ~15
+        pb = pctx.batch(n_pkts, n_pkts * stride + n_super * sup_stride)
+        for k, j in enumerate(mine.tolist()):
+            pkt = w5.supers[j]
+            o = n_pkts * stride + k * sup_stride
+            pb.ring[o:o + len(pkt)] = np.frombuffer(pkt, np.uint8)
+            sup[k] = (o, len(pkt), k * n_seg, n_seg, 40, mss, 20, 16, 6, (0, 0, 0))
+        pb.off[:n_pkts] = (np.arange(n_pkts, dtype=np.uint64) * np.uint64(stride)).astype(np.uint32)
+        pb.len[:n_pkts] = 40 + mss
+        pb.slot[:n_pkts] = np.repeat(slot_of[w5.peer[mine]], n_seg)
+        pb.gso_split(sup, n_pkts)  # uploads the ring once
+    now = 1_700_000_000 * 10**9
+    dist.barrier()
+    t_begin = time.time()
+    for it in range(W + K):
+        if not n_super:
+            break
+        pb.gso_split(sup, n_pkts, F_NO_H2D | F_TIMED)
+        split_ms.append(pb.last_kernel_ms())
+        pb.seal(n_pkts, F_NO_H2D | F_NO_D2H | F_NOTE_OUTBOUND | F_ASSIGN_COUNTERS | F_TIMED, now_ns=now + it)
+        seal5_ms.append(pb.last_kernel_ms())
+        pb.open(n_pkts, F_NO_H2D | F_NO_D2H | F_USE_OUT_LEN | F_DEMUX_INDEX | F_REPLAY | F_INNER_CHECK | F_CHECK_INBOUND | F_TIMED,
+                now_ns=now + it)
+        open5_ms.append(pb.last_kernel_ms())
+    windows.append((t_begin, time.time()))
+    mean = lambda v: statistics.mean(v[W:]) if len(v) > W else 0.0
+    t_local = mean(split_ms) + mean(seal5_ms) + mean(open5_ms)
+    if n_super:
+        pb.download(n_pkts)
+        st5 = np.array(pb.status[:n_pkts])
+        pb.close()
+    pctx.close()
+    ok_local = bool(((st5 == PKT_OK) | (st5 == PKT_FILTER_DENY)).all())
+    t5 = dist.max(t_local)  # the slowest rank decides
+    ok = dist.all_true(ok_local)
+    total_pkts = int(per_gpu.sum())
+    allowed = dist.sum(float((st5 == PKT_OK).sum()))
+    denied = dist.sum(float((st5 == PKT_FILTER_DENY).sum()))
+    return {"segments": total_pkts, "super_packets": PIPE5_SUPERS_PER_GPU * world, "peers": p_peers, "rules": 2000, "n_gpus": world,
+            "segments_per_gpu": [int(x) for x in per_gpu],
+            "load_imbalance": float(per_gpu.max() / per_gpu.mean()),
+            "load_imbalance_peer_mod_n": float((lambda c: c.max() / c.mean())(np.bincount(w5.peer % world, minlength=world))),
+            "heaviest_peer_share": float(np.bincount(w5.peer).max() / len(w5.peer)),
+            "placement": "bnk_place_peers on the per-peer load of an earlier period (heaviest first, least-loaded GPU); "
+                         "a peer is never split",
+            "split_ms": mean(split_ms), "seal_side_ms": mean(seal5_ms), "open_side_ms": mean(open5_ms),
+            "slowest_rank_ms": t5,
+            "gbps": 2.0 * total_pkts * (40 + mss) * 8 / (t5 * 1e-3) / 1e9 if t5 else None,
+            "mpps": 2.0 * total_pkts / (t5 * 1e-3) / 1e6 if t5 else None,
+            "allowed": int(allowed), "filter_deny": int(denied), "verified": ok,
+            "note": "every context plays sender and receiver of its peers (loopback); Zipf(1.1) peers, 47 x 1420 B per "
+                    "super-packet; split/seal/open times are rank 0's, the rate uses the slowest rank's total"}
 
 
 def run_ours(args, rank, world, local_rank):
@@ -299,56 +438,85 @@ def run_ours(args, rank, world, local_rank):
     windows = []
 
     # ---- device-resident: value + roofline ----
-    dev = setup_batch(ctx, n, stride, peers)
-    dev.upload(n)
-    dev.fill_random(plan.payload_seed)
+    # The step's 1,048,576 packets sit in DEVICE_BATCHES batches with disjoint peers, each on its own stream, as a
+    # forwarder keeps several batches in flight: the grouping, counter and replay kernels of one batch run beside
+    # the seal/open kernels of the other.  The work per step is the same whatever the number.
+    nbd = max(1, args.device_batches)
+    per_d, peers_d = n // nbd, max(1, peers // nbd)
+    devs = [setup_batch(ctx, per_d, stride, peers_d, first_peer=j * peers_d) for j in range(nbd)]
+    for j, d in enumerate(devs):
+        d.upload(per_d)
+        d.fill_random(plan.payload_seed + 101 * j)
+    dev = devs[0]
     SEAL = F_NO_H2D | F_NO_D2H | F_ASSIGN_COUNTERS
     OPEN = F_NO_H2D | F_NO_D2H | F_REPLAY | F_USE_OUT_LEN
 
     def step_dev():
-        dev.seal(n, SEAL, wait=False)
-        dev.open(n, OPEN, wait=False)
+        for d in devs:
+            d.seal(per_d, SEAL, wait=False)
+        for d in devs:
+            d.open(per_d, OPEN, wait=False)
 
     for _ in range(W):
         step_dev()
     ctx.synchronize()
-    dist.barrier()
-    launches0 = ctx.launch_count()
-    t_begin = time.time()
-    ctx.timer_start([dev])
-    for _ in range(K):
-        step_dev()
-    ms_local = ctx.timer_stop([dev])
-    ctx.synchronize()
-    dist.barrier()
-    windows.append((t_begin, time.time()))
-    launches = ctx.launch_count() - launches0
-    ms = dist.max(ms_local)
-    dev.wait()
-    dev.download(n)
-    verified = bool((dev.status[:n] == 0).all() and (dev.out_len[:n] == SIZE).all()
-                    and int(dev.counter[:n].max()) == 16 * (W + K) - 1 if n >= 16 * peers else True)
+    # The timed region of exactly K steps is taken REGIONS times and the median region is reported (with the
+    # fastest and the slowest), so that one clock blip cannot decide the number; every region is bracketed by a
+    # barrier and timed on the device, the maximum over ranks counts.
+    region_ms = []
+    launches = 0
+    for _ in range(REGIONS):
+        dist.barrier()
+        launches0 = ctx.launch_count()
+        t_begin = time.time()
+        ctx.timer_start(devs)
+        for _ in range(K):
+            step_dev()
+        ms_local = ctx.timer_stop(devs)
+        ctx.synchronize()
+        dist.barrier()
+        windows.append((t_begin, time.time()))
+        launches = ctx.launch_count() - launches0
+        region_ms.append(dist.max(ms_local))
+    ms = statistics.median(region_ms)
+    verified = True
+    for d in devs:
+        d.wait()
+        d.download(per_d)
+        verified = verified and bool((d.status[:per_d] == 0).all() and (d.out_len[:per_d] == SIZE).all()
+                                     and (int(d.counter[:per_d].max()) == (per_d // peers_d) * (W + REGIONS * K) - 1
+                                          if per_d >= 16 * peers_d else True))
     bits_per_step = 2.0 * n * SIZE * 8
     value = world * bits_per_step * K / (ms * 1e-3) / 1e9
+    value_spread = [world * bits_per_step * K / (t * 1e-3) / 1e9 for t in (max(region_ms), min(region_ms))]
+    for d in devs[1:]:
+        d.close()
+    n_launch = per_d  # packets per seal/open launch from here on (one batch alone on the device)
 
     # per-launch duration of the dominant kernels (CUDA events around the seal / open kernel alone)
     seal_ms, open_ms = [], []
     t_begin = time.time()
     for _ in range(max(K, 3)):
-        dev.seal(n, SEAL | F_TIMED, wait=False)
+        dev.seal(n_launch, SEAL | F_TIMED, wait=False)
         seal_ms.append(dev.last_aead_ms())
-        dev.open(n, OPEN | F_TIMED, wait=False)
+        dev.open(n_launch, OPEN | F_TIMED, wait=False)
         open_ms.append(dev.last_aead_ms())
     dev.wait()
     windows.append((t_begin, time.time()))
     seal_avg, open_avg = statistics.mean(seal_ms), statistics.mean(open_ms)
     aead_avg = 0.5 * (seal_avg + open_avg)
     peak, peak_src = measured_hbm_peak()
-    achieved = n * HBM_BYTES_PER_PACKET / (aead_avg * 1e-3) / 1e9
+    achieved = n_launch * HBM_BYTES_PER_PACKET / (aead_avg * 1e-3) / 1e9
+    cap_n, cap_bytes = min(NCU_DRAM_CAPTURES, key=lambda c: abs(c[0] - n_launch))
+    traffic = cap_bytes * n_launch // cap_n
+    traffic_note = (f"ncu dram__bytes_read.sum + dram__bytes_write.sum of a {cap_n}-packet seal launch, scaled by packet "
+                    f"count; a lower bound (output still dirty in L2 at kernel end is not counted: "
+                    f"~{50e6 / (cap_n * HBM_BYTES_PER_PACKET) * 100:.0f} % of that launch)")
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-        "traffic": None if NCU_DRAM_BYTES_PER_PACKET is None else NCU_DRAM_BYTES_PER_PACKET * n,
-        "kernel": "aead_kernel<seal> / aead_kernel<open> (one launch each per step, 2872 algorithmic bytes per packet)",
+        "traffic": traffic, "traffic_note": traffic_note,
+        "kernel": "aead_kernel<seal> / aead_kernel<open> (2872 algorithmic bytes per packet)", "packets_per_launch": n_launch,
+        "launch_note": "timed with one batch alone on the device; a step runs this launch once per batch and direction",
         "peak_source": peak_src, "seal_ms": seal_avg, "open_ms": open_avg,
         "note": "the path is bound by the 32-bit integer pipes, not by HBM: see `alu`",
     }
@@ -357,62 +525,73 @@ def run_ours(args, rank, world, local_rank):
         probes = {name: ctx.probe_int_throughput(mix) for mix, name in
                   enumerate(["add_xor", "chacha_rounds", "imad", "add_xor_plus_imad"])}
         int_peak = max(probes.values())
-        ops = n * INT_OPS_PER_PACKET / (aead_avg * 1e-3) / 1e12
+        ops = n_launch * INT_OPS_PER_PACKET / (aead_avg * 1e-3) / 1e12
         alu = {"bound": "int32 issue", "achieved": ops, "peak": int_peak, "unit": "Tops/s", "frac": ops / int_peak,
                "ops_per_packet": INT_OPS_PER_PACKET, "probes_tops": probes,
                "peak_source": "measured live by bnk_probe_int_throughput (best of the instruction mixes)"}
     dev.close()
 
-    # ---- IMIX, device-resident ----
+    # ---- IMIX, device-resident, the same number of batches in flight ----
     imix = None
     if not args.no_imix:
         g = gen.SplitMix64(gen.seed_for(2) + 7919 * rank)
-        sizes = gen.imix_sizes(g, n)
-        slots_sz = ((sizes.astype(np.uint64) + np.uint64(48 + 15)) // np.uint64(16)) * np.uint64(16)
-        offs = np.concatenate([[0], np.cumsum(slots_sz)[:-1]]).astype(np.uint64)
-        ib = ctx.batch(n, int(offs[-1] + slots_sz[-1]))
-        ib.off[:] = offs.astype(np.uint32)
-        ib.len[:] = sizes
-        ib.slot[:] = (np.arange(n, dtype=np.uint64) % np.uint64(peers)).astype(np.uint32)
-        ib.upload(n)
-        ib.fill_random(plan.payload_seed + 5)
+        ibs, size_sum = [], 0.0
+        for j in range(nbd):
+            sizes = gen.imix_sizes(g, per_d)
+            size_sum += float(sizes.sum())
+            slots_sz = ((sizes.astype(np.uint64) + np.uint64(48 + 15)) // np.uint64(16)) * np.uint64(16)
+            offs = np.concatenate([[0], np.cumsum(slots_sz)[:-1]]).astype(np.uint64)
+            ib = ctx.batch(per_d, int(offs[-1] + slots_sz[-1]))
+            ib.off[:] = offs.astype(np.uint32)
+            ib.len[:] = sizes
+            ib.slot[:] = (j * peers_d + np.arange(per_d, dtype=np.uint64) % np.uint64(peers_d)).astype(np.uint32)
+            ib.upload(per_d)
+            ib.fill_random(plan.payload_seed + 5 + j)
+            ibs.append(ib)
 
         def step_imix():
-            ib.seal(n, SEAL | F_SORT_BY_LENGTH, wait=False)
-            ib.open(n, OPEN | F_SORT_BY_LENGTH, wait=False)
+            for ib in ibs:
+                ib.seal(per_d, SEAL | F_SORT_BY_LENGTH, wait=False)
+            for ib in ibs:
+                ib.open(per_d, OPEN | F_SORT_BY_LENGTH, wait=False)
 
         for _ in range(W):
             step_imix()
         ctx.synchronize()
         dist.barrier()
         t_begin = time.time()
-        ctx.timer_start([ib])
+        ctx.timer_start(ibs)
         for _ in range(K):
             step_imix()
-        ims = dist.max(ctx.timer_stop([ib]))
+        ims = dist.max(ctx.timer_stop(ibs))
         dist.barrier()
         windows.append((t_begin, time.time()))
-        ib.wait()
-        # one more pass with events around the two AEAD launches
-        ib.seal(n, SEAL | F_SORT_BY_LENGTH | F_TIMED)
-        imix_seal_ms = ib.last_aead_ms()
-        ib.open(n, OPEN | F_SORT_BY_LENGTH | F_TIMED)
-        imix_open_ms = ib.last_aead_ms()
-        ib.download(n)
-        imix_ok = bool((ib.status[:n] == 0).all())
+        for ib in ibs:
+            ib.wait()
+        # one more pass over one batch alone with events around its two AEAD launches
+        ibs[0].seal(per_d, SEAL | F_SORT_BY_LENGTH | F_TIMED)
+        imix_seal_ms = ibs[0].last_aead_ms()
+        ibs[0].open(per_d, OPEN | F_SORT_BY_LENGTH | F_TIMED)
+        imix_open_ms = ibs[0].last_aead_ms()
+        imix_ok = True
+        for ib in ibs:
+            ib.download(per_d)
+            imix_ok = imix_ok and bool((ib.status[:per_d] == 0).all())
         imix = {"mpps": world * 2.0 * n * K / (ims * 1e-3) / 1e6, "unit": "Mpps",
                 "packets_counted": "packets sealed + packets opened", "sizes": "64/576/1420 B at 7:4:1",
-                "gbps": world * 2.0 * float(sizes.sum()) * 8 * K / (ims * 1e-3) / 1e9, "verified": imix_ok,
-                "ms_per_step": ims / K, "seal_kernel_ms": imix_seal_ms, "open_kernel_ms": imix_open_ms}
-        ib.close()
+                "gbps": world * 2.0 * size_sum * 8 * K / (ims * 1e-3) / 1e9, "verified": imix_ok,
+                "ms_per_step": ims / K, "batches_in_flight": nbd, "packets_per_launch": per_d,
+                "seal_kernel_ms": imix_seal_ms, "open_kernel_ms": imix_open_ms}
+        for ib in ibs:
+            ib.close()
 
-    e2e_value = e2e_ms = None
+    e2e_value = e2e_ms = e2e_roofline = None
     e2e_ok = True
     h2d = d2h = 0
     nb = E2E_BATCHES
     if not args.no_e2e:
         # ---- end to end: pinned host rings, H2D and D2H inside the timed region ----
-        nb = E2E_BATCHES
+        nb = max(1, args.e2e_batches)
         per = n // nb
         batches = [setup_batch(ctx, per, stride, peers, first_peer=peers) for _ in range(nb)]
         ppb = max(1, peers // nb)  # batches in flight together own disjoint peers: nonce and replay order is per peer
@@ -453,6 +632,35 @@ def run_ours(args, rank, world, local_rank):
         h2d = nb * ((ring_span + 3 * 4 * per) + (ring_span + 3 * 4 * per))
         d2h = nb * 2 * (ring_span + (8 + 4 + 1) * per)
         e2e_value = world * bits_per_step * K / (e2e_ms * 1e-3) / 1e9
+
+        # The ceiling of this leg: the same pinned rings, the same streams, the same copies in the same order,
+        # and no kernel in between.  What the host link carries at this N, with every rank copying at once.
+        def run_copy_only(steps):
+            for _ in range(2 * steps):
+                for b in batches:
+                    b.wait()
+                    b.copy_only(per, True, True, wait=False)
+            for b in batches:
+                b.wait()
+
+        run_copy_only(W)
+        ctx.synchronize()
+        dist.barrier()
+        t_begin = time.time()
+        ctx.timer_start(batches)
+        run_copy_only(K)
+        copy_ms = dist.max(ctx.timer_stop(batches))
+        dist.barrier()
+        windows.append((t_begin, time.time()))
+        e2e_roofline = {
+            "bound": "pcie", "unit": "GB/s each way",
+            "achieved": (h2d + d2h) / 2 / (e2e_ms / K * 1e-3) / 1e9,
+            "peak": (h2d + d2h) / 2 / (copy_ms / K * 1e-3) / 1e9,
+            "frac": copy_ms / e2e_ms,
+            "peak_source": f"measured in this run at this N: the leg's own copies without its kernels, all {world} "
+                           f"rank(s) copying at once ({copy_ms / K:.2f} ms per step against {e2e_ms / K:.2f} ms with kernels)",
+            "aggregate_gbs_each_way": world * (h2d + d2h) / 2 / (copy_ms / K * 1e-3) / 1e9,
+        }
         for b in batches:
             b.close()
 
@@ -509,60 +717,13 @@ def run_ours(args, rank, world, local_rank):
         fb.close()
         fctx.close()
 
-    # ---- configuration 5 as a loopback pipeline on one context, device resident:
+    # ---- configuration 5 over all ranks, device resident.  The offered batch (2,048 super-packets per GPU, Zipf(1.1)
+    #      over 10,000 peers) is the same on every rank; peers are placed on GPUs by the load measured over an earlier
+    #      period (bnk_place_peers, never splitting a peer) and every rank works on the super-packets of its peers:
     #      GSO split -> NoteOutbound -> counters -> seal, then demux -> open -> replay -> inner check -> CheckInbound ----
     pipe = None
-    if rank == 0 and not args.no_pipeline:
-        from bnk_b200.device import (F_CHECK_INBOUND, F_DEMUX_INDEX, F_INNER_CHECK, F_NOTE_OUTBOUND, GSO_SUPER_DTYPE,
-                                     PKT_FILTER_DENY, PKT_OK)
-        from bnk_b200.filter import flatten_rule_arrays
-
-        n_super, n_seg, mss, p_peers = 2048, 47, 1380, 10_000
-        w5 = gen.config5(n_super=n_super, n_peers=p_peers)
-        f5 = gen.config3(n_rules=2000, n_nodes=5000, n_out=16, n_in=16, seed=gen.seed_for(5) + 1)
-        hit = np.flatnonzero(f5.rules["proto"] == 6)[:3]
-        for rr in hit:
-            f5.srcs["addr"][f5.rules["src_begin"][rr]] = w5.self_ip
-        pctx = Context(device_id=local_rank, max_keypairs=p_peers, mtu=SIZE, flow_capacity=1 << 16)
-        pctx.set_keypairs(0, w5.keys, w5.keys, (0x1000 + np.arange(p_peers)).astype(np.uint32))
-        for p_ in sorted(set(w5.peer.tolist())):
-            pctx.index_set(0x1000 + p_, p_)
-            pctx.set_allowed_ip(p_, w5.self_ip)
-        pctx.acl_set(True, flatten_rule_arrays(f5.rules, f5.srcs, f5.ports))
-        n_pkts = n_super * n_seg
-        sup = np.zeros(n_super, GSO_SUPER_DTYPE)
-        sup_stride = (len(w5.supers[0]) + 15) & ~15
-        pb = pctx.batch(n_pkts, n_pkts * stride + n_super * sup_stride)
-        for j, pkt in enumerate(w5.supers):
-            o = n_pkts * stride + j * sup_stride
-            pb.ring[o:o + len(pkt)] = np.frombuffer(pkt, np.uint8)
-            sup[j] = (o, len(pkt), j * n_seg, n_seg, 40, mss, 20, 16, 6, (0, 0, 0))
-        pb.off[:n_pkts] = (np.arange(n_pkts, dtype=np.uint64) * np.uint64(stride)).astype(np.uint32)
-        pb.len[:n_pkts] = 40 + mss
-        pb.slot[:n_pkts] = np.repeat(w5.peer, n_seg)
-        pb.gso_split(sup, n_pkts)  # uploads the ring once
-        split_ms, seal5_ms, open5_ms = [], [], []
-        now = 1_700_000_000 * 10**9
-        for it in range(W + K):
-            pb.gso_split(sup, n_pkts, F_NO_H2D | F_TIMED)
-            split_ms.append(pb.last_kernel_ms())
-            pb.seal(n_pkts, F_NO_H2D | F_NO_D2H | F_NOTE_OUTBOUND | F_ASSIGN_COUNTERS | F_TIMED, now_ns=now + it)
-            seal5_ms.append(pb.last_kernel_ms())
-            pb.open(n_pkts, F_NO_H2D | F_NO_D2H | F_USE_OUT_LEN | F_DEMUX_INDEX | F_REPLAY | F_INNER_CHECK | F_CHECK_INBOUND | F_TIMED,
-                    now_ns=now + it)
-            open5_ms.append(pb.last_kernel_ms())
-        pb.download(n_pkts)
-        st5 = np.array(pb.status[:n_pkts])
-        t5 = statistics.mean(split_ms[W:]) + statistics.mean(seal5_ms[W:]) + statistics.mean(open5_ms[W:])
-        pipe = {"segments": n_pkts, "super_packets": n_super, "peers": p_peers, "rules": 2000,
-                "split_ms": statistics.mean(split_ms[W:]), "seal_side_ms": statistics.mean(seal5_ms[W:]),
-                "open_side_ms": statistics.mean(open5_ms[W:]),
-                "gbps": 2.0 * n_pkts * (40 + mss) * 8 / (t5 * 1e-3) / 1e9, "mpps": 2.0 * n_pkts / (t5 * 1e-3) / 1e6,
-                "allowed": int((st5 == PKT_OK).sum()), "filter_deny": int((st5 == PKT_FILTER_DENY).sum()),
-                "verified": bool(((st5 == PKT_OK) | (st5 == PKT_FILTER_DENY)).all()),
-                "note": "one context plays sender and receiver (loopback); Zipf(1.1) peers, 47 x 1420 B per super-packet"}
-        pb.close()
-        pctx.close()
+    if not args.no_pipeline:
+        pipe = run_pipeline5(rank, world, local_rank, dist, W, K, windows)
 
     # ---- one upstream-sized batch (128 packets, the reference's conn.IdealBatchSize): latency through the C ABI ----
     small = None
@@ -617,7 +778,7 @@ def run_ours(args, rank, world, local_rank):
                 x.close()
             return 2.0 * sn * nb * rounds * SIZE * 8 / dt / 1e9, ok
 
-        def threaded(threads, packets, rounds):
+        def threaded(threads, packets, rounds, lanes=2, queue=False):
             """bnk_b200/host/apps/mt_stress: host threads with two batches in flight each, one context, through the
             C ABI; it checks statuses, plaintext and replay verdicts itself.  -> Gbit/s or None"""
             import re
@@ -628,10 +789,10 @@ def run_ours(args, rank, world, local_rank):
                 return None
             rates = []
             for _ in range(5):  # the rate is bimodal on shared hosts (some runs are several times slower): median of five
-                res = subprocess.run([exe, str(threads), str(rounds), str(packets), str(SIZE), "2"], capture_output=True,
-                                     text=True, timeout=300)
+                res = subprocess.run([exe, str(threads), str(rounds), str(packets), str(SIZE), str(lanes), "1" if queue else "0"],
+                                     capture_output=True, text=True, timeout=300)
                 m = re.search(r"gbps=([0-9.]+)", res.stdout)
-                if res.returncode != 0 or not res.stdout.startswith("OK") or not m:
+                if res.returncode != 0 or "\nOK" not in "\n" + res.stdout or not m:
                     return None
                 rates.append(float(m.group(1)))
             return statistics.median(rates)
@@ -645,6 +806,14 @@ def run_ours(args, rank, world, local_rank):
                  # (a second process on this GPU: only in single-GPU runs, like the CPU baseline)
                  "gbps_8_threads_128_packets": threaded(8, 128, max(20, args.small_rounds)) if world == 1 else None,
                  "gbps_8_threads_1024_packets": threaded(8, 1024, max(10, args.small_rounds // 2)) if world == 1 else None,
+                 # every host core drives the GPU, as every host core runs the CPU baseline
+                 "gbps_all_cores_128_packets": threaded(host_threads(), 128, max(20, args.small_rounds)) if world == 1 else None,
+                 "host_cores": host_threads(),
+                 # the same 128-packet calls handed to the library's submit queue (bnk_queue), which packs them into
+                 # GPU batches; 2 and 4 caller batches outstanding per thread
+                 "gbps_8_threads_128_packets_queue": threaded(8, 128, max(20, args.small_rounds), 2, True) if world == 1 else None,
+                 "gbps_8_threads_128_packets_queue_4_outstanding": threaded(8, 128, max(20, args.small_rounds), 4, True) if world == 1 else None,
+                 "gbps_16_threads_128_packets_queue": threaded(16, 128, max(20, args.small_rounds), 2, True) if world == 1 else None,
                  "note": "host wall clock per submit+wait; seal = group+counters launch, seal launch; open = open "
                          "launch, group+replay launch; 128 x 1420 B goes through the copy engines, 16 x 1420 B (under "
                          "128 KiB) runs on the pinned host arrays without copies; gbps_16_batches_in_flight: sixteen "
@@ -654,14 +823,17 @@ def run_ours(args, rank, world, local_rank):
 
     sampler.stop()
     clocks = sampler.summary(windows)
-    ok = dist.all_true(verified and e2e_ok and (imix is None or imix["verified"]))
+    ok = dist.all_true(verified and e2e_ok and (imix is None or imix["verified"]) and (pipe is None or pipe["verified"]))
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = host_threads()
         sample_n = 1 << 18
         passes = 24  # about 20 core-seconds on a 16-thread host
-        gbps, secs = cpu_seal_open(threads, sample_n, passes)
+        arm = CpuArm(threads, sample_n)
+        arm.passes(1)
+        secs = arm.passes(passes)
+        gbps = arm.gbps(passes, secs)
         cpu = {"value": gbps, "unit": "Gbit/s", "cores": threads, "kind": "port",
                "sample": f"{sample_n} packets x {SIZE} B sealed then opened, {passes} passes "
                          f"({secs:.2f} s wall, {secs * threads:.0f} core-seconds)",
@@ -671,12 +843,14 @@ def run_ours(args, rank, world, local_rank):
         line = {
             "metric": "aead_seal_open_gbps_1420B", "value": value, "unit": "Gbit/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "u32", "data": "synthetic", "config": workload_config(world),
+            "dtype": "u32", "data": "synthetic", "config": workload_config(world, nbd),
             "mpps": world * 2.0 * n * K / (ms * 1e-3) / 1e6,
+            "timed_regions": {"count": REGIONS, "steps_each": K, "value_is": "median region", "value_min_max": value_spread,
+                              "ms": region_ms},
             "e2e": None if e2e_value is None else {
                 "value": e2e_value, "unit": "Gbit/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / K, "batches_in_flight": nb, "mpps": world * 2.0 * n * K / (e2e_ms * 1e-3) / 1e6,
-                "pcie_gbs_each_way": (h2d + d2h) / 2 / (e2e_ms / K * 1e-3) / 1e9},
+                "pcie_gbs_each_way": (h2d + d2h) / 2 / (e2e_ms / K * 1e-3) / 1e9, "roofline": e2e_roofline},
             "gpu_launches": int(launches), "roofline": roofline, "alu": alu, "imix": imix, "filter": filt, "pipeline5": pipe, "small_batch": small, "cpu_baseline": cpu,
             "clocks": clocks, "verified": ok, "placement": placement,
         }
@@ -694,6 +868,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--packets", type=int, default=N_PACKETS, help="packets per GPU (smaller only for profiling)")
+    ap.add_argument("--device-batches", type=int, default=DEVICE_BATCHES,
+                    help="batches (streams) the device-resident step spreads its packets over")
+    ap.add_argument("--e2e-batches", type=int, default=E2E_BATCHES, help="pinned rings in flight in the host-ring leg")
     ap.add_argument("--no-imix", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-probe", action="store_true")

@@ -110,6 +110,45 @@ def build_mt_stress(force: bool = False) -> str:
     return _build_cpp(os.path.join(HOST, "apps", "mt_stress.cpp"), os.path.join(HOST, "apps", "mt_stress"), force)
 
 
+SAN_FLAGS = {"asan": "-fsanitize=address,-fsanitize=undefined", "tsan": "-fsanitize=thread"}
+
+
+def sanitized_dir(kind: str) -> str:
+    return os.path.join(os.path.dirname(PKG_DIR), "build", "sanitized", kind)
+
+
+def build_sanitized(kind: str, force: bool = False) -> str:
+    """The library's host code (C ABI, submit queue, dispatcher, C++ mirror) and the two C++ test programs built
+    with AddressSanitizer + UndefinedBehaviorSanitizer ("asan") or ThreadSanitizer ("tsan"): nvcc hands the
+    flag to the host compiler, the device code is untouched.  Returns the directory that holds libbnkgpu.so,
+    host_test and mt_stress of that kind."""
+    out = sanitized_dir(kind)
+    lib = os.path.join(out, "libbnkgpu.so")
+    root = os.path.dirname(PKG_DIR)
+    progs = {"host_test": os.path.join(root, "tests", "cpp", "host_test.cpp"),
+             "mt_stress": os.path.join(HOST, "apps", "mt_stress.cpp")}
+    deps = _deps() + list(progs.values())
+    if not force and os.path.exists(lib) and all(os.path.exists(os.path.join(out, p)) for p in progs) and \
+            all(os.path.getmtime(d) <= os.path.getmtime(lib) for d in deps):
+        return out
+    os.makedirs(out, exist_ok=True)
+    flag = SAN_FLAGS[kind]
+    runtime = ["-Xlinker", "-lasan", "-Xlinker", "-lubsan"] if kind == "asan" else ["-Xlinker", "-ltsan"]
+    cmd = [nvcc_path(), "-O1", "-g", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler",
+           "-fPIC," + flag + ",-fno-omit-frame-pointer", "-shared", "-o", lib, *sources(), *runtime]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc (sanitized) failed:\n" + res.stdout + res.stderr)
+    cxx = shutil.which("g++") or "g++"
+    for name, src in progs.items():
+        cmd = [cxx, "-O1", "-g", "-std=c++17", "-pthread", *flag.split(","), "-fno-omit-frame-pointer", "-o", os.path.join(out, name),
+               src, "-L" + out, "-lbnkgpu", "-Wl,-rpath,$ORIGIN"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("g++ (sanitized) failed:\n" + res.stdout + res.stderr)
+    return out
+
+
 if __name__ == "__main__":
     import sys
 

@@ -106,6 +106,24 @@ class TableStats(C.Structure):
     ]
 
 
+class QueueCfg(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("max_pkts", C.c_uint32), ("max_packet", C.c_uint32), ("depth", C.c_uint32),
+                ("open_side", C.c_uint32), ("flags", C.c_uint32), ("reserved", C.c_uint32 * 2)]
+
+
+class MgpuCfg(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("n_devices", C.c_uint32),
+        ("devices", C.POINTER(C.c_int32)),
+        ("max_pkts_per_gpu", C.c_uint32),
+        ("max_packet", C.c_uint32),
+        ("max_peers", C.c_uint32),
+        ("reserved", C.c_uint32),
+        ("ctx", Cfg),
+    ]
+
+
 SRC_ADDR_STRIDE = 20
 CLASS_WIREGUARD, CLASS_DISCO, CLASS_STUN, CLASS_STRANGER = 0, 10, 11, 12
 
@@ -149,6 +167,25 @@ SYMBOLS = {
     "bnk_batch_upload": (_i, [_vp, _u32]),
     "bnk_batch_download": (_i, [_vp, _u32]),
     "bnk_assign_counters_noalloc": (_i, [_vp, _vp, _vp, _u32, _vp]),
+    "bnk_queue_create": (_i, [_vp, C.POINTER(QueueCfg), C.POINTER(_vp)]),
+    "bnk_queue_destroy": (_i, [_vp]),
+    "bnk_queue_submit": (_i, [_vp, _vp, _vp, _vp, _u32, _i64, C.POINTER(_u64)]),
+    "bnk_queue_wait": (_i, [_vp, _u64, _vp, _vp, _vp, _vp, _vp]),
+    "bnk_queue_wait_room": (_i, [_vp, _u64]),
+    "bnk_queue_stats_get": (_i, [_vp, C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u64)]),
+    "bnk_place_peers": (_i, [_vp, _u32, _u32, _u32, _vp, _vp, _vp]),
+    "bnk_mgpu_create": (_i, [C.POINTER(MgpuCfg), C.POINTER(_vp)]),
+    "bnk_mgpu_destroy": (_i, [_vp]),
+    "bnk_mgpu_last_error_string": (C.c_char_p, [_vp]),
+    "bnk_mgpu_ctx": (_vp, [_vp, _u32]),
+    "bnk_mgpu_place": (_i, [_vp, _vp]),
+    "bnk_mgpu_locate": (_i, [_vp, _u32, C.POINTER(_u32), C.POINTER(_u32)]),
+    "bnk_mgpu_peer_set": (_i, [_vp, _u32, _vp, _vp, _u32, _u32, _u32]),
+    "bnk_mgpu_peer_clear": (_i, [_vp, _u32]),
+    "bnk_mgpu_acl_set": (_i, [_vp, _i, _vp, _sz]),
+    "bnk_mgpu_seal": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _i64, _vp, _vp, _vp, _vp]),
+    "bnk_mgpu_open": (_i, [_vp, _vp, _vp, _u32, _u32, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "bnk_mgpu_loads_get": (_i, [_vp, _vp, _vp, _vp, _i]),
     "bnk_batch_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "bnk_batch_last_aead_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "bnk_kernel_launch_count": (_i, [_vp, C.POINTER(_u64)]),

@@ -783,6 +783,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         }
         b->dev_stale = false;
     }
+    if (b->order_wait) CK(ctx, cudaStreamWaitEvent(s, b->order_wait, 0));
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     if (flags & BNK_F_NOTE_OUTBOUND) {
         CK(ctx, launch_filter_note(b, npkts, now_unix_ns, s));
@@ -811,6 +812,7 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     b->kernel_timed = timed;
     b->aead_timed = timed;
     CK(ctx, tally_if_asked(b, npkts, flags, s));
+    if (b->order_record) CK(ctx, cudaEventRecord(b->order_record, s));
     if (!direct && !(flags & BNK_F_NO_D2H) && n) {
         if (b->joint_copy) {
             CK(ctx, cudaMemcpyAsync(b->h_desc, b->d_desc, b->desc_room + ext, cudaMemcpyDeviceToHost, s));
@@ -846,6 +848,7 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         }
         b->dev_stale = false;
     }
+    if (b->order_wait) CK(ctx, cudaStreamWaitEvent(s, b->order_wait, 0));
     if (timed) CK(ctx, cudaEventRecord(b->k_begin, s));
     const uint32_t *order = nullptr;
     AeadArgs oa = aead_args(b, npkts, true, nullptr);
@@ -879,6 +882,7 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
     CK(ctx, tally_if_asked(b, npkts, flags, s));
+    if (b->order_record) CK(ctx, cudaEventRecord(b->order_record, s));
     if (!direct && !(flags & BNK_F_NO_D2H) && n) {
         if (b->joint_copy) {
             CK(ctx, cudaMemcpyAsync(b->h_desc, b->d_desc, b->desc_room + ext, cudaMemcpyDeviceToHost, s));

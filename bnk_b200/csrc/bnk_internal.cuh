@@ -159,6 +159,9 @@ struct bnk_batch {
     bnk_batch_stats *h_stats; // pinned; written by the tally kernel
     unsigned long long *d_stats; // device accumulators of the tally kernel (zero between launches)
     cudaEvent_t ev_fence; // orders this batch's stream against table maintenance on another stream
+    // Set by the submit queue around one submit: the kernels of that submit start behind order_wait and
+    // order_record is recorded behind the last of them (copies on either side stay free to overlap).
+    cudaEvent_t order_wait, order_record;
 };
 
 // Small batches are two dependent launches with little work in each, so the gap between them counts.  A kernel

@@ -326,3 +326,66 @@ class Batch:
         v = _lib.BatchStats()
         self._ck(_lib.lib().bnk_batch_stats_get(self._h, C.byref(v)))
         return {"packets": v.packets, "bytes_out": v.bytes_out, "by_status": list(v.by_status)}
+
+
+class Queue:
+    """bnk_queue: many small caller batches packed into few large GPU batches (see include/bnk_gpu.h)."""
+
+    def __init__(self, ctx: Context, open_side: bool, flags: int = 0, max_pkts: int = 4096, max_packet: int = 1420,
+                 depth: int = 2):
+        self.ctx = ctx
+        self.open_side = open_side
+        self.max_packet = max_packet
+        cfg = _lib.QueueCfg(C.sizeof(_lib.QueueCfg), max_pkts, max_packet, depth, int(open_side), flags)
+        h = C.c_void_p()
+        ctx._ck(_lib.lib().bnk_queue_create(ctx._h, C.byref(cfg), C.byref(h)))
+        self._h = h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            _lib.lib().bnk_queue_destroy(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def submit(self, packets: Sequence[bytes], slots=None, now_ns: int = 0):
+        """-> ticket (opaque), or None when every GPU batch is taken (collect a ticket and try again)."""
+        n = len(packets)
+        lens = np.array([len(p) for p in packets], np.uint32)
+        offs = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.uint64)
+        src = np.frombuffer(b"".join(packets) + b"\0", np.uint8)
+        ptrs = (np.uint64(src.ctypes.data) + offs).astype(np.uint64)
+        sp = None
+        if slots is not None:
+            slots = np.ascontiguousarray(slots, np.uint32)
+            sp = slots.ctypes.data
+        t = C.c_uint64()
+        rc = _lib.lib().bnk_queue_submit(self._h, ptrs.ctypes.data, lens.ctypes.data, sp, n, now_ns, C.byref(t))
+        if rc == _lib.EBUSY:
+            return None
+        self.ctx._ck(rc)
+        return (t.value, n)
+
+    def wait(self, ticket):
+        """-> (outputs: list[bytes], status, counters, slots)"""
+        t, n = ticket
+        stride = self.max_packet + 64
+        dst = np.zeros(n * stride, np.uint8)
+        ptrs = (np.uint64(dst.ctypes.data) + np.arange(n, dtype=np.uint64) * np.uint64(stride)).astype(np.uint64)
+        out_len = np.zeros(n, np.uint32)
+        counter = np.zeros(n, np.uint64)
+        slot = np.zeros(n, np.uint32)
+        status = np.zeros(n, np.uint8)
+        self.ctx._ck(_lib.lib().bnk_queue_wait(self._h, t, ptrs.ctypes.data, out_len.ctypes.data, counter.ctypes.data,
+                                               slot.ctypes.data, status.ctypes.data))
+        outs = [dst[k * stride:k * stride + int(out_len[k])].tobytes() for k in range(n)]
+        return outs, status, counter, slot
+
+    def stats(self):
+        a, b, c = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        self.ctx._ck(_lib.lib().bnk_queue_stats_get(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return {"gpu_batches": a.value, "packets": b.value, "caller_batches": c.value}

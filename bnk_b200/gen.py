@@ -393,6 +393,14 @@ def zipf_ranks(g: SplitMix64, n: int, n_items: int, s: float = 1.1) -> np.ndarra
     return np.minimum(np.searchsorted(cdf, u, side="left"), n_items - 1).astype(np.uint32)
 
 
+def config5_peers(n_super: int, n_peers: int = 10_000, seed: int | None = None) -> np.ndarray:
+    """Only the peer draws of config5 (same stream, same positions): what a dispatcher sees of a period of
+    traffic when it measures the load per peer."""
+    g = SplitMix64(seed_for(5) if seed is None else seed)
+    g.bytes(n_peers * 32)
+    return zipf_ranks(g, n_super, n_peers)
+
+
 def config5(n_super: int = 64, n_peers: int = 10_000, n_seg: int = 47, mss: int = 1380, seed: int | None = None) -> GsoWorkload:
     """Draw order: n_peers*32 key bytes; n_super Zipf(1.1) peer draws; per super-packet: source port,
     destination port, sequence number, IP id (one u64 each), then n_seg*mss payload bytes.  Peer p has tunnel

@@ -5,12 +5,17 @@
 // window on, and checks that the plaintext came back and that a second open of the same messages is refused.
 // Prints the aggregate rate; exits non-zero on any mismatch.
 //
-//   mt_stress [threads] [rounds] [packets per batch] [payload bytes] [batches per thread]
+// With a sixth argument of 1 the threads do the same through two shared submit queues (bnk_queue, one per
+// direction) instead of batches of their own: their 128-packet calls are packed into GPU batches by the library.
+//
+//   mt_stress [threads] [rounds] [packets per batch] [payload bytes] [batches per thread] [0 = own batches | 1 = queue]
+//             [queue: packets per GPU batch] [queue: GPU batches in flight]
 #include <atomic>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <thread>
 #include <vector>
 
@@ -76,7 +81,117 @@ int main(int argc, char **argv) {
     std::atomic<int> ready{0};
     std::atomic<bool> go{false};
     std::atomic<uint64_t> packets{0};
+    const bool use_queue = argc > 6 && std::atoi(argv[6]) == 1;
+    bnk_queue *sealq = nullptr, *openq = nullptr;
+    if (use_queue) {
+        bnk_queue_cfg qc{};
+        qc.struct_size = sizeof qc;
+        // GPU batches of up to 1024 packets stay on the library's short path (one grouping launch, one seal or open
+        // launch, one copy each way); three of them in flight keep the copy engines and the SMs busy together
+        qc.max_pkts = argc > 7 ? (uint32_t)std::atoi(argv[7]) : 1024;
+        qc.max_packet = size ? size : 16;
+        qc.depth = argc > 8 ? (uint32_t)std::atoi(argv[8]) : 3;
+        qc.open_side = 0;
+        qc.flags = 0;
+        if (bnk_queue_create(ctx, &qc, &sealq) != BNK_SUCCESS) return 2;
+        qc.open_side = 1;
+        qc.flags = BNK_F_REPLAY;
+        if (bnk_queue_create(ctx, &qc, &openq) != BNK_SUCCESS) return 2;
+    }
+    // The same work through the queues.  A lane is one caller batch in flight: its plaintext, the sealed messages
+    // that came back, the opened packets; `lanes` tickets per thread are out at any time.
+    auto queue_worker = [&](int t) {
+        struct QLane {
+            std::vector<uint8_t> plain, sealed, opened;
+            std::vector<const uint8_t *> in;
+            std::vector<uint8_t *> out;
+            std::vector<uint32_t> len, slot, out_len;
+            std::vector<uint64_t> counter;
+            std::vector<uint8_t> status;
+            bnk_ticket ticket = 0;
+        };
+        const uint32_t msg_room = stride;
+        std::vector<QLane> ls(lanes);
+        uint64_t rs = 1000 + t;
+        for (QLane &L : ls) {
+            L.plain.resize((size_t)n * (size ? size : 1));
+            for (auto &x : L.plain) x = (uint8_t)mix(rs);
+            L.sealed.resize((size_t)n * msg_room);
+            L.opened.resize((size_t)n * msg_room);
+            L.in.resize(n); L.out.resize(n); L.len.resize(n); L.slot.resize(n); L.out_len.resize(n);
+            L.counter.resize(n); L.status.resize(n);
+        }
+        std::vector<uint64_t> next_counter(max_peers, 0);
+        // A submit that finds every GPU batch taken returns BNK_EBUSY; the caller then collects its oldest ticket
+        // (which may be what keeps a batch from being reused) and tries again.
+        int r = 0;
+        auto collect_sealed = [&](QLane &L) {
+            CHECK(bnk_queue_wait(sealq, L.ticket, L.out.data(), L.out_len.data(), L.counter.data(), nullptr, L.status.data()) == BNK_SUCCESS,
+                  "queue_wait after seal");
+            for (uint32_t i = 0; i < n; i++) {
+                CHECK(L.status[i] == BNK_PKT_OK, "seal status %u", L.status[i]);
+                CHECK(L.counter[i] == next_counter[L.slot[i]]++, "thread %d round %d packet %u: nonce out of order", t, r, i);
+                L.in[i] = L.sealed.data() + (size_t)i * msg_room;
+                L.len[i] = L.out_len[i];
+                L.out[i] = L.opened.data() + (size_t)i * msg_room;
+            }
+        };
+        auto collect_opened = [&](QLane &L) {
+            CHECK(bnk_queue_wait(openq, L.ticket, L.out.data(), L.out_len.data(), nullptr, nullptr, L.status.data()) == BNK_SUCCESS,
+                  "queue_wait after open");
+            for (uint32_t i = 0; i < n; i++) {
+                CHECK(L.status[i] == (size ? BNK_PKT_OK : BNK_PKT_KEEPALIVE), "thread %d round %d packet %u: open status %u", t, r, i, L.status[i]);
+                CHECK(std::memcmp(L.opened.data() + (size_t)i * msg_room, L.plain.data() + (size_t)i * size, size) == 0,
+                      "thread %d round %d packet %u: plaintext differs", t, r, i);
+            }
+        };
+        // one phase: submit every lane, collecting the oldest outstanding one whenever the queue is full
+        auto phase = [&](bnk_queue *q, const std::function<void(QLane &)> &prepare, const std::function<void(QLane &)> &collect) {
+            int collected = 0;
+            for (int l = 0; l < lanes; l++) {
+                prepare(ls[l]);
+                for (;;) {
+                    const int rc = bnk_queue_submit(q, ls[l].in.data(), ls[l].len.data(), ls[l].slot.data(), n, 0, &ls[l].ticket);
+                    if (rc == BNK_SUCCESS) break;
+                    CHECK(rc == BNK_EBUSY, "queue_submit: %d %s", rc, bnk_last_error_string(ctx));
+                    if (rc != BNK_EBUSY) return;
+                    if (collected < l) collect(ls[collected++]);
+                    else bnk_queue_wait_room(q, 1000000); // nothing of this thread is outstanding: others are ahead
+                }
+            }
+            while (collected < lanes) collect(ls[collected++]);
+        };
+        const int warm = rounds / 10 + 1;
+        int lane_no = 0;
+        for (r = -warm; r < rounds; r++) {
+            if (r == 0) {
+                ready.fetch_add(1);
+                while (!go.load()) std::this_thread::yield();
+            }
+            lane_no = 0;
+            phase(sealq, [&](QLane &L) {
+                const uint32_t first_peer = (uint32_t)(t * lanes + lane_no++) * peers_per_lane;
+                for (uint32_t i = 0; i < n; i++) {
+                    L.in[i] = L.plain.data() + (size_t)i * size;
+                    L.len[i] = size;
+                    L.slot[i] = first_peer + (uint32_t)(mix(rs) % peers_per_lane);
+                    L.out[i] = L.sealed.data() + (size_t)i * msg_room;
+                }
+            }, collect_sealed);
+            phase(openq, [](QLane &) {}, collect_opened);
+            if (r >= 0) packets.fetch_add((uint64_t)n * lanes);
+        }
+        // the last sealed messages once more: all replays
+        QLane &L = ls[0];
+        while (bnk_queue_submit(openq, L.in.data(), L.len.data(), L.slot.data(), n, 0, &L.ticket) == BNK_EBUSY) bnk_queue_wait_room(openq, 1000000);
+        CHECK(bnk_queue_wait(openq, L.ticket, L.out.data(), L.out_len.data(), nullptr, nullptr, L.status.data()) == BNK_SUCCESS, "queue_wait");
+        for (uint32_t i = 0; i < n; i++) CHECK(L.status[i] == BNK_PKT_REPLAY, "thread %d: replayed packet %u has status %u", t, i, L.status[i]);
+    };
     auto worker = [&](int t) {
+        if (use_queue) {
+            queue_worker(t);
+            return;
+        }
         std::vector<Lane> ls(lanes);
         uint64_t rs = 1000 + t;
         for (int l = 0; l < lanes; l++) {
@@ -158,10 +273,18 @@ int main(int argc, char **argv) {
     go.store(true);
     for (auto &th : pool) th.join();
     const double secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if (use_queue) {
+        uint64_t gb = 0, pk = 0, cb = 0;
+        bnk_queue_stats_get(sealq, &gb, &pk, &cb);
+        std::printf("seal queue: %llu caller batches in %llu gpu batches (%.1f packets per gpu batch)\n", (unsigned long long)cb,
+                    (unsigned long long)gb, gb ? (double)pk / (double)gb : 0.0);
+        bnk_queue_destroy(sealq);
+        bnk_queue_destroy(openq);
+    }
     bnk_ctx_destroy(ctx);
     const double gbps = 2.0 * (double)packets.load() * size * 8 / secs / 1e9; // sealed + opened payload bits
-    std::printf("%s threads=%d lanes=%d packets_per_batch=%u payload=%u rounds=%d seconds=%.3f mpps=%.3f gbps=%.2f failures=%d\n",
-                failures.load() ? "FAILED" : "OK", threads, lanes, n, size, rounds, secs,
+    std::printf("%s mode=%s threads=%d lanes=%d packets_per_batch=%u payload=%u rounds=%d seconds=%.3f mpps=%.3f gbps=%.2f failures=%d\n",
+                failures.load() ? "FAILED" : "OK", use_queue ? "queue" : "batches", threads, lanes, n, size, rounds, secs,
                 2.0 * packets.load() / secs / 1e6, gbps, failures.load());
     return failures.load() ? 1 : 0;
 }

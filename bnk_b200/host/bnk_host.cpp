@@ -340,4 +340,92 @@ int Device::PumpInbound() {
     return (int)up.size();
 }
 
+// ---- Dispatcher ----
+Dispatcher::Dispatcher(const std::vector<int32_t> &devices, uint32_t max_peers, uint32_t max_pkts_per_gpu,
+                       uint32_t max_packet, uint32_t flow_capacity)
+    : max_peers_(max_peers), max_packet_(max_packet) {
+    bnk_mgpu_cfg cfg{};
+    cfg.struct_size = sizeof cfg;
+    cfg.n_devices = (uint32_t)devices.size();
+    cfg.devices = devices.data();
+    cfg.max_pkts_per_gpu = max_pkts_per_gpu;
+    cfg.max_packet = max_packet;
+    cfg.max_peers = max_peers;
+    cfg.ctx.struct_size = sizeof cfg.ctx;
+    cfg.ctx.max_keypairs = max_peers;
+    cfg.ctx.replay_ring_blocks = 128;
+    cfg.ctx.mtu = max_packet;
+    cfg.ctx.flow_capacity = flow_capacity;
+    const int rc = bnk_mgpu_create(&cfg, &m_);
+    if (rc != BNK_SUCCESS) throw Error(rc, std::string("bnk_mgpu_create: ") + bnk_last_error_string(nullptr));
+}
+
+Dispatcher::~Dispatcher() {
+    if (m_) bnk_mgpu_destroy(m_);
+}
+
+void Dispatcher::Check(int rc) const {
+    if (rc < 0) throw Error(rc, std::string(bnk_strerror(rc)) + ": " + bnk_mgpu_last_error_string(m_));
+}
+
+void Dispatcher::Place(const std::vector<uint64_t> &load) {
+    if (!load.empty() && load.size() != max_peers_) throw Error(BNK_EINVAL, "one load per peer");
+    Check(bnk_mgpu_place(m_, load.empty() ? nullptr : load.data()));
+}
+
+void Dispatcher::SetPeer(uint32_t peer, const uint8_t send_key[32], const uint8_t recv_key[32], uint32_t remote_index,
+                         uint32_t local_index, uint32_t allowed_ip) {
+    Check(bnk_mgpu_peer_set(m_, peer, send_key, recv_key, remote_index, local_index, allowed_ip));
+}
+
+void Dispatcher::RemovePeer(uint32_t peer) { Check(bnk_mgpu_peer_clear(m_, peer)); }
+
+void Dispatcher::SetRules(const std::vector<CompiledRule> &rules) {
+    const std::vector<bnk_acl_tuple> t = FlattenRules(rules);
+    Check(bnk_mgpu_acl_set(m_, 1, t.empty() ? nullptr : t.data(), t.size()));
+}
+
+Dispatcher::Result Dispatcher::Seal(const std::vector<Packet> &pkts, const std::vector<uint32_t> &peers, uint32_t flags,
+                                    TimeNs now) {
+    const uint32_t n = (uint32_t)pkts.size();
+    if (peers.size() != n) throw Error(BNK_EINVAL, "one peer per packet");
+    Result r;
+    r.out.assign(n, Packet(max_packet_ + 64));
+    r.status.assign(n, 0);
+    r.counter.assign(n, 0);
+    std::vector<const uint8_t *> in(n);
+    std::vector<uint8_t *> out(n);
+    std::vector<uint32_t> len(n), out_len(n);
+    for (uint32_t i = 0; i < n; i++) {
+        in[i] = pkts[i].data();
+        len[i] = (uint32_t)pkts[i].size();
+        out[i] = r.out[i].data();
+    }
+    Check(bnk_mgpu_seal(m_, in.data(), len.data(), peers.data(), n, flags, now, out.data(), out_len.data(), r.counter.data(),
+                        r.status.data()));
+    for (uint32_t i = 0; i < n; i++) r.out[i].resize(out_len[i]);
+    return r;
+}
+
+Dispatcher::Result Dispatcher::Open(const std::vector<Packet> &msgs, uint32_t flags, TimeNs now) {
+    const uint32_t n = (uint32_t)msgs.size();
+    Result r;
+    r.out.assign(n, Packet(max_packet_ + 64));
+    r.status.assign(n, 0);
+    r.counter.assign(n, 0);
+    r.peer.assign(n, 0);
+    std::vector<const uint8_t *> in(n);
+    std::vector<uint8_t *> out(n);
+    std::vector<uint32_t> len(n), out_len(n);
+    for (uint32_t i = 0; i < n; i++) {
+        in[i] = msgs[i].data();
+        len[i] = (uint32_t)msgs[i].size();
+        out[i] = r.out[i].data();
+    }
+    Check(bnk_mgpu_open(m_, in.data(), len.data(), n, flags, now, out.data(), out_len.data(), r.counter.data(), r.peer.data(),
+                        r.status.data()));
+    for (uint32_t i = 0; i < n; i++) r.out[i].resize(out_len[i]);
+    return r;
+}
+
 } // namespace bnk

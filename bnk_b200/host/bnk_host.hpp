@@ -189,4 +189,36 @@ class Device {
     Counters stats_;
 };
 
+// ---- several GPUs ----
+// RAII over bnk_mgpu: one context per listed device, peers placed by measured load, mixed batches routed by
+// peer (see include/bnk_gpu.h).  Stands where Device stands when a box has more than one GPU; a peer's packets
+// always meet on one GPU, as the reference gives each peer one sequential worker (bind.go:325-328).
+class Dispatcher {
+  public:
+    Dispatcher(const std::vector<int32_t> &devices, uint32_t max_peers, uint32_t max_pkts_per_gpu = 4096,
+               uint32_t max_packet = 1420, uint32_t flow_capacity = 1u << 16);
+    ~Dispatcher();
+    Dispatcher(const Dispatcher &) = delete;
+    Dispatcher &operator=(const Dispatcher &) = delete;
+    bnk_mgpu *raw() const { return m_; }
+    void Check(int rc) const;
+    void Place(const std::vector<uint64_t> &load); // empty = equal loads
+    void SetPeer(uint32_t peer, const uint8_t send_key[32], const uint8_t recv_key[32], uint32_t remote_index,
+                 uint32_t local_index, uint32_t allowed_ip);
+    void RemovePeer(uint32_t peer);
+    void SetRules(const std::vector<CompiledRule> &rules); // on every GPU
+    struct Result {
+        std::vector<Packet> out;      // sealed messages, or opened plaintexts
+        std::vector<uint8_t> status;  // BNK_PKT_*
+        std::vector<uint64_t> counter;
+        std::vector<uint32_t> peer;   // open: the peer each message belongs to
+    };
+    Result Seal(const std::vector<Packet> &pkts, const std::vector<uint32_t> &peers, uint32_t flags = 0, TimeNs now = 0);
+    Result Open(const std::vector<Packet> &msgs, uint32_t flags = BNK_F_REPLAY, TimeNs now = 0);
+
+  private:
+    bnk_mgpu *m_ = nullptr;
+    uint32_t max_peers_, max_packet_;
+};
+
 } // namespace bnk

@@ -300,6 +300,115 @@ int bnk_gso_split_submit(bnk_batch *b, const bnk_gso_super *supers, uint32_t n_s
 int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uint32_t *dev_slot, uint32_t npkts,
                                 uint64_t *dev_counter);
 
+/* ---- submit queue: many small caller batches, few large GPU batches ----
+ * The reference moves packets in batches of conn.IdealBatchSize = 128 (internal/magicsock/bind.go:97,372-377),
+ * from one goroutine per receive function and one per peer (bind.go:152,327-328).  A 128-packet submit does not
+ * fill a GPU; a queue takes such batches from any number of threads, packs them into GPU batches of up to
+ * max_pkts packets (a batch goes as soon as the device has a free slot, so a lone caller is not held up, and
+ * grows by itself while the device is busy), keeps up to `depth` GPU batches in flight with their copies
+ * overlapping each other's kernels, and hands every caller its own results.  One queue works in one direction
+ * with one set of flags.  Per keypair, nonces follow the order of the bnk_queue_submit calls and replay
+ * verdicts the order of arrival, across GPU batches too (their kernels are chained); the packets of one
+ * keypair should come through one queue at a time.
+ *   bnk_queue_submit  copies the caller's packets in (the caller's buffers are free again on return) and
+ *                     returns a ticket; BNK_EBUSY when every GPU batch is taken: collect a ticket, then retry.
+ *                     slot[] names the keypair of each packet (open side: may be NULL with BNK_F_DEMUX_INDEX).
+ *   bnk_queue_wait    blocks until the ticket's GPU batch is done and copies the caller's results out:
+ *                     sealed messages (room for len + 48 bytes each) or opened plaintexts, out_len[], status[],
+ *                     and if not NULL counter[] and slot_out[].  Every ticket must be collected exactly once.
+ * Seal queues always take counters from the keypairs' send counters. */
+typedef struct bnk_queue bnk_queue;
+typedef uint64_t bnk_ticket;
+typedef struct bnk_queue_cfg {
+    uint32_t struct_size; /* sizeof(bnk_queue_cfg) */
+    uint32_t max_pkts;    /* packets per GPU batch, up to 32768 */
+    uint32_t max_packet;  /* longest plaintext packet */
+    uint32_t depth;       /* GPU batches in flight at once, 1..8 (2 or 3 keeps copies and kernels overlapped) */
+    uint32_t open_side;   /* 0 = seal queue, 1 = open queue */
+    uint32_t flags;       /* BNK_F_* of every submit (BNK_F_NOTE_OUTBOUND, BNK_F_REPLAY, BNK_F_CHECK_INBOUND ...) */
+    uint32_t reserved[2];
+} bnk_queue_cfg;
+int bnk_queue_create(bnk_ctx *ctx, const bnk_queue_cfg *cfg, bnk_queue **out);
+int bnk_queue_destroy(bnk_queue *q);
+int bnk_queue_submit(bnk_queue *q, const uint8_t *const *pkts, const uint32_t *len, const uint32_t *slot, uint32_t n,
+                     int64_t now_unix_ns, bnk_ticket *ticket);
+int bnk_queue_wait(bnk_queue *q, bnk_ticket ticket, uint8_t *const *out, uint32_t *out_len, uint64_t *counter,
+                   uint32_t *slot_out, uint8_t *status);
+/* Blocks until bnk_queue_submit has room again (some GPU batch has been emptied by its callers), at most
+ * timeout_ns (UINT64_MAX = no limit; BNK_ETIMEDOUT otherwise).  For callers that hold no ticket they could
+ * collect instead. */
+int bnk_queue_wait_room(bnk_queue *q, uint64_t timeout_ns);
+/* GPU batches submitted, packets in them, and caller batches taken so far (packets / GPU batches = how well the
+ * queue packs). */
+int bnk_queue_stats_get(bnk_queue *q, uint64_t *gpu_batches, uint64_t *packets, uint64_t *caller_batches);
+
+/* ---- several GPUs: placement of peers and a dispatcher that routes mixed batches ----
+ * All per-peer state (keys, send counter, replay window, the flows of the peer's /32) lives in one context, so
+ * peers shard over GPUs with no traffic between the GPUs; the reference likewise gives each peer one /32
+ * (internal/dataplane/engine.go:294) and one sequential worker (internal/magicsock/bind.go:325-328).  A peer is
+ * never split over two GPUs (its nonce order and its replay window are sequential).
+ *
+ * bnk_place_peers decides where peers go from a measured load per peer (packets or bytes of a past period):
+ * peers in order of falling load, each to the GPU that carries the least so far (ties: the GPU with fewer
+ * peers, then the lower ordinal), at most max_per_gpu peers per GPU.  With equal loads that is round robin;
+ * with skewed loads (a few heavy peers) the heavy ones end up on different GPUs.  Pure host arithmetic, the
+ * same on every caller that passes the same loads: processes that each drive one GPU agree on the placement
+ * without talking to each other.  Outputs: gpu_of[p] and slot_of[p] (the peer's keypair slot in that GPU's
+ * context, handed out in placement order), load_per_gpu[g] (may be NULL).  Returns BNK_EFULL when
+ * n_gpus * max_per_gpu < n_peers. */
+int bnk_place_peers(const uint64_t *load, uint32_t n_peers, uint32_t n_gpus, uint32_t max_per_gpu, uint32_t *gpu_of,
+                    uint32_t *slot_of, uint64_t *load_per_gpu);
+
+/* The dispatcher: one context per listed device, driven by one host thread each.  It stands where the
+ * reference's device.NewDevice stands when a box has several GPUs: bnk_mgpu_seal / bnk_mgpu_open take one
+ * mixed batch in the caller's buffers (a tun.Device.Read or conn.ReceiveFunc batch, or many of them), route
+ * every packet to its peer's GPU, keep batch order inside each peer, run the per-GPU submits side by side and
+ * hand the results back in the caller's order.  Plain cudaMemcpyAsync per GPU; no peer access, no collective. */
+typedef struct bnk_mgpu bnk_mgpu;
+typedef struct bnk_mgpu_cfg {
+    uint32_t struct_size;       /* sizeof(bnk_mgpu_cfg) */
+    uint32_t n_devices;
+    const int32_t *devices;     /* CUDA ordinals; one listed twice gets two contexts (for tests on one GPU) */
+    uint32_t max_pkts_per_gpu;  /* packets one submit of one GPU carries; longer batches go in rounds */
+    uint32_t max_packet;        /* longest plaintext packet */
+    uint32_t max_peers;         /* peers numbered 0 .. max_peers-1 */
+    uint32_t reserved;
+    bnk_cfg ctx;                /* per-GPU context settings; device_id is ignored, max_keypairs is per GPU */
+} bnk_mgpu_cfg;
+int bnk_mgpu_create(const bnk_mgpu_cfg *cfg, bnk_mgpu **out);
+int bnk_mgpu_destroy(bnk_mgpu *m);
+const char *bnk_mgpu_last_error_string(bnk_mgpu *m);
+/* The context of GPU g (0 .. n_devices-1), for table calls the dispatcher does not wrap. */
+bnk_ctx *bnk_mgpu_ctx(bnk_mgpu *m, uint32_t g);
+/* Places all peers from `load` (NULL = equal loads) with bnk_place_peers.  Allowed while no peer is set:
+ * a live peer moves with its next keypair (remove it, place, set it again), as a rekey would bring it. */
+int bnk_mgpu_place(bnk_mgpu *m, const uint64_t *load);
+int bnk_mgpu_locate(bnk_mgpu *m, uint32_t peer, uint32_t *gpu, uint32_t *slot);
+/* What bnk_keypair_set + bnk_index_set + bnk_keypair_set_allowed_ip do, on the peer's GPU. */
+int bnk_mgpu_peer_set(bnk_mgpu *m, uint32_t peer, const uint8_t send_key[32], const uint8_t recv_key[32],
+                      uint32_t remote_index, uint32_t local_index, uint32_t allowed_ipv4);
+int bnk_mgpu_peer_clear(bnk_mgpu *m, uint32_t peer);
+/* bnk_acl_set on every GPU (the rule table is replicated, flows stay with their peer's GPU). */
+int bnk_mgpu_acl_set(bnk_mgpu *m, int enforce, const bnk_acl_tuple *tuples, size_t n);
+/* Seals packets pkts[i][0 .. len[i]) of peer peer[i]; the message goes to out[i] (room for len + 48 bytes),
+ * its length to out_len[i], the nonce used to counter[i] (may be NULL), the outcome to status[i].  flags as for
+ * bnk_seal_submit; counters are always taken from the peers' send counters.  A peer that is not set yields
+ * BNK_PKT_NO_KEYPAIR.  Blocks until every GPU has finished. */
+int bnk_mgpu_seal(bnk_mgpu *m, const uint8_t *const *pkts, const uint32_t *len, const uint32_t *peer, uint32_t n,
+                  uint32_t flags, int64_t now_unix_ns, uint8_t *const *out, uint32_t *out_len, uint64_t *counter,
+                  uint8_t *status);
+/* Opens messages msgs[i][0 .. len[i]); the GPU is chosen by the receiver index in each header (bytes 4..7)
+ * through the indices given to bnk_mgpu_peer_set, the peer found goes to peer_out[i] (may be NULL), the
+ * plaintext to out[i] (room for len bytes), its length to out_len[i].  flags as for bnk_open_submit
+ * (BNK_F_REPLAY, BNK_F_INNER_CHECK, BNK_F_CHECK_INBOUND ...). */
+int bnk_mgpu_open(bnk_mgpu *m, const uint8_t *const *msgs, const uint32_t *len, uint32_t n, uint32_t flags,
+                  int64_t now_unix_ns, uint8_t *const *out, uint32_t *out_len, uint64_t *counter, uint32_t *peer_out,
+                  uint8_t *status);
+/* Packets and bytes the dispatcher has routed per peer since the last call with reset != 0: the measured load
+ * for the next placement.  Packets handed to each GPU since creation go to per_gpu (may be NULL). */
+int bnk_mgpu_loads_get(bnk_mgpu *m, uint64_t *packets_per_peer, uint64_t *bytes_per_peer, uint64_t *packets_per_gpu,
+                       int reset);
+
 /* ---- stage timing (tracing) ----
  * A submit made with BNK_F_TIMED brackets its kernels with CUDA events on the batch's stream. */
 /* Duration of the kernels of the batch's most recent submit made with BNK_F_TIMED (excluding copies), milliseconds. */

@@ -22,7 +22,7 @@ def test_reference_go_tests_restated_in_cpp(gpu_lib):
     res = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     print(res.stdout[-3000:])
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
-    assert "0 failed" in res.stdout and res.stdout.count("ran Test") == 15
+    assert "0 failed" in res.stdout and res.stdout.count("ran Test") == 16
 
 
 @pytest.mark.gpu
@@ -37,3 +37,46 @@ def test_threads_share_a_context(gpu_lib):
                              env={**os.environ, **env_extra})
         print(res.stdout[-500:], res.stderr[-2000:])
         assert res.returncode == 0 and res.stdout.startswith("OK"), res.stdout[-500:] + res.stderr[-2000:]
+
+
+
+@pytest.mark.gpu
+def test_threads_share_the_submit_queues(gpu_lib):
+    """The same eight threads hand their 128-packet calls to two shared submit queues (bnk_queue) instead of
+    batches of their own: nonces per keypair in call order, plaintext back, second delivery refused."""
+    from bnk_b200 import _build
+
+    exe = _build.build_mt_stress()
+    for threads, lanes in ((8, 2), (5, 3)):
+        res = subprocess.run([exe, str(threads), "60", "128", "1420", str(lanes), "1"], capture_output=True, text=True, timeout=300)
+        print(res.stdout[-500:], res.stderr[-2000:])
+        assert res.returncode == 0 and "\nOK mode=queue" in "\n" + res.stdout, res.stdout[-500:] + res.stderr[-2000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["asan", "tsan"])
+def test_host_layer_under_sanitizers(gpu_lib, kind):
+    """The library's host code (C ABI plumbing, submit queue, dispatcher, C++ mirror) built with
+    AddressSanitizer + UndefinedBehaviorSanitizer, and with ThreadSanitizer, runs the restated Go tests and the
+    threaded stress (own batches and shared queues) without a report.  Device code is not instrumented; the GPU
+    calls are ordinary host API calls to the sanitizers."""
+    from bnk_b200 import _build
+
+    out = _build.build_sanitized(kind)
+    env = dict(os.environ)
+    if kind == "asan":
+        # the CUDA driver maps memory where ASan keeps a gap, and keeps allocations of its own for the process's lifetime
+        env["ASAN_OPTIONS"] = "protect_shadow_gap=0:detect_leaks=0:abort_on_error=0"
+        env["UBSAN_OPTIONS"] = "print_stacktrace=1"
+    else:
+        env["TSAN_OPTIONS"] = "report_signal_unsafe=0"
+    runs = [[os.path.join(out, "host_test")],
+            [os.path.join(out, "mt_stress"), "4", "20", "128", "1420", "2", "0"],
+            [os.path.join(out, "mt_stress"), "4", "20", "128", "1420", "2", "1"]]
+    for cmd in runs:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+        text = res.stdout + res.stderr
+        print(text[-1500:])
+        assert res.returncode == 0, text[-3000:]
+        for mark in ("ThreadSanitizer", "AddressSanitizer", "runtime error"):
+            assert mark not in text, text[-3000:]

@@ -1,0 +1,149 @@
+"""The submit queue: upstream-sized caller batches from several threads, packed into GPU batches.  Whatever the
+packing, every caller gets its own packets back, byte for byte what the CPU checker makes of them; nonces run
+per keypair in submit order and replay verdicts follow arrival order across GPU batches."""
+import threading
+import time
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("depth,max_pkts", [(1, 256), (2, 1024), (3, 4096)])
+def test_queue_round_trip_from_several_threads(gpu_lib, oracle, depth, max_pkts):
+    from bnk_b200 import Context
+    from bnk_b200.device import F_REPLAY, PKT_KEEPALIVE, PKT_OK, PKT_REPLAY, Queue
+
+    n_threads, peers_per_thread, rounds, per_call = 6, 5, 12, 128
+    n_peers = n_threads * peers_per_thread
+    rng = np.random.default_rng(depth)
+    keys = rng.integers(0, 256, (n_peers, 32), dtype=np.uint8)
+    c = Context(max_keypairs=n_peers, mtu=1420, flow_capacity=0)
+    errors = []
+    try:
+        c.set_keypairs(0, keys, keys, (0x300 + np.arange(n_peers)).astype(np.uint32))
+        sealq = Queue(c, False, 0, max_pkts=max_pkts, depth=depth)
+        openq = Queue(c, True, F_REPLAY, max_pkts=max_pkts, depth=depth)
+
+        def collect(q, pending):
+            t = pending.pop(0)
+            return q.wait(t[0]), t[1]
+
+        def worker(t):
+            try:
+                r = np.random.default_rng(100 + t)
+                nxt = {}
+                sealed_all = []
+                pending = []
+
+                def check_sealed(res, meta):
+                    (msgs, st, ctr, _), (pkts, slots) = res, meta
+                    for k in range(len(pkts)):
+                        s = int(slots[k])
+                        want_ctr = nxt.get(s, 0)
+                        nxt[s] = want_ctr + 1
+                        assert st[k] == PKT_OK and ctr[k] == want_ctr, (t, k, st[k], ctr[k], want_ctr)
+                        if k % 7 == 0:  # the checker is scalar: a spread sample of the bytes, all of the counters
+                            assert msgs[k] == oracle.wg_seal(keys[s].tobytes(), 0x300 + s, want_ctr, pkts[k], 1420)
+                    sealed_all.append((msgs, pkts, slots))
+
+                for _ in range(rounds):
+                    n = int(r.integers(1, per_call + 1))
+                    sizes = r.choice([0, 64, 576, 1420], n)
+                    pkts = [r.integers(0, 256, int(s), dtype=np.uint8).tobytes() for s in sizes]
+                    slots = (t * peers_per_thread + r.integers(0, peers_per_thread, n)).astype(np.uint32)
+                    while True:
+                        ticket = sealq.submit(pkts, slots)
+                        if ticket is not None:
+                            break
+                        if pending:   # what this thread holds may be what keeps a GPU batch from being reused
+                            check_sealed(*collect(sealq, pending))
+                        else:         # the other threads are ahead: let them collect
+                            time.sleep(0)
+                    pending.append((ticket, (pkts, slots)))
+                    if len(pending) >= 3:
+                        check_sealed(*collect(sealq, pending))
+                while pending:
+                    check_sealed(*collect(sealq, pending))
+                # receive side: everything once, then everything again (all replays), two tickets in flight
+                for second in (False, True):
+                    pend = []
+
+                    def check_opened(res, meta):
+                        (pts, st, ctr, _), (pkts, slots) = res, meta
+                        for k in range(len(pkts)):
+                            if second:
+                                assert st[k] == PKT_REPLAY and pts[k] == b"", (t, k, st[k])
+                            else:
+                                assert st[k] == (PKT_OK if len(pkts[k]) else PKT_KEEPALIVE), (t, k, st[k])
+                                assert pts[k][:len(pkts[k])] == pkts[k]
+
+                    for msgs, pkts, slots in sealed_all:
+                        while True:
+                            ticket = openq.submit(msgs, slots)
+                            if ticket is not None:
+                                break
+                            if pend:
+                                check_opened(*collect(openq, pend))
+                            else:
+                                time.sleep(0)
+                        pend.append((ticket, (pkts, slots)))
+                        if len(pend) >= 2:
+                            check_opened(*collect(openq, pend))
+                    while pend:
+                        check_opened(*collect(openq, pend))
+            except BaseException as e:  # noqa: BLE001
+                errors.append((t, repr(e)))
+
+        threads = [threading.Thread(target=worker, args=(t,)) for t in range(n_threads)]
+        for th in threads:
+            th.start()
+        for th in threads:
+            th.join()
+        assert not errors, errors[:3]
+        ss, so = sealq.stats(), openq.stats()
+        assert ss["caller_batches"] == n_threads * rounds and ss["gpu_batches"] <= ss["caller_batches"]
+        assert so["caller_batches"] == 2 * n_threads * rounds
+        sealq.close()
+        openq.close()
+    finally:
+        c.close()
+
+
+def test_queue_refuses_what_it_cannot_take(gpu_lib):
+    import ctypes as C
+
+    from bnk_b200 import Context, _lib
+    from bnk_b200.device import Queue
+
+    c = Context(max_keypairs=4, mtu=1420, flow_capacity=0)
+    try:
+        c.set_keypair(0, bytes(32), bytes(range(32)), 1)
+        q = Queue(c, False, 0, max_pkts=8, max_packet=100, depth=1)
+        with pytest.raises(_lib.BnkError):
+            q.submit([b"x"] * 9, np.zeros(9, np.uint32))          # more than a GPU batch holds
+        with pytest.raises(_lib.BnkError):
+            q.submit([bytes(101)], np.zeros(1, np.uint32))         # longer than max_packet
+        t1 = q.submit([b"abc"] * 8, np.zeros(8, np.uint32))
+        outs, st, ctr, _ = q.wait(t1)
+        assert (st == 0).all() and list(ctr) == list(range(8)) and all(len(o) == 16 + 16 + 16 for o in outs)
+        dummy = np.zeros(64, np.uint8)
+        assert _lib.lib().bnk_queue_wait(q._h, t1[0], dummy.ctypes.data, dummy.ctypes.data, None, None,
+                                         dummy.ctypes.data) == _lib.EINVAL  # a ticket is good for one wait
+        # tickets held without being collected: the rotation runs out and submit says so instead of blocking
+        held = []
+        for _ in range(8):
+            t = q.submit([b"abc"] * 8, np.zeros(8, np.uint32))
+            if t is None:
+                break
+            held.append(t)
+        assert 1 <= len(held) < 8
+        assert _lib.lib().bnk_queue_wait_room(q._h, 1000) == _lib.ETIMEDOUT  # nobody collects: no room appears
+        for t in held:
+            q.wait(t)
+        assert _lib.lib().bnk_queue_wait_room(q._h, 0xFFFFFFFFFFFFFFFF) == 0
+        assert q.submit([b"abc"], np.zeros(1, np.uint32)) is not None
+        q.close()
+    finally:
+        c.close()
