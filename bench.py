@@ -45,7 +45,7 @@ REGIONS = 5  # timed regions of K steps each; the median one is reported
 # the output is still dirty in the 126 MB L2 when the launch ends has not reached DRAM yet (about 50 MB, so the
 # larger the launch the smaller the share).  The capture closest in size to the benchmark's launch is used and
 # scaled by the packet count.
-NCU_DRAM_CAPTURES = [(131072, 131072 * 2569)]
+NCU_DRAM_CAPTURES = [(131072, 131072 * 2569), (524288, 780716032 + 718754304)]
 
 
 # ----------------------------------------------------------------------------------------------
@@ -511,7 +511,7 @@ def run_ours(args, rank, world, local_rank):
     traffic = cap_bytes * n_launch // cap_n
     traffic_note = (f"ncu dram__bytes_read.sum + dram__bytes_write.sum of a {cap_n}-packet seal launch, scaled by packet "
                     f"count; a lower bound (output still dirty in L2 at kernel end is not counted: "
-                    f"~{50e6 / (cap_n * HBM_BYTES_PER_PACKET) * 100:.0f} % of that launch)")
+                    f"~{42e6 / (cap_n * HBM_BYTES_PER_PACKET) * 100:.0f} % of that launch)")
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
         "traffic": traffic, "traffic_note": traffic_note,
@@ -521,14 +521,30 @@ def run_ours(args, rank, world, local_rank):
         "note": "the path is bound by the 32-bit integer pipes, not by HBM: see `alu`",
     }
     alu = None
+    ctx_sm_count = 148  # B200; only used to turn the measured kernel time into cycles per block
     if rank == 0 and not args.no_probe:
         probes = {name: ctx.probe_int_throughput(mix) for mix, name in
                   enumerate(["add_xor", "chacha_rounds", "imad", "add_xor_plus_imad"])}
         int_peak = max(probes.values())
         ops = n_launch * INT_OPS_PER_PACKET / (aead_avg * 1e-3) / 1e12
+        # what Poly1305's multiplies (or any stand-in for them) cost beside the rounds: scheduler cycles per ChaCha20
+        # double round per warp with k extra operations interleaved; 128 is the ALU-pipe bound of the rounds alone
+        co = {name: ctx.probe_coissue(kind, k) for name, kind, k in
+              [("rounds_alone", 0, 0), ("mad_wide_x8", 1, 8), ("mad_wide_x16", 1, 16), ("fp64_fma_x16", 2, 16),
+               ("fp64_fma_x32", 2, 32), ("mad_lo_x16", 3, 16), ("mad_lo_x32", 3, 32), ("fp32_fma_x16", 4, 16),
+               ("fp32_fma_x32", 4, 32), ("mul_hi_x8", 5, 8), ("mul_hi_x16", 5, 16)]}
+        # per 64-byte block: 10 double rounds + 85 wide multiply-adds (4 Poly1305 blocks) at their interleaved cost,
+        # + the ~100 ALU-pipe instructions of Poly1305's carries and the data exclusive-ors at 2 cycles each
+        wide_each = (co["mad_wide_x8"] - co["rounds_alone"]) / 8.0
+        floor_cycles = 10 * co["rounds_alone"] + 85 * wide_each + 100 * 2
+        cycles_now = aead_avg * 1e-3 * 1.965e9 * 4 * ctx_sm_count / (n_launch / 32.0) / 24.0  # 4 schedulers per SM, 24 blocks per packet
         alu = {"bound": "int32 issue", "achieved": ops, "peak": int_peak, "unit": "Tops/s", "frac": ops / int_peak,
                "ops_per_packet": INT_OPS_PER_PACKET, "probes_tops": probes,
-               "peak_source": "measured live by bnk_probe_int_throughput (best of the instruction mixes)"}
+               "peak_source": "measured live by bnk_probe_int_throughput (best of the instruction mixes)",
+               "coissue_cycles_per_double_round": co,
+               "cycles_per_64B_block_per_warp": {"kernel_now": cycles_now, "floor_from_probes": floor_cycles,
+                                                  "kernel_over_floor": cycles_now / floor_cycles,
+                                                  "alu_pipe_bound_of_the_rounds_alone": 1280.0}}
     dev.close()
 
     # ---- IMIX, device-resident, the same number of batches in flight ----

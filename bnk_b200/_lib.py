@@ -195,6 +195,7 @@ BENCH_SYMBOLS = {
     "bnk_timer_start": (_i, [_vp, C.POINTER(_vp), _u32]),
     "bnk_timer_stop": (_i, [_vp, C.POINTER(_vp), _u32, C.POINTER(C.c_float)]),
     "bnk_probe_int_throughput": (_i, [_vp, _i, C.POINTER(C.c_double)]),
+    "bnk_probe_coissue": (_i, [_vp, _i, _i, C.POINTER(C.c_double)]),
     "bnk_batch_fill_random": (_i, [_vp, _u64]),
     "bnk_batch_copy_only": (_i, [_vp, _u32, _i, _i]),
 }

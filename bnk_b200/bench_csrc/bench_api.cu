@@ -5,6 +5,7 @@
 
 cudaError_t launch_fill_random(uint8_t *dst, uint64_t bytes, uint64_t seed, int sm_count, cudaStream_t s);
 cudaError_t probe_int_throughput(bnk_ctx *ctx, int mix, double *tops);
+cudaError_t probe_coissue(bnk_ctx *ctx, int kind, int k, double *clk);
 
 namespace {
 
@@ -57,6 +58,13 @@ int bnk_probe_int_throughput(bnk_ctx *ctx, int mix, double *tera_ops_per_s) {
     if (!ctx || !tera_ops_per_s) return BNK_EINVAL;
     CK(ctx, cudaSetDevice(ctx->device));
     CK(ctx, probe_int_throughput(ctx, mix, tera_ops_per_s));
+    return BNK_SUCCESS;
+}
+
+int bnk_probe_coissue(bnk_ctx *ctx, int kind, int k, double *cycles_per_double_round) {
+    if (!ctx || !cycles_per_double_round) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, probe_coissue(ctx, kind, k, cycles_per_double_round));
     return BNK_SUCCESS;
 }
 

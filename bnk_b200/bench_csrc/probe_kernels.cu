@@ -155,6 +155,115 @@ cudaError_t launch_fill_random(uint8_t *dst, uint64_t bytes, uint64_t seed, int 
     return cudaGetLastError();
 }
 
+// ---- what other work costs beside ChaCha20 rounds ----
+// The seal/open kernels are ChaCha20 rounds (bound by the ALU pipe) plus Poly1305 and data movement.  This probe
+// runs ChaCha20 double rounds, 4 warps per scheduler like the kernels, and adds K operations of one kind per
+// double round from independent chains: 1 = 32x32+64 multiply-add (Poly1305's product form), 2 = FP64 fused
+// multiply-add, 3 = 32-bit multiply-add, 4 = FP32 fused multiply-add, 5 = high half of a 32x32 product.  The
+// result is scheduler cycles per double round per warp; the difference to K = 0 is what the extra work costs when
+// it is interleaved as well as a compiler can interleave it, i.e. how much of it hides under the rounds.
+constexpr int kCoIters = 2048;
+__device__ __forceinline__ void probe_qr(uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
+    a += b; d = __byte_perm(d ^ a, 0, 0x1032);
+    c += d; b = __funnelshift_l(b ^ c, b ^ c, 12);
+    a += b; d = __byte_perm(d ^ a, 0, 0x2103);
+    c += d; b = __funnelshift_l(b ^ c, b ^ c, 7);
+}
+template <int KIND, int K>
+__device__ __forceinline__ void probe_extra(int first, int last, uint64_t (&w)[8], double (&f)[8], float (&g)[8], uint32_t (&y)[8],
+                                            uint32_t mul, double dm) {
+#pragma unroll
+    for (int j = first; j < last; j++) {
+        if (KIND == 1) w[j & 7] = (uint64_t)(uint32_t)w[j & 7] * mul + w[j & 7];
+        if (KIND == 2) f[j & 7] = fma(f[j & 7], dm, f[(j + 1) & 7]);
+        if (KIND == 3) y[j & 7] = y[j & 7] * mul + y[(j + 1) & 7];
+        if (KIND == 4) g[j & 7] = fmaf(g[j & 7], (float)dm, g[(j + 1) & 7]);
+        if (KIND == 5) y[j & 7] = __umulhi(y[j & 7], mul) + y[(j + 1) & 7];
+    }
+}
+template <int KIND, int K>
+__global__ void __launch_bounds__(128, 4) coissue_probe_kernel(uint32_t *sink, uint32_t seed, uint32_t mul, double dm) {
+    uint32_t x[16], y[8];
+    uint64_t w[8];
+    double f[8];
+    float g[8];
+#pragma unroll
+    for (int i = 0; i < 16; i++) x[i] = seed * (i + 1) + threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        w[i] = seed * 77ull + i + threadIdx.x;
+        f[i] = 1.0 + (double)(threadIdx.x + i) * 1e-3;
+        g[i] = (float)f[i];
+        y[i] = seed + i * 7 + threadIdx.x;
+    }
+#pragma unroll 1
+    for (int it = 0; it < kCoIters; it++) {
+        probe_qr(x[0], x[4], x[8], x[12]); probe_qr(x[1], x[5], x[9], x[13]);
+        probe_qr(x[2], x[6], x[10], x[14]); probe_qr(x[3], x[7], x[11], x[15]);
+        probe_extra<KIND, K>(0, K / 2, w, f, g, y, mul, dm);
+        probe_qr(x[0], x[5], x[10], x[15]); probe_qr(x[1], x[6], x[11], x[12]);
+        probe_qr(x[2], x[7], x[8], x[13]); probe_qr(x[3], x[4], x[9], x[14]);
+        probe_extra<KIND, K>(K / 2, K, w, f, g, y, mul, dm);
+    }
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) acc ^= x[i];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc ^= (uint32_t)w[i] ^ (uint32_t)(w[i] >> 32) ^ (uint32_t)__double2loint(f[i]) ^ __float_as_uint(g[i]) ^ y[i];
+    if (acc == 0x12345678u) sink[blockIdx.x * blockDim.x + threadIdx.x] = acc;
+}
+
+template <int KIND, int K>
+cudaError_t run_coissue(bnk_ctx *ctx, double sm_hz, double *clk) {
+    const int waves = 4, ctas = ctx->sm_count * 4 * waves; // 4 CTAs of 4 warps per SM: 4 warps per scheduler
+    uint32_t *sink = nullptr;
+    cudaError_t e = cudaMalloc(&sink, (size_t)ctas * 128 * sizeof(uint32_t));
+    if (e != cudaSuccess) return e;
+    cudaEvent_t t0, t1;
+    cudaEventCreate(&t0);
+    cudaEventCreate(&t1);
+    cudaStream_t s = ctx->admin_stream;
+    float best = 1e30f;
+    for (int rep = 0; rep < 4; rep++) {
+        cudaEventRecord(t0, s);
+        coissue_probe_kernel<KIND, K><<<ctas, 128, 0, s>>>(sink, 17u + rep, 3u, 1.0000001);
+        cudaEventRecord(t1, s);
+        ctx->launches += 1;
+        if ((e = cudaEventSynchronize(t1)) != cudaSuccess) break;
+        float ms = 0;
+        cudaEventElapsedTime(&ms, t0, t1);
+        if (rep >= 1 && ms < best) best = ms;
+    }
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+    cudaFree(sink);
+    if (e != cudaSuccess) return e;
+    *clk = best * 1e-3 * sm_hz / kCoIters / waves / 4.0; // per double round, per warp, in cycles of its scheduler
+    return cudaSuccess;
+}
+
+cudaError_t probe_coissue(bnk_ctx *ctx, int kind, int k, double *clk) {
+    int khz = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device);
+    if (e != cudaSuccess) return e;
+    const double hz = khz * 1e3;
+    const int key = kind * 100 + k;
+    switch (key) {
+    case 0: return run_coissue<0, 0>(ctx, hz, clk);
+    case 108: return run_coissue<1, 8>(ctx, hz, clk);
+    case 116: return run_coissue<1, 16>(ctx, hz, clk);
+    case 216: return run_coissue<2, 16>(ctx, hz, clk);
+    case 232: return run_coissue<2, 32>(ctx, hz, clk);
+    case 316: return run_coissue<3, 16>(ctx, hz, clk);
+    case 332: return run_coissue<3, 32>(ctx, hz, clk);
+    case 416: return run_coissue<4, 16>(ctx, hz, clk);
+    case 432: return run_coissue<4, 32>(ctx, hz, clk);
+    case 508: return run_coissue<5, 8>(ctx, hz, clk);
+    case 516: return run_coissue<5, 16>(ctx, hz, clk);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
 cudaError_t probe_int_throughput(bnk_ctx *ctx, int mix, double *tops) {
     if (mix < 0 || mix > 7) return cudaErrorInvalidValue;
     const int ctas = ctx->sm_count * 8, threads = 256;

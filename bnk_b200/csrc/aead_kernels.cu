@@ -30,9 +30,6 @@ namespace {
 #ifndef BNK_MIN_CTAS
 #define BNK_MIN_CTAS 4
 #endif
-#ifndef BNK_PEEL
-#define BNK_PEEL 0
-#endif
 #ifndef BNK_WARPS_PER_CTA
 #define BNK_WARPS_PER_CTA 4
 #endif
@@ -120,16 +117,6 @@ __device__ __forceinline__ void poly_init(Poly &p, uint32_t k0, uint32_t k1, uin
     p.s3 = p.r3 + (p.r3 >> 2);
 }
 
-#ifndef BNK_POLY_FOLD
-#define BNK_POLY_FOLD 0
-#endif
-// a * b + c with a 64-bit addend: one instruction (the compiler is not left to choose another shape)
-__device__ __forceinline__ uint64_t mad_wide(uint32_t a, uint32_t b, uint64_t c) {
-    uint64_t d;
-    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
-    return d;
-}
-
 // h = (h + m + 2^128) * r, partially reduced.
 __device__ __forceinline__ void poly_block(Poly &p, uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3) {
     uint32_t h0 = p.h0, h1 = p.h1, h2 = p.h2, h3 = p.h3, h4 = p.h4;
@@ -140,16 +127,6 @@ __device__ __forceinline__ void poly_block(Poly &p, uint32_t m0, uint32_t m1, ui
         "addc.u32 %4, %4, 1;"
         : "+r"(h0), "+r"(h1), "+r"(h2), "+r"(h3), "+r"(h4)
         : "r"(m0), "r"(m1), "r"(m2), "r"(m3));
-#if BNK_POLY_FOLD
-    // The carry out of each column enters the next column as the addend of its first multiply-add, so the three
-    // 64-bit additions that would move the carries along (two instructions each, on the pipe the ChaCha20
-    // rounds are waiting for) disappear; the columns then depend on each other, which the other warps hide.
-    uint64_t d0 = mad_wide(h3, p.s1, mad_wide(h2, p.s2, mad_wide(h1, p.s3, (uint64_t)h0 * p.r0)));
-    uint64_t d1 = mad_wide(h4, p.s1, mad_wide(h3, p.s2, mad_wide(h2, p.s3, mad_wide(h1, p.r0, mad_wide(h0, p.r1, d0 >> 32)))));
-    uint64_t d2 = mad_wide(h4, p.s2, mad_wide(h3, p.s3, mad_wide(h2, p.r0, mad_wide(h1, p.r1, mad_wide(h0, p.r2, d1 >> 32)))));
-    uint64_t d3 = mad_wide(h4, p.s3, mad_wide(h3, p.r0, mad_wide(h2, p.r1, mad_wide(h1, p.r2, mad_wide(h0, p.r3, d2 >> 32)))));
-    uint32_t top = h4 * p.r0 + (uint32_t)(d3 >> 32);
-#else
     uint64_t d0 = (uint64_t)h0 * p.r0 + (uint64_t)h1 * p.s3 + (uint64_t)h2 * p.s2 + (uint64_t)h3 * p.s1;
     uint64_t d1 = (uint64_t)h0 * p.r1 + (uint64_t)h1 * p.r0 + (uint64_t)h2 * p.s3 + (uint64_t)h3 * p.s2 +
                   (uint64_t)h4 * p.s1;
@@ -162,7 +139,6 @@ __device__ __forceinline__ void poly_block(Poly &p, uint32_t m0, uint32_t m1, ui
     d2 += d1 >> 32;
     d3 += d2 >> 32;
     top += (uint32_t)(d3 >> 32);
-#endif
     // everything at or above 2^130 comes back multiplied by 5
     uint32_t c = (top >> 2) + (top & ~3u);
     h0 = (uint32_t)d0;
@@ -347,29 +323,11 @@ __global__ void __launch_bounds__(kThreads, BNK_MIN_CTAS) aead_kernel(const Aead
 
     // (Splitting off a branch-free loop over the whole blocks so that the Poly1305 multiplies can be scheduled
     // into the ChaCha20 rounds of the same thread, with the seal side absorbing the previous block's ciphertext,
-    // was measured: no gain for seal, 10 % slower for open.  The warps of an SM already overlap the two phases.)
-    uint32_t b = 0;
-#if BNK_PEEL
-    // Whole blocks of real bytes first, in a loop that asks nothing: four loads, the rounds, four Poly1305 blocks,
-    // four stores.  The comparisons against the ends of input and body are left to the one ragged block below.
-    for (const uint32_t whole = in_len >> 6; b < whole; b++) {
-        uint8_t *const at = data + b * 64u;
-        uint4 v[4];
-#pragma unroll
-        for (int c = 0; c < 4; c++) v[c] = *reinterpret_cast<const uint4 *>(at + 16 * c);
-        uint32_t x[16];
-        chacha20_block(x, key, b + 1u, n_lo, n_hi);
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const uint32_t o0 = v[c].x ^ x[4 * c + 0], o1 = v[c].y ^ x[4 * c + 1];
-            const uint32_t o2 = v[c].z ^ x[4 * c + 2], o3 = v[c].w ^ x[4 * c + 3];
-            if (OPEN) poly_block(poly, v[c].x, v[c].y, v[c].z, v[c].w);
-            else poly_block(poly, o0, o1, o2, o3);
-            *reinterpret_cast<uint4 *>(at + 16 * c) = make_uint4(o0, o1, o2, o3);
-        }
-    }
-#endif
-    for (; b < nblk; b++) {
+    // was measured: no gain for seal, 10 % slower for open.  The warps of an SM already overlap the two phases.
+    // Measured again on 1,048,576 x 1420 B with the comparisons peeled off the whole-block loop: seal 1.279 ms
+    // against 1.276, open 1.383 against 1.261.  Feeding each Poly1305 column's carry into the next column's
+    // first multiply-add instead of three 64-bit additions: seal 1.256, open 1.276: within the run-to-run spread.)
+    for (uint32_t b = 0; b < nblk; b++) {
         const uint32_t base = b * 64u;
         uint32_t d[16];
 #pragma unroll

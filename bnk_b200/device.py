@@ -180,6 +180,11 @@ class Context:
         self._ck(_lib.bench_lib().bnk_probe_int_throughput(self._h, mix, C.byref(v)))
         return v.value
 
+    def probe_coissue(self, kind: int, k: int) -> float:
+        v = C.c_double()
+        self._ck(_lib.bench_lib().bnk_probe_coissue(self._h, kind, k, C.byref(v)))
+        return v.value
+
     def timer_start(self, batches: Sequence["Batch"]):
         arr = (C.c_void_p * len(batches))(*[b._h for b in batches])
         self._ck(_lib.bench_lib().bnk_timer_start(self._h, arr, len(batches)))
