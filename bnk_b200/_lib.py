@@ -90,6 +90,11 @@ class BatchView(C.Structure):
     ]
 
 
+class FlowEntry(C.Structure):
+    _fields_ = [("remote_addr", C.c_uint32), ("remote_port", C.c_uint16), ("local_port", C.c_uint16), ("proto", C.c_uint8),
+                ("reserved", C.c_uint8 * 7), ("expiry_unix_ns", C.c_int64)]
+
+
 class BatchStats(C.Structure):
     _fields_ = [("packets", C.c_uint64), ("bytes_out", C.c_uint64), ("by_status", C.c_uint64 * 16)]
 
@@ -150,6 +155,8 @@ SYMBOLS = {
     "bnk_acl_set": (_i, [_vp, _i, _vp, _sz]),
     "bnk_flows_clear": (_i, [_vp]),
     "bnk_flows_count": (_i, [_vp, C.POINTER(_u64)]),
+    "bnk_flows_export": (_i, [_vp, _vp, _sz, C.POINTER(_sz)]),
+    "bnk_flows_import": (_i, [_vp, _vp, _sz]),
     "bnk_table_stats_get": (_i, [_vp, C.POINTER(TableStats)]),
     "bnk_batch_create": (_i, [_vp, _u32, _u64, C.POINTER(_vp)]),
     "bnk_batch_destroy": (_i, [_vp]),

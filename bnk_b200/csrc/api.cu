@@ -561,6 +561,24 @@ int bnk_flows_count(bnk_ctx *ctx, uint64_t *live) {
     return BNK_SUCCESS;
 }
 
+int bnk_flows_export(bnk_ctx *ctx, bnk_flow_entry *out, size_t capacity, size_t *count) {
+    if (!ctx || !count || (capacity && !out)) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    std::unique_lock<std::shared_mutex> tables(ctx->submit_mu);
+    CK(ctx, cudaDeviceSynchronize());
+    const int rc = filter_flows_export(ctx, out, capacity, count);
+    return rc == BNK_SUCCESS ? rc : fail(ctx, rc, "flow table export failed");
+}
+
+int bnk_flows_import(bnk_ctx *ctx, const bnk_flow_entry *entries, size_t n) {
+    if (!ctx || (n && !entries)) return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    std::unique_lock<std::shared_mutex> tables(ctx->submit_mu);
+    CK(ctx, cudaDeviceSynchronize());
+    const int rc = filter_flows_import(ctx, entries, n);
+    return rc == BNK_SUCCESS ? rc : fail(ctx, rc, rc == BNK_EFULL ? "flow table full" : "flow table import failed");
+}
+
 int bnk_table_stats_get(bnk_ctx *ctx, bnk_table_stats *out) {
     if (!ctx || !out) return BNK_EINVAL;
     CK(ctx, cudaSetDevice(ctx->device));

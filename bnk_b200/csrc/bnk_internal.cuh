@@ -244,6 +244,8 @@ void filter_tables_free(bnk_ctx *ctx);
 int filter_acl_upload(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n);
 cudaError_t filter_flows_clear(bnk_ctx *ctx, cudaStream_t s);
 cudaError_t filter_flow_stats(bnk_ctx *ctx, uint64_t *live, uint32_t used[3], uint32_t dead[3]);
+int filter_flows_export(bnk_ctx *ctx, bnk_flow_entry *out, size_t capacity, size_t *count);
+int filter_flows_import(bnk_ctx *ctx, const bnk_flow_entry *entries, size_t n);
 cudaError_t launch_flow_report(bnk_batch *b, cudaStream_t s); // copies the flow table's control block to b->h_flow
 // Rebuilds the regions whose deleted entries have piled up; called by a submit that feeds the flow table,
 // before it takes submit_mu.  Returns without doing anything in the common case.

@@ -446,6 +446,108 @@ cudaError_t filter_flow_stats(bnk_ctx *ctx, uint64_t *live, uint32_t used[3], ui
     return cudaSuccess;
 }
 
+// Export and import work on host copies of the tables: they are for tests and state hand-over, not for the packet
+// path, and the caller has quiesced the context.  The host applies the same hash and the same probing as the kernels.
+namespace {
+struct FlowTablesHost {
+    std::vector<unsigned long long> keys;
+    std::vector<long long> exp;
+    long long special[3];
+    FlowCtl ctl;
+};
+cudaError_t flows_download(bnk_ctx *ctx, FlowTablesHost &h) {
+    const FilterTables &ft = ctx->ft;
+    const size_t total = (size_t)6 * ft.flow_capacity;
+    h.keys.resize(total);
+    h.exp.resize(total);
+    cudaError_t e = cudaSuccess;
+    if (total) {
+        e = cudaMemcpy(h.keys.data(), ft.flow_keys, total * sizeof(uint64_t), cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) e = cudaMemcpy(h.exp.data(), ft.flow_exp, total * sizeof(long long), cudaMemcpyDeviceToHost);
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(h.special, ft.flow_special_exp, sizeof h.special, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemcpy(&h.ctl, ft.flow_live, sizeof h.ctl, cudaMemcpyDeviceToHost);
+    return e;
+}
+int class_of(uint8_t proto) { return proto == 6 ? 0 : (proto == 17 ? 1 : 2); }
+uint8_t proto_of(int cls) { return cls == 0 ? 6 : (cls == 1 ? 17 : 1); }
+bool absent_host(long long exp) { return exp <= FLOW_FRESH; }
+} // namespace
+
+int filter_flows_export(bnk_ctx *ctx, bnk_flow_entry *out, size_t capacity, size_t *count) {
+    FlowTablesHost h;
+    if (flows_download(ctx, h) != cudaSuccess) return BNK_ECUDA;
+    const FilterTables &ft = ctx->ft;
+    size_t n = 0;
+    auto emit = [&](int cls, unsigned long long key, long long exp) {
+        if (n < capacity && out) {
+            bnk_flow_entry e{};
+            e.remote_addr = (uint32_t)(key >> 32);
+            e.remote_port = (uint16_t)(key >> 16);
+            e.local_port = (uint16_t)key;
+            e.proto = proto_of(cls);
+            e.expiry_unix_ns = exp;
+            out[n] = e;
+        }
+        n++;
+    };
+    for (int cls = 0; cls < 3; cls++) {
+        const size_t base = flow_region(ft, cls);
+        for (size_t k = 0; k < ft.flow_capacity; k++)
+            if (h.keys[base + k] != FLOW_EMPTY && !absent_host(h.exp[base + k])) emit(cls, h.keys[base + k], h.exp[base + k]);
+        if (!absent_host(h.special[cls])) emit(cls, FLOW_EMPTY, h.special[cls]);
+    }
+    *count = n;
+    return BNK_SUCCESS;
+}
+
+int filter_flows_import(bnk_ctx *ctx, const bnk_flow_entry *entries, size_t n) {
+    FlowTablesHost h;
+    if (flows_download(ctx, h) != cudaSuccess) return BNK_ECUDA;
+    const FilterTables &ft = ctx->ft;
+    const uint32_t cap = ft.flow_capacity;
+    for (size_t i = 0; i < n; i++) {
+        const bnk_flow_entry &e = entries[i];
+        if (e.proto != 6 && e.proto != 17 && e.proto != 1) return BNK_EINVAL;
+        if (absent_host(e.expiry_unix_ns)) return BNK_EINVAL;
+        const int cls = class_of(e.proto);
+        const unsigned long long key = ((unsigned long long)e.remote_addr << 32) | ((unsigned long long)e.remote_port << 16) | e.local_port;
+        if (key == FLOW_EMPTY) {
+            if (absent_host(h.special[cls])) h.ctl.live++;
+            h.special[cls] = e.expiry_unix_ns;
+            continue;
+        }
+        if (cap == 0) return BNK_EFULL;
+        const size_t base = flow_region(ft, cls);
+        uint32_t at = (uint32_t)mix64(key) & (cap - 1);
+        bool placed = false;
+        for (uint32_t probe = 0; probe < cap && !placed; probe++, at = (at + 1) & (cap - 1)) {
+            unsigned long long &k = h.keys[base + at];
+            if (k != FLOW_EMPTY && k != key) continue;
+            if (k == FLOW_EMPTY) {
+                k = key;
+                h.ctl.rep.used[cls]++;
+            }
+            long long &x = h.exp[base + at];
+            if (absent_host(x)) h.ctl.live++;
+            if (x == FLOW_DEAD) h.ctl.rep.dead[cls]--;
+            x = e.expiry_unix_ns;
+            placed = true;
+        }
+        if (!placed) return BNK_EFULL;
+    }
+    h.ctl.swept_valid = 0;
+    const size_t total = (size_t)6 * cap;
+    cudaError_t e = cudaSuccess;
+    if (total) {
+        e = cudaMemcpy(ft.flow_keys, h.keys.data(), total * sizeof(uint64_t), cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(ft.flow_exp, h.exp.data(), total * sizeof(long long), cudaMemcpyHostToDevice);
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(ft.flow_special_exp, h.special, sizeof h.special, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(ft.flow_live, &h.ctl, sizeof h.ctl, cudaMemcpyHostToDevice);
+    return e == cudaSuccess ? BNK_SUCCESS : BNK_ECUDA;
+}
+
 cudaError_t launch_flow_report(bnk_batch *b, cudaStream_t s) {
     const FlowCtl *ctl = reinterpret_cast<const FlowCtl *>(b->ctx->ft.flow_live);
     b->flow_reported = true;

@@ -40,6 +40,7 @@ from ._lib import (  # noqa: F401  (re-exported)
 
 ACL_TUPLE_DTYPE = np.dtype(_lib.AclTuple)
 GSO_SUPER_DTYPE = np.dtype(_lib.GsoSuper)
+FLOW_ENTRY_DTYPE = np.dtype(_lib.FlowEntry)
 
 
 def _np_view(ptr: int, dtype, count: int) -> np.ndarray:
@@ -160,6 +161,19 @@ class Context:
         v = C.c_uint64()
         self._ck(_lib.lib().bnk_flows_count(self._h, C.byref(v)))
         return v.value
+
+    def flows_export(self) -> np.ndarray:
+        """The flow table's live entries as a FLOW_ENTRY_DTYPE array sorted by key."""
+        n = C.c_size_t()
+        self._ck(_lib.lib().bnk_flows_export(self._h, None, 0, C.byref(n)))
+        out = np.zeros(max(n.value, 1), FLOW_ENTRY_DTYPE)
+        self._ck(_lib.lib().bnk_flows_export(self._h, out.ctypes.data, n.value, C.byref(n)))
+        out = out[:n.value]
+        return out[np.lexsort((out["local_port"], out["remote_port"], out["remote_addr"], out["proto"]))]
+
+    def flows_import(self, entries: np.ndarray):
+        entries = np.ascontiguousarray(entries, FLOW_ENTRY_DTYPE)
+        self._ck(_lib.lib().bnk_flows_import(self._h, entries.ctypes.data, len(entries)))
 
     def table_stats(self) -> "_lib.TableStats":
         v = _lib.TableStats()

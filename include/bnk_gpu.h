@@ -178,6 +178,20 @@ int bnk_replay_import(bnk_ctx *ctx, uint32_t slot, uint64_t last, const uint64_t
 int bnk_acl_set(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, size_t n);
 int bnk_flows_clear(bnk_ctx *ctx);
 int bnk_flows_count(bnk_ctx *ctx, uint64_t *live);
+/* The flow table's contents, for tests and for handing state over (the reference never persists it: it is rebuilt
+ * by traffic).  One entry = one key of Go's map f.flows (internal/filter/filter.go:26-31) with its expiry.
+ * bnk_flows_export writes up to `capacity` live entries in no particular order and always stores the number of
+ * live entries in *count; bnk_flows_import adds entries (an existing key gets the new expiry), BNK_EFULL when a
+ * class's region has no room.  Both wait for submitted work and must not run beside submits. */
+typedef struct bnk_flow_entry {
+    uint32_t remote_addr;   /* host order */
+    uint16_t remote_port, local_port;
+    uint8_t proto;          /* 6 tcp, 17 udp, 1 icmp */
+    uint8_t reserved[7];
+    int64_t expiry_unix_ns;
+} bnk_flow_entry;
+int bnk_flows_export(bnk_ctx *ctx, bnk_flow_entry *out, size_t capacity, size_t *count);
+int bnk_flows_import(bnk_ctx *ctx, const bnk_flow_entry *entries, size_t n);
 /* Occupancy of the context's hash tables, for monitoring: entries in use, entries deleted but not yet
  * reclaimed, and slots.  Deleted entries are reclaimed by the library itself (the flow table is compacted
  * between batches once a quarter of a class's slots are deleted entries, the two host-maintained tables are

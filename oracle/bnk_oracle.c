@@ -699,6 +699,24 @@ void bnko_filter_set_allow_all(bnko_filter *f) {
 
 size_t bnko_filter_flow_count(const bnko_filter *f) { return f->live; }
 
+/* the map's contents, in no particular order: Go's f.flows as (key, expiry) pairs */
+size_t bnko_filter_flows_export(const bnko_filter *f, bnko_flow *out, size_t cap) {
+    size_t n = 0;
+    for (size_t k = 0; k < f->cap; k++) {
+        if (f->tab[k].state != 1) continue;
+        if (n < cap) {
+            out[n].remote = f->tab[k].remote;
+            out[n].rport = f->tab[k].rport;
+            out[n].lport = f->tab[k].lport;
+            out[n].proto = f->tab[k].proto;
+            memset(out[n].reserved, 0, sizeof out[n].reserved);
+            out[n].exp = f->tab[k].exp;
+        }
+        n++;
+    }
+    return n;
+}
+
 /* filter.go:121-147 */
 int bnko_filter_check_inbound(bnko_filter *f, const uint8_t *pkt, size_t len, int64_t now_ns) {
     if (!f->enforce) return 1;

@@ -134,6 +134,17 @@ void bnko_filter_set_allow_all(bnko_filter *f);
 int bnko_filter_check_inbound(bnko_filter *f, const uint8_t *pkt, size_t len, int64_t now_ns);
 void bnko_filter_note_outbound(bnko_filter *f, const uint8_t *pkt, size_t len, int64_t now_ns);
 size_t bnko_filter_flow_count(const bnko_filter *f);
+/* one entry of the flow map: key {remote, remote port, local port, proto} -> expiry (unix ns); same layout as
+ * bnk_flow_entry of the GPU library */
+typedef struct {
+    uint32_t remote;
+    uint16_t rport, lport;
+    uint8_t proto;
+    uint8_t reserved[7];
+    int64_t exp;
+} bnko_flow;
+/* writes up to cap entries, returns how many the map holds */
+size_t bnko_filter_flows_export(const bnko_filter *f, bnko_flow *out, size_t cap);
 /* header-array forms: packet i is hdr + i*stride, length len[i] */
 void bnko_filter_check_batch(bnko_filter *f, const uint8_t *hdr, size_t stride, const uint32_t *len, size_t n,
                              int64_t now_ns, uint8_t *verdict);

@@ -120,6 +120,8 @@ def lib() -> C.CDLL:
     L.bnko_filter_note_outbound.restype = None
     L.bnko_filter_flow_count.argtypes = [vp]
     L.bnko_filter_flow_count.restype = sz
+    L.bnko_filter_flows_export.argtypes = [vp, vp, sz]
+    L.bnko_filter_flows_export.restype = sz
     L.bnko_filter_check_batch.argtypes = [vp, vp, sz, vp, sz, C.c_int64, vp]
     L.bnko_filter_check_batch.restype = None
     L.bnko_filter_check_batch_mt.argtypes = [vp, vp, sz, vp, sz, C.c_int64, vp, C.c_int]
@@ -374,7 +376,18 @@ class Filter:
     def flow_count(self) -> int:
         return lib().bnko_filter_flow_count(self._h)
 
+    def flows(self) -> np.ndarray:
+        """The map's entries as a FLOW_DTYPE array sorted by key."""
+        n = self.flow_count
+        out = np.zeros(max(n, 1), FLOW_DTYPE)
+        got = lib().bnko_filter_flows_export(self._h, _ptr(out), n)
+        assert got == n
+        out = out[:n]
+        return out[np.lexsort((out["lport"], out["rport"], out["remote"], out["proto"]))]
 
+
+FLOW_DTYPE = np.dtype([("remote", "<u4"), ("rport", "<u2"), ("lport", "<u2"), ("proto", "u1"), ("reserved", "u1", 7),
+                       ("exp", "<i8")])
 RULE_DTYPE = np.dtype(Rule)
 PREFIX_DTYPE = np.dtype(Prefix)
 PORT_DTYPE = np.dtype(PortRange)

@@ -74,4 +74,15 @@ def spans_equal(a: np.ndarray, b: np.ndarray, off, lengths, start: int = 0) -> l
     return bad
 
 
+def flows_equal(gpu_flows: np.ndarray, checker_flows: np.ndarray) -> bool:
+    """The library's exported flow table against the checker's map: same keys, same expiries (both sorted by key)."""
+    if len(gpu_flows) != len(checker_flows):
+        return False
+    return bool(np.array_equal(gpu_flows["remote_addr"], checker_flows["remote"])
+                and np.array_equal(gpu_flows["remote_port"], checker_flows["rport"])
+                and np.array_equal(gpu_flows["local_port"], checker_flows["lport"])
+                and np.array_equal(gpu_flows["proto"], checker_flows["proto"])
+                and np.array_equal(gpu_flows["expiry_unix_ns"], checker_flows["exp"]))
+
+
 __all__ = [n for n in dir() if not n.startswith("_")] + ["slot_size"]

@@ -95,12 +95,17 @@ def _run_config3(oracle, n_rules, n_nodes, n_out, n_in, seed=None, flow_capacity
         b.filter_check(n, w.t0_ns + 2 * RC.SEC)
         got_again = (np.array(b.status[:n]) == PKT_OK).astype(np.uint8)
         got_flows = c.flows_count()
+        got_table = c.flows_export()
     finally:
         c.close()
     assert np.array_equal(got, want), f"{np.flatnonzero(got != want)[:10]} differ"
     assert np.array_equal(got_late, want_late)
     assert np.array_equal(got_again, want_again)
     assert got_flows == want_flows
+    # not only the verdicts: the whole flow table, key for key and expiry for expiry, equals the checker's map
+    from tests.helpers import flows_equal
+
+    assert len(got_table) == want_flows and flows_equal(got_table, f.flows())
     return w, got, want_late
 
 
@@ -190,3 +195,44 @@ def test_policy_to_verdicts_end_to_end(make):
     # the policy is withdrawn: allow all (flows are kept, rules are gone)
     acl.apply_netmap_filter(f, {"filter_enabled": False})
     assert f.check_inbound(RC.tcp(c, a, 1, 2), RC.T0)
+
+
+def test_flow_table_export_and_import(gpu_lib, oracle):
+    """State hand-over: the entries exported from one context, imported into a fresh one, give the same verdicts
+    and the same table there (all three protocol classes, the all-ones key, a deleted entry is not exported)."""
+    from bnk_b200 import Context
+    from bnk_b200.filter import Filter
+    from tests.helpers import flows_equal
+
+    a = Context(max_keypairs=4, flow_capacity=1 << 10)
+    b = Context(max_keypairs=4, flow_capacity=1 << 12)
+    o = oracle.Filter()
+    o.set_rules([])
+    try:
+        fa, fb = Filter(a, batch_pkts=64), Filter(b, batch_pkts=64)
+        fa.set_rules([])
+        fb.set_rules([])
+        out = ([RC.udp(RC.SELF, RC.PEER, 1000 + i, 53) for i in range(20)] + [RC.tcp(RC.SELF, RC.OTHER, 2000 + i, 443) for i in range(20)]
+               + [RC.icmp_echo(RC.SELF, RC.PEER, False), RC.udp(RC.SELF, 0xFFFFFFFF, 65535, 65535)])
+        fa.note_outbound_batch(out, RC.T0)
+        for p in out:
+            o.note_outbound(p, RC.T0)
+        # one udp flow runs out and is deleted by a lookup
+        late = RC.udp(RC.PEER, RC.SELF, 53, 1000)
+        assert not fa.check_inbound(late, RC.T0 + 31 * RC.SEC) and not o.check_inbound(late, RC.T0 + 31 * RC.SEC)
+        table = a.flows_export()
+        assert len(table) == 41 and flows_equal(table, o.flows())
+        b.flows_import(table)
+        assert b.flows_count() == 41 and flows_equal(b.flows_export(), o.flows())
+        for pkt, want in ((RC.udp(RC.PEER, RC.SELF, 53, 1001), True), (late, False),
+                          (RC.tcp(RC.OTHER, RC.SELF, 443, 2005, False), True), (RC.icmp_echo(RC.PEER, RC.SELF, True), True),
+                          (RC.udp(0xFFFFFFFF, RC.SELF, 65535, 65535), True), (RC.tcp(RC.OTHER, RC.SELF, 443, 2999, False), False)):
+            assert fb.check_inbound(pkt, RC.T0 + RC.SEC) == want == o.check_inbound(pkt, RC.T0 + RC.SEC)
+        assert flows_equal(b.flows_export(), o.flows())  # the refreshed expiries too
+        b.flows_import(table[:3])                         # importing a key again only moves its expiry
+        assert b.flows_count() == 41
+        fa._batch.close()
+        fb._batch.close()
+    finally:
+        a.close()
+        b.close()

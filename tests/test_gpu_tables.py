@@ -6,6 +6,7 @@ import threading
 import numpy as np
 import pytest
 
+from tests import helpers as H
 from tests import reference_cases as RC
 
 pytestmark = pytest.mark.gpu
@@ -182,6 +183,7 @@ def test_flow_table_survives_ten_times_its_capacity(gpu_lib, oracle):
             if r % 16 == 15:
                 st = c.table_stats()
                 assert st.flow_live == f.flow_count, r
+                assert H.flows_equal(c.flows_export(), f.flows()), r   # the whole table, not only its size
                 worst_dead = max(worst_dead, st.flow_dead[1])
                 assert st.flow_used[1] <= cap // 2 + 2 * per_round, (r, st.flow_used[1])
         assert worst_dead > 0  # the churn did produce deleted entries, and they were reclaimed
