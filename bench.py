@@ -826,16 +826,20 @@ def run_ours(args, rank, world, local_rank):
                  "gbps_all_cores_128_packets": threaded(host_threads(), 128, max(20, args.small_rounds)) if world == 1 else None,
                  "host_cores": host_threads(),
                  # the same 128-packet calls handed to the library's submit queue (bnk_queue), which packs them into
-                 # GPU batches; 2 and 4 caller batches outstanding per thread
+                 # GPU batches of up to 1024 packets; 2 and 4 caller batches outstanding per thread; the queue has no
+                 # thread of its own, so its callers may outnumber the cores (a waiting caller gives its core away)
                  "gbps_8_threads_128_packets_queue": threaded(8, 128, max(20, args.small_rounds), 2, True) if world == 1 else None,
                  "gbps_8_threads_128_packets_queue_4_outstanding": threaded(8, 128, max(20, args.small_rounds), 4, True) if world == 1 else None,
-                 "gbps_16_threads_128_packets_queue": threaded(16, 128, max(20, args.small_rounds), 2, True) if world == 1 else None,
+                 "gbps_all_cores_128_packets_queue": threaded(host_threads(), 128, max(20, args.small_rounds), 2, True) if world == 1 else None,
+                 "gbps_all_cores_128_packets_queue_4_outstanding": threaded(host_threads(), 128, max(20, args.small_rounds), 4, True) if world == 1 else None,
+                 "gbps_2x_cores_128_packets_queue_4_outstanding": threaded(2 * host_threads(), 128, max(20, args.small_rounds), 4, True) if world == 1 else None,
                  "note": "host wall clock per submit+wait; seal = group+counters launch, seal launch; open = open "
                          "launch, group+replay launch; 128 x 1420 B goes through the copy engines, 16 x 1420 B (under "
                          "128 KiB) runs on the pinned host arrays without copies; gbps_16_batches_in_flight: sixteen "
                          "128-packet batches submitted round-robin by this one Python thread, seal then open; "
                          "gbps_8_threads_*: eight C++ host threads, two batches in flight each, same context "
-                         "(bnk_b200/host/apps/mt_stress.cpp), median of five runs"}
+                         "(bnk_b200/host/apps/mt_stress.cpp), median of five runs; *_queue: the same threads hand "
+                         "their 128-packet calls (pageable buffers, copied in and out by the library) to bnk_queue"}
 
     sampler.stop()
     clocks = sampler.summary(windows)

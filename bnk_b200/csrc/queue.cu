@@ -12,31 +12,30 @@
 // on its own stream, so the upload of one runs beside the kernels of the one in front and the download of the
 // one before; the KERNELS of consecutive batches are chained with events, which keeps what the library promises
 // per keypair: nonces in submit order, replay verdicts in arrival order.
+#include <atomic>
 #include <chrono>
-#include <condition_variable>
-#include <deque>
 #include <new>
 #include <thread>
+#include <vector>
 
 #include "bnk_internal.cuh"
 
 namespace {
 
-enum State { FREE, FILLING, CLOSED, IN_FLIGHT, DONE };
+enum State : int { FREE, FILLING, CLOSED, IN_FLIGHT, DONE };
 
 struct GpuBatch {
     bnk_batch *b = nullptr;
     bnk_batch_view v{};
     cudaEvent_t kernels_done = nullptr; // recorded behind the batch's last kernel
-    State state = FREE;
-    uint32_t reserved = 0; // packets handed out to callers
-    uint32_t filled = 0;   // of those, copied in
-    uint32_t users = 0;    // caller batches whose results have not been collected
-    uint32_t gen = 0;      // how often the batch has been reused (part of the ticket)
+    std::atomic<int> state{FREE};       // written under the queue's lock; its callers watch it without
+    uint32_t reserved = 0;              // packets handed out to callers
+    std::atomic<uint32_t> filled{0};    // of those, copied in
+    uint32_t users = 0;                 // caller batches whose results have not been collected
+    uint32_t gen = 0;                   // how often the batch has been reused (part of the ticket)
     int64_t now = 0;
     int rc = BNK_SUCCESS;
     std::chrono::steady_clock::time_point first_at; // when the first caller arrived
-    std::condition_variable done;                   // its callers wait here, nobody else is woken
 };
 
 constexpr uint32_t kMaxQueuePkts = 32768; // ticket fields are 16 bits
@@ -46,103 +45,166 @@ constexpr uint32_t kMaxQueuePkts = 32768; // ticket fields are 16 bits
 constexpr std::chrono::nanoseconds kGatherNs(40000);
 constexpr uint32_t kRotationExtra = 6; // GPU batches beyond `depth`: filling, and done but not yet emptied by their callers
 
+inline void cpu_relax() {
+#if defined(__x86_64__) || defined(__i386__)
+    __builtin_ia32_pause();
+#else
+    std::this_thread::yield();
+#endif
+}
+
+// The critical sections below are a few dozen instructions and contain no system or driver call, and the threads
+// that contend are callers that would otherwise sit in a driver wait loop: a lock that spins costs a fraction of a
+// microsecond, a sleeping one costs a wake-up (tens of microseconds on a virtual machine) on every hand-over.
+class SpinLock {
+  public:
+    void lock() {
+        for (uint32_t spins = 0; flag_.exchange(true, std::memory_order_acquire); ++spins) {
+            while (flag_.load(std::memory_order_relaxed)) {
+                if (++spins & 0x3ffu) cpu_relax();
+                else std::this_thread::yield(); // more threads than cores: let the holder run
+            }
+        }
+    }
+    void unlock() { flag_.store(false, std::memory_order_release); }
+
+  private:
+    std::atomic<bool> flag_{false};
+};
+struct Locked {
+    explicit Locked(SpinLock &l) : l_(l) { l_.lock(); }
+    ~Locked() { l_.unlock(); }
+    SpinLock &l_;
+};
+
+// fixed-capacity first-in first-out list of batch indices (no allocation under the lock)
+struct IndexFifo {
+    std::vector<uint32_t> slot;
+    uint32_t head = 0, count = 0;
+    bool empty() const { return count == 0; }
+    uint32_t front() const { return slot[head]; }
+    void push(uint32_t v) { slot[(head + count++) % slot.size()] = v; }
+    void pop() { head = (head + 1) % slot.size(); --count; }
+};
+
 } // namespace
 
+// No thread of its own: the queue moves inside the calls of its users.  Whoever hands packets in or waits for a
+// ticket also looks whether a GPU batch is ready to go (and submits it) and whether the oldest one in flight has
+// come back (and marks it done); a caller that waits does so by watching its batch's state word and taking those
+// two turns in between, the way it would otherwise spin inside the driver's own wait.
 struct bnk_queue {
     bnk_ctx *ctx;
     bnk_queue_cfg cfg;
     uint32_t slot_bytes;
-    std::deque<GpuBatch> gb; // (a deque: the entries hold condition variables and never move)
-    uint32_t cur = 0;              // the batch that is filling (or will be, once it is free)
-    std::deque<uint32_t> closed;   // full or cut off, waiting for the device, in order
-    std::deque<uint32_t> inflight; // submitted, in order
+    std::vector<GpuBatch> gb;
+    SpinLock mu;
+    uint32_t cur = 0;    // the batch that is filling (or will be, once it is free)
+    IndexFifo closed;    // full or cut off, waiting for the device, in order
+    IndexFifo inflight;  // submitted, in order
     int last_submitted = -1;
     uint64_t n_gpu_batches = 0, n_packets = 0, n_caller_batches = 0;
-    bool stop = false;
-    std::mutex mu;
-    uint32_t submitting = 0;       // 1 while the submitter is inside bnk_seal_submit / bnk_open_submit
-    std::condition_variable cv_work, cv_complete, cv_room;
-    std::thread submitter, completer;
+    // mirrors that let a waiting caller decide without the lock whether a turn could do anything
+    std::atomic<bool> submitting{false}; // somebody is inside bnk_seal_submit / bnk_open_submit
+    std::atomic<bool> polling{false};    // somebody is asking the driver about the oldest batch in flight
+    std::atomic<uint32_t> n_inflight{0}, n_pending{0}; // n_pending: closed batches + a filling one that holds packets
 };
 
 namespace {
 
-// true when the filling batch should go now; otherwise *until says when to look again (if it holds anything)
-bool ripe(const bnk_queue *q, std::chrono::steady_clock::time_point *until, bool *timed) {
-    *timed = false;
+// Under the lock: should the filling batch go now?
+bool ripe(const bnk_queue *q) {
     const GpuBatch &c = q->gb[q->cur];
-    if (c.state != FILLING || c.reserved == 0 || c.filled != c.reserved) return false;
-    if (q->inflight.empty() && q->submitting == 0) return true;             // the device is idle
+    if (c.state.load(std::memory_order_relaxed) != FILLING || c.reserved == 0 ||
+        c.filled.load(std::memory_order_acquire) != c.reserved)
+        return false;
+    if (q->inflight.empty()) return true;                                   // the device is idle
     if (c.reserved >= (q->cfg.max_pkts + 3) / 4) return true;               // worth a launch
-    *until = c.first_at + kGatherNs;
-    *timed = true;
-    return std::chrono::steady_clock::now() >= *until;                      // waited long enough
+    return std::chrono::steady_clock::now() >= c.first_at + kGatherNs;      // waited long enough
 }
 
-void submitter_loop(bnk_queue *q) {
-    std::unique_lock<std::mutex> lk(q->mu);
+// Submit whatever is ready while the device has a free slot.  One thread at a time is inside the library's
+// submit call (the kernels of consecutive GPU batches are chained in that order); the others pass by.
+void pump(bnk_queue *q) {
     for (;;) {
-        // work: a closed batch, or a filling one that is ripe, while the device has a free slot
-        for (;;) {
-            if (q->stop) return;
-            std::chrono::steady_clock::time_point until;
-            bool timed = false;
-            if (q->inflight.size() + q->submitting < q->cfg.depth) {
-                if (!q->closed.empty()) {
-                    const GpuBatch &f = q->gb[q->closed.front()];
-                    if (f.filled == f.reserved) break;
-                } else if (ripe(q, &until, &timed)) {
-                    break;
-                }
+        if (q->n_pending.load(std::memory_order_relaxed) == 0 || q->submitting.load(std::memory_order_relaxed) ||
+            q->n_inflight.load(std::memory_order_relaxed) >= q->cfg.depth)
+            return;
+        uint32_t idx, n;
+        int prev;
+        {
+            Locked lk(q->mu);
+            if (q->submitting.load(std::memory_order_relaxed) || q->inflight.count >= q->cfg.depth) return;
+            if (!q->closed.empty()) {
+                const GpuBatch &f = q->gb[q->closed.front()];
+                if (f.filled.load(std::memory_order_acquire) != f.reserved) return; // a caller is still copying in
+                idx = q->closed.front();
+                q->closed.pop();
+            } else if (ripe(q)) { // cut the filling batch off
+                idx = q->cur;
+                q->cur = (q->cur + 1) % q->gb.size();
+            } else {
+                return;
             }
-            if (timed) q->cv_work.wait_until(lk, until);
-            else q->cv_work.wait(lk);
+            GpuBatch &g = q->gb[idx];
+            n = g.reserved;
+            prev = q->last_submitted;
+            q->last_submitted = (int)idx;
+            g.state.store(IN_FLIGHT, std::memory_order_relaxed);
+            q->submitting.store(true, std::memory_order_relaxed);
+            q->n_pending.fetch_sub(1, std::memory_order_relaxed);
+            q->n_gpu_batches++;
+            q->n_packets += n;
         }
-        if (q->closed.empty()) { // cut the filling batch off
-            q->gb[q->cur].state = CLOSED;
-            q->closed.push_back(q->cur);
-            q->cur = (q->cur + 1) % q->gb.size();
-            q->cv_room.notify_all();
-        }
-        const uint32_t idx = q->closed.front();
-        q->closed.pop_front();
         GpuBatch &g = q->gb[idx];
-        const uint32_t n = g.reserved;
-        const int prev = q->last_submitted;
-        q->last_submitted = (int)idx;
-        g.state = IN_FLIGHT;
-        q->submitting = 1;
-        q->n_gpu_batches++;
-        q->n_packets += n;
-        lk.unlock();
         // kernels of this batch start behind the kernels of the batch submitted before it
         g.b->order_wait = prev >= 0 ? q->gb[prev].kernels_done : nullptr;
         g.b->order_record = g.kernels_done;
         g.rc = q->cfg.open_side ? bnk_open_submit(g.b, n, q->cfg.flags, g.now) : bnk_seal_submit(g.b, n, q->cfg.flags, g.now);
         g.b->order_wait = nullptr;
         g.b->order_record = nullptr;
-        lk.lock();
-        q->submitting = 0;
-        q->inflight.push_back(idx); // only now may the completer wait for it
-        q->cv_complete.notify_all();
+        {
+            Locked lk(q->mu);
+            q->inflight.push(idx); // only now may anybody ask the driver about it
+            q->n_inflight.store(q->inflight.count, std::memory_order_relaxed);
+            q->submitting.store(false, std::memory_order_release);
+        }
     }
 }
 
-void completer_loop(bnk_queue *q) {
-    std::unique_lock<std::mutex> lk(q->mu);
+// Has the oldest batch in flight come back?  (In submit order: kernels are chained, and a caller's ticket can
+// only be in a batch behind it if the caller came later.)
+void poll(bnk_queue *q) {
+    if (q->n_inflight.load(std::memory_order_relaxed) == 0 || q->polling.exchange(true, std::memory_order_acquire)) return;
     for (;;) {
-        q->cv_complete.wait(lk, [&] { return q->stop || !q->inflight.empty(); });
-        if (q->inflight.empty()) return; // stop, and nothing left to wait for
-        const uint32_t idx = q->inflight.front();
+        uint32_t idx;
+        {
+            Locked lk(q->mu);
+            if (q->inflight.empty()) break;
+            idx = q->inflight.front();
+        }
         GpuBatch &g = q->gb[idx];
-        lk.unlock();
-        const int rc = bnk_wait(g.b, UINT64_MAX);
-        lk.lock();
+        const int rc = bnk_wait(g.b, 0);
+        if (rc == BNK_ETIMEDOUT) break;
+        Locked lk(q->mu);
         if (g.rc == BNK_SUCCESS) g.rc = rc;
-        q->inflight.pop_front();
-        g.state = DONE;
-        g.done.notify_all();
-        q->cv_work.notify_all(); // a slot on the device is free again
+        q->inflight.pop();
+        q->n_inflight.store(q->inflight.count, std::memory_order_relaxed);
+        g.state.store(DONE, std::memory_order_release);
+    }
+    q->polling.store(false, std::memory_order_release);
+}
+
+// One turn of a waiting caller.
+inline void turn(bnk_queue *q, uint32_t &spins) {
+    pump(q);
+    poll(q);
+    // A GPU batch is back within ~100 us: that long a waiting caller stays on its core; a longer wait means the
+    // callers outnumber the cores (or the device is far behind), and the core goes to whoever has work.
+    if (++spins < 64u) {
+        for (int i = 0; i < 16; i++) cpu_relax();
+    } else {
+        std::this_thread::yield();
     }
 }
 
@@ -156,17 +218,12 @@ extern "C" {
 
 int bnk_queue_destroy(bnk_queue *q) {
     if (!q) return BNK_EINVAL;
-    {
-        std::lock_guard<std::mutex> g(q->mu);
-        q->stop = true;
-    }
-    q->cv_work.notify_all();
-    q->cv_complete.notify_all();
-    if (q->submitter.joinable()) q->submitter.join();
-    if (q->completer.joinable()) q->completer.join();
     cudaSetDevice(q->ctx->device);
     for (GpuBatch &g : q->gb) {
-        if (g.b) bnk_batch_destroy(g.b);
+        if (g.b) {
+            bnk_wait(g.b, UINT64_MAX);
+            bnk_batch_destroy(g.b);
+        }
         if (g.kernels_done) cudaEventDestroy(g.kernels_done);
     }
     delete q;
@@ -186,7 +243,9 @@ int bnk_queue_create(bnk_ctx *ctx, const bnk_queue_cfg *cfg, bnk_queue **out) {
     q->cfg.flags &= ~(BNK_F_NO_H2D | BNK_F_NO_D2H | BNK_F_USE_OUT_LEN | BNK_F_TIMED | BNK_F_STATS);
     if (!cfg->open_side) q->cfg.flags |= BNK_F_ASSIGN_COUNTERS;
     q->slot_bytes = (16u + ((cfg->max_packet + 15u) & ~15u) + 16u + 15u) & ~15u;
-    q->gb.resize(cfg->depth + kRotationExtra);
+    q->gb = std::vector<GpuBatch>(cfg->depth + kRotationExtra);
+    q->closed.slot.resize(q->gb.size());
+    q->inflight.slot.resize(q->gb.size());
     cudaSetDevice(ctx->device);
     for (GpuBatch &g : q->gb) {
         int rc = bnk_batch_create(ctx, cfg->max_pkts, (uint64_t)cfg->max_pkts * q->slot_bytes, &g.b);
@@ -197,8 +256,6 @@ int bnk_queue_create(bnk_ctx *ctx, const bnk_queue_cfg *cfg, bnk_queue **out) {
             return rc;
         }
     }
-    q->submitter = std::thread(submitter_loop, q);
-    q->completer = std::thread(completer_loop, q);
     *out = q;
     return BNK_SUCCESS;
 }
@@ -212,38 +269,43 @@ int bnk_queue_submit(bnk_queue *q, const uint8_t *const *pkts, const uint32_t *l
     const uint32_t room = open_side ? q->cfg.max_packet + 32u : q->cfg.max_packet;
     for (uint32_t i = 0; i < n; i++)
         if (len[i] > room) return BNK_EINVAL;
-    std::unique_lock<std::mutex> lk(q->mu);
     GpuBatch *g;
-    for (;;) {
-        g = &q->gb[q->cur];
-        if (g->state == FREE) {
-            g->state = FILLING;
-            g->reserved = g->filled = g->users = 0;
-            g->gen++;
-            g->now = now_unix_ns;
-            g->rc = BNK_SUCCESS;
-            g->first_at = std::chrono::steady_clock::now();
+    uint32_t first, idx;
+    {
+        Locked lk(q->mu);
+        for (;;) {
+            g = &q->gb[q->cur];
+            int st = g->state.load(std::memory_order_relaxed);
+            if (st == FREE) {
+                g->state.store(st = FILLING, std::memory_order_relaxed);
+                g->reserved = g->users = 0;
+                g->filled.store(0, std::memory_order_relaxed);
+                g->gen++;
+                g->now = now_unix_ns;
+                g->rc = BNK_SUCCESS;
+                g->first_at = std::chrono::steady_clock::now();
+            }
+            if (st == FILLING && g->reserved + n <= q->cfg.max_pkts) break;
+            if (st == FILLING) { // no room for this caller's batch: the GPU batch is complete
+                g->state.store(CLOSED, std::memory_order_relaxed);
+                q->closed.push(q->cur);
+                q->cur = (q->cur + 1) % q->gb.size();
+                continue;
+            }
+            // The next batch in the rotation is still on the device or has not been emptied by its callers: the
+            // callers are ahead of the device.  No waiting here: the caller may itself hold the tickets that keep
+            // that batch from being reused.
+            return BNK_EBUSY;
         }
-        if (g->state == FILLING && g->reserved + n <= q->cfg.max_pkts) break;
-        if (g->state == FILLING) { // no room for this caller's batch: the GPU batch is complete
-            g->state = CLOSED;
-            q->closed.push_back(q->cur);
-            q->cur = (q->cur + 1) % q->gb.size();
-            q->cv_work.notify_all();
-            continue;
-        }
-        // The next batch in the rotation is still on the device or has not been emptied by its callers: the
-        // callers are ahead of the device.  No waiting here: the caller may itself hold the tickets that keep
-        // that batch from being reused.
-        return BNK_EBUSY;
+        first = g->reserved;
+        idx = q->cur;
+        if (first == 0) q->n_pending.fetch_add(1, std::memory_order_relaxed);
+        g->reserved += n;
+        g->users++;
+        if (now_unix_ns > g->now) g->now = now_unix_ns;
+        q->n_caller_batches++;
+        *ticket = make_ticket(idx, g->gen, first, n);
     }
-    const uint32_t first = g->reserved, idx = q->cur;
-    g->reserved += n;
-    g->users++;
-    if (now_unix_ns > g->now) g->now = now_unix_ns;
-    q->n_caller_batches++;
-    *ticket = make_ticket(idx, g->gen, first, n);
-    lk.unlock();
     // copy in, outside the lock: callers fill their own stretches of the ring side by side
     const bnk_batch_view &v = g->v;
     const uint32_t head = open_side ? 0u : 16u;
@@ -254,9 +316,8 @@ int bnk_queue_submit(bnk_queue *q, const uint8_t *const *pkts, const uint32_t *l
         v.slot[at] = slot ? slot[k] : 0u;
         if (len[k]) memcpy(v.ring + (size_t)at * q->slot_bytes + head, pkts[k], len[k]);
     }
-    lk.lock();
-    g->filled += n;
-    q->cv_work.notify_all();
+    g->filled.fetch_add(n, std::memory_order_release);
+    pump(q);
     return BNK_SUCCESS;
 }
 
@@ -267,11 +328,13 @@ int bnk_queue_wait(bnk_queue *q, bnk_ticket ticket, uint8_t *const *out, uint32_
     const uint32_t first = (uint32_t)(ticket >> 16) & 0xffff, n = (uint32_t)ticket & 0xffff;
     if (idx >= q->gb.size() || first + n > q->cfg.max_pkts) return BNK_EINVAL;
     GpuBatch &g = q->gb[idx];
-    std::unique_lock<std::mutex> lk(q->mu);
-    if ((g.gen & 0xffffff) != gen || g.state == FREE || g.users == 0) return BNK_EINVAL; // not a ticket that is out
-    g.done.wait(lk, [&] { return g.state == DONE; });
+    {
+        Locked lk(q->mu);
+        if ((g.gen & 0xffffff) != gen || g.state.load(std::memory_order_relaxed) == FREE || g.users == 0)
+            return BNK_EINVAL; // not a ticket that is out
+    }
+    for (uint32_t spins = 0; g.state.load(std::memory_order_acquire) != DONE;) turn(q, spins);
     const int rc = g.rc;
-    lk.unlock();
     const bnk_batch_view &v = g.v;
     const bool open_side = q->cfg.open_side != 0;
     for (uint32_t k = 0; k < n; k++) {
@@ -284,28 +347,32 @@ int bnk_queue_wait(bnk_queue *q, bnk_ticket ticket, uint8_t *const *out, uint32_
         if (slot_out) slot_out[k] = v.slot[at];
         if (out_len[k]) memcpy(out[k], v.ring + (size_t)at * q->slot_bytes + (open_side ? 16u : 0u), out_len[k]);
     }
-    lk.lock();
-    if (--g.users == 0) {
-        g.state = FREE;
-        q->cv_room.notify_all();
+    {
+        Locked lk(q->mu);
+        if (--g.users == 0) g.state.store(FREE, std::memory_order_release);
     }
     return rc;
 }
 
 int bnk_queue_wait_room(bnk_queue *q, uint64_t timeout_ns) {
     if (!q) return BNK_EINVAL;
-    std::unique_lock<std::mutex> lk(q->mu);
-    auto room = [&] { return q->gb[q->cur].state == FREE || q->gb[q->cur].state == FILLING; };
-    if (timeout_ns == UINT64_MAX) {
-        q->cv_room.wait(lk, room);
-        return BNK_SUCCESS;
+    const auto deadline = std::chrono::steady_clock::now() +
+                          std::chrono::nanoseconds(timeout_ns == UINT64_MAX ? (uint64_t)INT64_MAX / 2 : timeout_ns);
+    for (uint32_t spins = 0;;) {
+        int st;
+        {
+            Locked lk(q->mu);
+            st = q->gb[q->cur].state.load(std::memory_order_relaxed);
+        }
+        if (st == FREE || st == FILLING) return BNK_SUCCESS;
+        if (timeout_ns != UINT64_MAX && std::chrono::steady_clock::now() >= deadline) return BNK_ETIMEDOUT;
+        turn(q, spins);
     }
-    return q->cv_room.wait_for(lk, std::chrono::nanoseconds(timeout_ns), room) ? BNK_SUCCESS : BNK_ETIMEDOUT;
 }
 
 int bnk_queue_stats_get(bnk_queue *q, uint64_t *gpu_batches, uint64_t *packets, uint64_t *caller_batches) {
     if (!q) return BNK_EINVAL;
-    std::lock_guard<std::mutex> g(q->mu);
+    Locked lk(q->mu);
     if (gpu_batches) *gpu_batches = q->n_gpu_batches;
     if (packets) *packets = q->n_packets;
     if (caller_batches) *caller_batches = q->n_caller_batches;

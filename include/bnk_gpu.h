@@ -330,7 +330,11 @@ int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uint32_t *dev_
  *   bnk_queue_wait    blocks until the ticket's GPU batch is done and copies the caller's results out:
  *                     sealed messages (room for len + 48 bytes each) or opened plaintexts, out_len[], status[],
  *                     and if not NULL counter[] and slot_out[].  Every ticket must be collected exactly once.
- * Seal queues always take counters from the keypairs' send counters. */
+ * Seal queues always take counters from the keypairs' send counters.
+ * A queue has no thread of its own: GPU batches are submitted and collected inside these calls, by whichever
+ * caller comes by first.  A caller that waits watches its batch and takes those turns in between; after ~100 us
+ * it gives its core away between turns (sched_yield), so callers may outnumber the cores.  Packets handed in are
+ * therefore on their way at the latest when some caller of the queue submits again or waits. */
 typedef struct bnk_queue bnk_queue;
 typedef uint64_t bnk_ticket;
 typedef struct bnk_queue_cfg {
