@@ -707,7 +707,7 @@ cudaError_t launch_aead(const AeadArgs &a, cudaStream_t s, bnk_ctx *ctx) {
         // one CTA per 128 packets; the hardware hands CTAs to SMs as slots free up, which measured faster
         // than persistent warps with an even static share of the packets
         const uint32_t ctas = (a.n + kThreads - 1) / kThreads;
-        launch_kernel(a.n <= kDependentLaunchUpTo, aead_kernel<OPEN>, dim3(ctas), dim3(kThreads), s, a);
+        launch_kernel(a.n <= dependent_launch_up_to(), aead_kernel<OPEN>, dim3(ctas), dim3(kThreads), s, a);
     }
     ++ctx->launches;
     return cudaGetLastError();

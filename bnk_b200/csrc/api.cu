@@ -224,6 +224,11 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     if (const char *m = getenv("BNK_HOST_DIRECT_BYTES")) // largest ring extent served without copies; 0 = never
         ctx->host_direct_bytes = strtoull(m, nullptr, 0);
     if (!prop.unifiedAddressing || !prop.canMapHostMemory) ctx->host_direct_bytes = 0; // pinned memory must have one address
+    ctx->aead_side_stream_from = 1u << 18; // below, the seal/open launch is too short for the hand-over between streams to pay
+    if (const char *m = getenv("BNK_AEAD_SIDE_STREAM_FROM")) // tuning aid: 0 = seal/open always on the batch's own stream
+        ctx->aead_side_stream_from = (uint32_t)strtoul(m, nullptr, 0);
+    ctx->prio_low = ctx->prio_high = 0;
+    cudaDeviceGetStreamPriorityRange(&ctx->prio_low, &ctx->prio_high);
     ctx->kt = KeypairTables{};
     ctx->ft = FilterTables{};
     const size_t k = cfg->max_keypairs;
@@ -640,6 +645,9 @@ int bnk_batch_destroy(bnk_batch *b) {
     if (b->ev_fork) cudaEventDestroy(b->ev_fork);
     if (b->ev_join) cudaEventDestroy(b->ev_join);
     if (b->ev_fence) cudaEventDestroy(b->ev_fence);
+    if (b->ev_aead_go) cudaEventDestroy(b->ev_aead_go);
+    if (b->ev_aead_done) cudaEventDestroy(b->ev_aead_done);
+    if (b->aead_stream) cudaStreamDestroy(b->aead_stream);
     if (b->aux_stream) cudaStreamDestroy(b->aux_stream);
     if (b->stream) cudaStreamDestroy(b->stream);
     delete b;
@@ -716,8 +724,13 @@ int bnk_batch_create(bnk_ctx *ctx, uint32_t max_pkts, uint64_t ring_bytes, bnk_b
     D((void **)&d.counters32, 2048 * 4);
     D((void **)&d.gso, n * sizeof(bnk_gso_super));
     D((void **)&b->d_stats, 20 * sizeof(unsigned long long));
-    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&b->aux_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&b->stream, cudaStreamNonBlocking, ctx->prio_high);
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&b->aux_stream, cudaStreamNonBlocking, ctx->prio_high);
+    if (e == cudaSuccess && ctx->aead_side_stream_from && max_pkts >= ctx->aead_side_stream_from && ctx->prio_low != ctx->prio_high) {
+        e = cudaStreamCreateWithPriority(&b->aead_stream, cudaStreamNonBlocking, ctx->prio_low);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_aead_go, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_aead_done, cudaEventDisableTiming);
+    }
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_join, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b->ev_fence, cudaEventDisableTiming);
@@ -823,9 +836,19 @@ int bnk_seal_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         CK(ctx, launch_length_order(b, npkts, b->dev.len, false, s));
         order = b->dev.len_order;
     }
-    if (timed) CK(ctx, cudaEventRecord(b->a_begin, s));
-    CK(ctx, launch_seal(aead_args(b, npkts, false, order), s, ctx));
-    if (timed) CK(ctx, cudaEventRecord(b->a_end, s));
+    const bool side = b->aead_stream && npkts >= ctx->aead_side_stream_from;
+    cudaStream_t as = side ? b->aead_stream : s;
+    if (side) {
+        CK(ctx, cudaEventRecord(b->ev_aead_go, s));
+        CK(ctx, cudaStreamWaitEvent(as, b->ev_aead_go, 0));
+    }
+    if (timed) CK(ctx, cudaEventRecord(b->a_begin, as));
+    CK(ctx, launch_seal(aead_args(b, npkts, false, order), as, ctx));
+    if (timed) CK(ctx, cudaEventRecord(b->a_end, as));
+    if (side) {
+        CK(ctx, cudaEventRecord(b->ev_aead_done, as));
+        CK(ctx, cudaStreamWaitEvent(s, b->ev_aead_done, 0));
+    }
     if (timed) CK(ctx, cudaEventRecord(b->k_end, s));
     b->kernel_timed = timed;
     b->aead_timed = timed;
@@ -885,9 +908,19 @@ int bnk_open_submit(bnk_batch *b, uint32_t npkts, uint32_t flags, int64_t now_un
         CK(ctx, launch_group_by_slot(b, npkts, false, b->aux_stream));
         CK(ctx, cudaEventRecord(b->ev_join, b->aux_stream));
     }
-    if (timed) CK(ctx, cudaEventRecord(b->a_begin, s));
-    CK(ctx, launch_open(oa, s, ctx));
-    if (timed) CK(ctx, cudaEventRecord(b->a_end, s));
+    const bool side = b->aead_stream && npkts >= ctx->aead_side_stream_from;
+    cudaStream_t as = side ? b->aead_stream : s;
+    if (side) {
+        CK(ctx, cudaEventRecord(b->ev_aead_go, s));
+        CK(ctx, cudaStreamWaitEvent(as, b->ev_aead_go, 0));
+    }
+    if (timed) CK(ctx, cudaEventRecord(b->a_begin, as));
+    CK(ctx, launch_open(oa, as, ctx));
+    if (timed) CK(ctx, cudaEventRecord(b->a_end, as));
+    if (side) {
+        CK(ctx, cudaEventRecord(b->ev_aead_done, as));
+        CK(ctx, cudaStreamWaitEvent(s, b->ev_aead_done, 0));
+    }
     b->aead_timed = timed;
     if (replay_fused) { // small batch: one launch sorts and walks; the stream hand-over would cost more than it hides
         CK(ctx, launch_group_and_replay(b, npkts, s));

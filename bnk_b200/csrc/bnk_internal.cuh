@@ -4,6 +4,7 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include <atomic>
 #include <mutex>
@@ -84,6 +85,8 @@ struct bnk_ctx {
     int sm_count;
     uint64_t host_direct_bytes; // batches up to this ring extent run on the caller's pinned buffers (BNK_HOST_DIRECT_BYTES)
     int aead_mode; // 0 = choose by batch size, 1 = always thread per packet, 2 = always warp per packet (BNK_AEAD_KERNEL)
+    uint32_t aead_side_stream_from; // batches of at least this many packets run seal/open on the low-priority stream (BNK_AEAD_SIDE_STREAM_FROM; 0 = never)
+    int prio_low, prio_high;        // stream priority range of the device
     std::atomic<uint64_t> launches;
     std::mutex mu;
     std::string last_error;
@@ -142,6 +145,14 @@ struct bnk_batch {
     DeviceBatch dev;
     cudaStream_t stream;
     cudaStream_t aux_stream;   // grouping work that can run beside the open kernel
+    // The seal/open launches of a large batch go to a stream of their own with the lowest priority, the short
+    // kernels around them (grouping, counters, replay window, length classes) stay on `stream` / `aux_stream`
+    // with the highest: a large seal/open launch fills every SM for hundreds of microseconds, and the short
+    // kernels of the NEXT batch would otherwise get no SM until its last wave.  With priorities their CTAs take
+    // the places seal/open CTAs leave as they retire, so the chain of one batch really runs beside the seal/open
+    // kernel of another.
+    cudaStream_t aead_stream;
+    cudaEvent_t ev_aead_go, ev_aead_done;
     cudaEvent_t ev_fork, ev_join;
     cudaEvent_t k_begin, k_end, t_end, a_begin, a_end;
     bool in_flight;
@@ -175,8 +186,16 @@ __device__ __forceinline__ void wait_for_kernel_in_front() { asm volatile("gridd
 __device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;"); }
 // The chains of short kernels around a large batch (grouping, counters, replay window, length classes) are
 // launched the same way while they are short: measured on 96,256 packets both sides of the pipeline got 7 % faster,
-// on 1,048,576 packets 1 % slower, hence the limit.
-constexpr uint32_t kDependentLaunchUpTo = 1u << 18;
+// on 1,048,576 packets 1 % slower.  With several large batches in flight it costs: CTAs that sit in their wait hold
+// SM slots that the seal/open kernel of another batch could use (four batches of 262,144 mixed packets: 1.05 ms
+// per step with dependent launches, 0.93 without).  Hence the limit.
+inline uint32_t dependent_launch_up_to() {
+    static const uint32_t v = [] {
+        const char *m = getenv("BNK_DEPENDENT_LAUNCH_UP_TO"); // tuning aid
+        return m ? (uint32_t)strtoul(m, nullptr, 0) : (1u << 17);
+    }();
+    return v;
+}
 template <typename... KArgs, typename... Args>
 cudaError_t launch_after_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};

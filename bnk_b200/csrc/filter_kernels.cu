@@ -595,7 +595,7 @@ cudaError_t launch_tally(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (grid == 0) grid = 1;
     if (grid > (uint32_t)ctx->sm_count * 4) grid = ctx->sm_count * 4;
     bnk_batch_stats *out = b->h_stats; // pinned memory has the same address on the device
-    launch_kernel(n <= kDependentLaunchUpTo, tally_kernel, dim3(grid), dim3(256), s, b->dev.status, b->dev.out_len, n,
+    launch_kernel(n <= dependent_launch_up_to(), tally_kernel, dim3(grid), dim3(256), s, b->dev.status, b->dev.out_len, n,
                   b->d_stats, out);
     ctx->launches += 1;
     return cudaGetLastError();
@@ -711,12 +711,12 @@ int filter_acl_upload(bnk_ctx *ctx, int enforce, const bnk_acl_tuple *tuples, si
 cudaError_t launch_filter_note(bnk_batch *b, uint32_t n, long long now_ns, cudaStream_t s) {
     bnk_ctx *ctx = b->ctx;
     if (n == 0 || !ctx->ft.enforce || ctx->ft.flow_capacity == 0) return cudaSuccess; // filter.go:192-194
-    launch_kernel(n <= kDependentLaunchUpTo, filter_note_kernel, dim3((n + 255) / 256), dim3(256), s, ctx->ft,
+    launch_kernel(n <= dependent_launch_up_to(), filter_note_kernel, dim3((n + 255) / 256), dim3(256), s, ctx->ft,
         b->dev.ring, b->dev.off, b->dev.len, n, b->ring_bytes, now_ns);
-    launch_kernel(n <= kDependentLaunchUpTo, filter_sweep_decide_kernel, dim3(1), dim3(1), s, ctx->ft, now_ns);
-    launch_kernel(n <= kDependentLaunchUpTo, filter_sweep_kernel, dim3(ctx->sm_count * 4), dim3(256), s, ctx->ft,
+    launch_kernel(n <= dependent_launch_up_to(), filter_sweep_decide_kernel, dim3(1), dim3(1), s, ctx->ft, now_ns);
+    launch_kernel(n <= dependent_launch_up_to(), filter_sweep_kernel, dim3(ctx->sm_count * 4), dim3(256), s, ctx->ft,
         now_ns);
-    launch_kernel(n <= kDependentLaunchUpTo, filter_sweep_finish_kernel, dim3(1), dim3(1), s, ctx->ft, now_ns);
+    launch_kernel(n <= dependent_launch_up_to(), filter_sweep_finish_kernel, dim3(1), dim3(1), s, ctx->ft, now_ns);
     ctx->launches += 4;
     return cudaGetLastError();
 }
@@ -726,7 +726,7 @@ cudaError_t launch_filter_check(bnk_batch *b, uint32_t n, long long now_ns, bool
     if (n == 0) return cudaSuccess;
     // open pipeline: the packet handed to the filter is the decrypted payload of out_len bytes
     const uint32_t *lens = only_status_ok ? b->dev.out_len : b->dev.len;
-    launch_kernel(n <= kDependentLaunchUpTo, filter_check_kernel, dim3((n + 255) / 256), dim3(256), s, ctx->ft,
+    launch_kernel(n <= dependent_launch_up_to(), filter_check_kernel, dim3((n + 255) / 256), dim3(256), s, ctx->ft,
         b->dev.ring, b->dev.off, lens, b->dev.status, n, b->ring_bytes, now_ns, only_status_ok ? 1 : 0);
     ctx->launches += 1;
     return cudaGetLastError();

@@ -778,7 +778,8 @@ __global__ void __launch_bounds__(kSortThreads) group_small_kernel(SortKeySrc sr
 
 // --- scheduling order by length class (mixed packet sizes) ------------------------------
 // Packets with the same number of 64-byte cipher blocks end up next to each other so that
-// the lanes of a seal/open warp finish together.  Order inside a class does not matter.
+// the lanes of a seal/open warp finish together; classes in falling order of length.  Order inside a class does
+// not matter.
 constexpr uint32_t kLenBins = 1026;
 __device__ __forceinline__ uint32_t len_bin(uint32_t len, bool open_side) {
     uint32_t body = open_side ? (len >= 32u ? len - 32u : 0u) : len;
@@ -835,7 +836,9 @@ __global__ void __launch_bounds__(256) len_scatter_kernel(const uint32_t *len, u
 #pragma unroll
     for (uint32_t k = 0; k < kLenItems; k++) {
         const uint32_t i = first + k * 256u;
-        if (i < n) order[h[bin[k]] + rank[k]] = i;
+        // longest class first: the launch then ends with the short packets, whose CTAs take a tenth of the time of
+        // the long ones, instead of a last, half-empty wave of the longest
+        if (i < n) order[n - 1u - (h[bin[k]] + rank[k])] = i;
     }
 }
 
@@ -869,11 +872,11 @@ struct SortBuffers {
 template <uint32_t TILES>
 void sort_pass(const SortKeySrc &src, const uint32_t *kin, const uint32_t *vin, uint32_t n, uint32_t shift,
                uint32_t bins, uint32_t chunks, const SortBuffers &sb, uint32_t *kout, uint32_t *vout, cudaStream_t s) {
-    launch_kernel(n <= kDependentLaunchUpTo, radix_hist_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src, kin,
+    launch_kernel(n <= dependent_launch_up_to(), radix_hist_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src, kin,
         n, shift, bins, chunks, sb.hist);
-    launch_kernel(n <= kDependentLaunchUpTo, radix_rowscan_kernel,
+    launch_kernel(n <= dependent_launch_up_to(), radix_rowscan_kernel,
         dim3((bins * 32 + kSortThreads - 1) / kSortThreads), dim3(kSortThreads), s, sb.hist, bins, chunks, sb.totals);
-    launch_kernel(n <= kDependentLaunchUpTo, radix_scatter_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src,
+    launch_kernel(n <= dependent_launch_up_to(), radix_scatter_kernel<TILES>, dim3(chunks), dim3(kSortThreads), s, src,
         kin, vin, n, shift, bins, chunks, sb.hist, sb.totals, kout, vout);
 }
 
@@ -945,9 +948,9 @@ cudaError_t launch_assign_counters(bnk_batch *b, uint32_t n, cudaStream_t s) {
     cudaError_t e = launch_group_by_slot(b, n, false, s);
     if (e != cudaSuccess) return e;
     DeviceBatch &d = b->dev;
-    launch_kernel(n <= kDependentLaunchUpTo, assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s,
+    launch_kernel(n <= dependent_launch_up_to(), assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s,
         d.keys_tmp + b->max_pkts, d.order, n, b->ctx->cfg.max_keypairs, b->ctx->kt.send_counter, d.counter);
-    launch_kernel(n <= kDependentLaunchUpTo, advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s,
+    launch_kernel(n <= dependent_launch_up_to(), advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s,
         d.keys_tmp + b->max_pkts, n, b->ctx->cfg.max_keypairs, b->ctx->kt.send_counter);
     b->ctx->launches += 2;
     return cudaGetLastError();
@@ -1001,16 +1004,16 @@ cudaError_t launch_replay(bnk_batch *b, uint32_t n, cudaStream_t s) {
     const ReplayArgs a = replay_args(b, n);
     const uint32_t tiles = (n + kScanTile - 1) / kScanTile, grid = (n + 255) / 256;
     uint32_t *flag = d.replay_tile_head + replay_scan_tiles(b->max_pkts);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_scan_tiles_kernel, dim3(tiles), dim3(256), s, a,
+    launch_kernel(n <= dependent_launch_up_to(), replay_scan_tiles_kernel, dim3(tiles), dim3(256), s, a,
         d.replay_tile_head, d.replay_tile_max, flag);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_scan_carry_kernel, dim3(1), dim3(1024), s, d.replay_tile_head,
+    launch_kernel(n <= dependent_launch_up_to(), replay_scan_carry_kernel, dim3(1), dim3(1024), s, d.replay_tile_head,
         d.replay_tile_max, tiles, d.replay_tile_carry);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_classify_kernel, dim3(tiles), dim3(256), s, a,
+    launch_kernel(n <= dependent_launch_up_to(), replay_classify_kernel, dim3(tiles), dim3(256), s, a,
         d.replay_tile_carry, flag);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_advance_kernel, dim3(grid), dim3(256), s, a);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_hash_clear_kernel, dim3(b->ctx->sm_count * 4), dim3(256), s, a, flag);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_hash_insert_kernel, dim3(grid), dim3(256), s, a, flag);
-    launch_kernel(n <= kDependentLaunchUpTo, replay_finish_kernel, dim3(grid), dim3(256), s, a);
+    launch_kernel(n <= dependent_launch_up_to(), replay_advance_kernel, dim3(grid), dim3(256), s, a);
+    launch_kernel(n <= dependent_launch_up_to(), replay_hash_clear_kernel, dim3(b->ctx->sm_count * 4), dim3(256), s, a, flag);
+    launch_kernel(n <= dependent_launch_up_to(), replay_hash_insert_kernel, dim3(grid), dim3(256), s, a, flag);
+    launch_kernel(n <= dependent_launch_up_to(), replay_finish_kernel, dim3(grid), dim3(256), s, a);
     b->ctx->launches += 7;
     return cudaGetLastError();
 }
@@ -1020,10 +1023,10 @@ cudaError_t launch_length_order(bnk_batch *b, uint32_t n, const uint32_t *len, b
     DeviceBatch &d = b->dev;
     cudaError_t e = cudaMemsetAsync(d.counters32, 0, kLenBins * sizeof(uint32_t), s);
     if (e != cudaSuccess) return e;
-    launch_kernel(n <= kDependentLaunchUpTo, len_hist_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s, len,
+    launch_kernel(n <= dependent_launch_up_to(), len_hist_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s, len,
         n, open_side ? 1 : 0, d.counters32);
-    launch_kernel(n <= kDependentLaunchUpTo, exclusive_scan_kernel, dim3(1), dim3(1024), s, d.counters32, kLenBins);
-    launch_kernel(n <= kDependentLaunchUpTo, len_scatter_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s,
+    launch_kernel(n <= dependent_launch_up_to(), exclusive_scan_kernel, dim3(1), dim3(1024), s, d.counters32, kLenBins);
+    launch_kernel(n <= dependent_launch_up_to(), len_scatter_kernel, dim3((n + kLenTile - 1) / kLenTile), dim3(256), s,
         len, n, open_side ? 1 : 0, d.counters32, d.len_order);
     b->ctx->launches += 3;
     return cudaGetLastError();
@@ -1109,9 +1112,9 @@ extern "C" int bnk_assign_counters_noalloc(bnk_ctx *ctx, void *stream, const uin
     SortKeySrc src{dev_slot, nullptr, ctx->cfg.max_keypairs, 0};
     SortBuffers sb{keys_a, keys_b, vals_a, order, hist + kMaxBins, hist};
     const uint32_t sort_launches = group_sort(src, n, kNoAllocMaxChunks, sb, s);
-    launch_kernel(n <= kDependentLaunchUpTo, assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b,
+    launch_kernel(n <= dependent_launch_up_to(), assign_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b,
         order, n, ctx->cfg.max_keypairs, ctx->kt.send_counter, dev_counter);
-    launch_kernel(n <= kDependentLaunchUpTo, advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b, n,
+    launch_kernel(n <= dependent_launch_up_to(), advance_counters_kernel, dim3((n + 255) / 256), dim3(256), s, keys_b, n,
         ctx->cfg.max_keypairs, ctx->kt.send_counter);
     ctx->launches += sort_launches + 2;
     if ((e = cudaGetLastError()) != cudaSuccess) return noalloc_fail(ctx, BNK_ECUDA, "kernel launch", e);

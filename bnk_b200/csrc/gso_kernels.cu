@@ -182,11 +182,11 @@ cudaError_t launch_gso_split(bnk_batch *b, uint32_t n_super, uint32_t n_pkts, cu
     if (n_pkts == 0 || n_super == 0) return cudaSuccess;
     DeviceBatch &d = b->dev;
     uint32_t *seg_super = d.order_tmp; // grouping scratch is idle here
-    launch_kernel(n_pkts <= kDependentLaunchUpTo, fill_u32_kernel, dim3((n_pkts + 255) / 256), dim3(256), s,
+    launch_kernel(n_pkts <= dependent_launch_up_to(), fill_u32_kernel, dim3((n_pkts + 255) / 256), dim3(256), s,
         seg_super, n_pkts, n_super);
-    launch_kernel(n_pkts <= kDependentLaunchUpTo, gso_map_kernel, dim3((n_super + 127) / 128), dim3(128), s, d.gso,
+    launch_kernel(n_pkts <= dependent_launch_up_to(), gso_map_kernel, dim3((n_super + 127) / 128), dim3(128), s, d.gso,
         n_super, n_pkts, seg_super);
-    launch_kernel(n_pkts <= kDependentLaunchUpTo, gso_split_kernel, dim3((n_pkts + 7) / 8), dim3(256), s, d.gso,
+    launch_kernel(n_pkts <= dependent_launch_up_to(), gso_split_kernel, dim3((n_pkts + 7) / 8), dim3(256), s, d.gso,
         n_super, d.ring, d.off, d.len, d.slot, n_pkts, b->ring_bytes, seg_super);
     b->ctx->launches += 3;
     return cudaGetLastError();

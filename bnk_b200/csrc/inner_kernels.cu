@@ -122,7 +122,7 @@ __global__ void classify_kernel(KeypairTables kt, const uint8_t *ring, const uin
 
 cudaError_t launch_classify(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    launch_kernel(n <= kDependentLaunchUpTo, classify_kernel, dim3((n + 255) / 256), dim3(256), s, b->ctx->kt,
+    launch_kernel(n <= dependent_launch_up_to(), classify_kernel, dim3((n + 255) / 256), dim3(256), s, b->ctx->kt,
         b->dev.ring, b->dev.off, b->dev.len, b->dev.src_addr, b->dev.slot, b->dev.status, n, b->ring_bytes);
     ++b->ctx->launches;
     return cudaGetLastError();
@@ -130,7 +130,7 @@ cudaError_t launch_classify(bnk_batch *b, uint32_t n, cudaStream_t s) {
 
 cudaError_t launch_demux_index(bnk_batch *b, uint32_t n, const uint32_t *len, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    launch_kernel(n <= kDependentLaunchUpTo, demux_index_kernel, dim3((n + 255) / 256), dim3(256), s, b->ctx->kt,
+    launch_kernel(n <= dependent_launch_up_to(), demux_index_kernel, dim3((n + 255) / 256), dim3(256), s, b->ctx->kt,
         b->dev.ring, b->dev.off, len, b->dev.slot, n, b->ring_bytes);
     ++b->ctx->launches;
     return cudaGetLastError();
@@ -138,7 +138,7 @@ cudaError_t launch_demux_index(bnk_batch *b, uint32_t n, const uint32_t *len, cu
 
 cudaError_t launch_inner_check(bnk_batch *b, uint32_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    launch_kernel(n <= kDependentLaunchUpTo, inner_check_kernel, dim3((n + 255) / 256), dim3(256), s, b->ctx->kt,
+    launch_kernel(n <= dependent_launch_up_to(), inner_check_kernel, dim3((n + 255) / 256), dim3(256), s, b->ctx->kt,
         b->dev.ring, b->dev.off, b->dev.slot, b->dev.out_len, b->dev.status, n);
     ++b->ctx->launches;
     return cudaGetLastError();
