@@ -74,6 +74,19 @@ def spans_equal(a: np.ndarray, b: np.ndarray, off, lengths, start: int = 0) -> l
     return bad
 
 
+def spans_differ_count(a: np.ndarray, b: np.ndarray, off, lengths, start: int = 0) -> int:
+    """Number of differing bytes inside the packets' spans [off+start, off+start+len), for rings too large to walk
+    packet by packet in Python (spans must not overlap)."""
+    n = min(len(a), len(b))
+    edge = np.zeros(n + 1, dtype=np.int8)
+    lo = np.asarray(off, dtype=np.int64) + start
+    hi = lo + np.asarray(lengths, dtype=np.int64)
+    np.add.at(edge, lo, 1)
+    np.add.at(edge, hi, -1)
+    inside = np.cumsum(edge[:n], dtype=np.int8).astype(bool)
+    return int(np.count_nonzero((a[:n] != b[:n]) & inside))
+
+
 def flows_equal(gpu_flows: np.ndarray, checker_flows: np.ndarray) -> bool:
     """The library's exported flow table against the checker's map: same keys, same expiries (both sorted by key)."""
     if len(gpu_flows) != len(checker_flows):

@@ -384,3 +384,71 @@ def test_config4_full_size_every_byte(gpu_lib, oracle):
         b.close()
     finally:
         c.close()
+
+
+def test_imix_full_size_two_batches_in_flight(gpu_lib, oracle):
+    """The benchmark's mixed-size leg at its size: 2 x 524,288 packets of 64/576/1420 B (7:4:1) in packed rings,
+    two batches in flight on their own streams with the by-length scheduling order, counters handed out on the
+    device, replay window on.  At this size the seal/open launches run on the low-priority stream beside the short
+    kernels of the other batch and the length classes are laid out longest first; none of that may change a byte:
+    every sealed message equals OpenSSL's (all host cores), every opened packet its plaintext, every packet is
+    refused when the same messages come again."""
+    from bnk_b200 import Context, gen
+    from bnk_b200.device import (F_ASSIGN_COUNTERS, F_NO_D2H, F_NO_H2D, F_REPLAY, F_SORT_BY_LENGTH, F_USE_OUT_LEN,
+                                 PKT_OK, PKT_REPLAY)
+
+    per, peers_b, nb = 1 << 19, 1 << 15, 2
+    g = gen.SplitMix64(gen.seed_for(2) + 31)
+    keys = gen.SplitMix64(99).bytes(nb * peers_b * 32).reshape(nb * peers_b, 32)
+    ridx = np.arange(nb * peers_b, dtype=np.uint32)
+    c = Context(max_keypairs=nb * peers_b, mtu=1420, flow_capacity=0)
+    try:
+        c.set_keypairs(0, keys, keys, ridx)
+        bs, plans = [], []
+        for j in range(nb):
+            sizes = gen.imix_sizes(g, per)
+            slot_bytes = ((sizes.astype(np.uint64) + np.uint64(48 + 15)) // np.uint64(16)) * np.uint64(16)
+            off = np.concatenate([[0], np.cumsum(slot_bytes)[:-1]]).astype(np.uint32)
+            total = int(off[-1]) + int(slot_bytes[-1])
+            slot = (j * peers_b + np.arange(per, dtype=np.uint64) % np.uint64(peers_b)).astype(np.uint32)
+            b = c.batch(per, total)
+            b.off[:], b.len[:], b.slot[:] = off, sizes, slot
+            b.upload(per)
+            b.fill_random(4242 + j)
+            b.download(per)  # the plaintext ring as the device made it
+            plain_ring = np.array(b.ring[:total])
+            bs.append(b)
+            plans.append((sizes, off, slot, total, plain_ring))
+        dev = F_NO_H2D | F_NO_D2H
+        for b in bs:
+            b.seal(per, dev | F_ASSIGN_COUNTERS | F_SORT_BY_LENGTH, wait=False)
+        for b in bs:
+            b.wait()
+        for b, (sizes, off, slot, total, plain_ring) in zip(bs, plans):
+            b.download(per)
+            want_ctr = np.arange(per, dtype=np.uint64) // np.uint64(peers_b)  # packet i of a batch is the peer's (i div peers)-th
+            assert np.array_equal(b.counter[:per], want_ctr)
+            want = plain_ring.copy()
+            _, st, ol = oracle.cpu_aead_batch(False, oracle.host_cores(), keys, ridx, 1420, want, off, sizes, slot, want_ctr)
+            assert (st == 0).all()
+            assert (b.status[:per] == PKT_OK).all() and np.array_equal(b.out_len[:per], ol)
+            assert H.spans_differ_count(np.asarray(b.ring[:total]), want, off, ol) == 0
+        for b in bs:
+            b.open(per, dev | F_REPLAY | F_USE_OUT_LEN | F_SORT_BY_LENGTH, wait=False)
+        for b in bs:
+            b.wait()
+        for b, (sizes, off, slot, total, plain_ring) in zip(bs, plans):
+            b.download(per)
+            assert (b.status[:per] == PKT_OK).all() and np.array_equal(b.out_len[:per], sizes)
+            assert H.spans_differ_count(np.asarray(b.ring[:total]), plain_ring, off, sizes, start=16) == 0
+        # the same messages again: seal with the counters that came down, open: all replays
+        for b in bs:
+            b.seal(per, dev | F_SORT_BY_LENGTH, wait=False)
+            b.open(per, dev | F_REPLAY | F_USE_OUT_LEN | F_SORT_BY_LENGTH, wait=False)
+        for b in bs:
+            b.wait()
+            b.download(per)
+            assert (b.status[:per] == PKT_REPLAY).all()
+            b.close()
+    finally:
+        c.close()
