@@ -805,7 +805,7 @@ def run_ours(args, rank, world, local_rank):
                 return None
             rates = []
             for _ in range(5):  # the rate is bimodal on shared hosts (some runs are several times slower): median of five
-                res = subprocess.run([exe, str(threads), str(rounds), str(packets), str(SIZE), str(lanes), "1" if queue else "0"],
+                res = subprocess.run([exe, str(threads), str(rounds), str(packets), str(SIZE), str(lanes), str(int(queue))],
                                      capture_output=True, text=True, timeout=300)
                 m = re.search(r"gbps=([0-9.]+)", res.stdout)
                 if res.returncode != 0 or "\nOK" not in "\n" + res.stdout or not m:
@@ -833,6 +833,11 @@ def run_ours(args, rank, world, local_rank):
                  "gbps_all_cores_128_packets_queue": threaded(host_threads(), 128, max(20, args.small_rounds), 2, True) if world == 1 else None,
                  "gbps_all_cores_128_packets_queue_4_outstanding": threaded(host_threads(), 128, max(20, args.small_rounds), 4, True) if world == 1 else None,
                  "gbps_2x_cores_128_packets_queue_4_outstanding": threaded(2 * host_threads(), 128, max(20, args.small_rounds), 4, True) if world == 1 else None,
+                 # the queue's calls without host copies inside the library (bnk_queue_reserve / commit / wait_span /
+                 # release): the caller's reads and writes land in the GPU batch's pinned ring
+                 "gbps_8_threads_128_packets_queue_spans": threaded(8, 128, max(20, args.small_rounds), 2, 2) if world == 1 else None,
+                 "gbps_8_threads_128_packets_queue_spans_4_outstanding": threaded(8, 128, max(20, args.small_rounds), 4, 2) if world == 1 else None,
+                 "gbps_all_cores_128_packets_queue_spans_4_outstanding": threaded(host_threads(), 128, max(20, args.small_rounds), 4, 2) if world == 1 else None,
                  "note": "host wall clock per submit+wait; seal = group+counters launch, seal launch; open = open "
                          "launch, group+replay launch; 128 x 1420 B goes through the copy engines, 16 x 1420 B (under "
                          "128 KiB) runs on the pinned host arrays without copies; gbps_16_batches_in_flight: sixteen "

@@ -116,6 +116,12 @@ class QueueCfg(C.Structure):
                 ("open_side", C.c_uint32), ("flags", C.c_uint32), ("reserved", C.c_uint32 * 2)]
 
 
+class QueueSpan(C.Structure):
+    _fields_ = [("data", C.POINTER(C.c_uint8)), ("stride", C.c_uint32), ("reserved", C.c_uint32),
+                ("len", C.POINTER(C.c_uint32)), ("slot", C.POINTER(C.c_uint32)), ("out_len", C.POINTER(C.c_uint32)),
+                ("counter", C.POINTER(C.c_uint64)), ("status", C.POINTER(C.c_uint8))]
+
+
 class MgpuCfg(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32),
@@ -178,6 +184,10 @@ SYMBOLS = {
     "bnk_queue_destroy": (_i, [_vp]),
     "bnk_queue_submit": (_i, [_vp, _vp, _vp, _vp, _u32, _i64, C.POINTER(_u64)]),
     "bnk_queue_wait": (_i, [_vp, _u64, _vp, _vp, _vp, _vp, _vp]),
+    "bnk_queue_reserve": (_i, [_vp, _u32, _i64, C.POINTER(_u64), C.POINTER(QueueSpan)]),
+    "bnk_queue_commit": (_i, [_vp, _u64]),
+    "bnk_queue_wait_span": (_i, [_vp, _u64, C.POINTER(QueueSpan)]),
+    "bnk_queue_release": (_i, [_vp, _u64]),
     "bnk_queue_wait_room": (_i, [_vp, _u64]),
     "bnk_queue_stats_get": (_i, [_vp, C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u64)]),
     "bnk_place_peers": (_i, [_vp, _u32, _u32, _u32, _vp, _vp, _vp]),

@@ -260,6 +260,123 @@ int bnk_queue_create(bnk_ctx *ctx, const bnk_queue_cfg *cfg, bnk_queue **out) {
     return BNK_SUCCESS;
 }
 
+// Room for n packets in the GPU batch that is filling (under the lock); BNK_EBUSY when every batch is taken.
+static int reserve(bnk_queue *q, uint32_t n, int64_t now_unix_ns, bnk_ticket *ticket, GpuBatch **gout, uint32_t *first_out) {
+    Locked lk(q->mu);
+    GpuBatch *g;
+    for (;;) {
+        g = &q->gb[q->cur];
+        int st = g->state.load(std::memory_order_relaxed);
+        if (st == FREE) {
+            g->state.store(st = FILLING, std::memory_order_relaxed);
+            g->reserved = g->users = 0;
+            g->filled.store(0, std::memory_order_relaxed);
+            g->gen++;
+            g->now = now_unix_ns;
+            g->rc = BNK_SUCCESS;
+            g->first_at = std::chrono::steady_clock::now();
+        }
+        if (st == FILLING && g->reserved + n <= q->cfg.max_pkts) break;
+        if (st == FILLING) { // no room for this caller's batch: the GPU batch is complete
+            g->state.store(CLOSED, std::memory_order_relaxed);
+            q->closed.push(q->cur);
+            q->cur = (q->cur + 1) % q->gb.size();
+            continue;
+        }
+        // The next batch in the rotation is still on the device or has not been emptied by its callers: the
+        // callers are ahead of the device.  No waiting here: the caller may itself hold the tickets that keep
+        // that batch from being reused.
+        return BNK_EBUSY;
+    }
+    const uint32_t first = g->reserved;
+    if (first == 0) q->n_pending.fetch_add(1, std::memory_order_relaxed);
+    g->reserved += n;
+    g->users++;
+    if (now_unix_ns > g->now) g->now = now_unix_ns;
+    q->n_caller_batches++;
+    *ticket = make_ticket(q->cur, g->gen, first, n);
+    *gout = g;
+    *first_out = first;
+    return BNK_SUCCESS;
+}
+
+// The GPU batch a ticket belongs to, if the ticket is out.
+static GpuBatch *batch_of(bnk_queue *q, bnk_ticket ticket, uint32_t *first, uint32_t *n) {
+    const uint32_t idx = (uint32_t)(ticket >> 56), gen = (uint32_t)(ticket >> 32) & 0xffffff;
+    *first = (uint32_t)(ticket >> 16) & 0xffff;
+    *n = (uint32_t)ticket & 0xffff;
+    if (idx >= q->gb.size() || *first + *n > q->cfg.max_pkts) return nullptr;
+    GpuBatch &g = q->gb[idx];
+    Locked lk(q->mu);
+    if ((g.gen & 0xffffff) != gen || g.state.load(std::memory_order_relaxed) == FREE || g.users == 0) return nullptr;
+    return &g;
+}
+
+static void fill_span(const bnk_queue *q, const GpuBatch *g, uint32_t first, bnk_queue_span *span) {
+    const bnk_batch_view &v = g->v;
+    span->data = v.ring + (size_t)first * q->slot_bytes;
+    span->stride = q->slot_bytes;
+    span->len = v.len + first;
+    span->slot = v.slot + first;
+    span->out_len = v.out_len + first;
+    span->counter = v.counter + first;
+    span->status = v.status + first;
+}
+
+static void release(bnk_queue *q, GpuBatch *g) {
+    Locked lk(q->mu);
+    if (--g->users == 0) g->state.store(FREE, std::memory_order_release);
+}
+
+int bnk_queue_reserve(bnk_queue *q, uint32_t n, int64_t now_unix_ns, bnk_ticket *ticket, bnk_queue_span *span) {
+    if (!q || !ticket || !span || n == 0 || n > q->cfg.max_pkts) return BNK_EINVAL;
+    GpuBatch *g;
+    uint32_t first;
+    const int rc = reserve(q, n, now_unix_ns, ticket, &g, &first);
+    if (rc != BNK_SUCCESS) return rc;
+    for (uint32_t k = 0; k < n; k++) g->v.off[first + k] = (first + k) * q->slot_bytes;
+    fill_span(q, g, first, span);
+    return BNK_SUCCESS;
+}
+
+int bnk_queue_commit(bnk_queue *q, bnk_ticket ticket) {
+    if (!q) return BNK_EINVAL;
+    uint32_t first, n;
+    GpuBatch *g = batch_of(q, ticket, &first, &n);
+    if (!g) return BNK_EINVAL;
+    const uint32_t room = q->cfg.open_side ? q->cfg.max_packet + 32u : q->cfg.max_packet;
+    int rc = BNK_SUCCESS;
+    for (uint32_t k = 0; k < n; k++)
+        if (g->v.len[first + k] > room) { // would run into the next packet's slot: the packet is refused on the device
+            g->v.len[first + k] = 0;                // (open: too short to be a message -> MALFORMED)
+            g->v.slot[first + k] = 0xfffffffeu;     // (seal: no such keypair -> BAD_DESC)
+            rc = BNK_EINVAL;
+        }
+    g->filled.fetch_add(n, std::memory_order_release);
+    pump(q);
+    return rc;
+}
+
+int bnk_queue_wait_span(bnk_queue *q, bnk_ticket ticket, bnk_queue_span *span) {
+    if (!q) return BNK_EINVAL;
+    uint32_t first, n;
+    GpuBatch *g = batch_of(q, ticket, &first, &n);
+    if (!g) return BNK_EINVAL;
+    for (uint32_t spins = 0; g->state.load(std::memory_order_acquire) != DONE;) turn(q, spins);
+    if (span) fill_span(q, g, first, span);
+    return g->rc;
+}
+
+int bnk_queue_release(bnk_queue *q, bnk_ticket ticket) {
+    if (!q) return BNK_EINVAL;
+    uint32_t first, n;
+    GpuBatch *g = batch_of(q, ticket, &first, &n);
+    if (!g) return BNK_EINVAL;
+    if (g->state.load(std::memory_order_acquire) != DONE) return BNK_EBUSY; // wait first: the batch may be on the device
+    release(q, g);
+    return BNK_SUCCESS;
+}
+
 int bnk_queue_submit(bnk_queue *q, const uint8_t *const *pkts, const uint32_t *len, const uint32_t *slot, uint32_t n,
                      int64_t now_unix_ns, bnk_ticket *ticket) {
     if (!q || !ticket || n == 0 || n > q->cfg.max_pkts || !pkts || !len) return BNK_EINVAL;
@@ -270,42 +387,9 @@ int bnk_queue_submit(bnk_queue *q, const uint8_t *const *pkts, const uint32_t *l
     for (uint32_t i = 0; i < n; i++)
         if (len[i] > room) return BNK_EINVAL;
     GpuBatch *g;
-    uint32_t first, idx;
-    {
-        Locked lk(q->mu);
-        for (;;) {
-            g = &q->gb[q->cur];
-            int st = g->state.load(std::memory_order_relaxed);
-            if (st == FREE) {
-                g->state.store(st = FILLING, std::memory_order_relaxed);
-                g->reserved = g->users = 0;
-                g->filled.store(0, std::memory_order_relaxed);
-                g->gen++;
-                g->now = now_unix_ns;
-                g->rc = BNK_SUCCESS;
-                g->first_at = std::chrono::steady_clock::now();
-            }
-            if (st == FILLING && g->reserved + n <= q->cfg.max_pkts) break;
-            if (st == FILLING) { // no room for this caller's batch: the GPU batch is complete
-                g->state.store(CLOSED, std::memory_order_relaxed);
-                q->closed.push(q->cur);
-                q->cur = (q->cur + 1) % q->gb.size();
-                continue;
-            }
-            // The next batch in the rotation is still on the device or has not been emptied by its callers: the
-            // callers are ahead of the device.  No waiting here: the caller may itself hold the tickets that keep
-            // that batch from being reused.
-            return BNK_EBUSY;
-        }
-        first = g->reserved;
-        idx = q->cur;
-        if (first == 0) q->n_pending.fetch_add(1, std::memory_order_relaxed);
-        g->reserved += n;
-        g->users++;
-        if (now_unix_ns > g->now) g->now = now_unix_ns;
-        q->n_caller_batches++;
-        *ticket = make_ticket(idx, g->gen, first, n);
-    }
+    uint32_t first;
+    const int rc = reserve(q, n, now_unix_ns, ticket, &g, &first);
+    if (rc != BNK_SUCCESS) return rc;
     // copy in, outside the lock: callers fill their own stretches of the ring side by side
     const bnk_batch_view &v = g->v;
     const uint32_t head = open_side ? 0u : 16u;
@@ -324,15 +408,10 @@ int bnk_queue_submit(bnk_queue *q, const uint8_t *const *pkts, const uint32_t *l
 int bnk_queue_wait(bnk_queue *q, bnk_ticket ticket, uint8_t *const *out, uint32_t *out_len, uint64_t *counter,
                    uint32_t *slot_out, uint8_t *status) {
     if (!q || !out || !out_len || !status) return BNK_EINVAL;
-    const uint32_t idx = (uint32_t)(ticket >> 56), gen = (uint32_t)(ticket >> 32) & 0xffffff;
-    const uint32_t first = (uint32_t)(ticket >> 16) & 0xffff, n = (uint32_t)ticket & 0xffff;
-    if (idx >= q->gb.size() || first + n > q->cfg.max_pkts) return BNK_EINVAL;
-    GpuBatch &g = q->gb[idx];
-    {
-        Locked lk(q->mu);
-        if ((g.gen & 0xffffff) != gen || g.state.load(std::memory_order_relaxed) == FREE || g.users == 0)
-            return BNK_EINVAL; // not a ticket that is out
-    }
+    uint32_t first, n;
+    GpuBatch *gp = batch_of(q, ticket, &first, &n);
+    if (!gp) return BNK_EINVAL; // not a ticket that is out
+    GpuBatch &g = *gp;
     for (uint32_t spins = 0; g.state.load(std::memory_order_acquire) != DONE;) turn(q, spins);
     const int rc = g.rc;
     const bnk_batch_view &v = g.v;
@@ -347,10 +426,7 @@ int bnk_queue_wait(bnk_queue *q, bnk_ticket ticket, uint8_t *const *out, uint32_
         if (slot_out) slot_out[k] = v.slot[at];
         if (out_len[k]) memcpy(out[k], v.ring + (size_t)at * q->slot_bytes + (open_side ? 16u : 0u), out_len[k]);
     }
-    {
-        Locked lk(q->mu);
-        if (--g.users == 0) g.state.store(FREE, std::memory_order_release);
-    }
+    release(q, &g);
     return rc;
 }
 

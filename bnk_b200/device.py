@@ -404,6 +404,36 @@ class Queue:
         outs = [dst[k * stride:k * stride + int(out_len[k])].tobytes() for k in range(n)]
         return outs, status, counter, slot
 
+    # -- the same without host copies: the caller works on the pinned ring of the GPU batch itself --
+    def _span_views(self, sp: "_lib.QueueSpan", n: int) -> dict:
+        as_np = np.ctypeslib.as_array
+        return {"data": as_np(sp.data, shape=(n, sp.stride)), "len": as_np(sp.len, shape=(n,)),
+                "slot": as_np(sp.slot, shape=(n,)), "out_len": as_np(sp.out_len, shape=(n,)),
+                "counter": as_np(sp.counter, shape=(n,)), "status": as_np(sp.status, shape=(n,))}
+
+    def reserve(self, n: int, now_ns: int = 0):
+        """-> (ticket, views) or None when every GPU batch is taken.  views["data"][k] is packet k's slot: a seal
+        queue wants the plaintext from byte 16 on, an open queue the message from byte 0; set views["len"][k] and
+        views["slot"][k], then commit(ticket)."""
+        t, sp = C.c_uint64(), _lib.QueueSpan()
+        rc = _lib.lib().bnk_queue_reserve(self._h, n, now_ns, C.byref(t), C.byref(sp))
+        if rc == _lib.EBUSY:
+            return None
+        self.ctx._ck(rc)
+        return (t.value, n), self._span_views(sp, n)
+
+    def commit(self, ticket):
+        self.ctx._ck(_lib.lib().bnk_queue_commit(self._h, ticket[0]))
+
+    def wait_span(self, ticket) -> dict:
+        """Blocks until the ticket's GPU batch is done -> views of the results in place (valid until release)."""
+        sp = _lib.QueueSpan()
+        self.ctx._ck(_lib.lib().bnk_queue_wait_span(self._h, ticket[0], C.byref(sp)))
+        return self._span_views(sp, ticket[1])
+
+    def release(self, ticket):
+        self.ctx._ck(_lib.lib().bnk_queue_release(self._h, ticket[0]))
+
     def stats(self):
         a, b, c = C.c_uint64(), C.c_uint64(), C.c_uint64()
         self.ctx._ck(_lib.lib().bnk_queue_stats_get(self._h, C.byref(a), C.byref(b), C.byref(c)))

@@ -8,7 +8,7 @@
 // With a sixth argument of 1 the threads do the same through two shared submit queues (bnk_queue, one per
 // direction) instead of batches of their own: their 128-packet calls are packed into GPU batches by the library.
 //
-//   mt_stress [threads] [rounds] [packets per batch] [payload bytes] [batches per thread] [0 = own batches | 1 = queue]
+//   mt_stress [threads] [rounds] [packets per batch] [payload bytes] [batches per thread] [0 = own batches | 1 = queue | 2 = queue, spans]
 //             [queue: packets per GPU batch] [queue: GPU batches in flight]
 #include <atomic>
 #include <chrono>
@@ -81,7 +81,9 @@ int main(int argc, char **argv) {
     std::atomic<int> ready{0};
     std::atomic<bool> go{false};
     std::atomic<uint64_t> packets{0};
-    const bool use_queue = argc > 6 && std::atoi(argv[6]) == 1;
+    const int queue_mode = argc > 6 ? std::atoi(argv[6]) : 0; // 1: copying calls, 2: spans (no host copies inside the library)
+    const bool use_queue = queue_mode == 1 || queue_mode == 2;
+    const bool use_spans = queue_mode == 2;
     bnk_queue *sealq = nullptr, *openq = nullptr;
     if (use_queue) {
         bnk_queue_cfg qc{};
@@ -126,6 +128,17 @@ int main(int argc, char **argv) {
         // (which may be what keeps a batch from being reused) and tries again.
         int r = 0;
         auto collect_sealed = [&](QLane &L) {
+            if (use_spans) { // results are read where they lie; the copy below stands for Bind.Send + the peer's receive
+                bnk_queue_span sp{};
+                CHECK(bnk_queue_wait_span(sealq, L.ticket, &sp) == BNK_SUCCESS, "queue_wait_span after seal");
+                for (uint32_t i = 0; i < n; i++) {
+                    L.status[i] = sp.status[i];
+                    L.counter[i] = sp.counter[i];
+                    L.out_len[i] = sp.out_len[i];
+                    std::memcpy(L.sealed.data() + (size_t)i * msg_room, sp.data + (size_t)i * sp.stride, sp.out_len[i]);
+                }
+                CHECK(bnk_queue_release(sealq, L.ticket) == BNK_SUCCESS, "queue_release after seal");
+            } else
             CHECK(bnk_queue_wait(sealq, L.ticket, L.out.data(), L.out_len.data(), L.counter.data(), nullptr, L.status.data()) == BNK_SUCCESS,
                   "queue_wait after seal");
             for (uint32_t i = 0; i < n; i++) {
@@ -137,6 +150,17 @@ int main(int argc, char **argv) {
             }
         };
         auto collect_opened = [&](QLane &L) {
+            if (use_spans) { // compared in place, as tun.Device.Write would read it in place
+                bnk_queue_span sp{};
+                CHECK(bnk_queue_wait_span(openq, L.ticket, &sp) == BNK_SUCCESS, "queue_wait_span after open");
+                for (uint32_t i = 0; i < n; i++) {
+                    CHECK(sp.status[i] == (size ? BNK_PKT_OK : BNK_PKT_KEEPALIVE), "thread %d round %d packet %u: open status %u", t, r, i, sp.status[i]);
+                    CHECK(std::memcmp(sp.data + (size_t)i * sp.stride + 16, L.plain.data() + (size_t)i * size, size) == 0,
+                          "thread %d round %d packet %u: plaintext differs", t, r, i);
+                }
+                CHECK(bnk_queue_release(openq, L.ticket) == BNK_SUCCESS, "queue_release after open");
+                return;
+            }
             CHECK(bnk_queue_wait(openq, L.ticket, L.out.data(), L.out_len.data(), nullptr, nullptr, L.status.data()) == BNK_SUCCESS,
                   "queue_wait after open");
             for (uint32_t i = 0; i < n; i++) {
@@ -145,13 +169,26 @@ int main(int argc, char **argv) {
                       "thread %d round %d packet %u: plaintext differs", t, r, i);
             }
         };
+        // hand lane L's packets (L.in / L.len / L.slot) to q: copying call, or reserve + write in place + commit
+        auto hand_in = [&](bnk_queue *q, QLane &L, bool seal_side) -> int {
+            if (!use_spans) return bnk_queue_submit(q, L.in.data(), L.len.data(), L.slot.data(), n, 0, &L.ticket);
+            bnk_queue_span sp{};
+            const int rc = bnk_queue_reserve(q, n, 0, &L.ticket, &sp);
+            if (rc != BNK_SUCCESS) return rc;
+            for (uint32_t i = 0; i < n; i++) { // stands for tun.Device.Read / the receive call landing in the ring
+                sp.len[i] = L.len[i];
+                sp.slot[i] = L.slot[i];
+                if (L.len[i]) std::memcpy(sp.data + (size_t)i * sp.stride + (seal_side ? 16 : 0), L.in[i], L.len[i]);
+            }
+            return bnk_queue_commit(q, L.ticket);
+        };
         // one phase: submit every lane, collecting the oldest outstanding one whenever the queue is full
         auto phase = [&](bnk_queue *q, const std::function<void(QLane &)> &prepare, const std::function<void(QLane &)> &collect) {
             int collected = 0;
             for (int l = 0; l < lanes; l++) {
                 prepare(ls[l]);
                 for (;;) {
-                    const int rc = bnk_queue_submit(q, ls[l].in.data(), ls[l].len.data(), ls[l].slot.data(), n, 0, &ls[l].ticket);
+                    const int rc = hand_in(q, ls[l], q == sealq);
                     if (rc == BNK_SUCCESS) break;
                     CHECK(rc == BNK_EBUSY, "queue_submit: %d %s", rc, bnk_last_error_string(ctx));
                     if (rc != BNK_EBUSY) return;
@@ -183,7 +220,13 @@ int main(int argc, char **argv) {
         }
         // the last sealed messages once more: all replays
         QLane &L = ls[0];
-        while (bnk_queue_submit(openq, L.in.data(), L.len.data(), L.slot.data(), n, 0, &L.ticket) == BNK_EBUSY) bnk_queue_wait_room(openq, 1000000);
+        while (hand_in(openq, L, false) == BNK_EBUSY) bnk_queue_wait_room(openq, 1000000);
+        if (use_spans) {
+            bnk_queue_span sp{};
+            CHECK(bnk_queue_wait_span(openq, L.ticket, &sp) == BNK_SUCCESS, "queue_wait_span");
+            for (uint32_t i = 0; i < n; i++) L.status[i] = sp.status[i];
+            CHECK(bnk_queue_release(openq, L.ticket) == BNK_SUCCESS, "queue_release");
+        } else
         CHECK(bnk_queue_wait(openq, L.ticket, L.out.data(), L.out_len.data(), nullptr, nullptr, L.status.data()) == BNK_SUCCESS, "queue_wait");
         for (uint32_t i = 0; i < n; i++) CHECK(L.status[i] == BNK_PKT_REPLAY, "thread %d: replayed packet %u has status %u", t, i, L.status[i]);
     };
@@ -284,7 +327,7 @@ int main(int argc, char **argv) {
     bnk_ctx_destroy(ctx);
     const double gbps = 2.0 * (double)packets.load() * size * 8 / secs / 1e9; // sealed + opened payload bits
     std::printf("%s mode=%s threads=%d lanes=%d packets_per_batch=%u payload=%u rounds=%d seconds=%.3f mpps=%.3f gbps=%.2f failures=%d\n",
-                failures.load() ? "FAILED" : "OK", use_queue ? "queue" : "batches", threads, lanes, n, size, rounds, secs,
+                failures.load() ? "FAILED" : "OK", use_spans ? "queue-spans" : use_queue ? "queue" : "batches", threads, lanes, n, size, rounds, secs,
                 2.0 * packets.load() / secs / 1e6, gbps, failures.load());
     return failures.load() ? 1 : 0;
 }

@@ -352,6 +352,33 @@ int bnk_queue_submit(bnk_queue *q, const uint8_t *const *pkts, const uint32_t *l
                      int64_t now_unix_ns, bnk_ticket *ticket);
 int bnk_queue_wait(bnk_queue *q, bnk_ticket ticket, uint8_t *const *out, uint32_t *out_len, uint64_t *counter,
                    uint32_t *slot_out, uint8_t *status);
+/* The same without the two host copies: the caller writes its packets straight into the pinned ring of the GPU
+ * batch that is filling and reads the results there (a tun.Device.Read or ReceiveFunc can be pointed at the span's
+ * slots, and Bind.Send / tun.Device.Write at the results).
+ *   bnk_queue_reserve    room for n packets: packet k of the span lives at data + k * stride; a seal queue wants the
+ *                        plaintext at +16 (the message is built in place from +0), an open queue the message at +0
+ *                        (the plaintext comes back at +16); the caller sets len[k] and slot[k].  BNK_EBUSY as above.
+ *   bnk_queue_commit     the packets are in: the GPU batch may go.  Must follow the reserve promptly (the GPU batch,
+ *                        with other callers' packets, waits for it).  A packet whose len[] exceeds max_packet
+ *                        is refused (BNK_EINVAL; its status comes back BAD_DESC or MALFORMED).
+ *   bnk_queue_wait_span  blocks until the ticket's GPU batch is done; status[], out_len[], counter[] (and slot[] of
+ *                        an open queue with BNK_F_DEMUX_INDEX) of the span are then valid, and the bytes stay where
+ *                        they are until the release.  Look at status[k] before using packet k.
+ *   bnk_queue_release    the caller is done with the span (once per ticket, after the wait). */
+typedef struct bnk_queue_span {
+    uint8_t *data;
+    uint32_t stride;
+    uint32_t reserved;
+    uint32_t *len;
+    uint32_t *slot;
+    const uint32_t *out_len;
+    const uint64_t *counter;
+    const uint8_t *status;
+} bnk_queue_span;
+int bnk_queue_reserve(bnk_queue *q, uint32_t n, int64_t now_unix_ns, bnk_ticket *ticket, bnk_queue_span *span);
+int bnk_queue_commit(bnk_queue *q, bnk_ticket ticket);
+int bnk_queue_wait_span(bnk_queue *q, bnk_ticket ticket, bnk_queue_span *span);
+int bnk_queue_release(bnk_queue *q, bnk_ticket ticket);
 /* Blocks until bnk_queue_submit has room again (some GPU batch has been emptied by its callers), at most
  * timeout_ns (UINT64_MAX = no limit; BNK_ETIMEDOUT otherwise).  For callers that hold no ticket they could
  * collect instead. */

@@ -147,3 +147,124 @@ def test_queue_refuses_what_it_cannot_take(gpu_lib):
         q.close()
     finally:
         c.close()
+
+
+def test_queue_spans_without_host_copies(gpu_lib, oracle):
+    """reserve / commit / wait_span / release: callers write into the GPU batch's pinned ring and read the results in
+    place.  Three threads, mixed with a fourth that uses the copying calls on the same queues; every sealed message
+    equals the checker's, counters run per keypair in submit order, opened packets equal their plaintext, a second
+    delivery is refused, an oversized packet is refused without touching its neighbours."""
+    from bnk_b200 import Context
+    from bnk_b200.device import F_REPLAY, PKT_BAD_DESC, PKT_KEEPALIVE, PKT_OK, PKT_REPLAY, Queue
+
+    n_threads, peers_per_thread, rounds = 4, 4, 10
+    n_peers = n_threads * peers_per_thread
+    rng = np.random.default_rng(5)
+    keys = rng.integers(0, 256, (n_peers, 32), dtype=np.uint8)
+    c = Context(max_keypairs=n_peers, mtu=1420, flow_capacity=0)
+    errors = []
+    try:
+        c.set_keypairs(0, keys, keys, (0x500 + np.arange(n_peers)).astype(np.uint32))
+        sealq = Queue(c, False, 0, max_pkts=512, depth=2)
+        openq = Queue(c, True, F_REPLAY, max_pkts=512, depth=2)
+
+        def take(q, n):
+            while True:
+                r = q.reserve(n)
+                if r is not None:
+                    return r
+                time.sleep(0)
+
+        def span_worker(t):
+            try:
+                r = np.random.default_rng(200 + t)
+                nxt = {}
+                for _ in range(rounds):
+                    n = int(r.integers(1, 97))
+                    sizes = r.choice([0, 64, 576, 1420], n).astype(np.uint32)
+                    pkts = [r.integers(0, 256, int(s), dtype=np.uint8) for s in sizes]
+                    slots = (t * peers_per_thread + r.integers(0, peers_per_thread, n)).astype(np.uint32)
+                    ticket, v = take(sealq, n)
+                    for k in range(n):
+                        v["data"][k, 16:16 + int(sizes[k])] = pkts[k]
+                    v["len"][:] = sizes
+                    v["slot"][:] = slots
+                    sealq.commit(ticket)
+                    res = sealq.wait_span(ticket)
+                    msgs = []
+                    for k in range(n):
+                        s = int(slots[k])
+                        want_ctr = nxt.get(s, 0)
+                        nxt[s] = want_ctr + 1
+                        assert res["status"][k] == PKT_OK and res["counter"][k] == want_ctr
+                        msg = res["data"][k, :int(res["out_len"][k])].tobytes()
+                        if k % 5 == 0:
+                            assert msg == oracle.wg_seal(keys[s].tobytes(), 0x500 + s, want_ctr, pkts[k].tobytes(), 1420)
+                        msgs.append(msg)
+                    sealq.release(ticket)
+                    for second in (False, True):
+                        ticket, v = take(openq, n)
+                        for k in range(n):
+                            v["data"][k, :len(msgs[k])] = np.frombuffer(msgs[k], np.uint8)
+                            v["len"][k] = len(msgs[k])
+                        v["slot"][:] = slots
+                        openq.commit(ticket)
+                        res = openq.wait_span(ticket)
+                        for k in range(n):
+                            if second:
+                                assert res["status"][k] == PKT_REPLAY
+                            else:
+                                assert res["status"][k] == (PKT_OK if sizes[k] else PKT_KEEPALIVE)
+                                assert res["out_len"][k] >= sizes[k]
+                                assert np.array_equal(res["data"][k, 16:16 + int(sizes[k])], pkts[k])
+                        openq.release(ticket)
+            except Exception as e:  # noqa: BLE001
+                errors.append((t, repr(e)))
+
+        def copy_worker(t):
+            try:
+                r = np.random.default_rng(300 + t)
+                nxt = {}
+                for _ in range(rounds):
+                    n = int(r.integers(1, 65))
+                    pkts = [r.integers(0, 256, int(s), dtype=np.uint8).tobytes() for s in r.choice([64, 1420], n)]
+                    slots = (t * peers_per_thread + r.integers(0, peers_per_thread, n)).astype(np.uint32)
+                    while (ticket := sealq.submit(pkts, slots)) is None:
+                        time.sleep(0)
+                    msgs, st, ctr, _ = sealq.wait(ticket)
+                    for k in range(n):
+                        s = int(slots[k])
+                        want_ctr = nxt.get(s, 0)
+                        nxt[s] = want_ctr + 1
+                        assert st[k] == PKT_OK and ctr[k] == want_ctr
+                    while (ticket := openq.submit(msgs, slots)) is None:
+                        time.sleep(0)
+                    pts, st, _, _ = openq.wait(ticket)
+                    assert all(st[k] == PKT_OK and pts[k][:len(pkts[k])] == pkts[k] for k in range(n))
+            except Exception as e:  # noqa: BLE001
+                errors.append((t, repr(e)))
+
+        th = [threading.Thread(target=span_worker, args=(t,)) for t in range(3)]
+        th.append(threading.Thread(target=copy_worker, args=(3,)))
+        for x in th:
+            x.start()
+        for x in th:
+            x.join()
+        assert errors == []
+        # an oversized length is refused at commit, the packet comes back BAD_DESC, its neighbours are sealed
+        ticket, v = take(sealq, 3)
+        v["data"][:, 16:16 + 64] = 7
+        v["len"][:] = (64, 5000, 64)
+        v["slot"][:] = 0
+        with pytest.raises(Exception):
+            sealq.commit(ticket)
+        res = sealq.wait_span(ticket)
+        assert list(res["status"]) == [PKT_OK, PKT_BAD_DESC, PKT_OK]
+        assert res["counter"][2] == res["counter"][0] + 1
+        sealq.release(ticket)
+        with pytest.raises(Exception):
+            sealq.release(ticket)  # once per ticket
+        sealq.close()
+        openq.close()
+    finally:
+        c.close()
