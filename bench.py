@@ -813,12 +813,19 @@ def run_ours(args, rank, world, local_rank):
                 rates.append(float(m.group(1)))
             return statistics.median(rates)
 
+        # what the host link gives copies of one 128-packet batch (186 KB each way), kernels or not
+        one_batch_bytes = 128 * (16 + ((SIZE + 15) & ~15) + 16 + 24)
+        copy_rounds = ctx.probe_copy_rounds(8, one_batch_bytes, max(200, 5 * args.small_rounds))
+        copy_rounds_8x = ctx.probe_copy_rounds(8, 8 * one_batch_bytes, max(100, 2 * args.small_rounds))
         s128, o128, ok128 = small_latency(128)
         pipe_gbps, pipe_ok = small_pipelined(128, 16)
         s16, o16, ok16 = small_latency(16)
         small = {"packets": 128, "payload_bytes": SIZE, "seal_us": s128, "open_us": o128,
                  "seal_us_16_packets": s16, "open_us_16_packets": o16, "verified": ok128 and ok16 and pipe_ok,
                  "gbps_16_batches_in_flight": pipe_gbps,
+                 # seal + open of one batch = two copy rounds; the rate a batch per worker cannot exceed on this host
+                 "copy_only_ceiling_gbps_128_packet_copies": copy_rounds / 2 * 2 * 128 * SIZE * 8 / 1e9,
+                 "copy_only_ceiling_gbps_1024_packet_copies": copy_rounds_8x / 2 * 2 * 1024 * SIZE * 8 / 1e9,
                  # (a second process on this GPU: only in single-GPU runs, like the CPU baseline)
                  "gbps_8_threads_128_packets": threaded(8, 128, max(20, args.small_rounds)) if world == 1 else None,
                  "gbps_8_threads_1024_packets": threaded(8, 1024, max(10, args.small_rounds // 2)) if world == 1 else None,
@@ -843,7 +850,9 @@ def run_ours(args, rank, world, local_rank):
                          "128 KiB) runs on the pinned host arrays without copies; gbps_16_batches_in_flight: sixteen "
                          "128-packet batches submitted round-robin by this one Python thread, seal then open; "
                          "gbps_8_threads_*: eight C++ host threads, two batches in flight each, same context "
-                         "(bnk_b200/host/apps/mt_stress.cpp), median of five runs; *_queue: the same threads hand "
+                         "(bnk_b200/host/apps/mt_stress.cpp), median of five runs; copy_only_ceiling_*: eight threads and streams "
+                         "copying one batch's bytes up and down with no kernel between (bnk_probe_copy_rounds), as "
+                         "payload Gbit/s sealed + opened; *_queue: the same threads hand "
                          "their 128-packet calls (pageable buffers, copied in and out by the library) to bnk_queue"}
 
     sampler.stop()

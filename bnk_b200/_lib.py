@@ -215,6 +215,7 @@ BENCH_SYMBOLS = {
     "bnk_probe_coissue": (_i, [_vp, _i, _i, C.POINTER(C.c_double)]),
     "bnk_batch_fill_random": (_i, [_vp, _u64]),
     "bnk_batch_copy_only": (_i, [_vp, _u32, _i, _i]),
+    "bnk_probe_copy_rounds": (_i, [_vp, _u32, _u64, _u32, _i, C.POINTER(C.c_double)]),
 }
 
 _LIB = None

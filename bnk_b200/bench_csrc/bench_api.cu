@@ -1,5 +1,12 @@
 // libbnkgpu_bench.so: the measurement helpers declared in include/bnk_gpu_bench.h.  They work on the
 // handles of libbnkgpu.so (same struct layouts, same build) and use nothing of it but those layouts.
+#include <atomic>
+#include <chrono>
+#include <cstring>
+#include <functional>
+#include <thread>
+#include <vector>
+
 #include "../csrc/bnk_internal.cuh"
 #include "../../include/bnk_gpu_bench.h"
 
@@ -103,6 +110,57 @@ int bnk_batch_copy_only(bnk_batch *b, uint32_t npkts, int up, int down) {
         CK(ctx, cudaMemcpyAsync(b->h_desc + 12 * np, b->d_desc + 12 * np, 12 * np + n, cudaMemcpyDeviceToHost,
                                 b->stream)); // counter, out_len, status
     }
+    return BNK_SUCCESS;
+}
+
+int bnk_probe_copy_rounds(bnk_ctx *ctx, uint32_t threads, uint64_t bytes, uint32_t rounds, int directions,
+                          double *rounds_per_s) {
+    if (!ctx || !rounds_per_s || threads == 0 || threads > 256 || bytes == 0 || rounds == 0 || !(directions & 3))
+        return BNK_EINVAL;
+    CK(ctx, cudaSetDevice(ctx->device));
+    struct Lane {
+        cudaStream_t s = nullptr;
+        uint8_t *h = nullptr, *d = nullptr;
+    };
+    std::vector<Lane> lanes(threads);
+    cudaError_t e = cudaSuccess;
+    for (Lane &l : lanes) {
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&l.s, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaHostAlloc((void **)&l.h, bytes, cudaHostAllocDefault);
+        if (e == cudaSuccess) e = cudaMalloc((void **)&l.d, bytes);
+        if (e == cudaSuccess) memset(l.h, 0x5a, bytes);
+    }
+    std::atomic<int> failed{0};
+    auto body = [&](Lane &l, uint32_t n) {
+        cudaSetDevice(ctx->device);
+        for (uint32_t r = 0; r < n; r++) {
+            cudaError_t x = cudaSuccess;
+            if (directions & 1) x = cudaMemcpyAsync(l.d, l.h, bytes, cudaMemcpyHostToDevice, l.s);
+            if (x == cudaSuccess && (directions & 2)) x = cudaMemcpyAsync(l.h, l.d, bytes, cudaMemcpyDeviceToHost, l.s);
+            if (x == cudaSuccess) x = cudaStreamSynchronize(l.s);
+            if (x != cudaSuccess) {
+                failed.store((int)x);
+                return;
+            }
+        }
+    };
+    double secs = 0;
+    if (e == cudaSuccess) {
+        for (Lane &l : lanes) body(l, 20); // warm
+        const auto t0 = std::chrono::steady_clock::now();
+        std::vector<std::thread> pool;
+        for (Lane &l : lanes) pool.emplace_back(body, std::ref(l), rounds);
+        for (auto &t : pool) t.join();
+        secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    }
+    for (Lane &l : lanes) {
+        if (l.s) cudaStreamDestroy(l.s);
+        if (l.h) cudaFreeHost(l.h);
+        if (l.d) cudaFree(l.d);
+    }
+    if (e != cudaSuccess) return fail(ctx, BNK_ECUDA, "copy probe setup", e);
+    if (failed.load()) return fail(ctx, BNK_ECUDA, "copy probe", (cudaError_t)failed.load());
+    *rounds_per_s = (double)threads * rounds / secs;
     return BNK_SUCCESS;
 }
 

@@ -199,6 +199,12 @@ class Context:
         self._ck(_lib.bench_lib().bnk_probe_coissue(self._h, kind, k, C.byref(v)))
         return v.value
 
+    def probe_copy_rounds(self, threads: int, nbytes: int, rounds: int, directions: int = 3) -> float:
+        """Copy rounds per second (nbytes up and/or down, then wait) over `threads` host threads: see the bench header."""
+        v = C.c_double()
+        self._ck(_lib.bench_lib().bnk_probe_copy_rounds(self._h, threads, nbytes, rounds, directions, C.byref(v)))
+        return v.value
+
     def timer_start(self, batches: Sequence["Batch"]):
         arr = (C.c_void_p * len(batches))(*[b._h for b in batches])
         self._ck(_lib.bench_lib().bnk_timer_start(self._h, arr, len(batches)))

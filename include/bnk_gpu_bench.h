@@ -40,6 +40,13 @@ int bnk_batch_fill_random(bnk_batch *b, uint64_t seed);
  * ceiling of the host link for the end-to-end numbers.  Completion is reported by bnk_wait as usual. */
 int bnk_batch_copy_only(bnk_batch *b, uint32_t npkts, int up, int down);
 
+/* What the host link gives small batches: `threads` host threads, each with a stream and pinned buffers of its
+ * own, copy `bytes` to the device and `bytes` back and wait, `rounds` times in a closed loop, no kernel in
+ * between (directions: 1 = up only, 2 = down only, 3 = both).  Result: copy rounds per second over all threads.
+ * 190,000 bytes is one 128-packet batch of 1420-byte packets. */
+int bnk_probe_copy_rounds(bnk_ctx *ctx, uint32_t threads, uint64_t bytes, uint32_t rounds, int directions,
+                          double *rounds_per_s);
+
 #ifdef __cplusplus
 }
 #endif
