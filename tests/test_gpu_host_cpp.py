@@ -47,8 +47,10 @@ def test_threads_share_the_submit_queues(gpu_lib):
     from bnk_b200 import _build
 
     exe = _build.build_mt_stress()
-    for threads, lanes in ((8, 2), (5, 3)):
-        res = subprocess.run([exe, str(threads), "60", "128", "1420", str(lanes), "1"], capture_output=True, text=True, timeout=300)
+    # (threads, calls outstanding per thread, 1 = copying calls / 2 = spans on the pinned ring); 24 threads: more
+    # callers than cores, the waiting ones give their cores away
+    for threads, lanes, mode in ((8, 2, 1), (5, 3, 1), (8, 2, 2), (5, 3, 2), (24, 2, 1)):
+        res = subprocess.run([exe, str(threads), "60", "128", "1420", str(lanes), str(mode)], capture_output=True, text=True, timeout=300)
         print(res.stdout[-500:], res.stderr[-2000:])
         assert res.returncode == 0 and "\nOK mode=queue" in "\n" + res.stdout, res.stdout[-500:] + res.stderr[-2000:]
 
@@ -72,7 +74,8 @@ def test_host_layer_under_sanitizers(gpu_lib, kind):
         env["TSAN_OPTIONS"] = "report_signal_unsafe=0"
     runs = [[os.path.join(out, "host_test")],
             [os.path.join(out, "mt_stress"), "4", "20", "128", "1420", "2", "0"],
-            [os.path.join(out, "mt_stress"), "4", "20", "128", "1420", "2", "1"]]
+            [os.path.join(out, "mt_stress"), "4", "20", "128", "1420", "2", "1"],
+            [os.path.join(out, "mt_stress"), "4", "20", "128", "1420", "2", "2"]]
     for cmd in runs:
         res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
         text = res.stdout + res.stderr
