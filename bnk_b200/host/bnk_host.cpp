@@ -428,4 +428,68 @@ Dispatcher::Result Dispatcher::Open(const std::vector<Packet> &msgs, uint32_t fl
     return r;
 }
 
+// ---- Queue ----
+Queue::Queue(Context &ctx, bool open_side, uint32_t flags, uint32_t max_pkts, uint32_t max_packet, uint32_t depth)
+    : ctx_(ctx), open_side_(open_side), max_packet_(max_packet) {
+    bnk_queue_cfg cfg{};
+    cfg.struct_size = sizeof cfg;
+    cfg.max_pkts = max_pkts;
+    cfg.max_packet = max_packet;
+    cfg.depth = depth;
+    cfg.open_side = open_side ? 1u : 0u;
+    cfg.flags = flags;
+    ctx_.Check(bnk_queue_create(ctx.raw(), &cfg, &q_));
+}
+
+Queue::~Queue() {
+    if (q_) bnk_queue_destroy(q_);
+}
+
+Queue::Result Queue::Run(const std::vector<Packet> &pkts, const std::vector<uint32_t> &slots, TimeNs now) {
+    const uint32_t n = (uint32_t)pkts.size();
+    Result r;
+    if (n == 0) return r;
+    std::vector<const uint8_t *> in(n);
+    std::vector<uint32_t> len(n);
+    static const uint8_t none = 0;
+    for (uint32_t i = 0; i < n; i++) {
+        in[i] = pkts[i].empty() ? &none : pkts[i].data();
+        len[i] = (uint32_t)pkts[i].size();
+    }
+    bnk_ticket t = 0;
+    for (;;) {
+        const int rc = bnk_queue_submit(q_, in.data(), len.data(), slots.empty() ? nullptr : slots.data(), n, now, &t);
+        if (rc == BNK_SUCCESS) break;
+        if (rc != BNK_EBUSY) ctx_.Check(rc);
+        bnk_queue_wait_room(q_, 1000000);
+    }
+    const uint32_t room = max_packet_ + 64;
+    std::vector<uint8_t> flat((size_t)n * room);
+    std::vector<uint8_t *> out(n);
+    std::vector<uint32_t> out_len(n);
+    for (uint32_t i = 0; i < n; i++) out[i] = flat.data() + (size_t)i * room;
+    r.status.resize(n);
+    r.counter.resize(n);
+    r.slot.resize(n);
+    ctx_.Check(bnk_queue_wait(q_, t, out.data(), out_len.data(), r.counter.data(), r.slot.data(), r.status.data()));
+    r.out.resize(n);
+    for (uint32_t i = 0; i < n; i++) r.out[i].assign(out[i], out[i] + out_len[i]);
+    return r;
+}
+
+Queue::Span Queue::Reserve(uint32_t n, TimeNs now) {
+    Span sp;
+    sp.n = n;
+    for (;;) {
+        const int rc = bnk_queue_reserve(q_, n, now, &sp.ticket, &sp.s);
+        if (rc == BNK_SUCCESS) return sp;
+        if (rc != BNK_EBUSY) ctx_.Check(rc);
+        bnk_queue_wait_room(q_, 1000000);
+    }
+}
+
+void Queue::Commit(const Span &sp) { ctx_.Check(bnk_queue_commit(q_, sp.ticket)); }
+void Queue::Wait(Span &sp) { ctx_.Check(bnk_queue_wait_span(q_, sp.ticket, &sp.s)); }
+void Queue::Release(const Span &sp) { ctx_.Check(bnk_queue_release(q_, sp.ticket)); }
+
 } // namespace bnk

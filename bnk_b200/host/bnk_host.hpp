@@ -221,4 +221,41 @@ class Dispatcher {
     uint32_t max_peers_, max_packet_;
 };
 
+// RAII over bnk_queue: the workers of one direction hand their upstream-sized batches (conn.IdealBatchSize = 128,
+// bind.go:97) to one queue, which packs them into GPU batches (see include/bnk_gpu.h).  Thread-safe; one Queue per
+// direction and set of flags.
+class Queue {
+  public:
+    Queue(Context &ctx, bool open_side, uint32_t flags, uint32_t max_pkts = 1024, uint32_t max_packet = 1420, uint32_t depth = 3);
+    ~Queue();
+    Queue(const Queue &) = delete;
+    Queue &operator=(const Queue &) = delete;
+    bnk_queue *raw() const { return q_; }
+    struct Result {
+        std::vector<Packet> out;     // sealed messages, or opened plaintexts; empty where the packet was refused
+        std::vector<uint8_t> status; // BNK_PKT_*
+        std::vector<uint64_t> counter;
+        std::vector<uint32_t> slot;
+    };
+    // Copying form: hand in, wait, get everything back (blocks; collects room by itself when the queue is full).
+    Result Run(const std::vector<Packet> &pkts, const std::vector<uint32_t> &slots, TimeNs now = 0);
+    // Span form: write into / read from the GPU batch's pinned ring.  Reserve blocks until there is room.
+    struct Span {
+        bnk_ticket ticket = 0;
+        uint32_t n = 0;
+        bnk_queue_span s{};
+        uint8_t *packet(uint32_t k) const { return s.data + (size_t)k * s.stride; }
+    };
+    Span Reserve(uint32_t n, TimeNs now = 0);
+    void Commit(const Span &sp);
+    void Wait(Span &sp);   // results of the span are valid from here until Release
+    void Release(const Span &sp);
+
+  private:
+    Context &ctx_;
+    bnk_queue *q_ = nullptr;
+    bool open_side_;
+    uint32_t max_packet_;
+};
+
 } // namespace bnk

@@ -5,7 +5,10 @@
 // Needs a B200: every verdict and every ciphertext byte is produced by libbnkgpu.so.
 #include <cstdio>
 #include <cstring>
+#include <algorithm>
+#include <atomic>
 #include <deque>
+#include <thread>
 #include <string>
 
 #include "../../bnk_b200/host/bnk_host.hpp"
@@ -376,6 +379,85 @@ static void TestDispatcherRoundTrip(Context &) {
     CHECK(ok, "the same messages again are replays on every GPU");
 }
 
+// Workers of both directions share one queue each (the reference's workers move conn.IdealBatchSize packets per
+// call, bind.go:97): four threads, copying calls and span calls mixed; nonces per peer in call order, every
+// plaintext back, a second delivery refused.
+static void TestWorkersShareQueues(Context &) {
+    Context ctx(0, 64, 1420, 0);
+    for (uint32_t p = 0; p < 64; p++) {
+        uint8_t key[32];
+        for (int i = 0; i < 32; i++) key[i] = (uint8_t)(p * 5 + i);
+        ctx.Check(bnk_keypair_set(ctx.raw(), p, key, key, 0x700 + p));
+    }
+    Queue sealq(ctx, false, 0, 512, 1420, 2), openq(ctx, true, BNK_F_REPLAY, 512, 1420, 2);
+    std::atomic<int> bad{0};
+    auto worker = [&](int t) {
+        std::vector<uint64_t> next(64, 0);
+        for (int round = 0; round < 8; round++) {
+            const uint32_t n = 20 + 13 * (uint32_t)t + (uint32_t)round;
+            std::vector<Packet> plain(n);
+            std::vector<uint32_t> slots(n);
+            for (uint32_t i = 0; i < n; i++) {
+                slots[i] = (uint32_t)t * 16 + (i * 7 + (uint32_t)round) % 16; // sixteen peers per worker
+                plain[i] = udp(ip(100, 64, 0, 1), ip(100, 64, 2, 1 + slots[i]), 3000 + i, 53);
+                plain[i].resize(28 + (i * 97) % 1300, (uint8_t)i);
+            }
+            std::vector<Packet> msgs(n);
+            if (t % 2 == 0) { // copying calls
+                Queue::Result r = sealq.Run(plain, slots);
+                for (uint32_t i = 0; i < n; i++) {
+                    if (r.status[i] != BNK_PKT_OK || r.counter[i] != next[slots[i]]++) bad++;
+                    msgs[i] = r.out[i];
+                }
+                Queue::Result o = openq.Run(msgs, slots);
+                for (uint32_t i = 0; i < n; i++)
+                    if (o.status[i] != BNK_PKT_OK || o.out[i].size() < plain[i].size() ||
+                        !std::equal(plain[i].begin(), plain[i].end(), o.out[i].begin()))
+                        bad++;
+                Queue::Result again = openq.Run(msgs, slots);
+                for (uint32_t i = 0; i < n; i++)
+                    if (again.status[i] != BNK_PKT_REPLAY || !again.out[i].empty()) bad++;
+            } else { // spans: written and read in the pinned ring
+                Queue::Span sp = sealq.Reserve(n);
+                for (uint32_t i = 0; i < n; i++) {
+                    std::copy(plain[i].begin(), plain[i].end(), sp.packet(i) + 16);
+                    sp.s.len[i] = (uint32_t)plain[i].size();
+                    sp.s.slot[i] = slots[i];
+                }
+                sealq.Commit(sp);
+                sealq.Wait(sp);
+                for (uint32_t i = 0; i < n; i++) {
+                    if (sp.s.status[i] != BNK_PKT_OK || sp.s.counter[i] != next[slots[i]]++) bad++;
+                    msgs[i].assign(sp.packet(i), sp.packet(i) + sp.s.out_len[i]);
+                }
+                sealq.Release(sp);
+                for (int pass = 0; pass < 2; pass++) {
+                    Queue::Span op = openq.Reserve(n);
+                    for (uint32_t i = 0; i < n; i++) {
+                        std::copy(msgs[i].begin(), msgs[i].end(), op.packet(i));
+                        op.s.len[i] = (uint32_t)msgs[i].size();
+                        op.s.slot[i] = slots[i];
+                    }
+                    openq.Commit(op);
+                    openq.Wait(op);
+                    for (uint32_t i = 0; i < n; i++) {
+                        if (pass == 0) {
+                            if (op.s.status[i] != BNK_PKT_OK || !std::equal(plain[i].begin(), plain[i].end(), op.packet(i) + 16)) bad++;
+                        } else if (op.s.status[i] != BNK_PKT_REPLAY) {
+                            bad++;
+                        }
+                    }
+                    openq.Release(op);
+                }
+            }
+        }
+    };
+    std::vector<std::thread> pool;
+    for (int t = 0; t < 4; t++) pool.emplace_back(worker, t);
+    for (auto &th : pool) th.join();
+    CHECK(bad.load() == 0, "four workers through two shared queues: nonces in call order, plaintext back, replays refused");
+}
+
 int main() {
     try {
         Context ctx(0, /*max_keypairs=*/16, /*mtu=*/1420, /*flow_capacity=*/1u << 12);
@@ -399,6 +481,7 @@ int main() {
         RUN(TestTwoDevicesRoundTrip)
         RUN(TestCoalescedPumps)
         RUN(TestDispatcherRoundTrip)
+        RUN(TestWorkersShareQueues)
     } catch (const Error &e) {
         printf("FAIL %s: exception %d %s\n", g_test, e.code, e.what());
         return 2;

@@ -22,7 +22,7 @@ def test_reference_go_tests_restated_in_cpp(gpu_lib):
     res = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     print(res.stdout[-3000:])
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
-    assert "0 failed" in res.stdout and res.stdout.count("ran Test") == 16
+    assert "0 failed" in res.stdout and res.stdout.count("ran Test") == 17
 
 
 @pytest.mark.gpu
