@@ -113,7 +113,7 @@ class TableStats(C.Structure):
 
 class QueueCfg(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("max_pkts", C.c_uint32), ("max_packet", C.c_uint32), ("depth", C.c_uint32),
-                ("open_side", C.c_uint32), ("flags", C.c_uint32), ("reserved", C.c_uint32 * 2)]
+                ("open_side", C.c_uint32), ("flags", C.c_uint32), ("min_fill", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 class QueueSpan(C.Structure):

@@ -7,11 +7,13 @@
 // a submit of a few thousand packets, and while such a small batch is on its way the GPU does nothing else.
 // Here callers copy their packets into the pinned ring of the GPU batch that is filling.  When the device is idle
 // the batch goes as it is (a lone caller waits for nobody); while something is in flight the batch keeps filling
-// until it holds a quarter of its capacity or its first packet has waited kGatherNs, whichever comes first, and
+// until it holds `min_fill` packets (by default one upstream batch of 128) and a slot on the device is free, or its
+// first packet has waited kGatherNs, whichever comes first, and
 // at the latest when it is full (under load batches grow by themselves).  Up to `depth` GPU batches are in flight, each
 // on its own stream, so the upload of one runs beside the kernels of the one in front and the download of the
 // one before; the KERNELS of consecutive batches are chained with events, which keeps what the library promises
 // per keypair: nonces in submit order, replay verdicts in arrival order.
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <new>
@@ -119,7 +121,7 @@ bool ripe(const bnk_queue *q) {
         c.filled.load(std::memory_order_acquire) != c.reserved)
         return false;
     if (q->inflight.empty()) return true;                                   // the device is idle
-    if (c.reserved >= (q->cfg.max_pkts + 3) / 4) return true;               // worth a launch
+    if (c.reserved >= q->cfg.min_fill) return true;                         // worth a launch
     return std::chrono::steady_clock::now() >= c.first_at + kGatherNs;      // waited long enough
 }
 
@@ -242,6 +244,7 @@ int bnk_queue_create(bnk_ctx *ctx, const bnk_queue_cfg *cfg, bnk_queue **out) {
     // the queue does the copies itself and hands out counters itself
     q->cfg.flags &= ~(BNK_F_NO_H2D | BNK_F_NO_D2H | BNK_F_USE_OUT_LEN | BNK_F_TIMED | BNK_F_STATS);
     if (!cfg->open_side) q->cfg.flags |= BNK_F_ASSIGN_COUNTERS;
+    if (q->cfg.min_fill == 0) q->cfg.min_fill = std::min(128u, (cfg->max_pkts + 3) / 4); // one upstream batch
     q->slot_bytes = (16u + ((cfg->max_packet + 15u) & ~15u) + 16u + 15u) & ~15u;
     q->gb = std::vector<GpuBatch>(cfg->depth + kRotationExtra);
     q->closed.slot.resize(q->gb.size());

@@ -9,7 +9,7 @@
 // direction) instead of batches of their own: their 128-packet calls are packed into GPU batches by the library.
 //
 //   mt_stress [threads] [rounds] [packets per batch] [payload bytes] [batches per thread] [0 = own batches | 1 = queue | 2 = queue, spans]
-//             [queue: packets per GPU batch] [queue: GPU batches in flight]
+//             [queue: packets per GPU batch] [queue: GPU batches in flight] [queue: min_fill]
 #include <atomic>
 #include <chrono>
 #include <cstdio>
@@ -93,6 +93,7 @@ int main(int argc, char **argv) {
         qc.max_pkts = argc > 7 ? (uint32_t)std::atoi(argv[7]) : 1024;
         qc.max_packet = size ? size : 16;
         qc.depth = argc > 8 ? (uint32_t)std::atoi(argv[8]) : 3;
+        qc.min_fill = argc > 9 ? (uint32_t)std::atoi(argv[9]) : 0;
         qc.open_side = 0;
         qc.flags = 0;
         if (bnk_queue_create(ctx, &qc, &sealq) != BNK_SUCCESS) return 2;

@@ -344,7 +344,10 @@ typedef struct bnk_queue_cfg {
     uint32_t depth;       /* GPU batches in flight at once, 1..8 (2 or 3 keeps copies and kernels overlapped) */
     uint32_t open_side;   /* 0 = seal queue, 1 = open queue */
     uint32_t flags;       /* BNK_F_* of every submit (BNK_F_NOTE_OUTBOUND, BNK_F_REPLAY, BNK_F_CHECK_INBOUND ...) */
-    uint32_t reserved[2];
+    uint32_t min_fill;    /* while the device is busy a GPU batch goes once it holds this many packets and a slot is
+                             free (0 = 128, one upstream batch, or max_pkts / 4 if that is less); it always goes when the
+                             device is idle, after 40 us, or full */
+    uint32_t reserved;
 } bnk_queue_cfg;
 int bnk_queue_create(bnk_ctx *ctx, const bnk_queue_cfg *cfg, bnk_queue **out);
 int bnk_queue_destroy(bnk_queue *q);
