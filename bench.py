@@ -532,7 +532,9 @@ def run_ours(args, rank, world, local_rank):
         co = {name: ctx.probe_coissue(kind, k) for name, kind, k in
               [("rounds_alone", 0, 0), ("mad_wide_x8", 1, 8), ("mad_wide_x16", 1, 16), ("fp64_fma_x16", 2, 16),
                ("fp64_fma_x32", 2, 32), ("mad_lo_x16", 3, 16), ("mad_lo_x32", 3, 32), ("fp32_fma_x16", 4, 16),
-               ("fp32_fma_x32", 4, 32), ("mul_hi_x8", 5, 8), ("mul_hi_x16", 5, 16)]}
+               ("fp32_fma_x32", 4, 32), ("mul_hi_x8", 5, 8), ("mul_hi_x16", 5, 16),
+               # two cipher blocks per thread at half the warps (what doubling the state registers would allow)
+               ("two_blocks_per_thread_half_the_warps", 6, 0)]}
         # per 64-byte block: 10 double rounds + 85 wide multiply-adds (4 Poly1305 blocks) at their interleaved cost,
         # + the ~100 ALU-pipe instructions of Poly1305's carries and the data exclusive-ors at 2 cycles each
         wide_each = (co["mad_wide_x8"] - co["rounds_alone"]) / 8.0

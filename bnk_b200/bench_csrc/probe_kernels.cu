@@ -213,6 +213,63 @@ __global__ void __launch_bounds__(128, 4) coissue_probe_kernel(uint32_t *sink, u
     if (acc == 0x12345678u) sink[blockIdx.x * blockDim.x + threadIdx.x] = acc;
 }
 
+// Two ChaCha20 states per thread (twice the independent quarter rounds in flight per warp) at HALF the warps: what a
+// seal/open kernel with two cipher blocks per thread would run at (its registers allow 2 CTAs per SM).  The CTAs ask
+// for enough dynamic shared memory that only two fit an SM.
+__global__ void __launch_bounds__(128, 2) coissue_two_blocks_kernel(uint32_t *sink, uint32_t seed) {
+    uint32_t x[16], z[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        x[i] = seed * (i + 1) + threadIdx.x;
+        z[i] = seed * (i + 33) + threadIdx.x * 3u;
+    }
+#pragma unroll 1
+    for (int it = 0; it < kCoIters; it++) {
+        probe_qr(x[0], x[4], x[8], x[12]); probe_qr(z[0], z[4], z[8], z[12]);
+        probe_qr(x[1], x[5], x[9], x[13]); probe_qr(z[1], z[5], z[9], z[13]);
+        probe_qr(x[2], x[6], x[10], x[14]); probe_qr(z[2], z[6], z[10], z[14]);
+        probe_qr(x[3], x[7], x[11], x[15]); probe_qr(z[3], z[7], z[11], z[15]);
+        probe_qr(x[0], x[5], x[10], x[15]); probe_qr(z[0], z[5], z[10], z[15]);
+        probe_qr(x[1], x[6], x[11], x[12]); probe_qr(z[1], z[6], z[11], z[12]);
+        probe_qr(x[2], x[7], x[8], x[13]); probe_qr(z[2], z[7], z[8], z[13]);
+        probe_qr(x[3], x[4], x[9], x[14]); probe_qr(z[3], z[4], z[9], z[14]);
+    }
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) acc ^= x[i] ^ z[i];
+    if (acc == 0x12345678u) sink[blockIdx.x * blockDim.x + threadIdx.x] = acc;
+}
+cudaError_t run_coissue_two_blocks(bnk_ctx *ctx, double sm_hz, double *clk) {
+    const int waves = 4, ctas = ctx->sm_count * 2 * waves; // 2 CTAs of 4 warps per SM: 2 warps per scheduler
+    const int smem = 100 << 10;
+    cudaError_t e = cudaFuncSetAttribute(coissue_two_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    uint32_t *sink = nullptr;
+    if ((e = cudaMalloc(&sink, (size_t)ctas * 128 * sizeof(uint32_t))) != cudaSuccess) return e;
+    cudaEvent_t t0, t1;
+    cudaEventCreate(&t0);
+    cudaEventCreate(&t1);
+    cudaStream_t s = ctx->admin_stream;
+    float best = 1e30f;
+    for (int rep = 0; rep < 4; rep++) {
+        cudaEventRecord(t0, s);
+        coissue_two_blocks_kernel<<<ctas, 128, smem, s>>>(sink, 17u + rep);
+        cudaEventRecord(t1, s);
+        ctx->launches += 1;
+        if ((e = cudaEventSynchronize(t1)) != cudaSuccess) break;
+        float ms = 0;
+        cudaEventElapsedTime(&ms, t0, t1);
+        if (rep >= 1 && ms < best) best = ms;
+    }
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+    cudaFree(sink);
+    if (e != cudaSuccess) return e;
+    // per double round of ONE cipher block, per scheduler: 2 warps x 2 blocks share a scheduler
+    *clk = best * 1e-3 * sm_hz / kCoIters / waves / 4.0;
+    return cudaSuccess;
+}
+
 template <int KIND, int K>
 cudaError_t run_coissue(bnk_ctx *ctx, double sm_hz, double *clk) {
     const int waves = 4, ctas = ctx->sm_count * 4 * waves; // 4 CTAs of 4 warps per SM: 4 warps per scheduler
@@ -260,6 +317,7 @@ cudaError_t probe_coissue(bnk_ctx *ctx, int kind, int k, double *clk) {
     case 432: return run_coissue<4, 32>(ctx, hz, clk);
     case 508: return run_coissue<5, 8>(ctx, hz, clk);
     case 516: return run_coissue<5, 16>(ctx, hz, clk);
+    case 600: return run_coissue_two_blocks(ctx, hz, clk);
     default: return cudaErrorInvalidValue;
     }
 }

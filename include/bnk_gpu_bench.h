@@ -30,7 +30,8 @@ int bnk_probe_int_throughput(bnk_ctx *ctx, int mix, double *tera_ops_per_s);
  * (4 warps per scheduler) with k extra operations of one kind per double round interleaved from independent chains,
  * and returns scheduler cycles per double round per warp.  kind: 0 none (k = 0), 1 = 32x32+64 multiply-add
  * (k = 8, 16), 2 = FP64 fused multiply-add (16, 32), 3 = 32-bit multiply-add (16, 32), 4 = FP32 fused multiply-add
- * (16, 32), 5 = high half of a 32x32 product (8, 16).  Other (kind, k) pairs are BNK_ECUDA / invalid value. */
+ * (16, 32), 5 = high half of a 32x32 product (8, 16); 6 (k = 0) = no extra work but TWO cipher blocks per thread at
+ * half the warps (2 per scheduler), per double round of one block.  Other (kind, k) pairs are BNK_ECUDA / invalid value. */
 int bnk_probe_coissue(bnk_ctx *ctx, int kind, int k, double *cycles_per_double_round);
 /* Fills the device mirror of the batch's ring with SplitMix64 output (seeded, position-dependent). */
 int bnk_batch_fill_random(bnk_batch *b, uint64_t seed);
