@@ -3,6 +3,8 @@ import ctypes
 import os
 import re
 
+import pytest
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -61,3 +63,30 @@ def test_no_cpu_fallback_in_product_path():
             if fn.endswith((".py", ".cu", ".cuh", ".cpp", ".hpp", ".h")):
                 src = open(os.path.join(dirpath, fn), errors="replace").read()
                 assert "oracle" not in src.lower(), os.path.join(dirpath, fn)
+
+
+def test_header_compiles_as_c_and_the_shim_calls_link(tmp_path):
+    """cgo hands include/bnk_gpu.h to a C compiler (not C++): the header must be plain C, and the calls the Go shim
+    of INTEGRATION.md makes (tests/c/cgo_shim_calls.c: the same calls with the same argument types) must compile
+    without a warning and link against libbnkgpu.so.  Nothing is run: the calls need a GPU."""
+    import shutil
+    import subprocess
+
+    from bnk_b200 import _build
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    inc = os.path.join(root, "include")
+    strict = ["-Wall", "-Wextra", "-Werror", "-pedantic"]
+    for std, header in (("c99", "bnk_gpu.h"), ("c11", "bnk_gpu.h"), ("c99", "bnk_gpu_bench.h")):
+        res = subprocess.run([gcc, f"-std={std}", *strict, "-I", inc, "-fsyntax-only", "-x", "c", os.path.join(inc, header)],
+                             capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
+    lib = _build.build()
+    out = str(tmp_path / "libshim.so")
+    res = subprocess.run([gcc, "-std=c11", *strict, "-I", inc, "-shared", "-fPIC", os.path.join(root, "tests", "c", "cgo_shim_calls.c"),
+                          "-o", out, "-L", os.path.dirname(lib), "-lbnkgpu", "-Wl,--no-undefined"],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
