@@ -115,7 +115,7 @@ class Latch {
     }
     void Wait() {
         std::unique_lock<std::mutex> g(mu_);
-        cv_.wait(g, [this] { return left_ == 0; });
+        cv_.wait(g, [this] { return left_ <= 0; });
     }
 
   private:
@@ -310,19 +310,29 @@ static int run_jobs(bnk_mgpu *m, const std::vector<std::vector<uint32_t>> &lists
     int busy = 0;
     for (uint32_t g = 0; g < ng; g++) busy += !lists[g].empty();
     if (busy == 0) return BNK_SUCCESS;
-    Latch latch(busy);
+    // The calling thread takes the last busy GPU itself: with one busy GPU (a small batch, a single-GPU box)
+    // nothing is handed to another thread at all, and otherwise the caller works instead of sleeping.
+    uint32_t own = 0;
+    for (uint32_t g = 0; g < ng; g++)
+        if (!lists[g].empty()) own = g;
+    Latch latch(busy - 1);
     std::vector<int> rcs(ng, BNK_SUCCESS);
+    auto job = [&](uint32_t g) {
+        const std::vector<uint32_t> &l = lists[g];
+        const uint32_t cap = m->cfg.max_pkts_per_gpu;
+        for (size_t first = 0; first < l.size() && rcs[g] == BNK_SUCCESS; first += cap)
+            rcs[g] = round(g, l.data() + first, (uint32_t)std::min<size_t>(cap, l.size() - first));
+    };
     for (uint32_t g = 0; g < ng; g++) {
         if (lists[g].empty()) continue;
         m->pkts_per_gpu[g] += lists[g].size();
+        if (g == own) continue;
         m->worker[g]->Post([&, g] {
-            const std::vector<uint32_t> &l = lists[g];
-            const uint32_t cap = m->cfg.max_pkts_per_gpu;
-            for (size_t first = 0; first < l.size() && rcs[g] == BNK_SUCCESS; first += cap)
-                rcs[g] = round(g, l.data() + first, (uint32_t)std::min<size_t>(cap, l.size() - first));
+            job(g);
             latch.Done();
         });
     }
+    job(own);
     latch.Wait();
     for (uint32_t g = 0; g < ng; g++)
         if (rcs[g] != BNK_SUCCESS) return mfail(m, rcs[g], bnk_last_error_string(m->ctx[g]));

@@ -441,7 +441,9 @@ int bnk_mgpu_acl_set(bnk_mgpu *m, int enforce, const bnk_acl_tuple *tuples, size
 /* Seals packets pkts[i][0 .. len[i]) of peer peer[i]; the message goes to out[i] (room for len + 48 bytes),
  * its length to out_len[i], the nonce used to counter[i] (may be NULL), the outcome to status[i].  flags as for
  * bnk_seal_submit; counters are always taken from the peers' send counters.  A peer that is not set yields
- * BNK_PKT_NO_KEYPAIR.  Blocks until every GPU has finished. */
+ * BNK_PKT_NO_KEYPAIR.  Blocks until every GPU has finished.  One GPU's share is worked on by the calling thread
+ * itself (with a single busy GPU nothing is handed to another thread); like the other calls of the library this
+ * leaves the thread's current CUDA device set to a GPU of the dispatcher. */
 int bnk_mgpu_seal(bnk_mgpu *m, const uint8_t *const *pkts, const uint32_t *len, const uint32_t *peer, uint32_t n,
                   uint32_t flags, int64_t now_unix_ns, uint8_t *const *out, uint32_t *out_len, uint64_t *counter,
                   uint8_t *status);
