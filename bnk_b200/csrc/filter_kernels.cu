@@ -126,6 +126,15 @@ __device__ __forceinline__ bool rules_allow(const FilterTables &ft, const Parsed
     return false;
 }
 
+// One atomic per group of lanes that add to the same counter at the same point of the code, instead of one per
+// lane: a batch of new flows otherwise sends a few hundred thousand atomics to two addresses (300,000 fresh flows
+// took 0.7 ms that way).
+template <typename T>
+__device__ __forceinline__ void add_one_aggregated(T *counter) {
+    const unsigned same = __match_any_sync(__activemask(), (unsigned long long)(uintptr_t)counter);
+    if ((threadIdx.x & 31u) == (unsigned)(__ffs(same) - 1)) atomicAdd(counter, (T)__popc(same));
+}
+
 // ---- NoteOutbound, filter.go:189-209 ----------------------------------------------------
 __global__ void filter_note_kernel(FilterTables ft, const uint8_t *ring, const uint32_t *off,
                                    const uint32_t *len, uint32_t n, uint64_t ring_bytes, long long now) {
@@ -154,9 +163,9 @@ __global__ void filter_note_kernel(FilterTables ft, const uint8_t *ring, const u
     for (uint32_t probe = 0; probe < ft.flow_capacity; probe++) {
         const unsigned long long old = atomicCAS(&keys[h], FLOW_EMPTY, key);
         if (old == FLOW_EMPTY || old == key) {
-            if (old == FLOW_EMPTY) atomicAdd(&ctl->rep.used[cls], 1u);
+            if (old == FLOW_EMPTY) add_one_aggregated(&ctl->rep.used[cls]);
             const long long prev = (long long)atomicExch((unsigned long long *)&exps[h], (unsigned long long)exp);
-            if (flow_absent(prev)) atomicAdd(&ctl->live, 1ull);
+            if (flow_absent(prev)) add_one_aggregated(&ctl->live);
             if (prev == FLOW_DEAD) atomicSub(&ctl->rep.dead[cls], 1u); // a deleted entry is back
             return;
         }
