@@ -361,7 +361,7 @@ __global__ void __launch_bounds__(256) tally_kernel(const uint8_t *status, const
     unsigned long long bytes = 0;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const uint8_t st = status[i];
-        atomicAdd(&cnt[st & 15u], 1u);
+        add_one_aggregated(&cnt[st & 15u]); // nearly every lane hits the same bin
         if (st == BNK_PKT_OK) bytes += out_len[i];
     }
     for (int o = 16; o > 0; o >>= 1) bytes += __shfl_down_sync(0xffffffffu, bytes, o);
