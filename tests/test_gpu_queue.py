@@ -268,3 +268,78 @@ def test_queue_spans_without_host_copies(gpu_lib, oracle):
         openq.close()
     finally:
         c.close()
+
+
+def test_queues_carry_the_filter_and_the_index_lookup(gpu_lib, oracle):
+    """The two queues as the device's two directions: the seal queue records outbound flows (BNK_F_NOTE_OUTBOUND),
+    the open queue finds the keypair from the receiver index in the header, runs the replay window and the inbound
+    filter.  With default-deny rules only replies to what went out come back in; the verdicts are the checker's
+    (filter.go:121-147, :189-209), whatever GPU batches the callers' packets happened to share."""
+    from tests import reference_cases as RC
+    from bnk_b200 import Context
+    from bnk_b200.device import (F_CHECK_INBOUND, F_DEMUX_INDEX, F_NOTE_OUTBOUND, F_REPLAY, PKT_FILTER_DENY, PKT_OK,
+                                 Queue)
+
+    n_peers = 6
+    rng = np.random.default_rng(11)
+    keys = rng.integers(0, 256, (n_peers, 32), dtype=np.uint8)
+    c = Context(max_keypairs=n_peers, mtu=1420, flow_capacity=1 << 12)
+    try:
+        # loopback: this context is both ends, so a peer's local and remote index are the same number
+        c.set_keypairs(0, keys, keys, (0x600 + np.arange(n_peers)).astype(np.uint32))
+        for p in range(n_peers):
+            c.index_set(0x600 + p, p)
+        c.acl_set(True, np.zeros(0, dtype=np.uint8))  # enforce, no allowances: replies only
+        out_q = Queue(c, False, F_NOTE_OUTBOUND, max_pkts=256, depth=2)
+        plain_q = Queue(c, False, 0, max_pkts=256, depth=2)  # stands for the far ends sealing what they send us
+        in_q = Queue(c, True, F_DEMUX_INDEX | F_REPLAY | F_CHECK_INBOUND, max_pkts=256, depth=2)
+        f = oracle.Filter()
+        f.set_rules([])
+        peer_ip = [RC.ip(f"100.64.3.{10 + p}") for p in range(n_peers)]
+        errors = []
+
+        def worker(t):
+            try:
+                r = np.random.default_rng(400 + t)
+                slots = np.full(40, t, np.uint32)
+                sent = [RC.udp(RC.SELF, peer_ip[t], 30000 + 50 * t + k, 53) for k in range(40)]
+                while (tk := out_q.submit(sent, slots, now_ns=RC.T0)) is None:
+                    time.sleep(0)
+                _, st, _, _ = out_q.wait(tk)
+                assert (st == PKT_OK).all()
+                # what comes back: replies to every second flow, and as many packets nobody asked for
+                back = [RC.udp(peer_ip[t], RC.SELF, 53, 30000 + 50 * t + k) for k in range(0, 40, 2)]
+                back += [RC.udp(peer_ip[t], RC.SELF, 53, 45000 + int(r.integers(0, 1000))) for _ in range(20)]
+                while (tk := plain_q.submit(back, slots[:40], now_ns=RC.T0)) is None:
+                    time.sleep(0)
+                msgs, st, _, _ = plain_q.wait(tk)
+                assert (st == PKT_OK).all()
+                while (tk := in_q.submit(msgs, None, now_ns=RC.T0 + RC.SEC)) is None:
+                    time.sleep(0)
+                pts, st, _, slot_found = in_q.wait(tk)
+                assert (slot_found == t).all()
+                return_value.append((t, sent, back, pts, st))
+            except Exception as e:  # noqa: BLE001
+                errors.append((t, repr(e)))
+
+        return_value = []
+        th = [threading.Thread(target=worker, args=(t,)) for t in range(n_peers)]
+        for x in th:
+            x.start()
+        for x in th:
+            x.join()
+        assert errors == []
+        # the checker, sequentially: all outbound first (one clock value), then each inbound packet
+        for _, sent, _, _, _ in return_value:
+            for pkt in sent:
+                f.note_outbound(pkt, RC.T0)
+        for t, _, back, pts, st in return_value:
+            for k, pkt in enumerate(back):
+                want = f.check_inbound(pkt, RC.T0 + RC.SEC)
+                assert st[k] == (PKT_OK if want else PKT_FILTER_DENY), (t, k, st[k], want)
+                assert (pts[k][:len(pkt)] == pkt) if want else (pts[k] == b"")
+            assert (st[:20] == PKT_OK).all() and (st[20:] == PKT_FILTER_DENY).all()
+        for q in (out_q, plain_q, in_q):
+            q.close()
+    finally:
+        c.close()
