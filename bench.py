@@ -39,6 +39,7 @@ HBM_BYTES_PER_PACKET = 2 * SIZE + 32          # seal: read 1420 + write 1452; op
 INT_OPS_PER_PACKET = 24 * 992 + 90 * 40
 E2E_BATCHES = 8
 DEVICE_BATCHES = 2  # device-resident legs: batches in flight, each with half of the step's packets
+IMIX_BATCHES = 3    # the mixed-size leg (--device-batches overrides both)
 REGIONS = 5  # timed regions of K steps each; the median one is reported
 # dram__bytes_read.sum + dram__bytes_write.sum of one seal launch, from the ncu captures summarised in profiles/:
 # (packets of the captured launch, bytes).  The figure is a LOWER bound of what a launch moves: whatever part of
@@ -553,25 +554,31 @@ def run_ours(args, rank, world, local_rank):
     imix = None
     if not args.no_imix:
         g = gen.SplitMix64(gen.seed_for(2) + 7919 * rank)
+        # Three batches in flight here (the sizes differ by at most one packet, the peers of the batches are
+        # disjoint): with packets this short the grouping, counter and replay kernels are a third of a batch's own
+        # time, and a third batch gives them more seal/open work of other batches to run beside.
+        nbi = IMIX_BATCHES if args.device_batches == DEVICE_BATCHES else nbd
+        per_i = [n // nbi + (1 if j < n % nbi else 0) for j in range(nbi)]
+        peers_i = max(1, peers // nbi)
         ibs, size_sum = [], 0.0
-        for j in range(nbd):
-            sizes = gen.imix_sizes(g, per_d)
+        for j in range(nbi):
+            sizes = gen.imix_sizes(g, per_i[j])
             size_sum += float(sizes.sum())
             slots_sz = ((sizes.astype(np.uint64) + np.uint64(48 + 15)) // np.uint64(16)) * np.uint64(16)
             offs = np.concatenate([[0], np.cumsum(slots_sz)[:-1]]).astype(np.uint64)
-            ib = ctx.batch(per_d, int(offs[-1] + slots_sz[-1]))
+            ib = ctx.batch(per_i[j], int(offs[-1] + slots_sz[-1]))
             ib.off[:] = offs.astype(np.uint32)
             ib.len[:] = sizes
-            ib.slot[:] = (j * peers_d + np.arange(per_d, dtype=np.uint64) % np.uint64(peers_d)).astype(np.uint32)
-            ib.upload(per_d)
+            ib.slot[:] = (j * peers_i + np.arange(per_i[j], dtype=np.uint64) % np.uint64(peers_i)).astype(np.uint32)
+            ib.upload(per_i[j])
             ib.fill_random(plan.payload_seed + 5 + j)
             ibs.append(ib)
 
         def step_imix():
-            for ib in ibs:
-                ib.seal(per_d, SEAL | F_SORT_BY_LENGTH, wait=False)
-            for ib in ibs:
-                ib.open(per_d, OPEN | F_SORT_BY_LENGTH, wait=False)
+            for ib, m_ in zip(ibs, per_i):
+                ib.seal(m_, SEAL | F_SORT_BY_LENGTH, wait=False)
+            for ib, m_ in zip(ibs, per_i):
+                ib.open(m_, OPEN | F_SORT_BY_LENGTH, wait=False)
 
         for _ in range(W):
             step_imix()
@@ -587,18 +594,18 @@ def run_ours(args, rank, world, local_rank):
         for ib in ibs:
             ib.wait()
         # one more pass over one batch alone with events around its two AEAD launches
-        ibs[0].seal(per_d, SEAL | F_SORT_BY_LENGTH | F_TIMED)
+        ibs[0].seal(per_i[0], SEAL | F_SORT_BY_LENGTH | F_TIMED)
         imix_seal_ms = ibs[0].last_aead_ms()
-        ibs[0].open(per_d, OPEN | F_SORT_BY_LENGTH | F_TIMED)
+        ibs[0].open(per_i[0], OPEN | F_SORT_BY_LENGTH | F_TIMED)
         imix_open_ms = ibs[0].last_aead_ms()
         imix_ok = True
-        for ib in ibs:
-            ib.download(per_d)
-            imix_ok = imix_ok and bool((ib.status[:per_d] == 0).all())
+        for ib, m_ in zip(ibs, per_i):
+            ib.download(m_)
+            imix_ok = imix_ok and bool((ib.status[:m_] == 0).all())
         imix = {"mpps": world * 2.0 * n * K / (ims * 1e-3) / 1e6, "unit": "Mpps",
                 "packets_counted": "packets sealed + packets opened", "sizes": "64/576/1420 B at 7:4:1",
                 "gbps": world * 2.0 * size_sum * 8 * K / (ims * 1e-3) / 1e9, "verified": imix_ok,
-                "ms_per_step": ims / K, "batches_in_flight": nbd, "packets_per_launch": per_d,
+                "ms_per_step": ims / K, "batches_in_flight": nbi, "packets_per_launch": per_i[0],
                 "seal_kernel_ms": imix_seal_ms, "open_kernel_ms": imix_open_ms}
         for ib in ibs:
             ib.close()
