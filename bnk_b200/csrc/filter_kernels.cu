@@ -100,10 +100,12 @@ __device__ __forceinline__ unsigned long long flow_key(uint32_t remote, uint16_t
 // measured: 10 % slower on configuration 3, where nearly half the packets match at one of the first lengths.)
 __device__ __forceinline__ bool rules_allow(const FilterTables &ft, const Parsed &p) {
     if (ft.rule_slots == 0) return false;
+    // longest prefixes first: acl.Compile emits /32s (acl.go:98), so a packet that some rule admits is most often
+    // admitted at the first probe; any match allows, the order changes no verdict
     uint64_t lens = ft.len_mask;
     while (lens) {
-        const uint32_t len = __ffsll((long long)lens) - 1;
-        lens &= lens - 1;
+        const uint32_t len = 63u - (uint32_t)__clzll((long long)lens);
+        lens &= ~(1ull << len);
         const uint64_t key = rule_key(len, p.src);
         uint32_t h = (uint32_t)mix64(key) & (ft.rule_slots - 1);
         for (uint32_t probe = 0; probe < ft.rule_slots; probe++) {
