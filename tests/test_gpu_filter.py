@@ -236,3 +236,74 @@ def test_flow_table_export_and_import(gpu_lib, oracle):
     finally:
         a.close()
         b.close()
+
+
+@pytest.mark.parametrize("shape", ["few_lengths_listed", "many_keys_per_length", "everything_listed", "default_route"])
+def test_rule_tables_with_many_prefix_lengths(gpu_lib, oracle, shape):
+    """Rule tables with several prefix lengths in very different numbers: every verdict equals the checker's rule
+    walk (acl.go:149-172: any prefix of any length that contains the source, filter.go:131-135).  Shapes: a handful
+    of hand-written prefixes beside thousands of /32s; hundreds of keys in each of four lengths; only a few prefixes;
+    a /0 rule.  (The index probes one hash table per prefix length in use; a variant that kept the rare lengths in a
+    short list in shared memory passed the same test and was no faster.)"""
+    from bnk_b200 import Context
+    from bnk_b200.filter import Filter, CompiledRule, PortRange
+
+    rng = np.random.default_rng({"few_lengths_listed": 1, "many_keys_per_length": 2, "everything_listed": 3,
+                                 "default_route": 4}[shape])
+    base = RC.ip("100.64.0.0")
+
+    def host(k):
+        return base + int(k)
+
+    def pfx(addr, bits):
+        import ipaddress
+        return f"{ipaddress.ip_address(addr & ((0xffffffff << (32 - bits)) & 0xffffffff) if bits else 0)}/{bits}"
+
+    rules = []
+    if shape in ("few_lengths_listed", "default_route"):
+        for k in rng.integers(1, 1 << 20, 3000):
+            rules.append(CompiledRule(srcs=[pfx(host(k), 32)], proto=str(rng.choice(["tcp", "udp"])),
+                                      ports=[PortRange(1, int(rng.integers(1, 40000)))]))
+        for bits in (8, 12, 16, 20, 24, 28, 30):
+            for _ in range(int(rng.integers(1, 6))):
+                rules.append(CompiledRule(srcs=[pfx(host(rng.integers(1, 1 << 20)), bits)], proto="udp",
+                                          ports=[PortRange(50, 60)]))
+        if shape == "default_route":
+            rules.append(CompiledRule(srcs=["0.0.0.0/0"], proto="icmp", ports=[]))
+    elif shape == "many_keys_per_length":
+        for bits in (24, 26, 28, 32):
+            for k in rng.integers(1, 1 << 20, 400):
+                rules.append(CompiledRule(srcs=[pfx(host(k), bits)], proto="tcp", ports=[PortRange(1000, 2000)]))
+    else:
+        for bits in (10, 16, 24, 32):
+            for _ in range(5):
+                rules.append(CompiledRule(srcs=[pfx(host(rng.integers(1, 1 << 20)), bits)], proto="tcp",
+                                          ports=[PortRange(22, 22), PortRange(80, 90)]))
+    c = Context(max_keypairs=4, flow_capacity=1 << 10)
+    try:
+        f = Filter(c, batch_pkts=4096)
+        f.set_rules(rules)
+        chk = oracle.Filter()
+        chk.set_rules([([(RC.ip(s.split("/")[0]), int(s.split("/")[1])) for s in r.srcs], r.proto,
+                        [(p.first, p.last) for p in r.ports]) for r in rules])
+        # sources: half of them taken from the rules' own prefixes (inside and just outside), half anywhere
+        pool = [RC.ip(s.split("/")[0]) for r in rules for s in r.srcs]
+        pkts = []
+        for k in range(4096):
+            src = int(pool[int(rng.integers(0, len(pool)))]) + int(rng.integers(0, 3)) if k % 2 else host(rng.integers(1, 1 << 20))
+            src &= 0xffffffff
+            kind = int(rng.integers(0, 3))
+            port = int(rng.choice([22, 55, 85, 1500, 30000, int(rng.integers(1, 65535))]))
+            if kind == 0:
+                pkts.append(RC.tcp(src, RC.SELF, 40000, port))
+            elif kind == 1:
+                pkts.append(RC.udp(src, RC.SELF, 40000, port))
+            else:
+                pkts.append(RC.icmp_echo(src, RC.SELF, False))
+        got = f.check_inbound_batch(pkts, RC.T0)
+        want = [chk.check_inbound(p, RC.T0) for p in pkts]
+        assert got == want
+        assert 50 < sum(want) < 4000
+        f._batch.close()
+    finally:
+        c.close()
