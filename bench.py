@@ -855,8 +855,8 @@ def run_ours(args, rank, world, local_rank):
                  "gbps_8_threads_128_packets_queue_spans_4_outstanding": threaded(8, 128, max(20, args.small_rounds), 4, 2) if world == 1 else None,
                  "gbps_all_cores_128_packets_queue_spans_4_outstanding": threaded(host_threads(), 128, max(20, args.small_rounds), 4, 2) if world == 1 else None,
                  "note": "host wall clock per submit+wait; seal = group+counters launch, seal launch; open = open "
-                         "launch, group+replay launch; 128 x 1420 B goes through the copy engines, 16 x 1420 B (under "
-                         "128 KiB) runs on the pinned host arrays without copies; gbps_16_batches_in_flight: sixteen "
+                         "launch, group+replay launch; batches of up to 256 packets and 384 KiB run on the pinned host arrays "
+                         "without copies (BNK_HOST_DIRECT_BYTES), larger ones go through the copy engines; gbps_16_batches_in_flight: sixteen "
                          "128-packet batches submitted round-robin by this one Python thread, seal then open; "
                          "gbps_8_threads_*: eight C++ host threads, two batches in flight each, same context "
                          "(bnk_b200/host/apps/mt_stress.cpp), median of five runs; copy_only_ceiling_*: eight threads and streams "

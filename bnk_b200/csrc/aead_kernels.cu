@@ -540,6 +540,7 @@ template <bool OPEN>
 __global__ void __launch_bounds__(128) aead_wpp_kernel(const AeadArgs a) {
     let_next_kernel_start();    // open side: the grouping + replay launch behind may take its place already
     wait_for_kernel_in_front(); // seal side: the counters come from the grouping launch in front
+    __shared__ uint4 stage_all[4][128]; // per warp: the 16-byte pieces of one round (up to 30 chunks of 64 bytes)
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (idx >= a.n) return; // a whole warp at a time
@@ -576,13 +577,33 @@ __global__ void __launch_bounds__(128) aead_wpp_kernel(const AeadArgs a) {
         const uint32_t chunk = is_tail ? full_total : done + (lane + F - 31u);
         const uint32_t base = chunk * 64u;
 
+        // The round's F chunks are 64 F consecutive bytes.  The warp fetches them as 16-byte pieces in piece order
+        // (lane l takes pieces l, 32 + l, ...: every load instruction covers 512 consecutive bytes) and hands each
+        // chunk lane its four pieces through shared memory.  Fetched chunk by chunk instead, a load instruction
+        // touches thirty-two separate 16-byte pieces 64 bytes apart: the same bytes from device memory, but when the
+        // ring is the caller's pinned host memory (small batches run there, no copies) every piece is a PCIe read
+        // of its own, and few of those can be in flight.
+        const uint32_t round_base = done * 64u;
+        uint4 *const stage = stage_all[threadIdx.x >> 5];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const uint32_t q = 32u * c + lane;
+            if (q < 4u * F) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (round_base + 16u * q < in_len) v = *reinterpret_cast<const uint4 *>(data + round_base + 16u * q);
+                stage[q] = v;
+            }
+        }
+        __syncwarp();
         uint32_t d[16];
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (works && base + 16u * c < in_len) v = *reinterpret_cast<const uint4 *>(data + base + 16u * c);
+            if (is_chunk) v = stage[4u * (chunk - done) + c];
+            else if (is_tail && base + 16u * c < in_len) v = *reinterpret_cast<const uint4 *>(data + base + 16u * c);
             d[4 * c + 0] = v.x; d[4 * c + 1] = v.y; d[4 * c + 2] = v.z; d[4 * c + 3] = v.w;
         }
+        __syncwarp(); // the pieces are read: the stage may take the output
         uint32_t x[16];
         chacha20_block(x, key, works ? chunk + 1u : 0u, dsc.n_lo, dsc.n_hi); // idle lanes and the carry lane: block 0
         if (first) {
@@ -606,7 +627,9 @@ __global__ void __launch_bounds__(128) aead_wpp_kernel(const AeadArgs a) {
                     o[w] = keep_bytes(in_w ^ x[4 * c + w], body_left - k);
                     ct[4 * c + w] = OPEN ? in_w : o[w];
                 }
-                if (16 * c + 16 <= body_left) {
+                if (is_chunk) { // a whole chunk lies inside the body: out through the stage, in piece order
+                    stage[4u * (chunk - done) + c] = make_uint4(o[0], o[1], o[2], o[3]);
+                } else if (16 * c + 16 <= body_left) {
                     *reinterpret_cast<uint4 *>(data + base + 16u * c) = make_uint4(o[0], o[1], o[2], o[3]);
                 } else if (16 * c < body_left) {
                     uint8_t *dst = data + base + 16u * c;
@@ -617,6 +640,13 @@ __global__ void __launch_bounds__(128) aead_wpp_kernel(const AeadArgs a) {
                 }
             }
         }
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const uint32_t q = 32u * c + lane;
+            if (q < 4u * F) *reinterpret_cast<uint4 *>(data + round_base + 16u * q) = stage[q];
+        }
+        __syncwarp(); // before the next round writes the stage
         // Horner over the lane's own four blocks (chunk lanes), or the state carried in (carry lane)
         P26 V = p26_zero();
         if (is_chunk) {

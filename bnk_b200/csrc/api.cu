@@ -86,11 +86,14 @@ cudaError_t tally_if_asked(bnk_batch *b, uint32_t npkts, uint32_t flags, cudaStr
 // a few hundred KB the four copies and the engine hand-overs either side of the kernels cost more than the
 // kernels themselves.  While a HostAlias lives, the launchers see the host arrays where the device copies
 // would be; the device copies fall behind (dev_stale) until the next full upload.
-// Reads through the bus come at roughly 10 GB/s from a kernel this small (about 20 us for 128 full-size
-// packets), so the mode pays up to a ring extent of about a hundred KB: measured 23 against 35 us for one
-// packet and 30 against 42 us for 64, seal submit to wait; level at 128.  Serving only the descriptors this
-// way and the ring by copy was measured too and gained nothing.
-constexpr uint32_t kHostDirectMaxPkts = 1024;
+// The seal/open kernel of such a batch (one warp per packet) moves its data in 512-byte stretches per load and store
+// instruction; with 16-byte pieces 64 bytes apart every piece was a bus transaction of its own, reads came at
+// ~10 GB/s and the mode stopped paying at a hundred KB and did not scale over threads.  Now, measured on 128 full-size
+// packets: 35 us against 38 per seal, and eight / sixteen host threads with batches of their own move 140 / 144
+// Gbit/s against 118 / 117 through the copy engines (256 packets: 154 / 170 against 155 / 137).  Beyond 256 packets
+// the copy engines win again (512: 184 against 60), hence the two limits.  Serving only the descriptors this way and
+// the ring by copy was measured too and gained nothing.
+constexpr uint32_t kHostDirectMaxPkts = 256;
 bool host_direct(const bnk_batch *b, uint32_t npkts, uint32_t flags, uint64_t ext) {
     return b->ctx->host_direct_bytes != 0 && npkts != 0 && npkts <= kHostDirectMaxPkts &&
            !(flags & (BNK_F_NO_H2D | BNK_F_NO_D2H | BNK_F_USE_OUT_LEN)) && ext <= b->ctx->host_direct_bytes;
@@ -220,7 +223,7 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     ctx->aead_mode = 0;
     if (const char *m = getenv("BNK_AEAD_KERNEL")) // tuning and test aid: tpp | wpp
         ctx->aead_mode = !strcmp(m, "tpp") ? 1 : (!strcmp(m, "wpp") ? 2 : 0);
-    ctx->host_direct_bytes = 128u << 10;
+    ctx->host_direct_bytes = 384u << 10; // 256 slots of 1456 bytes and their headroom
     if (const char *m = getenv("BNK_HOST_DIRECT_BYTES")) // largest ring extent served without copies; 0 = never
         ctx->host_direct_bytes = strtoull(m, nullptr, 0);
     if (!prop.unifiedAddressing || !prop.canMapHostMemory) ctx->host_direct_bytes = 0; // pinned memory must have one address

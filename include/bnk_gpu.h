@@ -24,7 +24,7 @@
  *     both BNK_F_NO_H2D and BNK_F_NO_D2H only queue kernels on the batch's stream
  *     and may be issued back to back.
  *   - Between a submit and its bnk_wait the batch's host arrays belong to the
- *     library.  Small batches (up to 1024 packets and a ring extent of 128 KiB,
+ *     library.  Small batches (up to 256 packets and a ring extent of 384 KiB,
  *     environment BNK_HOST_DIRECT_BYTES, 0 = never) are not copied: the kernels
  *     read and write the pinned arrays in place.  The results are the same bytes.
  *   - Send counters and replay windows are per keypair and ordered: batches that

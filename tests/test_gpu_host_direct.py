@@ -34,7 +34,7 @@ def _load(b, rng, n, n_peers):
     return off, sizes
 
 
-@pytest.mark.parametrize("n", [1, 7, 64, 300])
+@pytest.mark.parametrize("n", [1, 7, 64, 200, 256, 300])  # 300: beyond the mode's packet limit, copied both times
 def test_same_bytes_with_and_without_copies(gpu_lib, oracle, n):
     from bnk_b200.device import F_ASSIGN_COUNTERS, F_REPLAY
 
