@@ -94,9 +94,28 @@ cudaError_t tally_if_asked(bnk_batch *b, uint32_t npkts, uint32_t flags, cudaStr
 // the copy engines win again (512: 184 against 60), hence the two limits.  Serving only the descriptors this way and
 // the ring by copy was measured too and gained nothing.
 constexpr uint32_t kHostDirectMaxPkts = 256;
-bool host_direct(const bnk_batch *b, uint32_t npkts, uint32_t flags, uint64_t ext) {
-    return b->ctx->host_direct_bytes != 0 && npkts != 0 && npkts <= kHostDirectMaxPkts &&
-           !(flags & (BNK_F_NO_H2D | BNK_F_NO_D2H | BNK_F_USE_OUT_LEN)) && ext <= b->ctx->host_direct_bytes;
+// With many such batches in flight at once the mode can collapse (sixteen threads with four 128-packet batches each:
+// 51 Gbit/s in most runs, against 140-150 with two each or with eight threads), so at most kHostDirectInFlight
+// batches of a context run this way at a time and the next ones are copied, which does not degrade.  With the cap,
+// ten runs each: 8 threads x 2 batches median 140 Gbit/s (copies: 117), 16 x 2 152 (115), 16 x 4 127 (118); on a
+// shared host both ways show slow runs now and then.
+constexpr int kHostDirectInFlight = 16;
+bool host_direct(bnk_batch *b, uint32_t npkts, uint32_t flags, uint64_t ext) {
+    bnk_ctx *ctx = b->ctx;
+    if (!(ctx->host_direct_bytes != 0 && npkts != 0 && npkts <= kHostDirectMaxPkts &&
+          !(flags & (BNK_F_NO_H2D | BNK_F_NO_D2H | BNK_F_USE_OUT_LEN)) && ext <= ctx->host_direct_bytes))
+        return false;
+    if (b->direct_counted) return true; // a second submit on a batch that is already counted
+    if (ctx->direct_in_flight.load(std::memory_order_relaxed) >= kHostDirectInFlight) return false;
+    ctx->direct_in_flight.fetch_add(1, std::memory_order_relaxed);
+    b->direct_counted = true;
+    return true;
+}
+void direct_done(bnk_batch *b) {
+    if (b->direct_counted) {
+        b->direct_counted = false;
+        b->ctx->direct_in_flight.fetch_sub(1, std::memory_order_relaxed);
+    }
 }
 struct HostAlias {
     bnk_batch *b;
@@ -224,6 +243,7 @@ int bnk_ctx_create(const bnk_cfg *cfg, bnk_ctx **out) {
     if (const char *m = getenv("BNK_AEAD_KERNEL")) // tuning and test aid: tpp | wpp
         ctx->aead_mode = !strcmp(m, "tpp") ? 1 : (!strcmp(m, "wpp") ? 2 : 0);
     ctx->host_direct_bytes = 384u << 10; // 256 slots of 1456 bytes and their headroom
+
     if (const char *m = getenv("BNK_HOST_DIRECT_BYTES")) // largest ring extent served without copies; 0 = never
         ctx->host_direct_bytes = strtoull(m, nullptr, 0);
     if (!prop.unifiedAddressing || !prop.canMapHostMemory) ctx->host_direct_bytes = 0; // pinned memory must have one address
@@ -607,6 +627,7 @@ int bnk_table_stats_get(bnk_ctx *ctx, bnk_table_stats *out) {
 int bnk_batch_destroy(bnk_batch *b) {
     if (!b) return BNK_EINVAL;
     cudaSetDevice(b->ctx->device);
+    direct_done(b);
     {
         std::unique_lock<std::shared_mutex> tables(b->ctx->submit_mu); // not while table maintenance walks the registry
         std::lock_guard<std::mutex> g(b->ctx->mu);
@@ -1105,6 +1126,7 @@ int bnk_wait(bnk_batch *b, uint64_t timeout_ns) {
         }
     }
     b->in_flight = false;
+    direct_done(b);
     if (b->flow_reported) { // what the device said about the flow table after this batch: input of the next compaction
         b->flow_reported = false;
         for (int c = 0; c < 3; c++) ctx->flow_dead_hint[c] = b->h_flow->dead[c];

@@ -84,6 +84,7 @@ struct bnk_ctx {
     cudaEvent_t timer_start;
     int sm_count;
     uint64_t host_direct_bytes; // batches up to this ring extent run on the caller's pinned buffers (BNK_HOST_DIRECT_BYTES)
+    std::atomic<int> direct_in_flight{0}; // batches whose last submit ran that way and has not been waited for
     int aead_mode; // 0 = choose by batch size, 1 = always thread per packet, 2 = always warp per packet (BNK_AEAD_KERNEL)
     uint32_t aead_side_stream_from; // batches of at least this many packets run seal/open on the low-priority stream (BNK_AEAD_SIDE_STREAM_FROM; 0 = never)
     int prio_low, prio_high;        // stream priority range of the device
@@ -157,6 +158,7 @@ struct bnk_batch {
     cudaEvent_t k_begin, k_end, t_end, a_begin, a_end;
     bool in_flight;
     bool dev_stale; // a submit ran on the host arrays: the device copies of ring and descriptors are behind
+    bool direct_counted; // this batch is one of ctx->direct_in_flight
     bool kernel_timed;
     bool aead_timed;
     bnk_gso_super *h_gso; // pinned staging for the super-packet descriptors
