@@ -28,13 +28,16 @@ def test_reference_go_tests_restated_in_cpp(gpu_lib):
 @pytest.mark.gpu
 def test_threads_share_a_context(gpu_lib):
     """Eight host threads, two batches in flight each, one context: counters, replay verdicts and plaintext stay
-    right (bnk_b200/host/apps/mt_stress.cpp); once with copies, once on the pinned host arrays."""
+    right (bnk_b200/host/apps/mt_stress.cpp); on the pinned host arrays (the default for batches this small), with
+    copies, and with 24 batches in flight, more than may run on the host arrays at a time, so that both ways mix."""
     from bnk_b200 import _build
 
     exe = _build.build_mt_stress()
-    for env_extra, packets, size in (({}, 128, 1420), ({}, 32, 576), ({"BNK_HOST_DIRECT_BYTES": "0"}, 32, 576)):
-        res = subprocess.run([exe, "8", "60", str(packets), str(size), "2"], capture_output=True, text=True, timeout=300,
-                             env={**os.environ, **env_extra})
+    for env_extra, threads, packets, size, lanes in (({}, 8, 128, 1420, 2), ({}, 8, 32, 576, 2), ({}, 6, 128, 1420, 4),
+                                                    ({"BNK_HOST_DIRECT_BYTES": "0"}, 8, 128, 1420, 2),
+                                                    ({"BNK_HOST_DIRECT_BYTES": "0"}, 8, 32, 576, 2)):
+        res = subprocess.run([exe, str(threads), "60", str(packets), str(size), str(lanes)], capture_output=True, text=True,
+                             timeout=300, env={**os.environ, **env_extra})
         print(res.stdout[-500:], res.stderr[-2000:])
         assert res.returncode == 0 and res.stdout.startswith("OK"), res.stdout[-500:] + res.stderr[-2000:]
 
